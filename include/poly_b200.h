@@ -1,0 +1,124 @@
+/*
+ * poly_b200.h -- C ABI of the B200 (sm_100a) execution backend for polygrad.
+ *
+ * Part 1 is the drop-in boundary: the CUDA backend symbols that polygrad's
+ * exec_plan.c / frontend.c / instance.c call.  Linking this library in place of
+ * polygrad's src/render_cuda.c + src/runtime_cuda.c (and compiling the rest of
+ * polygrad with -DPOLY_HAS_CUDA=1) replaces the CUDA row of the backend table
+ * (polygrad src/exec_plan.c:753-787) without editing any polygrad file.
+ * Signatures are those of polygrad src/codegen.h:114-139.
+ *
+ * Part 2 are additions: device selection, stream-level synchronisation and
+ * timing, statistics, and direct entry points to the precompiled kernels.
+ *
+ * Conventions (same as polygrad's): int results are 0 on success and -1 on
+ * error with a line on stderr prefixed "polygrad: cuda:"; device pointers
+ * travel as unsigned long long; the library is driven from one host thread.
+ * All work is enqueued on one internal CUDA stream; only poly_cuda_copy_dtoh,
+ * poly_b200_synchronize and poly_b200_event_elapsed_ms wait for the device.
+ * There is no CPU fallback: without a usable GPU every compute entry fails.
+ */
+#ifndef POLY_B200_H
+#define POLY_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+#include <stdbool.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ── Part 1: polygrad CUDA backend symbols ───────────────────────────── */
+
+struct PolyUOp; struct PolyCtx;
+typedef struct PolyCudaProgram PolyCudaProgram;
+
+/* Replaces polygrad src/render_cuda.c:176.  Returns a malloc'd one-element
+ * array holding the simplified kernel SINK; the caller frees it. */
+struct PolyUOp **poly_linearize_cuda(struct PolyCtx *ctx, struct PolyUOp *sink, int *n_out);
+
+/* Replaces polygrad src/render_cuda.c:196.  Returns malloc'd program text: a
+ * "//PB200" header naming a precompiled kernel and its arguments, or the header
+ * followed by CUDA C for run-time compilation.  The caller frees it. */
+char *poly_render_cuda(struct PolyUOp **uops, int n, const char *fn_name, int launch_bounds);
+
+/* Replaces polygrad src/runtime_cuda.c:192 and :240. */
+int  poly_cuda_init(void);
+bool poly_cuda_available(void);
+
+/* Replace polygrad src/runtime_cuda.c:245, :259.  Pooled: freed blocks are
+ * kept for reuse until poly_b200_trim(). */
+unsigned long long poly_cuda_alloc(size_t bytes);
+void poly_cuda_free(unsigned long long ptr);
+
+/* Replace polygrad src/runtime_cuda.c:268, :278.  copy_dtoh returns after the
+ * data is in dst (it orders after all earlier work). */
+int poly_cuda_copy_htod(unsigned long long dst, const void *src, size_t bytes);
+int poly_cuda_copy_dtoh(void *dst, unsigned long long src, size_t bytes);
+
+/* Replaces polygrad src/runtime_cuda.c:288.  Accepts only text produced by
+ * poly_render_cuda. */
+PolyCudaProgram *poly_compile_cuda(const char *source, const char *fn_name);
+
+/* Replaces polygrad src/runtime_cuda.c:386.  args[i] points to the i-th
+ * argument: a device pointer for buffer parameters, and for each DEFINE_VAR
+ * parameter a pointer to the host int holding its value (what
+ * polygrad src/exec_plan.c:1039-1040 supplies).  The grid and block arguments
+ * are ignored. */
+int poly_cuda_launch(PolyCudaProgram *prog, void **args, int n_args,
+                     int gx, int gy, int gz, int bx, int by, int bz);
+
+/* Replaces polygrad src/runtime_cuda.c:408.  Reports errors seen so far; does
+ * not wait unless POLY_B200_SYNC=1 (later work is stream-ordered anyway). */
+int poly_cuda_sync(void);
+
+/* Replace polygrad src/runtime_cuda.c:418, :426.  A whole-buffer zero fill is
+ * recorded and only executed if something reads the buffer before a kernel
+ * overwrites all of it. */
+void poly_cuda_program_destroy(PolyCudaProgram *prog);
+int  poly_cuda_memset(unsigned long long ptr, unsigned char val, size_t bytes);
+
+/* ── Part 2: additions (no counterpart in polygrad) ──────────────────── */
+
+/* Select the CUDA device for this process.  Must be called before the first
+ * poly_cuda_init(); otherwise POLY_B200_DEVICE, then LOCAL_RANK, then 0. */
+int  poly_b200_set_device(int device);
+int  poly_b200_device(void);
+
+/* Wait for all enqueued work.  0 / -1. */
+int  poly_b200_synchronize(void);
+
+/* The internal stream as a cudaStream_t. */
+void *poly_b200_stream(void);
+
+/* Release cached free blocks of the pool back to the driver. */
+void poly_b200_trim(void);
+
+/* CUDA events on the internal stream, for timing. */
+void *poly_b200_event_create(void);
+int   poly_b200_event_record(void *event);
+float poly_b200_event_elapsed_ms(void *start, void *stop); /* waits for stop; <0 on error */
+void  poly_b200_event_destroy(void *event);
+
+/* Counters since process start (or since the last reset). */
+typedef struct {
+  uint64_t launches;            /* kernels launched by this library */
+  uint64_t launches_precompiled;/* ... of which precompiled (GEMM, gather, copy, convert) */
+  uint64_t launches_generated;  /* ... of which compiled at run time from rendered CUDA C */
+  uint64_t memsets_elided;      /* zero fills dropped because the buffer was fully overwritten first */
+  uint64_t memsets_executed;
+  uint64_t bytes_allocated;     /* bytes currently held from the driver (live + cached) */
+  uint64_t programs_compiled;   /* NVRTC compilations (cache misses) */
+  uint64_t programs_cached;     /* programs served from the in-process or disk cache */
+} PolyB200Stats;
+void poly_b200_stats(PolyB200Stats *out);
+void poly_b200_stats_reset(void);
+
+/* Text of the last error reported by this library ("" if none). */
+const char *poly_b200_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* POLY_B200_H */

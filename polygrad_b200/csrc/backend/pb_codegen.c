@@ -1,0 +1,978 @@
+/*
+ * pb_codegen.c -- renders one scheduled polygrad kernel as CUDA C for sm_100a.
+ *
+ * This is the backend's general path: every kernel that is not lowered to a
+ * precompiled kernel (GEMM, gather, strided copy) is rendered here and compiled
+ * at plan-compile time.  It replaces the reference renderer
+ * (src/render_cuda.c:196-570) and its thread mapping (src/codegen.c:4149-4218,
+ * which parallelises only the outermost loop): here
+ *   - every LOOP range of a store is folded into one flat 64-bit-safe thread
+ *     index, ordered so that the axis with the smallest store stride varies
+ *     fastest across a warp (coalesced stores and, for same-layout inputs,
+ *     coalesced loads);
+ *   - pure elementwise kernels whose operands are contiguous or broadcast along
+ *     that axis move 128 bits per thread per access;
+ *   - a kernel that is one reduction over a memory-contiguous axis gives each
+ *     output to a warp or a block: lanes stride over the reduce range, partials
+ *     are combined with warp shuffles and one shared-memory exchange, lane 0
+ *     applies the epilogue and stores;
+ *   - integer index arithmetic is integer arithmetic (the reference routes int
+ *     MULACC through __fmaf_rn, src/render_cuda.c:155-158) and widens to 64 bit
+ *     when a buffer or the thread count needs it;
+ *   - every access of the scalar paths is bounds-checked against the PARAM's
+ *     element count, so a mis-scheduled kernel cannot fault the device.
+ *
+ * Op semantics follow the reference CPU renderer (src/render_c.c:932-1033):
+ * MAX is (a>b)?a:b, WHERE is ?:, IDIV and MOD are C division and remainder,
+ * RECIPROCAL is 1/x, MULACC is a*b+c.  EXP2, LOG2, SIN and SQRT map to the CUDA
+ * math library instead of the reference's polynomial decompositions
+ * (src/codegen.c:2156-2679).
+ */
+#include "pb_kern.h"
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <math.h>
+
+typedef struct {
+  PbKern *k;
+  PbStr out;
+  int *emitted;        /* per node: scope depth of its declaration, -1 = none */
+  int *scope_log; int n_log, cap_log;
+  int *scope_mark; int depth;   /* scope_mark[d] = n_log when depth d opened */
+  uint64_t bound;
+  bool wide;
+  const char *idx_t;
+  int indent;
+  bool failed;
+  int vec;             /* >1 while emitting the lane-replicated body of a vector kernel */
+  int lane;            /* current lane when vec > 1 */
+  uint64_t lane_dep;   /* mask with the bit of the vectorised range */
+} Gen;
+
+static void ind(Gen *g) { for (int i = 0; i < g->indent; i++) pb_str_puts(&g->out, "  "); }
+
+static bool is_idx_dtype(PolyDType dt) {
+  return !dt.is_ptr && (dt.priority == 5 || (dt.priority == -1 && dt.bitsize == 800));
+}
+
+static const char *ctype_of(Gen *g, PolyDType dt) {
+  if (is_idx_dtype(dt)) return g->idx_t;
+  return pb_ctype(dt);
+}
+
+static bool is_float_dt(PolyDType dt) { return dt.priority >= 11 && dt.priority <= 14; }
+static bool is_small_float(PolyDType dt) { return dt.priority == 11 || dt.priority == 12; }
+
+/* Lane suffix: nodes that depend on the vectorised range get one temp per lane. */
+static void temp_name(Gen *g, int id, char *buf, size_t cap) {
+  if (g->vec > 1 && (g->k->nodes[id].deps & g->lane_dep))
+    snprintf(buf, cap, "t%d_%d", id, g->lane);
+  else
+    snprintf(buf, cap, "t%d", id);
+}
+
+static void const_literal(Gen *g, PolyUOp *u, char *buf, size_t cap) {
+  PolyDType dt = u->dtype;
+  double f = 0; int64_t i = 0;
+  switch (u->arg.kind) {
+  case POLY_ARG_FLOAT: f = u->arg.f; i = (int64_t)u->arg.f; break;
+  case POLY_ARG_INT:   i = u->arg.i; f = (double)u->arg.i; break;
+  case POLY_ARG_BOOL:  i = u->arg.b; f = u->arg.b; break;
+  default: break;
+  }
+  if (dt.priority == 0) { snprintf(buf, cap, "%s", i ? "true" : "false"); return; }
+  if (dt.priority == 13) {
+    float ff = (float)f; uint32_t bits; memcpy(&bits, &ff, 4);
+    snprintf(buf, cap, "__int_as_float(0x%08x) /*%.9g*/", bits, (double)ff); return;
+  }
+  if (dt.priority == 14) {
+    uint64_t bits; memcpy(&bits, &f, 8);
+    snprintf(buf, cap, "__longlong_as_double(0x%016llxLL) /*%.17g*/", (unsigned long long)bits, f); return;
+  }
+  if (is_small_float(dt)) {
+    float ff = (float)f; uint32_t bits; memcpy(&bits, &ff, 4);
+    snprintf(buf, cap, "(%s)__int_as_float(0x%08x)", pb_ctype(dt), bits); return;
+  }
+  if (is_idx_dtype(dt)) {
+    if (g->wide) snprintf(buf, cap, "%lldLL", (long long)i);
+    else snprintf(buf, cap, "%lld", (long long)i);
+    return;
+  }
+  const char *ct = pb_ctype(dt);
+  if (!ct) { g->failed = true; snprintf(buf, cap, "0"); return; }
+  if (poly_dtype_is_unsigned(dt)) snprintf(buf, cap, "(%s)%lluULL", ct, (unsigned long long)i);
+  else snprintf(buf, cap, "(%s)%lldLL", ct, (long long)i);
+}
+
+static void ref(Gen *g, PolyUOp *u, char *buf, size_t cap) {
+  switch (u->op) {
+  case POLY_OP_CONST: const_literal(g, u, buf, cap); return;
+  case POLY_OP_RANGE: {
+    int r = pb_kern_range_id(g->k, u);
+    if (g->vec > 1 && ((uint64_t)1 << r) == g->lane_dep) snprintf(buf, cap, "(r%d+%d)", r, g->lane);
+    else snprintf(buf, cap, "r%d", r);
+    return;
+  }
+  case POLY_OP_DEFINE_VAR:
+    for (int v = 0; v < g->k->n_vars; v++)
+      if (g->k->vars[v] == u) { snprintf(buf, cap, "((%s)v%d)", g->idx_t, v); return; }
+    g->failed = true; snprintf(buf, cap, "0"); return;
+  case POLY_OP_PARAM: snprintf(buf, cap, "p%d", (int)u->arg.i); return;
+  default: temp_name(g, pb_kern_node(g->k, u), buf, cap); return;
+  }
+}
+
+static void log_emit(Gen *g, int id) {
+  g->emitted[id] = g->depth;
+  if (g->n_log == g->cap_log) {
+    g->cap_log = g->cap_log ? g->cap_log * 2 : 256;
+    g->scope_log = realloc(g->scope_log, sizeof(int) * (size_t)g->cap_log);
+  }
+  g->scope_log[g->n_log++] = id;
+}
+static void open_scope(Gen *g) { g->depth++; g->scope_mark[g->depth] = g->n_log; }
+static void close_scope(Gen *g) {
+  while (g->n_log > g->scope_mark[g->depth]) g->emitted[g->scope_log[--g->n_log]] = -1;
+  g->depth--;
+}
+
+static void emit(Gen *g, int id);
+
+static void emit_src(Gen *g, PolyUOp *u) {
+  switch (u->op) {
+  case POLY_OP_CONST: case POLY_OP_RANGE: case POLY_OP_DEFINE_VAR: case POLY_OP_PARAM: return;
+  default: emit(g, pb_kern_node(g->k, u));
+  }
+}
+
+static const char *reduce_identity(PolyOps op, PolyDType dt, char *buf, size_t cap, Gen *g) {
+  const char *ct = ctype_of(g, dt);
+  if (op == POLY_OP_ADD) snprintf(buf, cap, "(%s)0", ct);
+  else if (op == POLY_OP_MUL) snprintf(buf, cap, "(%s)1", ct);
+  else if (op == POLY_OP_MAX) {
+    if (dt.priority == 13) snprintf(buf, cap, "__int_as_float(0xff800000)");
+    else if (dt.priority == 14) snprintf(buf, cap, "(-__longlong_as_double(0x7ff0000000000000LL))");
+    else if (is_small_float(dt)) snprintf(buf, cap, "(%s)__int_as_float(0xff800000)", ct);
+    else if (dt.priority == 0) snprintf(buf, cap, "false");
+    else if (poly_dtype_is_unsigned(dt)) snprintf(buf, cap, "(%s)0", ct);
+    else if (is_idx_dtype(dt)) snprintf(buf, cap, g->wide ? "(-9223372036854775807LL-1)" : "(-2147483647-1)");
+    else if (dt.priority == 7) snprintf(buf, cap, "(-9223372036854775807LL-1)");
+    else if (dt.priority == 3) snprintf(buf, cap, "(short)-32768");
+    else if (dt.priority == 1) snprintf(buf, cap, "(signed char)-128");
+    else { g->failed = true; snprintf(buf, cap, "0"); }
+  } else { g->failed = true; snprintf(buf, cap, "0"); }
+  return buf;
+}
+
+static void combine_expr(PolyOps op, const char *a, const char *b, char *buf, size_t cap) {
+  if (op == POLY_OP_ADD) snprintf(buf, cap, "(%s+%s)", a, b);
+  else if (op == POLY_OP_MUL) snprintf(buf, cap, "(%s*%s)", a, b);
+  else snprintf(buf, cap, "((%s>%s)?%s:%s)", a, b, a, b);
+}
+
+static PolyOps reduce_op(PolyUOp *u) {
+  if (u->arg.kind == POLY_ARG_OPS) return u->arg.ops;
+  if (u->arg.kind == POLY_ARG_INT) return (PolyOps)u->arg.i;
+  if (u->arg.kind == POLY_ARG_REDUCE_AXIS) return u->arg.reduce_axis.op;
+  return POLY_OP_ADD;
+}
+
+/* Emit, at the current scope, every node under `id` that can already be
+ * computed (all its ranges bound): loop-invariant code motion before a loop. */
+static void hoist(Gen *g, int id) {
+  PbNode *n = &g->k->nodes[id];
+  if (g->emitted[id] >= 0) return;
+  switch (n->u->op) {
+  case POLY_OP_CONST: case POLY_OP_RANGE: case POLY_OP_DEFINE_VAR: case POLY_OP_PARAM: return;
+  default: break;
+  }
+  if ((n->deps & ~g->bound) == 0 && n->u->op != POLY_OP_INDEX) { emit(g, id); return; }
+  int first = (n->u->op == POLY_OP_REDUCE) ? 1 : n->u->n_src; /* only the value of a REDUCE */
+  for (int i = 0; i < (n->u->op == POLY_OP_REDUCE ? first : n->u->n_src); i++)
+    hoist(g, pb_kern_node(g->k, n->u->src[i]));
+}
+
+static void range_bound_str(Gen *g, int r, char *buf, size_t cap) {
+  if (g->k->extent[r] >= 0) snprintf(buf, cap, g->wide ? "%lldLL" : "%lld", (long long)g->k->extent[r]);
+  else snprintf(buf, cap, "((%s)v%d)", g->idx_t, g->k->extent_var[r]);
+}
+
+static void emit_reduce_serial(Gen *g, int id) {
+  PolyUOp *u = g->k->nodes[id].u;
+  PolyOps op = reduce_op(u);
+  int vid = pb_kern_node(g->k, u->src[0]);
+  hoist(g, vid);
+  char idn[96], name[32];
+  temp_name(g, id, name, sizeof name);
+  reduce_identity(op, u->dtype, idn, sizeof idn, g);
+  ind(g); pb_str_printf(&g->out, "%s acc_%s = %s;\n", ctype_of(g, u->dtype), name, idn);
+  uint64_t saved = g->bound;
+  for (int i = 1; i < u->n_src; i++) {
+    int r = pb_kern_range_id(g->k, u->src[i]);
+    char bs[64]; range_bound_str(g, r, bs, sizeof bs);
+    ind(g); pb_str_printf(&g->out, "for (%s r%d = 0; r%d < %s; ++r%d) {\n", g->idx_t, r, r, bs, r);
+    g->indent++;
+    g->bound |= (uint64_t)1 << r;
+  }
+  open_scope(g);
+  emit_src(g, u->src[0]);
+  char v[64], cmb[256], acc[48];
+  ref(g, u->src[0], v, sizeof v);
+  snprintf(acc, sizeof acc, "acc_%s", name);
+  combine_expr(op, acc, v, cmb, sizeof cmb);
+  ind(g); pb_str_printf(&g->out, "%s = %s;\n", acc, cmb);
+  close_scope(g);
+  for (int i = 1; i < u->n_src; i++) { g->indent--; ind(g); pb_str_puts(&g->out, "}\n"); }
+  g->bound = saved;
+  ind(g); pb_str_printf(&g->out, "const %s %s = %s;\n", ctype_of(g, u->dtype), name, acc);
+  log_emit(g, id);
+}
+
+static void emit_load(Gen *g, int id) {
+  PolyUOp *u = g->k->nodes[id].u;
+  PolyUOp *ix = u->src[0];
+  if (ix->op != POLY_OP_INDEX || ix->src[0]->op != POLY_OP_PARAM) { g->failed = true; return; }
+  PolyUOp *p = ix->src[0];
+  emit_src(g, ix->src[1]);
+  if (ix->n_src > 2) emit_src(g, ix->src[2]);
+  char name[32], is[64], gs[64];
+  temp_name(g, id, name, sizeof name);
+  ref(g, ix->src[1], is, sizeof is);
+  const char *ct = ctype_of(g, u->dtype);
+  if (!ct) { g->failed = true; return; }
+  ind(g);
+  if (ix->n_src > 2) {
+    ref(g, ix->src[2], gs, sizeof gs);
+    pb_str_printf(&g->out, "const %s %s = (%s) ? (%s)pb_ld(p%d, %s, %lldLL) : (%s)0;\n",
+                  ct, name, gs, ct, (int)p->arg.i, is, (long long)p->dtype.ptr_size, ct);
+  } else {
+    pb_str_printf(&g->out, "const %s %s = (%s)pb_ld(p%d, %s, %lldLL);\n",
+                  ct, name, ct, (int)p->arg.i, is, (long long)p->dtype.ptr_size);
+  }
+  log_emit(g, id);
+}
+
+static void unary_math(Gen *g, PolyUOp *u, const char *f32, const char *f64, const char *a, char *buf, size_t cap) {
+  if (u->dtype.priority == 14) snprintf(buf, cap, "%s(%s)", f64, a);
+  else if (is_small_float(u->dtype)) snprintf(buf, cap, "(%s)%s((float)%s)", pb_ctype(u->dtype), f32, a);
+  else snprintf(buf, cap, "%s(%s)", f32, a);
+  (void)g;
+}
+
+static void emit(Gen *g, int id) {
+  if (id < 0) { g->failed = true; return; }
+  if (g->emitted[id] >= 0) return;
+  PolyUOp *u = g->k->nodes[id].u;
+  switch (u->op) {
+  case POLY_OP_CONST: case POLY_OP_RANGE: case POLY_OP_DEFINE_VAR: case POLY_OP_PARAM: case POLY_OP_INDEX:
+    return;
+  case POLY_OP_REDUCE: emit_reduce_serial(g, id); return;
+  case POLY_OP_LOAD: emit_load(g, id); return;
+  default: break;
+  }
+  for (int i = 0; i < u->n_src; i++) emit_src(g, u->src[i]);
+  char a[96] = "", b[96] = "", c[96] = "", e[512], name[32];
+  if (u->n_src > 0) ref(g, u->src[0], a, sizeof a);
+  if (u->n_src > 1) ref(g, u->src[1], b, sizeof b);
+  if (u->n_src > 2) ref(g, u->src[2], c, sizeof c);
+  const char *ct = ctype_of(g, u->dtype);
+  if (!ct) { g->failed = true; return; }
+  PolyDType dt = u->dtype;
+  switch (u->op) {
+  case POLY_OP_CAST: {
+    PolyDType sd = u->src[0]->dtype;
+    if (is_small_float(sd) && !is_float_dt(dt)) snprintf(e, sizeof e, "(%s)(float)(%s)", ct, a);
+    else if (is_small_float(dt) && !is_float_dt(sd)) snprintf(e, sizeof e, "(%s)(float)(%s)", ct, a);
+    else if (is_small_float(dt) && is_small_float(sd) && dt.priority != sd.priority) snprintf(e, sizeof e, "(%s)(float)(%s)", ct, a);
+    else if (dt.priority == 0 && is_float_dt(sd)) snprintf(e, sizeof e, "((float)(%s) != 0.0f)", a);
+    else snprintf(e, sizeof e, "(%s)(%s)", ct, a);
+    break;
+  }
+  case POLY_OP_BITCAST: snprintf(e, sizeof e, "pb_bitcast<%s>(%s)", ct, a); break;
+  case POLY_OP_EXP2: unary_math(g, u, "exp2f", "exp2", a, e, sizeof e); break;
+  case POLY_OP_LOG2: unary_math(g, u, "log2f", "log2", a, e, sizeof e); break;
+  case POLY_OP_SIN:  unary_math(g, u, "sinf", "sin", a, e, sizeof e); break;
+  case POLY_OP_SQRT: unary_math(g, u, "sqrtf", "sqrt", a, e, sizeof e); break;
+  case POLY_OP_TRUNC: unary_math(g, u, "truncf", "trunc", a, e, sizeof e); break;
+  case POLY_OP_RECIPROCAL:
+    if (dt.priority == 14) snprintf(e, sizeof e, "(1.0/%s)", a);
+    else if (is_small_float(dt)) snprintf(e, sizeof e, "(%s)(1.0f/(float)%s)", ct, a);
+    else snprintf(e, sizeof e, "(1.0f/%s)", a);
+    break;
+  case POLY_OP_NEG:
+    if (dt.priority == 0) snprintf(e, sizeof e, "(!%s)", a); else snprintf(e, sizeof e, "(-%s)", a);
+    break;
+  case POLY_OP_ADD: snprintf(e, sizeof e, "(%s+%s)", a, b); break;
+  case POLY_OP_SUB: snprintf(e, sizeof e, "(%s-%s)", a, b); break;
+  case POLY_OP_MUL:
+    if (dt.priority == 0) snprintf(e, sizeof e, "(%s&&%s)", a, b); else snprintf(e, sizeof e, "(%s*%s)", a, b);
+    break;
+  case POLY_OP_FDIV: snprintf(e, sizeof e, "(%s/%s)", a, b); break;
+  case POLY_OP_IDIV: snprintf(e, sizeof e, "(%s/%s)", a, b); break;
+  case POLY_OP_MOD:  snprintf(e, sizeof e, "(%s%%%s)", a, b); break;
+  case POLY_OP_SHL:  snprintf(e, sizeof e, "(%s<<%s)", a, b); break;
+  case POLY_OP_SHR:  snprintf(e, sizeof e, "(%s>>%s)", a, b); break;
+  case POLY_OP_AND:  snprintf(e, sizeof e, dt.priority == 0 ? "(%s&&%s)" : "(%s&%s)", a, b); break;
+  case POLY_OP_OR:   snprintf(e, sizeof e, dt.priority == 0 ? "(%s||%s)" : "(%s|%s)", a, b); break;
+  case POLY_OP_XOR:  snprintf(e, sizeof e, dt.priority == 0 ? "(%s!=%s)" : "(%s^%s)", a, b); break;
+  case POLY_OP_CMPLT: snprintf(e, sizeof e, "(%s<%s)", a, b); break;
+  case POLY_OP_CMPNE: snprintf(e, sizeof e, "(%s!=%s)", a, b); break;
+  case POLY_OP_CMPEQ: snprintf(e, sizeof e, "(%s==%s)", a, b); break;
+  case POLY_OP_MAX:  snprintf(e, sizeof e, "((%s>%s)?%s:%s)", a, b, a, b); break;
+  case POLY_OP_POW:
+    if (dt.priority == 14) snprintf(e, sizeof e, "pow(%s,%s)", a, b);
+    else snprintf(e, sizeof e, "(%s)powf((float)%s,(float)%s)", ct, a, b);
+    break;
+  case POLY_OP_WHERE: {
+    PolyDType cd = u->src[0]->dtype;
+    if (is_small_float(cd)) snprintf(e, sizeof e, "(((float)%s != 0.0f)?%s:%s)", a, b, c);
+    else snprintf(e, sizeof e, "(%s?%s:%s)", a, b, c);
+    break;
+  }
+  case POLY_OP_MULACC:
+    if (dt.priority == 13) snprintf(e, sizeof e, "fmaf(%s,%s,%s)", a, b, c);
+    else if (dt.priority == 14) snprintf(e, sizeof e, "fma(%s,%s,%s)", a, b, c);
+    else snprintf(e, sizeof e, "((%s*%s)+%s)", a, b, c);
+    break;
+  default:
+    snprintf(g->k->err, sizeof g->k->err, "no rendering for %s", poly_op_name(u->op));
+    g->failed = true; return;
+  }
+  temp_name(g, id, name, sizeof name);
+  ind(g); pb_str_printf(&g->out, "const %s %s = %s;\n", ct, name, e);
+  log_emit(g, id);
+}
+
+/* ── launch-size expression: product of constants and var arguments ──── */
+static void size_expr(PbKern *k, const int *ranges, int n, PbStr *s) {
+  int64_t c = 1; bool any_var = false;
+  for (int i = 0; i < n; i++) {
+    int r = ranges[i];
+    if (k->extent[r] >= 0) c *= k->extent[r];
+  }
+  pb_str_printf(s, "c%lld", (long long)c);
+  for (int i = 0; i < n; i++) {
+    int r = ranges[i];
+    if (k->extent[r] < 0) { pb_str_printf(s, "*v%d", k->extent_var[r]); any_var = true; }
+  }
+  (void)any_var;
+}
+
+static int64_t range_max(const PbKern *k, int r) {
+  return k->extent[r] >= 0 ? k->extent[r] : k->vars[k->extent_var[r]]->arg.define_var.max_val;
+}
+
+/* Order a store's loop axes: smallest |store stride| first (fastest thread axis). */
+static void order_loop_axes(PbKern *k, PbStore *st, int *order, PbAffine *aff_out) {
+  uint64_t m = 0;
+  for (int i = 0; i < st->n_loop; i++) m |= (uint64_t)1 << st->loop[i];
+  PbAffine aff;
+  pb_fit_affine(k, st->index->src[1], m, &aff);
+  for (int i = 0; i < st->n_loop; i++) order[i] = st->loop[i];
+  if (aff.ok) {
+    for (int i = 1; i < st->n_loop; i++) {
+      int r = order[i]; int j = i - 1;
+      int64_t sr = llabs(aff.stride[r]); if (sr == 0) sr = INT64_MAX;
+      while (j >= 0) {
+        int64_t sj = llabs(aff.stride[order[j]]); if (sj == 0) sj = INT64_MAX;
+        if (sj <= sr) break;
+        order[j + 1] = order[j]; j--;
+      }
+      order[j + 1] = r;
+    }
+  }
+  if (aff_out) *aff_out = aff;
+}
+
+static void emit_decompose(Gen *g, const char *lin, const int *order, int n) {
+  ind(g); pb_str_printf(&g->out, "%s rem_ = %s;\n", g->idx_t, lin);
+  for (int i = 0; i < n; i++) {
+    int r = order[i];
+    char bs[64]; range_bound_str(g, r, bs, sizeof bs);
+    ind(g);
+    if (i == n - 1) pb_str_printf(&g->out, "const %s r%d = rem_;\n", g->idx_t, r);
+    else pb_str_printf(&g->out, "const %s r%d = rem_ %% %s; rem_ /= %s;\n", g->idx_t, r, bs, bs);
+    g->bound |= (uint64_t)1 << r;
+  }
+}
+
+static void emit_store(Gen *g, PbStore *st) {
+  PolyUOp *ix = st->index;
+  emit_src(g, ix->src[1]);
+  if (ix->n_src > 2) emit_src(g, ix->src[2]);
+  emit_src(g, st->value);
+  char is[64], vs[96], gs[64];
+  ref(g, ix->src[1], is, sizeof is);
+  ref(g, st->value, vs, sizeof vs);
+  PolyUOp *p = ix->src[0];
+  PolyDType base = p->dtype; base.is_ptr = false; base.count = 1;
+  const char *pt = pb_ctype(base);
+  ind(g);
+  if (ix->n_src > 2) {
+    ref(g, ix->src[2], gs, sizeof gs);
+    pb_str_printf(&g->out, "if (%s) pb_st(p%d, %s, %lldLL, (%s)(%s));\n", gs, st->param, is,
+                  (long long)p->dtype.ptr_size, pt, vs);
+  } else {
+    pb_str_printf(&g->out, "pb_st(p%d, %s, %lldLL, (%s)(%s));\n", st->param, is,
+                  (long long)p->dtype.ptr_size, pt, vs);
+  }
+}
+
+static const char *PRELUDE =
+  "template <class T> __device__ __forceinline__ T pb_ld(const T* __restrict__ p, long long i, long long n) {\n"
+  "  return ((unsigned long long)i < (unsigned long long)n) ? p[i] : T(0);\n"
+  "}\n"
+  "template <class T> __device__ __forceinline__ void pb_st(T* __restrict__ p, long long i, long long n, T v) {\n"
+  "  if ((unsigned long long)i < (unsigned long long)n) p[i] = v;\n"
+  "}\n"
+  "template <class T, class S> __device__ __forceinline__ T pb_bitcast(S s) {\n"
+  "  static_assert(sizeof(T) == sizeof(S), \"bitcast size\");\n"
+  "  T t; memcpy(&t, &s, sizeof(T)); return t;\n"
+  "}\n";
+
+static void emit_signature(Gen *g, const bool *written, int block) {
+  PbKern *k = g->k;
+  pb_str_printf(&g->out, "extern \"C\" __global__ void __launch_bounds__(%d) pb200_kernel(", block);
+  bool first = true;
+  for (int i = 0; i < k->n_params; i++) {
+    if (!first) pb_str_puts(&g->out, ", ");
+    first = false;
+    if (!k->params[i]) { pb_str_printf(&g->out, "const void* __restrict__ p%d", i); continue; }
+    PolyDType base = k->params[i]->dtype; base.is_ptr = false; base.count = 1;
+    const char *ct = pb_ctype(base);
+    if (!ct) { g->failed = true; ct = "float"; }
+    pb_str_printf(&g->out, "%s%s* __restrict__ p%d", written[i] ? "" : "const ", ct, i);
+  }
+  for (int v = 0; v < k->n_vars; v++) {
+    if (!first) pb_str_puts(&g->out, ", ");
+    first = false;
+    pb_str_printf(&g->out, "const int v%d", v);
+  }
+  if (!first) pb_str_puts(&g->out, ", ");
+  pb_str_puts(&g->out, "const long long n_work)");
+}
+
+/* Which params are read (bit 0) / written (bit 1), and whether the write covers
+ * the whole buffer exactly once (bit 2). */
+static void param_usage(PbKern *k, int *usage) {
+  for (int i = 0; i < k->n_params; i++) usage[i] = 0;
+  for (int i = 0; i < k->n_nodes; i++) {
+    PolyUOp *u = k->nodes[i].u;
+    if (u->op == POLY_OP_LOAD && u->src[0]->op == POLY_OP_INDEX && u->src[0]->src[0]->op == POLY_OP_PARAM)
+      usage[u->src[0]->src[0]->arg.i] |= 1;
+  }
+  for (int s = 0; s < k->n_stores; s++) {
+    PbStore *st = &k->stores[s];
+    usage[st->param] |= 2;
+    if (st->index->n_src > 2) continue;           /* gated store: partial */
+    uint64_t m = 0; int64_t total = 1; bool var = false;
+    for (int i = 0; i < st->n_loop; i++) {
+      m |= (uint64_t)1 << st->loop[i];
+      if (k->extent[st->loop[i]] < 0) var = true; else total *= k->extent[st->loop[i]];
+    }
+    if (var) continue;
+    PbAffine aff; pb_fit_affine(k, st->index->src[1], m, &aff);
+    if (!aff.ok || aff.offset != 0) continue;
+    if (total != k->params[st->param]->dtype.ptr_size) continue;
+    /* strides must be a permutation of a dense layout: sort by stride, check products */
+    int ord[PB_MAX_AXES]; int n = 0;
+    for (int i = 0; i < st->n_loop; i++) if (k->extent[st->loop[i]] > 1) ord[n++] = st->loop[i];
+    for (int i = 1; i < n; i++) {
+      int r = ord[i], j = i - 1;
+      while (j >= 0 && aff.stride[ord[j]] > aff.stride[r]) { ord[j + 1] = ord[j]; j--; }
+      ord[j + 1] = r;
+    }
+    int64_t expect = 1; bool dense = true;
+    for (int i = 0; i < n; i++) {
+      if (aff.stride[ord[i]] != expect) { dense = false; break; }
+      expect *= k->extent[ord[i]];
+    }
+    if (dense) usage[st->param] |= 4;
+  }
+}
+
+static void emit_header(PbKern *k, PbStr *h, const char *launch_line, const int *usage) {
+  pb_str_puts(h, "//PB200 1\n//kind jit\n//entry pb200_kernel\n");
+  pb_str_printf(h, "//nparams %d\n//nvars %d\n", k->n_params, k->n_vars);
+  pb_str_printf(h, "%s\n", launch_line);
+  pb_str_puts(h, "//rw");
+  for (int i = 0; i < k->n_params; i++) {
+    const char *c = "-";
+    if ((usage[i] & 3) == 1) c = "r";
+    else if ((usage[i] & 3) == 3) c = "rw";
+    else if (usage[i] & 4) c = "W";
+    else if (usage[i] & 2) c = "w";
+    pb_str_printf(h, " %s", c);
+  }
+  pb_str_puts(h, "\n");
+}
+
+/* ── collect the loads feeding a value (for layout decisions) ────────── */
+typedef struct { int node; PbAffine aff; } LoadInfo;
+
+static int collect_loads(PbKern *k, int id, LoadInfo *out, int cap, int n, bool *seen) {
+  if (seen[id]) return n;
+  seen[id] = true;
+  PolyUOp *u = k->nodes[id].u;
+  if (u->op == POLY_OP_LOAD) {
+    if (n < cap) { out[n].node = id; n++; }
+  }
+  for (int i = 0; i < u->n_src; i++) {
+    int s = pb_kern_node(k, u->src[i]);
+    if (s >= 0) n = collect_loads(k, s, out, cap, n, seen);
+  }
+  return n;
+}
+
+/* ── reduction kernel: one warp or one block per output element ──────── */
+static bool reduce_dtype_ok(PolyDType dt) {
+  return dt.priority == 13 || dt.priority == 14 || dt.priority == 5 || dt.priority == 7 ||
+         dt.priority == 6 || dt.priority == 8 || (dt.priority == -1 && dt.bitsize == 800);
+}
+
+static char *render_group_reduce(PbKern *k, const int *usage) {
+  if (k->n_stores != 1 || k->n_reduce_nodes != 1) return NULL;
+  PbStore *st = &k->stores[0];
+  int rid = -1;
+  for (int i = 0; i < k->n_nodes; i++) if (k->nodes[i].u->op == POLY_OP_REDUCE) rid = i;
+  PolyUOp *red = k->nodes[rid].u;
+  if (!reduce_dtype_ok(red->dtype)) return NULL;
+  PolyOps op = reduce_op(red);
+  if (op != POLY_OP_ADD && op != POLY_OP_MAX && op != POLY_OP_MUL) return NULL;
+  /* the REDUCE must feed the store value, not the store index or gate */
+  if (k->nodes[pb_kern_node(k, st->index)].has_reduce) return NULL;
+
+  int raxes[PB_MAX_AXES]; int nr = 0; int64_t ktot = 1;
+  uint64_t rmask = 0;
+  for (int i = 1; i < red->n_src; i++) {
+    int r = pb_kern_range_id(k, red->src[i]);
+    if (r < 0 || nr >= PB_MAX_AXES) return NULL;
+    if (k->extent[r] < 0) return NULL;
+    raxes[nr++] = r; ktot *= k->extent[r]; rmask |= (uint64_t)1 << r;
+  }
+  if (ktot < 64) return NULL;
+
+  /* loads under the reduction: is there one that is contiguous along a reduce axis? */
+  bool *seen = calloc((size_t)k->n_nodes, 1);
+  LoadInfo loads[32];
+  int nl = collect_loads(k, pb_kern_node(k, red->src[0]), loads, 32, 0, seen);
+  free(seen);
+  uint64_t all = 0;
+  for (int r = 0; r < k->n_ranges; r++) all |= (uint64_t)1 << r;
+  int fastest = -1; int64_t best = INT64_MAX;
+  int64_t loop_best = INT64_MAX;      /* smallest stride any loop axis has in a reduce-dependent load */
+  for (int i = 0; i < nl; i++) {
+    PolyUOp *ld = k->nodes[loads[i].node].u;
+    if (!(k->nodes[loads[i].node].deps & rmask)) continue;
+    pb_fit_affine(k, ld->src[0]->src[1], all, &loads[i].aff);
+    if (!loads[i].aff.ok) continue;
+    for (int j = 0; j < nr; j++) {
+      int64_t s = llabs(loads[i].aff.stride[raxes[j]]);
+      if (s != 0 && k->extent[raxes[j]] > 1 && s < best) { best = s; fastest = raxes[j]; }
+    }
+    for (int j = 0; j < st->n_loop; j++) {
+      int64_t s = llabs(loads[i].aff.stride[st->loop[j]]);
+      if (s != 0 && range_max(k, st->loop[j]) > 1 && s < loop_best) loop_best = s;
+    }
+  }
+  if (fastest < 0) return NULL;
+  /* when an output axis is the memory-contiguous one, a thread per output is
+   * already coalesced and this mapping would not be */
+  if (best != 1 && loop_best == 1) return NULL;
+
+  int64_t n_out_max = 1;
+  for (int i = 0; i < st->n_loop; i++) n_out_max *= range_max(k, st->loop[i]);
+
+  int group, block;
+  if (ktot >= 2048 || n_out_max < 2048) { group = ktot >= 8192 ? 512 : 256; if (ktot < 512) group = 128; block = group; }
+  else { group = 32; block = 256; }
+
+  Gen g; memset(&g, 0, sizeof g);
+  g.k = k;
+  g.emitted = malloc(sizeof(int) * (size_t)k->n_nodes);
+  for (int i = 0; i < k->n_nodes; i++) g.emitted[i] = -1;
+  g.scope_mark = calloc(64, sizeof(int));
+  bool wide = n_out_max * (int64_t)group >= ((int64_t)1 << 31);
+  for (int i = 0; i < k->n_params; i++)
+    if (k->params[i] && k->params[i]->dtype.ptr_size >= ((int64_t)1 << 31)) wide = true;
+  g.wide = wide; g.idx_t = wide ? "long long" : "int";
+  pb_str_init(&g.out);
+
+  bool written[PB_MAX_PARAMS];
+  for (int i = 0; i < k->n_params; i++) written[i] = (usage[i] & 2) != 0;
+
+  const char *rt = ctype_of(&g, red->dtype);
+  pb_str_puts(&g.out, PRELUDE);
+  emit_signature(&g, written, block);
+  pb_str_puts(&g.out, " {\n");
+  g.indent = 1;
+  int per_block = block / group;
+  ind(&g); pb_str_printf(&g.out, "const int lane_ = threadIdx.x %% %d;\n", group);
+  ind(&g); pb_str_printf(&g.out, "const long long out_ = (long long)blockIdx.x * %d + threadIdx.x / %d;\n", per_block, group);
+  if (group == block) { ind(&g); pb_str_printf(&g.out, "__shared__ %s red_[32];\n", rt); }
+  /* whole groups leave together, so the shuffles below always see full warps */
+  ind(&g); pb_str_puts(&g.out, "if (out_ >= n_work) return;\n");
+  int order[PB_MAX_AXES];
+  order_loop_axes(k, st, order, NULL);
+  if (st->n_loop > 0) emit_decompose(&g, wide ? "out_" : "(int)out_", order, st->n_loop);
+
+  /* loop-invariant part of the reduced value */
+  int vid = pb_kern_node(k, red->src[0]);
+  hoist(&g, vid);
+
+  char idn[96];
+  reduce_identity(op, red->dtype, idn, sizeof idn, &g);
+  ind(&g); pb_str_printf(&g.out, "%s acc_ = %s;\n", rt, idn);
+  /* reduce axes: the contiguous one fastest */
+  int rorder[PB_MAX_AXES]; int n = 0;
+  rorder[n++] = fastest;
+  for (int j = nr - 1; j >= 0; j--) if (raxes[j] != fastest) rorder[n++] = raxes[j];
+  ind(&g); pb_str_printf(&g.out, "for (%s k_ = lane_; k_ < %lld; k_ += %d) {\n", g.idx_t, (long long)ktot, group);
+  g.indent++;
+  uint64_t saved = g.bound;
+  open_scope(&g);
+  if (nr == 1) {
+    ind(&g); pb_str_printf(&g.out, "const %s r%d = k_;\n", g.idx_t, fastest);
+    g.bound |= (uint64_t)1 << fastest;
+  } else {
+    emit_decompose(&g, "k_", rorder, nr);
+  }
+  emit_src(&g, red->src[0]);
+  char v[64], cmb[256];
+  ref(&g, red->src[0], v, sizeof v);
+  combine_expr(op, "acc_", v, cmb, sizeof cmb);
+  ind(&g); pb_str_printf(&g.out, "acc_ = %s;\n", cmb);
+  close_scope(&g);
+  g.bound = saved;
+  g.indent--;
+  ind(&g); pb_str_puts(&g.out, "}\n");
+
+  /* combine across the group */
+  char sh[256];
+  ind(&g); pb_str_puts(&g.out, "#pragma unroll\n");
+  ind(&g); pb_str_puts(&g.out, "for (int o_ = 16; o_ > 0; o_ >>= 1) {\n");
+  ind(&g); pb_str_printf(&g.out, "  const %s x_ = __shfl_xor_sync(0xffffffffu, acc_, o_);\n", rt);
+  combine_expr(op, "acc_", "x_", sh, sizeof sh);
+  ind(&g); pb_str_printf(&g.out, "  acc_ = %s;\n", sh);
+  ind(&g); pb_str_puts(&g.out, "}\n");
+  if (group == block) {
+    int nw = block / 32;
+    ind(&g); pb_str_puts(&g.out, "if ((threadIdx.x & 31) == 0) red_[threadIdx.x >> 5] = acc_;\n");
+    ind(&g); pb_str_puts(&g.out, "__syncthreads();\n");
+    ind(&g); pb_str_puts(&g.out, "if (threadIdx.x != 0) return;\n");
+    ind(&g); pb_str_puts(&g.out, "acc_ = red_[0];\n");
+    ind(&g); pb_str_printf(&g.out, "for (int w_ = 1; w_ < %d; ++w_) { const %s x_ = red_[w_]; acc_ = %s; }\n", nw, rt, sh);
+  } else {
+    ind(&g); pb_str_puts(&g.out, "if (lane_ != 0) return;\n");
+  }
+  char name[32]; temp_name(&g, rid, name, sizeof name);
+  ind(&g); pb_str_printf(&g.out, "const %s %s = acc_;\n", rt, name);
+  log_emit(&g, rid);
+  emit_store(&g, st);
+  pb_str_puts(&g.out, "}\n");
+
+  char *res = NULL;
+  if (!g.failed) {
+    PbStr h; pb_str_init(&h);
+    PbStr sz; pb_str_init(&sz);
+    size_expr(k, st->loop, st->n_loop, &sz);
+    char line[512];
+    snprintf(line, sizeof line, "//launch group block=%d group=%d work=%s", block, group, sz.s);
+    pb_str_free(&sz);
+    emit_header(k, &h, line, usage);
+    if (k->uses_half) pb_str_puts(&h, "#include <cuda_fp16.h>\n");
+    if (k->uses_bf16) pb_str_puts(&h, "#include <cuda_bf16.h>\n");
+    pb_str_puts(&h, g.out.s);
+    res = pb_str_take(&h);
+  }
+  pb_str_free(&g.out);
+  free(g.emitted); free(g.scope_log); free(g.scope_mark);
+  return res;
+}
+
+/* ── vectorised elementwise kernel ───────────────────────────────────── */
+/* Conditions: one store, no REDUCE, all extents constant, the fastest store
+ * axis x has store stride 1 and extent % 4 == 0, every load is affine with
+ * stride 1 or 0 along x, and every other stride and offset of a stride-1
+ * operand keeps 16-byte alignment.  All element types 4 bytes wide.
+ * Each thread handles 4 consecutive x; grid-stride is not needed because the
+ * grid covers the element count exactly. */
+static char *render_vec_elementwise(PbKern *k, const int *usage) {
+  if (k->n_stores != 1 || k->n_reduce_nodes != 0 || k->n_vars != 0) return NULL;
+  PbStore *st = &k->stores[0];
+  if (st->index->n_src > 2 || st->n_loop == 0) return NULL;
+  for (int i = 0; i < st->n_loop; i++) if (k->extent[st->loop[i]] < 0) return NULL;
+  int order[PB_MAX_AXES]; PbAffine saff;
+  order_loop_axes(k, st, order, &saff);
+  if (!saff.ok) return NULL;
+  int x = -1;
+  for (int i = 0; i < st->n_loop; i++) if (k->extent[order[i]] > 1) { x = order[i]; break; }
+  if (x < 0 || saff.stride[x] != 1 || k->extent[x] % 4 != 0) return NULL;
+  uint64_t m = 0;
+  for (int i = 0; i < st->n_loop; i++) m |= (uint64_t)1 << st->loop[i];
+  PolyDType ob = k->params[st->param]->dtype;
+  if (ob.bitsize != 32 || (ob.priority != 13 && ob.priority != 5 && ob.priority != 6)) return NULL;
+  if (saff.offset % 4) return NULL;
+  for (int i = 0; i < st->n_loop; i++) if (st->loop[i] != x && saff.stride[st->loop[i]] % 4) return NULL;
+
+  bool *seen = calloc((size_t)k->n_nodes, 1);
+  LoadInfo loads[24];
+  int nl = collect_loads(k, pb_kern_node(k, st->value), loads, 24, 0, seen);
+  free(seen);
+  if (nl >= 24) return NULL;
+  bool vec_load[24];
+  for (int i = 0; i < nl; i++) {
+    PolyUOp *ld = k->nodes[loads[i].node].u;
+    PolyUOp *ix = ld->src[0];
+    if (ix->op != POLY_OP_INDEX || ix->src[0]->op != POLY_OP_PARAM || ix->n_src > 2) return NULL;
+    if (ix->src[0]->dtype.bitsize != 32) return NULL;
+    if ((int)ix->src[0]->arg.i == st->param) {
+      /* reading the buffer being written is only safe element-for-element */
+      pb_fit_affine(k, ix->src[1], m, &loads[i].aff);
+      if (!loads[i].aff.ok) return NULL;
+      if (loads[i].aff.offset != saff.offset) return NULL;
+      for (int j = 0; j < st->n_loop; j++)
+        if (loads[i].aff.stride[st->loop[j]] != saff.stride[st->loop[j]]) return NULL;
+    }
+    pb_fit_affine(k, ix->src[1], m, &loads[i].aff);
+    if (!loads[i].aff.ok) return NULL;
+    int64_t sx = loads[i].aff.stride[x];
+    if (sx == 1) {
+      if (loads[i].aff.offset % 4) return NULL;
+      for (int j = 0; j < st->n_loop; j++)
+        if (st->loop[j] != x && loads[i].aff.stride[st->loop[j]] % 4) return NULL;
+      vec_load[i] = true;
+    } else if (sx == 0) vec_load[i] = false;
+    else return NULL;
+    /* bounds: the largest index must stay inside the buffer */
+    int64_t lo = loads[i].aff.offset, hi = loads[i].aff.offset;
+    for (int j = 0; j < st->n_loop; j++) {
+      int64_t s = loads[i].aff.stride[st->loop[j]] * (k->extent[st->loop[j]] - 1);
+      if (s > 0) hi += s; else lo += s;
+    }
+    if (lo < 0 || hi >= ix->src[0]->dtype.ptr_size) return NULL;
+  }
+  {
+    int64_t lo = saff.offset, hi = saff.offset;
+    for (int j = 0; j < st->n_loop; j++) {
+      int64_t s = saff.stride[st->loop[j]] * (k->extent[st->loop[j]] - 1);
+      if (s > 0) hi += s; else lo += s;
+    }
+    if (lo < 0 || hi >= ob.ptr_size) return NULL;
+  }
+
+  int64_t total = 1;
+  for (int i = 0; i < st->n_loop; i++) total *= k->extent[st->loop[i]];
+  int64_t n_threads = total / 4;
+
+  Gen g; memset(&g, 0, sizeof g);
+  g.k = k;
+  g.emitted = malloc(sizeof(int) * (size_t)k->n_nodes);
+  for (int i = 0; i < k->n_nodes; i++) g.emitted[i] = -1;
+  g.scope_mark = calloc(64, sizeof(int));
+  bool wide = total >= ((int64_t)1 << 31);
+  for (int i = 0; i < k->n_params; i++)
+    if (k->params[i] && k->params[i]->dtype.ptr_size >= ((int64_t)1 << 31)) wide = true;
+  g.wide = wide; g.idx_t = wide ? "long long" : "int";
+  pb_str_init(&g.out);
+  bool written[PB_MAX_PARAMS];
+  for (int i = 0; i < k->n_params; i++) written[i] = (usage[i] & 2) != 0;
+
+  pb_str_puts(&g.out, PRELUDE);
+  pb_str_puts(&g.out,
+    "template <class T> struct pb_v4 { T x, y, z, w; };\n"
+    "template <class T> __device__ __forceinline__ void pb_ld4(const T* p, T* o) {\n"
+    "  const uint4 v = *reinterpret_cast<const uint4*>(p);\n"
+    "  memcpy(o, &v, 16);\n"
+    "}\n"
+    "template <class T> __device__ __forceinline__ void pb_st4(T* p, const T* o) {\n"
+    "  uint4 v; memcpy(&v, o, 16);\n"
+    "  *reinterpret_cast<uint4*>(p) = v;\n"
+    "}\n");
+  emit_signature(&g, written, 256);
+  pb_str_puts(&g.out, " {\n");
+  g.indent = 1;
+  ind(&g); pb_str_puts(&g.out, "const long long gid_ = (long long)blockIdx.x * blockDim.x + threadIdx.x;\n");
+  ind(&g); pb_str_puts(&g.out, "if (gid_ >= n_work) return;\n");
+  /* decompose: x in units of 4 */
+  ind(&g); pb_str_printf(&g.out, "%s rem_ = %s;\n", g.idx_t, wide ? "gid_" : "(int)gid_");
+  for (int i = 0; i < st->n_loop; i++) {
+    int r = order[i];
+    int64_t ext = (r == x) ? k->extent[r] / 4 : k->extent[r];
+    ind(&g);
+    if (i == st->n_loop - 1) pb_str_printf(&g.out, "const %s q%d = rem_;\n", g.idx_t, r);
+    else pb_str_printf(&g.out, "const %s q%d = rem_ %% %lld; rem_ /= %lld;\n", g.idx_t, r, (long long)ext, (long long)ext);
+    ind(&g);
+    if (r == x) pb_str_printf(&g.out, "const %s r%d = q%d * 4;\n", g.idx_t, r, r);
+    else pb_str_printf(&g.out, "const %s r%d = q%d;\n", g.idx_t, r, r);
+    g.bound |= (uint64_t)1 << r;
+  }
+  /* vector loads first (independent, so they are all in flight together) */
+  for (int i = 0; i < nl; i++) {
+    if (!vec_load[i]) continue;
+    PolyUOp *ld = k->nodes[loads[i].node].u;
+    PolyUOp *ix = ld->src[0];
+    PolyDType base = ix->src[0]->dtype; base.is_ptr = false; base.count = 1;
+    const char *pt = pb_ctype(base);
+    ind(&g); pb_str_printf(&g.out, "%s l%d_[4]; { %s o_ = %lld", pt, loads[i].node, g.idx_t, (long long)loads[i].aff.offset);
+    for (int j = 0; j < st->n_loop; j++) {
+      int64_t s = loads[i].aff.stride[st->loop[j]];
+      if (s) pb_str_printf(&g.out, " + r%d*%lld", st->loop[j], (long long)s);
+    }
+    pb_str_printf(&g.out, "; pb_ld4(p%d + o_, l%d_); }\n", (int)ix->src[0]->arg.i, loads[i].node);
+  }
+  ind(&g); {
+    PolyDType base = ob; base.is_ptr = false; base.count = 1;
+    pb_str_printf(&g.out, "%s o4_[4];\n", pb_ctype(base));
+  }
+  /* lane-independent part once */
+  g.vec = 1;
+  g.lane_dep = (uint64_t)1 << x;
+  /* emit nodes not depending on x */
+  {
+    uint64_t saved = g.bound;
+    g.bound &= ~((uint64_t)1 << x);
+    hoist(&g, pb_kern_node(k, st->value));
+    g.bound = saved;
+  }
+  g.vec = 4;
+  for (int lane = 0; lane < 4; lane++) {
+    g.lane = lane;
+    /* bind vector loads for this lane */
+    for (int i = 0; i < nl; i++) {
+      if (!vec_load[i]) continue;
+      char nm[32]; temp_name(&g, loads[i].node, nm, sizeof nm);
+      PolyUOp *ld = k->nodes[loads[i].node].u;
+      ind(&g); pb_str_printf(&g.out, "const %s %s = (%s)l%d_[%d];\n", ctype_of(&g, ld->dtype), nm,
+                             ctype_of(&g, ld->dtype), loads[i].node, lane);
+      log_emit(&g, loads[i].node);
+    }
+    emit_src(&g, st->value);
+    char vs[96]; ref(&g, st->value, vs, sizeof vs);
+    PolyDType base = ob; base.is_ptr = false; base.count = 1;
+    ind(&g); pb_str_printf(&g.out, "o4_[%d] = (%s)(%s);\n", lane, pb_ctype(base), vs);
+    /* forget lane-dependent temps so the next lane re-emits them under its own names */
+    for (int i = 0; i < k->n_nodes; i++)
+      if (g.emitted[i] >= 0 && (k->nodes[i].deps & g.lane_dep)) g.emitted[i] = -1;
+  }
+  ind(&g); pb_str_printf(&g.out, "{ %s o_ = %lld", g.idx_t, (long long)saff.offset);
+  for (int j = 0; j < st->n_loop; j++) {
+    int64_t s = saff.stride[st->loop[j]];
+    if (s) pb_str_printf(&g.out, " + r%d*%lld", st->loop[j], (long long)s);
+  }
+  pb_str_printf(&g.out, "; pb_st4(p%d + o_, o4_); }\n", st->param);
+  pb_str_puts(&g.out, "}\n");
+
+  char *res = NULL;
+  if (!g.failed) {
+    PbStr h; pb_str_init(&h);
+    char line[256];
+    snprintf(line, sizeof line, "//launch flat block=256 work=c%lld", (long long)n_threads);
+    emit_header(k, &h, line, usage);
+    pb_str_puts(&h, g.out.s);
+    res = pb_str_take(&h);
+  }
+  pb_str_free(&g.out);
+  free(g.emitted); free(g.scope_log); free(g.scope_mark);
+  return res;
+}
+
+/* ── general kernel: one thread per output element ───────────────────── */
+static char *render_flat(PbKern *k, const int *usage) {
+  Gen g; memset(&g, 0, sizeof g);
+  g.k = k;
+  g.emitted = malloc(sizeof(int) * (size_t)k->n_nodes);
+  for (int i = 0; i < k->n_nodes; i++) g.emitted[i] = -1;
+  g.scope_mark = calloc(64, sizeof(int));
+  bool wide = false;
+  for (int i = 0; i < k->n_params; i++)
+    if (k->params[i] && k->params[i]->dtype.ptr_size >= ((int64_t)1 << 31)) wide = true;
+  for (int s = 0; s < k->n_stores; s++) {
+    int64_t t = 1;
+    for (int i = 0; i < k->stores[s].n_loop; i++) t *= range_max(k, k->stores[s].loop[i]);
+    if (t >= ((int64_t)1 << 31)) wide = true;
+  }
+  g.wide = wide; g.idx_t = wide ? "long long" : "int";
+  pb_str_init(&g.out);
+  bool written[PB_MAX_PARAMS];
+  for (int i = 0; i < k->n_params; i++) written[i] = (usage[i] & 2) != 0;
+
+  pb_str_puts(&g.out, PRELUDE);
+  emit_signature(&g, written, 256);
+  pb_str_puts(&g.out, " {\n");
+  g.indent = 1;
+  ind(&g); pb_str_puts(&g.out, "const long long gid_ = (long long)blockIdx.x * blockDim.x + threadIdx.x;\n");
+
+  PbStr work; pb_str_init(&work);
+  /* stores with the same loop set share one section (and their common subexpressions) */
+  bool done[PB_MAX_STORES] = {0};
+  for (int s = 0; s < k->n_stores; s++) {
+    if (done[s]) continue;
+    PbStore *st = &k->stores[s];
+    uint64_t m = 0;
+    for (int i = 0; i < st->n_loop; i++) m |= (uint64_t)1 << st->loop[i];
+    if (work.n) pb_str_puts(&work, "|");
+    size_expr(k, st->loop, st->n_loop, &work);
+    ind(&g); pb_str_puts(&g.out, "{\n"); g.indent++;
+    /* section size */
+    ind(&g); pb_str_puts(&g.out, "long long tot_ = 1;");
+    for (int i = 0; i < st->n_loop; i++) {
+      char bs[64]; range_bound_str(&g, st->loop[i], bs, sizeof bs);
+      pb_str_printf(&g.out, " tot_ *= %s;", bs);
+    }
+    pb_str_puts(&g.out, "\n");
+    ind(&g); pb_str_puts(&g.out, "if (gid_ < tot_) {\n"); g.indent++;
+    open_scope(&g);
+    uint64_t saved = g.bound;
+    int order[PB_MAX_AXES];
+    order_loop_axes(k, st, order, NULL);
+    if (st->n_loop > 0) emit_decompose(&g, wide ? "gid_" : "(int)gid_", order, st->n_loop);
+    for (int s2 = s; s2 < k->n_stores; s2++) {
+      PbStore *st2 = &k->stores[s2];
+      uint64_t m2 = 0;
+      for (int i = 0; i < st2->n_loop; i++) m2 |= (uint64_t)1 << st2->loop[i];
+      if (done[s2] || m2 != m) continue;
+      done[s2] = true;
+      emit_store(&g, st2);
+    }
+    close_scope(&g);
+    g.bound = saved;
+    g.indent--; ind(&g); pb_str_puts(&g.out, "}\n");
+    g.indent--; ind(&g); pb_str_puts(&g.out, "}\n");
+  }
+  pb_str_puts(&g.out, "}\n");
+
+  char *res = NULL;
+  if (!g.failed) {
+    PbStr h; pb_str_init(&h);
+    PbStr line; pb_str_init(&line);
+    pb_str_printf(&line, "//launch flat block=256 work=%s", work.s);
+    emit_header(k, &h, line.s, usage);
+    pb_str_free(&line);
+    if (k->uses_half) pb_str_puts(&h, "#include <cuda_fp16.h>\n");
+    if (k->uses_bf16) pb_str_puts(&h, "#include <cuda_bf16.h>\n");
+    pb_str_puts(&h, g.out.s);
+    res = pb_str_take(&h);
+  } else if (!k->err[0]) {
+    snprintf(k->err, sizeof k->err, "rendering failed");
+  }
+  pb_str_free(&work);
+  pb_str_free(&g.out);
+  free(g.emitted); free(g.scope_log); free(g.scope_mark);
+  return res;
+}
+
+char *pb_render_jit(PbKern *k, const char *fn_name) {
+  (void)fn_name; /* the entry point has a fixed name so identical kernels share one binary */
+  int usage[PB_MAX_PARAMS];
+  param_usage(k, usage);
+  const char *force = getenv("POLY_B200_JIT");  /* "flat" forces the general mapping (debugging) */
+  if (!force || strcmp(force, "flat") != 0) {
+    char *r = render_group_reduce(k, usage);
+    if (r) return r;
+    r = render_vec_elementwise(k, usage);
+    if (r) return r;
+  }
+  return render_flat(k, usage);
+}
