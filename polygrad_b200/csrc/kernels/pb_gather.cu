@@ -1,0 +1,122 @@
+/*
+ * pb_gather.cu -- embedding lookup.
+ *
+ * polygrad expresses  out[t, d] = table[ids[t], d]  as a one-hot contraction
+ *   out[t, d] = sum_v  (ids[t] == arange[v]) ? table[v, d] : 0
+ * over the whole table (reference: src/modelzoo/models/gpt2.c:93-153), where ids
+ * and arange are float32 buffers.  The kernel keeps those semantics for any
+ * buffer contents: one block per token searches `arange` for every v that
+ * equals the token's id (none for NaN, out-of-range or fractional ids, which
+ * therefore give a row of +0), then adds the matching rows in ascending v
+ * starting from +0, exactly like the reference accumulation, so a -0.0f table
+ * entry comes out as +0.0f there and here.
+ *
+ * Cost per token: V floats of `arange` (L2-resident: 200 KB at V=50257) plus one
+ * table row; HBM traffic is the table rows read plus the output rows written.
+ */
+#include "../runtime/pb_runtime.h"
+#include <cstdio>
+
+struct GatherArgs {
+  float *out; const float *ids; const float *arange; const float *table;
+  long long vocab, table_vstride;
+  long long out_off, ids_off, table_off;
+  int ntok; long long tok_ext[4], tok_out[4], tok_ids[4];
+  int nfeat; long long feat_ext[3], feat_out[3], feat_tab[3];
+  long long n_tokens, n_feat;
+};
+
+#define GATHER_THREADS 256
+#define GATHER_MAX_MATCH 8
+
+__global__ void __launch_bounds__(GATHER_THREADS) pb200_gather_rows(const GatherArgs a) {
+  __shared__ int s_count;
+  __shared__ long long s_match[GATHER_MAX_MATCH];
+  for (long long tok = blockIdx.x; tok < a.n_tokens; tok += gridDim.x) {
+    long long rem = tok, o_out = a.out_off, o_ids = a.ids_off;
+    for (int i = 0; i < a.ntok; i++) {
+      const long long x = rem % a.tok_ext[i]; rem /= a.tok_ext[i];
+      o_out += x * a.tok_out[i]; o_ids += x * a.tok_ids[i];
+    }
+    if (threadIdx.x == 0) s_count = 0;
+    __syncthreads();
+    const float id = a.ids[o_ids];
+    /* fast candidate: arange is normally 0..V-1, but nothing relies on it */
+    for (long long v = threadIdx.x; v < a.vocab; v += GATHER_THREADS) {
+      if (a.arange[v] == id) {
+        const int slot = atomicAdd(&s_count, 1);
+        if (slot < GATHER_MAX_MATCH) s_match[slot] = v;
+      }
+    }
+    __syncthreads();
+    const int count = s_count;
+    if (count > 1 && count <= GATHER_MAX_MATCH && threadIdx.x == 0) {
+      /* ascending v: the order the reference adds in */
+      for (int i = 1; i < count; i++) {
+        long long x = s_match[i]; int j = i - 1;
+        while (j >= 0 && s_match[j] > x) { s_match[j + 1] = s_match[j]; j--; }
+        s_match[j + 1] = x;
+      }
+    }
+    __syncthreads();
+    for (long long f = threadIdx.x; f < a.n_feat; f += GATHER_THREADS) {
+      long long fr = f, o = o_out, t = a.table_off;
+      for (int i = 0; i < a.nfeat; i++) {
+        const long long x = fr % a.feat_ext[i]; fr /= a.feat_ext[i];
+        o += x * a.feat_out[i]; t += x * a.feat_tab[i];
+      }
+      float acc = 0.0f;
+      if (count <= GATHER_MAX_MATCH) {
+        for (int i = 0; i < count; i++) acc = acc + a.table[t + s_match[i] * a.table_vstride];
+      } else {
+        /* pathological arange with many duplicates: plain ordered scan */
+        for (long long v = 0; v < a.vocab; v++)
+          if (a.arange[v] == id) acc = acc + a.table[t + v * a.table_vstride];
+      }
+      a.out[o] = acc;
+    }
+    __syncthreads();
+  }
+}
+
+struct GatherProgram : PbAotProgram {
+  GatherArgs a{};
+  int p_out, p_ids, p_arange, p_table;
+  int launch(void *const *bufs, cudaStream_t stream) override {
+    GatherArgs g = a;
+    g.out = (float *)bufs[p_out]; g.ids = (const float *)bufs[p_ids];
+    g.arange = (const float *)bufs[p_arange]; g.table = (const float *)bufs[p_table];
+    if (g.n_tokens <= 0 || g.n_feat <= 0) return 0;
+    long long grid = g.n_tokens < 148LL * 16 ? g.n_tokens : 148LL * 16;
+    pb200_gather_rows<<<(unsigned)grid, GATHER_THREADS, 0, stream>>>(g);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { pb_set_error("gather launch: %s", cudaGetErrorString(e)); return -1; }
+    return 0;
+  }
+};
+
+PbAotProgram *pb_make_gather(const PbHeader &h, std::string &err) {
+  auto params = h.getv("params"), vocab = h.getv("vocab"), off = h.getv("offsets");
+  auto tok = h.getv("tok"), feat = h.getv("feat");
+  if (params.size() != 4 || vocab.size() != 2 || off.size() != 3 || tok.size() % 3 || feat.size() % 3 ||
+      tok.size() > 12 || feat.size() > 9) { err = "malformed gather header"; return nullptr; }
+  GatherProgram *p = new GatherProgram();
+  p->n_params = (int)h.geti("nparams");
+  p->p_out = (int)params[0]; p->p_ids = (int)params[1]; p->p_arange = (int)params[2]; p->p_table = (int)params[3];
+  p->rw.assign((size_t)p->n_params, '-');
+  for (int i = 1; i < 4; i++) p->rw[(size_t)params[i]] = 'r';
+  p->rw[(size_t)params[0]] = 'w';
+  GatherArgs &a = p->a;
+  a.vocab = vocab[0]; a.table_vstride = vocab[1];
+  a.out_off = off[0]; a.ids_off = off[1]; a.table_off = off[2];
+  a.ntok = (int)tok.size() / 3; a.nfeat = (int)feat.size() / 3;
+  a.n_tokens = 1; a.n_feat = 1;
+  for (int i = 0; i < a.ntok; i++) { a.tok_ext[i] = tok[3 * i]; a.tok_out[i] = tok[3 * i + 1]; a.tok_ids[i] = tok[3 * i + 2]; a.n_tokens *= a.tok_ext[i]; }
+  for (int i = 0; i < a.nfeat; i++) { a.feat_ext[i] = feat[3 * i]; a.feat_out[i] = feat[3 * i + 1]; a.feat_tab[i] = feat[3 * i + 2]; a.n_feat *= a.feat_ext[i]; }
+  /* feature axes: smallest output stride first so that consecutive threads write consecutive floats */
+  for (int i = 1; i < a.nfeat; i++)
+    for (int j = i; j > 0 && llabs(a.feat_out[j]) < llabs(a.feat_out[j - 1]); j--) {
+      std::swap(a.feat_ext[j], a.feat_ext[j - 1]); std::swap(a.feat_out[j], a.feat_out[j - 1]); std::swap(a.feat_tab[j], a.feat_tab[j - 1]);
+    }
+  return p;
+}

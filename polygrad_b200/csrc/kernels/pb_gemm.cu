@@ -1,0 +1,425 @@
+/*
+ * pb_gemm.cu -- plans a recognised contraction and runs it.
+ *
+ * polygrad's matmul (reference: src/frontend.c:1029-1129) reaches the backend as
+ * C[b.., m.., n..] = sum_k A[...] * B[...] (+ X[...]) (relu) with every operand
+ * described by an offset and one stride per axis.  The plan
+ *   1. orders the m axes (and the n axes) by output stride, which fixes the
+ *      canonical row and column index of C;
+ *   2. for A and B checks whether their strides nest in that same order; an
+ *      operand that does not (e.g. the head-merged attention output read as
+ *      [B, T, H*hd] from [B, H, T, hd] storage) is packed into a dense scratch
+ *      matrix by a strided copy first;
+ *   3. launches the fp32 CUDA-core kernel, or -- for bf16 operands or under the
+ *      bf16 compute policy (POLY_B200_GEMM=bf16) -- converts both operands to
+ *      K-major bf16 (weights once, cached per buffer version) and runs the
+ *      tcgen05 tensor-core kernel (pb_gemm_tc.cu).
+ *
+ * fp32 kernel: 128x128 block tile, 16-deep k slices, 256 threads, 8x8 register
+ * tile per thread as four 4x4 quadrants so that shared-memory reads are 128-bit
+ * and conflict-free; global loads are 128-bit when the operand's contiguous
+ * axis allows, register-staged double buffering.  FMA accumulation in k order
+ * within a thread (the reference CPU kernel adds products one by one in the
+ * same k order, unfused: results agree to fp32 rounding, not bitwise).
+ */
+#include "../runtime/pb_runtime.h"
+#include "pb_gemm.h"
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+
+/* ── strided pack: dst dense [outer..., inner] <- src with per-axis strides ── */
+struct PackArgs {
+  const void *src; void *dst;
+  int naxes; long long ext[PB_PACK_MAX_AXES], sstride[PB_PACK_MAX_AXES]; /* axis 0 is the fastest of dst */
+  long long total;
+};
+
+template <typename TS, typename TD>
+__global__ void __launch_bounds__(256) pb200_pack(const PackArgs a) {
+  const TS *__restrict__ src = (const TS *)a.src;
+  TD *__restrict__ dst = (TD *)a.dst;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.total; i += (long long)gridDim.x * blockDim.x) {
+    long long rem = i, o = 0;
+#pragma unroll 4
+    for (int d = 0; d < a.naxes; d++) { const long long x = rem % a.ext[d]; rem /= a.ext[d]; o += x * a.sstride[d]; }
+    dst[i] = (TD)src[o];
+  }
+}
+
+int pb_pack_launch(const void *src, void *dst, int naxes, const long long *ext, const long long *sstride,
+                   int src_dtype, int dst_dtype, cudaStream_t stream) {
+  PackArgs a; a.src = src; a.dst = dst; a.naxes = naxes; a.total = 1;
+  if (naxes > PB_PACK_MAX_AXES) { pb_set_error("pack: too many axes"); return -1; }
+  for (int i = 0; i < naxes; i++) { a.ext[i] = ext[i]; a.sstride[i] = sstride[i]; a.total *= ext[i]; }
+  if (a.total == 0) return 0;
+  long long blocks = (a.total + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  if (src_dtype == PB_F32 && dst_dtype == PB_F32) pb200_pack<float, float><<<(unsigned)blocks, 256, 0, stream>>>(a);
+  else if (src_dtype == PB_F32 && dst_dtype == PB_BF16) pb200_pack<float, __nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(a);
+  else if (src_dtype == PB_BF16 && dst_dtype == PB_BF16) pb200_pack<__nv_bfloat16, __nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(a);
+  else { pb_set_error("pack: unsupported dtypes"); return -1; }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { pb_set_error("pack launch: %s", cudaGetErrorString(e)); return -1; }
+  return 0;
+}
+
+/* ── fp32 kernel ─────────────────────────────────────────────────────── */
+#define BM 128
+#define BN 128
+#define BK 16
+
+struct SgemmArgs {
+  const float *A, *B; float *C; const float *X;
+  int M, N, K;
+  long long a_sm, a_sk, b_sk, b_sn, c_sm, c_sn, x_sm, x_sn;
+  int nb; int bext[4]; long long a_sb[4], b_sb[4], c_sb[4], x_sb[4];
+  int relu; int has_x;
+};
+
+/* Load a BMxBK tile of an operand whose "row" axis has stride s_row and whose k
+ * axis has stride s_k into smem laid out [BK][ROWS+PAD].  KMAJOR: k contiguous. */
+template <bool KMAJOR, bool VEC>
+__device__ __forceinline__ void load_tile(const float *__restrict__ base, long long s_row, long long s_k,
+                                          int row0, int k0, int rows, int K, float (&reg)[8]) {
+  const int tid = threadIdx.x;
+  if (KMAJOR) {
+    /* 128 rows x 16 k: thread t handles rows (t/4) and (t/4)+64, k quad (t%4)*4 */
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const int r = row0 + (tid >> 2) + h * 64;
+      const int k = k0 + (tid & 3) * 4;
+      if (VEC && r < rows && k + 3 < K) {
+        const float4 v = *reinterpret_cast<const float4 *>(base + (long long)r * s_row + k);
+        reg[h * 4 + 0] = v.x; reg[h * 4 + 1] = v.y; reg[h * 4 + 2] = v.z; reg[h * 4 + 3] = v.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          reg[h * 4 + j] = (r < rows && k + j < K) ? base[(long long)r * s_row + (long long)(k + j) * s_k] : 0.0f;
+      }
+    }
+  } else {
+    /* row axis contiguous: thread t handles k = t/32 and t/32+8, row quad (t%32)*4 */
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const int k = k0 + (tid >> 5) + h * 8;
+      const int r = row0 + (tid & 31) * 4;
+      if (VEC && k < K && r + 3 < rows) {
+        const float4 v = *reinterpret_cast<const float4 *>(base + (long long)k * s_k + r);
+        reg[h * 4 + 0] = v.x; reg[h * 4 + 1] = v.y; reg[h * 4 + 2] = v.z; reg[h * 4 + 3] = v.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          reg[h * 4 + j] = (k < K && r + j < rows) ? base[(long long)k * s_k + (long long)(r + j) * s_row] : 0.0f;
+      }
+    }
+  }
+}
+
+template <bool KMAJOR>
+__device__ __forceinline__ void store_tile(float (*sm)[BM + 4], const float (&reg)[8]) {
+  const int tid = threadIdx.x;
+  if (KMAJOR) {
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const int r = (tid >> 2) + h * 64;
+      const int k = (tid & 3) * 4;
+#pragma unroll
+      for (int j = 0; j < 4; j++) sm[k + j][r] = reg[h * 4 + j];
+    }
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const int k = (tid >> 5) + h * 8;
+      const int r = (tid & 31) * 4;
+      *reinterpret_cast<float4 *>(&sm[k][r]) = make_float4(reg[h * 4 + 0], reg[h * 4 + 1], reg[h * 4 + 2], reg[h * 4 + 3]);
+    }
+  }
+}
+
+template <bool A_KMAJOR, bool B_KMAJOR, bool VEC_A, bool VEC_B>
+__global__ void __launch_bounds__(256, 2) pb200_sgemm(const SgemmArgs g) {
+  __shared__ __align__(16) float As[2][BK][BM + 4];
+  __shared__ __align__(16) float Bs[2][BK][BN + 4];
+
+  /* batch offsets */
+  long long oa = 0, ob = 0, oc = 0, ox = 0;
+  {
+    int rem = blockIdx.z;
+    for (int i = 0; i < g.nb; i++) {
+      const int x = rem % g.bext[i]; rem /= g.bext[i];
+      oa += x * g.a_sb[i]; ob += x * g.b_sb[i]; oc += x * g.c_sb[i]; ox += x * g.x_sb[i];
+    }
+  }
+  const float *__restrict__ A = g.A + oa;
+  const float *__restrict__ B = g.B + ob;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+
+  float ra[8], rb[8];
+  load_tile<A_KMAJOR, VEC_A>(A, g.a_sm, g.a_sk, m0, 0, g.M, g.K, ra);
+  load_tile<B_KMAJOR, VEC_B>(B, g.b_sn, g.b_sk, n0, 0, g.N, g.K, rb);
+  store_tile<A_KMAJOR>(As[0], ra);
+  store_tile<B_KMAJOR>(Bs[0], rb);
+  __syncthreads();
+
+  const int nk = (g.K + BK - 1) / BK;
+  for (int kt = 0; kt < nk; kt++) {
+    const int cur = kt & 1;
+    if (kt + 1 < nk) {
+      load_tile<A_KMAJOR, VEC_A>(A, g.a_sm, g.a_sk, m0, (kt + 1) * BK, g.M, g.K, ra);
+      load_tile<B_KMAJOR, VEC_B>(B, g.b_sn, g.b_sk, n0, (kt + 1) * BK, g.N, g.K, rb);
+    }
+#pragma unroll
+    for (int k = 0; k < BK; k++) {
+      const float4 a0 = *reinterpret_cast<const float4 *>(&As[cur][k][ty * 4]);
+      const float4 a1 = *reinterpret_cast<const float4 *>(&As[cur][k][64 + ty * 4]);
+      const float4 b0 = *reinterpret_cast<const float4 *>(&Bs[cur][k][tx * 4]);
+      const float4 b1 = *reinterpret_cast<const float4 *>(&Bs[cur][k][64 + tx * 4]);
+      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    if (kt + 1 < nk) {
+      store_tile<A_KMAJOR>(As[cur ^ 1], ra);
+      store_tile<B_KMAJOR>(Bs[cur ^ 1], rb);
+    }
+    __syncthreads();
+  }
+
+  /* epilogue */
+  float *__restrict__ C = g.C + oc;
+  const float *__restrict__ X = g.has_x ? g.X + ox : nullptr;
+  const bool vec_c = (g.c_sn == 1) && ((g.c_sm & 3) == 0) && ((oc & 3) == 0) && ((reinterpret_cast<uintptr_t>(g.C) & 15) == 0);
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4);
+    if (m >= g.M) continue;
+#pragma unroll
+    for (int jh = 0; jh < 2; jh++) {
+      const int n = n0 + jh * 64 + tx * 4;
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float t = acc[i][jh * 4 + j];
+        if (X && n + j < g.N) t = t + X[(long long)m * g.x_sm + (long long)(n + j) * g.x_sn];
+        if (g.relu) t = (0.0f < t) ? t : 0.0f;
+        v[j] = t;
+      }
+      if (vec_c && n + 3 < g.N) {
+        *reinterpret_cast<float4 *>(C + (long long)m * g.c_sm + n) = make_float4(v[0], v[1], v[2], v[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          if (n + j < g.N) C[(long long)m * g.c_sm + (long long)(n + j) * g.c_sn] = v[j];
+      }
+    }
+  }
+}
+
+typedef void (*SgemmFn)(const SgemmArgs);
+template <bool AK, bool BKm>
+static SgemmFn pick_vec(bool va, bool vb) {
+  if (va && vb) return pb200_sgemm<AK, BKm, true, true>;
+  if (va) return pb200_sgemm<AK, BKm, true, false>;
+  if (vb) return pb200_sgemm<AK, BKm, false, true>;
+  return pb200_sgemm<AK, BKm, false, false>;
+}
+
+static int sgemm_launch(const SgemmArgs &g, long long nbatch, cudaStream_t stream) {
+  /* operand layout: contiguous along k, or along the row/column axis */
+  const bool a_k = (g.a_sk == 1) || g.K == 1, b_k = (g.b_sk == 1 && g.b_sn != 1);
+  const bool a_ok = a_k ? true : (g.a_sm == 1), b_ok = b_k ? true : (g.b_sn == 1);
+  auto aligned = [](const void *p, long long ld, const long long *sb, int nb) {
+    if (reinterpret_cast<uintptr_t>(p) & 15) return false;
+    if (ld & 3) return false;
+    for (int i = 0; i < nb; i++) if (sb[i] & 3) return false;
+    return true;
+  };
+  const bool va = a_ok && aligned(g.A, a_k ? g.a_sm : g.a_sk, g.a_sb, g.nb);
+  const bool vb = b_ok && aligned(g.B, b_k ? g.b_sn : g.b_sk, g.b_sb, g.nb);
+  SgemmFn fn;
+  if (a_k && b_k) fn = pick_vec<true, true>(va, vb);
+  else if (a_k) fn = pick_vec<true, false>(va, vb);
+  else if (b_k) fn = pick_vec<false, true>(va, vb);
+  else fn = pick_vec<false, false>(va, vb);
+  dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((g.M + BM - 1) / BM), (unsigned)nbatch);
+  if (grid.y > 65535 || grid.z > 65535) { pb_set_error("gemm: grid too large (%u, %u)", grid.y, grid.z); return -1; }
+  fn<<<grid, 256, 0, stream>>>(g);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { pb_set_error("sgemm launch: %s", cudaGetErrorString(e)); return -1; }
+  return 0;
+}
+
+/* ── plan ────────────────────────────────────────────────────────────── */
+typedef PbGemmAxis Axis;
+
+/* Do the strides sel(axes[i]) nest in this order?  Returns the innermost stride. */
+template <class F>
+static bool nests(const std::vector<Axis> &ax, F sel, long long *inner) {
+  if (ax.empty()) { *inner = 0; return true; }
+  for (size_t i = 0; i + 1 < ax.size(); i++)
+    if (sel(ax[i]) != sel(ax[i + 1]) * ax[i + 1].ext) return false;
+  *inner = sel(ax.back());
+  return true;
+}
+
+bool pb_gemm_policy_bf16(void) {
+  static int cached = -1;
+  if (cached < 0) { const char *e = getenv("POLY_B200_GEMM"); cached = (e && strcmp(e, "bf16") == 0) ? 1 : 0; }
+  return cached == 1;
+}
+
+PbGemmProgram::~PbGemmProgram() { pb_scratch_free(tc_a.data); pb_scratch_free(tc_b.data); }
+
+int PbGemmProgram::pack_into(void *dst, const void *src, long long off, bool is_a, int src_dtype, int dst_dtype, cudaStream_t stream) {
+  std::vector<long long> ext, str;
+  auto sel = [&](const Axis &x) { return is_a ? x.sa : x.sb; };
+  for (int i = (int)k_ax.size() - 1; i >= 0; i--) { ext.push_back(k_ax[i].ext); str.push_back(sel(k_ax[i])); }
+  const std::vector<Axis> &rows = is_a ? m_ax : n_ax;
+  for (int i = (int)rows.size() - 1; i >= 0; i--) { ext.push_back(rows[i].ext); str.push_back(sel(rows[i])); }
+  for (size_t i = 0; i < b_ax.size(); i++) { ext.push_back(b_ax[i].ext); str.push_back(sel(b_ax[i])); }
+  const char *s = (const char *)src + off * (src_dtype == PB_F32 ? 4 : 2);
+  if (pb_pack_launch(s, dst, (int)ext.size(), ext.data(), str.data(), src_dtype, dst_dtype, stream) != 0) return -1;
+  launches++;
+  return 0;
+}
+
+void *PbGemmProgram::pack_operand(const void *src, long long off, bool is_a, int src_dtype, int dst_dtype, cudaStream_t stream) {
+  const size_t esz = dst_dtype == PB_F32 ? 4 : 2;
+  const long long rowsz = is_a ? M : N;
+  void *dst = pb_scratch_alloc((size_t)(nbatch * rowsz * K) * esz);
+  if (!dst) return nullptr;
+  if (pack_into(dst, src, off, is_a, src_dtype, dst_dtype, stream) != 0) { pb_scratch_free(dst); return nullptr; }
+  return dst;
+}
+
+int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
+  launches = 0;
+  if (dtype == PB_BF16 || pb_gemm_policy_bf16()) {
+    int rc = pb_gemm_tc_run(*this, bufs, stream);
+    if (rc != PB_TC_UNSUPPORTED) return rc;
+    if (dtype == PB_BF16) { pb_set_error("gemm: bf16 operands need the tensor-core kernel, which rejected this shape"); return -1; }
+  }
+  SgemmArgs g{};
+  void *pa = nullptr, *pb = nullptr;
+  g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.nb = (int)b_ax.size();
+  for (int i = 0; i < g.nb; i++) {
+    g.bext[i] = (int)b_ax[i].ext; g.c_sb[i] = b_ax[i].sc; g.x_sb[i] = b_ax[i].sx;
+    g.a_sb[i] = b_ax[i].sa; g.b_sb[i] = b_ax[i].sb;
+  }
+  if (a_direct) { g.A = (const float *)bufs[p_a] + off_a; g.a_sm = a_sm; g.a_sk = a_sk; }
+  else {
+    pa = pack_operand(bufs[p_a], off_a, true, PB_F32, PB_F32, stream);
+    if (!pa) return -1;
+    g.A = (const float *)pa; g.a_sm = K; g.a_sk = 1;
+    long long s = M * K;
+    for (int i = 0; i < g.nb; i++) { g.a_sb[i] = s; s *= b_ax[i].ext; }
+  }
+  if (b_direct) { g.B = (const float *)bufs[p_b] + off_b; g.b_sk = b_sk; g.b_sn = b_sn; }
+  else {
+    pb = pack_operand(bufs[p_b], off_b, false, PB_F32, PB_F32, stream);
+    if (!pb) { pb_scratch_free(pa); return -1; }
+    g.B = (const float *)pb; g.b_sn = K; g.b_sk = 1;
+    long long s = N * K;
+    for (int i = 0; i < g.nb; i++) { g.b_sb[i] = s; s *= b_ax[i].ext; }
+  }
+  g.C = (float *)bufs[p_c] + off_c; g.c_sm = c_sm; g.c_sn = c_sn;
+  g.has_x = has_x ? 1 : 0; g.relu = relu ? 1 : 0;
+  if (has_x) { g.X = (const float *)bufs[p_x] + off_x; g.x_sm = x_sm; g.x_sn = x_sn; }
+  int rc;
+  if (g.c_sn != 1 && g.c_sm == 1) {
+    /* column-major output: compute the transposed problem so that stores stay contiguous */
+    SgemmArgs t = g;
+    t.A = g.B; t.B = g.A; t.M = g.N; t.N = g.M;
+    t.a_sm = g.b_sn; t.a_sk = g.b_sk; t.b_sk = g.a_sk; t.b_sn = g.a_sm;
+    t.c_sm = g.c_sn; t.c_sn = g.c_sm; t.x_sm = g.x_sn; t.x_sn = g.x_sm;
+    for (int i = 0; i < g.nb; i++) { t.a_sb[i] = g.b_sb[i]; t.b_sb[i] = g.a_sb[i]; }
+    rc = sgemm_launch(t, nbatch, stream);
+  } else rc = sgemm_launch(g, nbatch, stream);
+  launches++;
+  /* stream-ordered pool: the blocks may be reused by later launches on the same stream */
+  pb_scratch_free(pa); pb_scratch_free(pb);
+  return rc;
+}
+
+PbAotProgram *pb_make_gemm(const PbHeader &h, std::string &err) {
+  auto params = h.getv("params"), off = h.getv("offsets");
+  if (params.size() != 4 || off.size() != 4) { err = "malformed gemm header"; return nullptr; }
+  PbGemmProgram *p = new PbGemmProgram();
+  p->n_params = (int)h.geti("nparams");
+  p->p_c = (int)params[0]; p->p_a = (int)params[1]; p->p_b = (int)params[2]; p->p_x = (int)params[3];
+  p->has_x = p->p_x >= 0;
+  p->relu = h.geti("relu") != 0;
+  const std::string &dt = h.get("dtype");
+  if (dt == "f32") p->dtype = PB_F32; else if (dt == "bf16") p->dtype = PB_BF16;
+  else { err = "gemm operand dtype '" + dt + "' has no kernel"; delete p; return nullptr; }
+  p->off_c = off[0]; p->off_a = off[1]; p->off_b = off[2]; p->off_x = off[3];
+  p->rw.assign((size_t)p->n_params, '-');
+  p->rw[(size_t)p->p_a] = 'r'; p->rw[(size_t)p->p_b] = 'r';
+  if (p->has_x) p->rw[(size_t)p->p_x] = 'r';
+  int naxes = (int)h.geti("naxes");
+  p->M = p->N = p->K = p->nbatch = 1;
+  for (int i = 0; i < naxes; i++) {
+    char key[32]; snprintf(key, sizeof key, "axis%d", i);
+    const std::string &line = h.get(key);
+    Axis a{}; char kind = 0;
+    if (sscanf(line.c_str(), "%c %lld %lld %lld %lld %lld", &kind, &a.ext, &a.sc, &a.sa, &a.sb, &a.sx) != 6) {
+      err = "malformed gemm axis line"; delete p; return nullptr;
+    }
+    a.kind = kind;
+    if (kind == 'm') { p->m_ax.push_back(a); p->M *= a.ext; }
+    else if (kind == 'n') { p->n_ax.push_back(a); p->N *= a.ext; }
+    else if (kind == 'k') { p->k_ax.push_back(a); p->K *= a.ext; }
+    else if (kind == 'b') { p->b_ax.push_back(a); p->nbatch *= a.ext; }
+    else { err = "unknown gemm axis kind"; delete p; return nullptr; }
+  }
+  auto by_sc = [](const Axis &x, const Axis &y) { return x.sc > y.sc; };
+  std::sort(p->m_ax.begin(), p->m_ax.end(), by_sc);
+  std::sort(p->n_ax.begin(), p->n_ax.end(), by_sc);
+  std::sort(p->k_ax.begin(), p->k_ax.end(), [](const Axis &x, const Axis &y) { return x.sa > y.sa; });
+  if (!nests(p->m_ax, [](const Axis &x) { return x.sc; }, &p->c_sm) ||
+      !nests(p->n_ax, [](const Axis &x) { return x.sc; }, &p->c_sn)) { err = "gemm output axes do not nest"; delete p; return nullptr; }
+  if (p->has_x && (!nests(p->m_ax, [](const Axis &x) { return x.sx; }, &p->x_sm) ||
+                   !nests(p->n_ax, [](const Axis &x) { return x.sx; }, &p->x_sn))) { err = "gemm addend axes do not nest"; delete p; return nullptr; }
+  long long t;
+  p->a_direct = nests(p->m_ax, [](const Axis &x) { return x.sa; }, &p->a_sm) &&
+                nests(p->k_ax, [](const Axis &x) { return x.sa; }, &p->a_sk);
+  p->b_direct = nests(p->n_ax, [](const Axis &x) { return x.sb; }, &p->b_sn) &&
+                nests(p->k_ax, [](const Axis &x) { return x.sb; }, &p->b_sk);
+  (void)t;
+  if (p->m_ax.empty()) p->a_sm = 0;
+  if (p->n_ax.empty()) p->b_sn = 0;
+  /* the fp32 kernel wants one operand axis with unit stride, and positive strides */
+  if (p->a_direct && !((p->a_sk == 1 || p->a_sm == 1) && p->a_sk > 0 && p->a_sm >= 0)) p->a_direct = false;
+  if (p->b_direct && !((p->b_sk == 1 || p->b_sn == 1) && p->b_sk > 0 && p->b_sn >= 0)) p->b_direct = false;
+  if (p->M > 2147483647LL || p->N > 2147483647LL || p->K > 2147483647LL || p->nbatch > 65535) {
+    err = "gemm extents out of range"; delete p; return nullptr;
+  }
+  /* full overwrite of the output? dense if the output strides tile [0, numel) */
+  auto numel = h.getv("numel");
+  long long covered = p->M * p->N * p->nbatch;
+  bool dense = !numel.empty() && covered == numel[0] && p->off_c == 0;
+  if (dense) {
+    std::vector<std::pair<long long, long long>> se;
+    for (auto &a : p->m_ax) se.push_back({a.sc, a.ext});
+    for (auto &a : p->n_ax) se.push_back({a.sc, a.ext});
+    for (auto &a : p->b_ax) se.push_back({a.sc, a.ext});
+    std::sort(se.begin(), se.end());
+    long long expect = 1;
+    for (auto &x : se) { if (x.first != expect) { dense = false; break; } expect *= x.second; }
+  }
+  bool x_is_c = p->has_x && p->p_x == p->p_c;
+  p->rw[(size_t)p->p_c] = x_is_c ? 'b' : (dense ? 'W' : 'w');
+  return p;
+}

@@ -1,0 +1,58 @@
+/*
+ * pb_gemm.h -- the planned contraction shared by the fp32 kernel (pb_gemm.cu)
+ * and the tensor-core kernel (pb_gemm_tc.cu).
+ */
+#ifndef PB_GEMM_H
+#define PB_GEMM_H
+
+#include "../runtime/pb_runtime.h"
+#include <cuda_bf16.h>
+#include <vector>
+
+enum { PB_F32 = 0, PB_BF16 = 1 };
+#define PB_PACK_MAX_AXES 12
+#define PB_TC_UNSUPPORTED 77
+
+/* dst[i] (dense, axis 0 fastest) = (dst type) src[sum_d x_d * sstride[d]] */
+int pb_pack_launch(const void *src, void *dst, int naxes, const long long *ext, const long long *sstride,
+                   int src_dtype, int dst_dtype, cudaStream_t stream);
+
+/* One axis of the contraction: kind m/n/k/b, extent, and the stride it has in
+ * the output C, in A, in B and in the addend X (0 where it does not appear). */
+struct PbGemmAxis { char kind; long long ext, sc, sa, sb, sx; };
+
+/* A bf16, K-major copy of one operand, kept while the source is unchanged. */
+struct PbTcOperand {
+  void *data = nullptr; size_t bytes = 0;
+  const void *src = nullptr; uint64_t version = 0;
+};
+
+struct PbGemmProgram : PbAotProgram {
+  int p_c = -1, p_a = -1, p_b = -1, p_x = -1;
+  int dtype = PB_F32;                 /* storage type of A and B */
+  long long off_c = 0, off_a = 0, off_b = 0, off_x = 0;
+  bool relu = false, has_x = false;
+  std::vector<PbGemmAxis> m_ax, n_ax, k_ax, b_ax;   /* m, n by output stride (largest first); k by A stride */
+  long long M = 1, N = 1, K = 1, nbatch = 1;
+  bool a_direct = false, b_direct = false;          /* strides nest: usable without packing */
+  long long a_sm = 0, a_sk = 0, b_sk = 0, b_sn = 0, c_sm = 0, c_sn = 0, x_sm = 0, x_sn = 0;
+  int launches = 1;
+  PbTcOperand tc_a, tc_b;
+
+  ~PbGemmProgram() override;
+  int n_launches() const override { return launches; }
+  int launch(void *const *bufs, cudaStream_t stream) override;
+
+  /* Dense [batch.., rows.., k..] copy (k fastest) of A or B in dst_dtype into dst. */
+  int pack_into(void *dst, const void *src, long long off, bool is_a, int src_dtype, int dst_dtype, cudaStream_t stream);
+  void *pack_operand(const void *src, long long off, bool is_a, int src_dtype, int dst_dtype, cudaStream_t stream);
+};
+
+/* Tensor-core path: returns 0 / -1, or PB_TC_UNSUPPORTED when the shape is not handled. */
+int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream);
+
+/* POLY_B200_GEMM=bf16: run fp32 contractions with operands rounded to bf16
+ * (round-to-nearest-even), products and sums in fp32, on the tensor cores. */
+bool pb_gemm_policy_bf16(void);
+
+#endif
