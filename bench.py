@@ -1,0 +1,378 @@
+#!/usr/bin/env python
+"""GPT-2 forward throughput through polygrad's instance API on the B200 backend.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype bf16|fp32]
+                    [--workload gpt2-124m|gpt2-1.5b] [--impl b200|reference]
+
+One step = one forward pass of the workload's batch (8 x 1024 token ids) on every
+rank.  Ranks hold independent replicas (weights replicated, batch rows sharded),
+so the data path has no collective; the last-position logits of every rank are
+gathered to rank 0 with NCCL inside the timed region (the full logits can be
+gathered with --gather full).  Prints one JSON line on rank 0.
+
+--impl reference times stock polygrad's CPU backend (oracle/_ref, built from
+polygrad's own sources) on a bounded sample of the same workload.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+os.environ['PATH'] = os.path.join(ROOT, 'oracle', 'shim') + os.pathsep + os.environ.get('PATH', '')
+
+WORKLOADS = {
+    # BASELINE configs[3] and configs[4]; batch 8 x 1024 per plan (micro-batch of the 1.5B config)
+    'gpt2-124m': dict(vocab_size=50257, n_embd=768, n_head=12, n_layer=12, max_seq_len=1024, max_batch=8),
+    'gpt2-1.5b': dict(vocab_size=50257, n_embd=1600, n_head=25, n_layer=48, max_seq_len=1024, max_batch=8),
+}
+SEED = 1234
+CPU_SAMPLE_T = 16        # tokens of one sequence that the CPU baseline runs (full width and depth)
+
+
+def flops_per_token(cfg):
+    d, l, v, t = cfg['n_embd'], cfg['n_layer'], cfg['vocab_size'], cfg['max_seq_len']
+    per_layer = 2 * (d * 3 * d + d * d + d * 4 * d + 4 * d * d) + 4 * t * d   # projections + full T x T attention
+    return l * per_layer + 2 * d * v
+
+
+def read_peaks():
+    p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.isfile(p):
+        j = json.load(open(p))
+        return dict(hbm_gbs=j['hbm_gbs'], bf16_tflops=j['bf16_tflops'],
+                    bf16_tflops_sustained=j.get('bf16_tflops_sustained', j['bf16_tflops']), source='measured')
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source='fallback')
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi during the timed region."""
+    Q = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+         'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', '-i', str(self.index), '--query-gpu=' + self.Q,
+                                          '--format=csv,noheader,nounits', '-lms', '100'],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=['nvidia-smi unavailable'])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(',')]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith('active'):
+                    reasons.add(n)
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=mx, reasons=sorted(reasons),
+                    samples=len(sm))
+
+
+# ── reference arm: stock polygrad on the host cores ────────────────────────
+def cpu_forward_sample(cfg, steps, warmup):
+    """Stock polygrad (CPU backend) forward on one sequence of CPU_SAMPLE_T tokens
+    with the workload's full width, depth and vocabulary.  Returns tokens/s."""
+    from polygrad_b200 import ffi
+    from polygrad_b200.instance import Instance, gpt2_init
+    path = os.path.join(ROOT, 'oracle', '_ref', 'libpolygrad_ref.so')
+    ref = ffi.load_reference(path)
+    c = dict(cfg, max_seq_len=CPU_SAMPLE_T, max_batch=1)
+    inst = Instance.gpt2(ref, **c)
+    inst.init_params(gpt2_init(SEED))
+    tok = np.random.default_rng(SEED).integers(0, cfg['vocab_size'], (1, CPU_SAMPLE_T))
+    inputs = inst.gpt2_inputs(tok)
+    for _ in range(max(warmup, 1)):      # first call compiles the kernels (cached on disk afterwards)
+        inst.forward(**inputs)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        inst.forward(**inputs)
+    dt = (time.perf_counter() - t0) / steps
+    inst.free()
+    return CPU_SAMPLE_T / dt, dt
+
+
+def run_reference(args, cfg, rank):
+    if rank != 0:
+        return
+    tps, dt = cpu_forward_sample(cfg, args.steps, args.warmup)
+    sample = (f'1 sequence x {CPU_SAMPLE_T} tokens, full {cfg["n_layer"]} layers, d={cfg["n_embd"]}, '
+              f'vocab {cfg["vocab_size"]}; stock polygrad CPU backend (single-threaded by construction)')
+    line = dict(impl='reference', metric='gpt2_forward_tokens_per_s', value=tps, unit='tokens/s', n_gpus=args.gpus,
+                steps=args.steps, warmup=args.warmup, ms_per_step=dt * 1e3, higher_is_better=True,
+                scaling='weak', vs_baseline=None, dtype='f32', data='synthetic',
+                config=dict(workload=args.workload, sample=sample),
+                cpu_baseline=dict(value=tps, unit='tokens/s', cores=1, kind='reference', sample=sample),
+                e2e=dict(value=tps, unit='tokens/s', h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gpu_launches=0)
+    print(json.dumps(line), flush=True)
+
+
+# ── product arm ─────────────────────────────────────────────────────────────
+class DevArray:
+    """Zero-copy view of a device buffer for torch (CUDA array interface)."""
+
+    def __init__(self, ptr, shape, typestr='<f4'):
+        self.__cuda_array_interface__ = dict(shape=tuple(shape), typestr=typestr, data=(int(ptr), False), version=3)
+
+
+def run_b200(args, cfg, rank, world, local_rank):
+    from polygrad_b200 import ffi
+    from polygrad_b200.instance import Instance, gpt2_init
+
+    if args.dtype == 'bf16':
+        os.environ['POLY_B200_GEMM'] = 'bf16'
+    lib = ffi.product()
+    lib.poly_b200_set_device(local_rank)
+    if lib.poly_cuda_init() != 0:
+        raise SystemExit('bench: no usable B200: ' + lib.last_error())
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group('nccl', device_id=torch.device('cuda', local_rank))
+
+    B, T, V = cfg['max_batch'], cfg['max_seq_len'], cfg['vocab_size']
+    inst = Instance.gpt2(lib, **cfg)
+    inst.init_params(gpt2_init(SEED))          # replicas: same weights on every rank
+    inst.set_device(ffi.DEVICE_CUDA)
+    rng = np.random.default_rng([SEED, rank])  # each rank's own shard of the batch
+    tokens = rng.integers(0, V, (B, T)).astype(np.float32)
+    inputs = inst.gpt2_inputs(tokens)
+    out_idx = inst.bufs['output'][0]
+    n_logits = B * T * V
+
+    # pinned host buffers for the end-to-end leg
+    pin_tok = lib.poly_b200_host_alloc(tokens.nbytes)
+    pin_out = lib.poly_b200_host_alloc(n_logits * 4)
+    ctypes.memmove(pin_tok, tokens.ctypes.data, tokens.nbytes)
+    io = (ffi.PolyIOBinding * 1)()
+    io[0].name = b'x'
+    io[0].data = ctypes.cast(pin_tok, ctypes.POINTER(ctypes.c_float))
+
+    def forward_resident():
+        if lib.poly_instance_forward(inst.h, None, 0) != 0:
+            raise SystemExit('bench: forward failed: ' + lib.last_error())
+
+    def forward_e2e():
+        if lib.poly_instance_forward(inst.h, io, 1) != 0:
+            raise SystemExit('bench: forward failed: ' + lib.last_error())
+        if lib.poly_instance_readback_buf(inst.h, out_idx, pin_out, n_logits * 4) != 0:
+            raise SystemExit('bench: readback failed: ' + lib.last_error())
+
+    # first call: schedule + lower + compile the plan, upload inputs
+    inst.forward(**inputs)
+    lib.poly_b200_synchronize()
+    # where the logits live on the device (for the gather)
+    probe = np.empty(1, np.float32)
+    lib.poly_instance_readback_buf(inst.h, out_idx, probe.ctypes.data, 4)
+    logits_ptr = lib.poly_b200_last_dtoh_src()
+
+    gather = None
+    if dist is not None:
+        import torch
+        logits = torch.as_tensor(DevArray(logits_ptr, (B, T, V)), device=torch.device('cuda', local_rank))
+        if args.gather == 'full':
+            src = logits
+        else:
+            src = torch.empty((B, V), dtype=torch.float32, device=logits.device)
+        dst = [torch.empty_like(src) for _ in range(world)] if rank == 0 else None
+
+        def gather():
+            lib.poly_b200_synchronize()           # logits complete before NCCL's stream reads them
+            if args.gather != 'full':
+                src.copy_(logits[:, -1, :])
+            dist.gather(src, dst, dst=0)
+
+    def barrier():
+        lib.poly_b200_synchronize()
+        if dist is not None:
+            import torch
+            torch.cuda.synchronize()
+            dist.barrier()
+
+    def timed(fn, steps):
+        """`steps` calls of fn between two events on the launching stream; max over ranks."""
+        barrier()
+        e0, e1 = lib.poly_b200_event_create(), lib.poly_b200_event_create()
+        t0 = time.perf_counter()
+        lib.poly_b200_event_record(e0)
+        for _ in range(steps):
+            fn()
+            if gather is not None:
+                gather()
+        lib.poly_b200_event_record(e1)
+        ms = lib.poly_b200_event_elapsed_ms(e0, e1)
+        if dist is not None:
+            import torch
+            torch.cuda.synchronize()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        lib.poly_b200_event_destroy(e0); lib.poly_b200_event_destroy(e1)
+        # with a gather in the loop the NCCL stream is outside the events: use the host clock there
+        ms = max(ms, wall_ms) if gather is not None else ms
+        if dist is not None:
+            import torch
+            t = torch.tensor([ms], dtype=torch.float64, device='cuda')
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    for _ in range(args.warmup):
+        forward_resident()
+    lib.poly_b200_stats_reset()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms_step = timed(forward_resident, args.steps)
+    clocks = sampler.stop()
+    st = lib.stats()
+    launches_per_step = st['launches'] // max(args.steps, 1)
+
+    for _ in range(min(args.warmup, 2)):
+        forward_e2e()
+    ms_e2e = timed(forward_e2e, max(1, min(args.steps, 5)))
+
+    tokens_per_step = B * T * world
+    value = tokens_per_step / (ms_step * 1e-3)
+    e2e_value = tokens_per_step / (ms_e2e * 1e-3)
+
+    # roofline of the dominant kernel: the contraction; measured live per launch
+    roof = gemm_roofline(lib, args, cfg)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        tps, dt = cpu_forward_sample(cfg, 1, 1)
+        cpu = dict(value=tps, unit='tokens/s', cores=1, kind='reference',
+                   sample=f'1 sequence x {CPU_SAMPLE_T} tokens, full depth/width/vocabulary, stock polygrad CPU '
+                          f'backend, single-threaded by construction ({dt:.1f} s per forward)')
+
+    if rank == 0:
+        line = dict(metric='gpt2_forward_tokens_per_s', value=value, unit='tokens/s', n_gpus=world,
+                    steps=args.steps, warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True,
+                    scaling='weak', vs_baseline=None, dtype='bf16' if args.dtype == 'bf16' else 'f32',
+                    data='synthetic',
+                    config=dict(workload=args.workload, batch_per_gpu=B, seq_len=T, parallelism=f'dp{world}',
+                                gemm=('bf16 operands, fp32 accumulate (tcgen05)' if args.dtype == 'bf16' else 'fp32 CUDA cores'),
+                                l2='23 GB of activations per step, far above the 126 MB L2',
+                                gather=(args.gather if world > 1 else 'none'),
+                                model_tflops=flops_per_token(cfg) * value / 1e12),
+                    e2e=dict(value=e2e_value, unit='tokens/s', h2d_bytes_per_step=int(tokens.nbytes),
+                             d2h_bytes_per_step=int(n_logits * 4)),
+                    gpu_launches=int(launches_per_step * args.steps),
+                    launches_per_step=int(launches_per_step),
+                    clocks=clocks, roofline=roof, cpu_baseline=cpu, stats=st)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def gemm_roofline(lib, args, cfg):
+    """Times the workload's largest projection (tokens x 4d x d) alone through
+    poly_realize and reports it against the tensor-pipe (bf16) peak."""
+    from polygrad_b200 import ffi
+    from polygrad_b200.tensor import Device
+    peaks = read_peaks()
+    M, K, N = cfg['max_batch'] * cfg['max_seq_len'], cfg['n_embd'], 4 * cfg['n_embd']
+    dev = Device(lib, ffi.DEVICE_CUDA)
+    rng = np.random.default_rng(SEED)
+    a = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    b = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    ms = time_realize(lib, dev, a, b, reps=20)
+    flops = 2.0 * M * N * K
+    achieved = flops / (ms * 1e-3) / 1e12
+    if args.dtype == 'bf16':
+        peak, bound = peaks['bf16_tflops'], 'tensor'
+    else:
+        peak, bound = 75.0, 'fp32-cuda-core'
+    return dict(bound=bound, achieved=achieved, peak=peak, unit='TFLOP/s', frac=achieved / peak, traffic=None,
+                kernel=f'gemm {M}x{N}x{K}', peak_source=peaks['source'] if args.dtype == 'bf16' else 'nominal fp32 FMA rate',
+                ms_per_launch=ms)
+
+
+def time_realize(lib, dev, a, b, reps):
+    """Device time of one realize of a @ b with operands resident (events on the launching stream)."""
+    from polygrad_b200 import ffi
+    from polygrad_b200.tensor import _i64
+    ta, tb = dev.tensor(a), dev.tensor(b)
+    out = ta.dot(tb)
+    n = out.numel()
+    out_buf = lib.poly_buffer_by_id(dev.ctx, n, ffi.DTYPE_IDS['float32'])
+    store = lib.poly_store_val(dev.ctx, out_buf, lib.poly_reshape(dev.ctx, out.uop, _i64([n]), 1))
+    sink = lib.poly_sink1(dev.ctx, store)
+    pairs = list(out.leaves) + [(out_buf, np.empty(n, np.float32))]
+    binds = (ffi.PolyBufferBinding * len(pairs))()
+    for i, (buf, host) in enumerate(pairs):
+        d = lib.poly_cuda_alloc(host.nbytes)
+        if i < len(pairs) - 1:
+            lib.poly_cuda_copy_htod(d, host.ctypes.data, host.nbytes)
+        binds[i].buffer, binds[i].handle.ptr = buf, d
+        binds[i].handle.nbytes, binds[i].handle.domain = host.nbytes, ffi.DEVICE_CUDA
+    for _ in range(3):
+        assert lib.poly_realize(dev.ctx, sink, binds, len(pairs)) == 0, lib.last_error()
+    e0, e1 = lib.poly_b200_event_create(), lib.poly_b200_event_create()
+    lib.poly_b200_event_record(e0)
+    for _ in range(reps):
+        lib.poly_realize(dev.ctx, sink, binds, len(pairs))
+    lib.poly_b200_event_record(e1)
+    ms = lib.poly_b200_event_elapsed_ms(e0, e1) / reps
+    for i in range(len(pairs)):
+        lib.poly_cuda_free(binds[i].handle.ptr)
+    return ms
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
+    ap.add_argument('--workload', default='gpt2-124m', choices=sorted(WORKLOADS))
+    ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp32'])
+    ap.add_argument('--gather', default='last', choices=['last', 'full'])
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == 'b200' else max(args.warmup, 1)
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    cfg = WORKLOADS[args.workload]
+    if args.impl == 'reference':
+        run_reference(args, cfg, rank)
+    else:
+        run_b200(args, cfg, rank, world, local_rank)
+
+
+if __name__ == '__main__':
+    main()

@@ -92,6 +92,15 @@ int  poly_b200_synchronize(void);
 /* The internal stream as a cudaStream_t. */
 void *poly_b200_stream(void);
 
+/* Page-locked host memory for fast copies (cudaHostAlloc). */
+void *poly_b200_host_alloc(size_t bytes);
+void  poly_b200_host_free(void *p);
+
+/* Device address that the most recent poly_cuda_copy_dtoh read from.  polygrad's
+ * instance API hides device handles; a one-element readback followed by this
+ * call tells a caller where an instance buffer lives (for NCCL, for example). */
+unsigned long long poly_b200_last_dtoh_src(void);
+
 /* Release cached free blocks of the pool back to the driver. */
 void poly_b200_trim(void);
 

@@ -351,9 +351,28 @@ extern "C" int poly_cuda_copy_htod(unsigned long long dst, const void *src, size
   return 0;
 }
 
+static unsigned long long g_last_dtoh_src = 0;
+extern "C" unsigned long long poly_b200_last_dtoh_src(void) { return g_last_dtoh_src; }
+
+extern "C" void *poly_b200_host_alloc(size_t bytes) {
+  if (!ready()) return nullptr;
+  if (R.dry) return malloc(bytes ? bytes : 1);
+  void *p = nullptr;
+  if (cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocDefault) != cudaSuccess) {
+    pb_set_error("cudaHostAlloc(%zu) failed: %s", bytes, cudaGetErrorString(cudaGetLastError()));
+    return nullptr;
+  }
+  return p;
+}
+extern "C" void poly_b200_host_free(void *p) {
+  if (!p) return;
+  if (R.dry) free(p); else cudaFreeHost(p);
+}
+
 extern "C" int poly_cuda_copy_dtoh(void *dst, unsigned long long src, size_t bytes) {
   if (!ready()) return -1;
   void *p = (void *)(uintptr_t)src;
+  g_last_dtoh_src = src;
   if (note_access(p, 'r') != 0) return -1;
   if (R.dry) { memcpy(dst, p, bytes); return 0; }
   PB_CUDA(cudaMemcpyAsync(dst, p, bytes, cudaMemcpyDeviceToHost, R.stream));

@@ -141,6 +141,9 @@ def _declare_cuda(lib):
     _sig(lib, 'poly_b200_synchronize', ctypes.c_int, [])
     _sig(lib, 'poly_b200_stream', _ptr, [])
     _sig(lib, 'poly_b200_trim', None, [])
+    _sig(lib, 'poly_b200_host_alloc', _ptr, [S])
+    _sig(lib, 'poly_b200_host_free', None, [_ptr])
+    _sig(lib, 'poly_b200_last_dtoh_src', U, [])
     _sig(lib, 'poly_b200_event_create', _ptr, [])
     _sig(lib, 'poly_b200_event_record', ctypes.c_int, [_ptr])
     _sig(lib, 'poly_b200_event_elapsed_ms', ctypes.c_float, [_ptr, _ptr])

@@ -1,0 +1,91 @@
+"""Host-side logic, no GPU: the C-ABI library loads and exports what
+include/poly_b200.h declares; the kernel classifier and renderer process
+polygrad's scheduled kernels (dry run: programs are rendered and compiled by
+NVRTC, which needs no device, and launches are ignored)."""
+import ctypes
+import json
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+from conftest import ROOT
+
+HEADER = os.path.join(ROOT, 'include', 'poly_b200.h')
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r'/\*.*?\*/', '', text, flags=re.S)
+    return sorted(set(re.findall(r'\b(poly_(?:cuda|b200|linearize|render|compile)_?\w*)\s*\(', text)))
+
+
+def test_library_exports_every_declared_symbol(product_lib):
+    names = declared_symbols()
+    assert 'poly_cuda_launch' in names and 'poly_linearize_cuda' in names and len(names) >= 25
+    missing = [n for n in names if not hasattr(product_lib.c, n)]
+    assert not missing, missing
+
+
+def test_kernel_library_is_standalone():
+    """The runtime + kernels library has no polygrad dependency."""
+    from polygrad_b200 import ffi
+    lib = ctypes.CDLL(ffi.KERNEL_LIB)
+    for n in ('poly_cuda_init', 'poly_cuda_alloc', 'poly_compile_cuda', 'poly_cuda_launch', 'poly_b200_stats'):
+        assert hasattr(lib, n)
+
+
+def test_no_device_fails_loudly():
+    """Without a GPU (and without the dry-run switch) the backend reports an
+    error; it never computes on the CPU."""
+    code = ("import sys; sys.path.insert(0, %r)\n"
+            "from polygrad_b200 import ffi\n"
+            "lib = ffi.product()\n"
+            "import torch\n"
+            "if torch.cuda.is_available(): print('HAS_GPU'); sys.exit(0)\n"
+            "assert lib.poly_cuda_init() != 0\n"
+            "assert not lib.poly_cuda_available()\n"
+            "assert lib.poly_cuda_alloc(16) == 0\n"
+            "print('OK', lib.last_error())\n") % ROOT
+    env = dict(os.environ)
+    env.pop('POLY_B200_DRYRUN', None)
+    r = subprocess.run([sys.executable, '-c', code], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert 'OK' in r.stdout or 'HAS_GPU' in r.stdout
+
+
+DRY = r'''
+import json, os, sys
+sys.path.insert(0, %(root)r)
+import numpy as np
+from polygrad_b200 import ffi
+from polygrad_b200.instance import Instance, gpt2_init
+lib = ffi.product()
+assert lib.poly_cuda_init() == 0
+kinds = {}
+import ctypes
+cfg = dict(vocab_size=211, n_embd=96, n_head=4, n_layer=2, max_seq_len=48, max_batch=2)
+inst = Instance.gpt2(lib, **cfg)
+inst.init_params(gpt2_init(1))
+inst.set_device(ffi.DEVICE_CUDA)
+inst.forward(**inst.gpt2_inputs(np.zeros((2, 48))))
+print(json.dumps(lib.stats()))
+'''
+
+
+def test_gpt2_plan_lowers_in_dry_run():
+    env = dict(os.environ, POLY_B200_DRYRUN='1', POLY_DUMP_KERNELS='1', POLY_B200_CACHE='0')
+    r = subprocess.run([sys.executable, '-c', DRY % dict(root=ROOT)], env=env, capture_output=True, text=True,
+                       timeout=900)
+    assert r.returncode == 0, r.stderr[-4000:]
+    kinds = re.findall(r'^//kind (\w+)', r.stderr, flags=re.M)
+    n_layer = 2
+    assert len(kinds) == 10 + 26 * n_layer          # polygrad's kernel count for GPT-2
+    assert kinds.count('gather') == 2               # token and position embeddings
+    assert kinds.count('gemm') == 6 * n_layer + 1   # qkv, scores, attn.v, c_proj, fc, proj per layer + logits
+    launches = re.findall(r'^//launch (\w+)', r.stderr, flags=re.M)
+    assert launches.count('group') >= 4 * n_layer   # LN mean/var and softmax max/sum rows
+    stats = json.loads(r.stdout.strip().splitlines()[-1])
+    assert stats['memsets_executed'] <= 4           # zero fills are elided when kernels overwrite whole buffers
