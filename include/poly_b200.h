@@ -86,6 +86,14 @@ int  poly_cuda_memset(unsigned long long ptr, unsigned char val, size_t bytes);
 int  poly_b200_set_device(int device);
 int  poly_b200_device(void);
 
+/* Arithmetic of fp32 contractions (polygrad matmuls on float32 buffers):
+ *   0  fp32 operands, fp32 FMA on the CUDA cores (default);
+ *   1  operands rounded to bfloat16 (nearest even), products and sums in fp32,
+ *      on the tensor cores.  Also selected by POLY_B200_GEMM=bf16.
+ * Contractions whose buffers are bfloat16 always take the tensor-core kernel. */
+void poly_b200_set_gemm_policy(int bf16);
+int  poly_b200_gemm_policy(void);
+
 /* Wait for all enqueued work.  0 / -1. */
 int  poly_b200_synchronize(void);
 

@@ -33,6 +33,7 @@ struct PackArgs {
   const void *src; void *dst;
   int naxes; long long ext[PB_PACK_MAX_AXES], sstride[PB_PACK_MAX_AXES]; /* axis 0 is the fastest of dst */
   long long total;
+  long long inner, dpitch;   /* dst element i lives at (i / inner) * dpitch + i % inner */
 };
 
 template <typename TS, typename TD>
@@ -43,13 +44,14 @@ __global__ void __launch_bounds__(256) pb200_pack(const PackArgs a) {
     long long rem = i, o = 0;
 #pragma unroll 4
     for (int d = 0; d < a.naxes; d++) { const long long x = rem % a.ext[d]; rem /= a.ext[d]; o += x * a.sstride[d]; }
-    dst[i] = (TD)src[o];
+    dst[(i / a.inner) * a.dpitch + (i % a.inner)] = (TD)src[o];
   }
 }
 
 int pb_pack_launch(const void *src, void *dst, int naxes, const long long *ext, const long long *sstride,
-                   int src_dtype, int dst_dtype, cudaStream_t stream) {
+                   int src_dtype, int dst_dtype, long long inner, long long dpitch, cudaStream_t stream) {
   PackArgs a; a.src = src; a.dst = dst; a.naxes = naxes; a.total = 1;
+  a.inner = inner > 0 ? inner : 1; a.dpitch = inner > 0 ? dpitch : 1;
   if (naxes > PB_PACK_MAX_AXES) { pb_set_error("pack: too many axes"); return -1; }
   for (int i = 0; i < naxes; i++) { a.ext[i] = ext[i]; a.sstride[i] = sstride[i]; a.total *= ext[i]; }
   if (a.total == 0) return 0;
@@ -273,15 +275,18 @@ static bool nests(const std::vector<Axis> &ax, F sel, long long *inner) {
   return true;
 }
 
+static int g_policy = -1;
 bool pb_gemm_policy_bf16(void) {
-  static int cached = -1;
-  if (cached < 0) { const char *e = getenv("POLY_B200_GEMM"); cached = (e && strcmp(e, "bf16") == 0) ? 1 : 0; }
-  return cached == 1;
+  if (g_policy < 0) { const char *e = getenv("POLY_B200_GEMM"); g_policy = (e && strcmp(e, "bf16") == 0) ? 1 : 0; }
+  return g_policy == 1;
 }
+extern "C" void poly_b200_set_gemm_policy(int bf16) { g_policy = bf16 ? 1 : 0; }
+extern "C" int poly_b200_gemm_policy(void) { return pb_gemm_policy_bf16() ? 1 : 0; }
 
 PbGemmProgram::~PbGemmProgram() { pb_scratch_free(tc_a.data); pb_scratch_free(tc_b.data); }
 
-int PbGemmProgram::pack_into(void *dst, const void *src, long long off, bool is_a, int src_dtype, int dst_dtype, cudaStream_t stream) {
+int PbGemmProgram::pack_into(void *dst, const void *src, long long off, bool is_a, int src_dtype, int dst_dtype,
+                             long long kpitch, cudaStream_t stream) {
   std::vector<long long> ext, str;
   auto sel = [&](const Axis &x) { return is_a ? x.sa : x.sb; };
   for (int i = (int)k_ax.size() - 1; i >= 0; i--) { ext.push_back(k_ax[i].ext); str.push_back(sel(k_ax[i])); }
@@ -289,7 +294,7 @@ int PbGemmProgram::pack_into(void *dst, const void *src, long long off, bool is_
   for (int i = (int)rows.size() - 1; i >= 0; i--) { ext.push_back(rows[i].ext); str.push_back(sel(rows[i])); }
   for (size_t i = 0; i < b_ax.size(); i++) { ext.push_back(b_ax[i].ext); str.push_back(sel(b_ax[i])); }
   const char *s = (const char *)src + off * (src_dtype == PB_F32 ? 4 : 2);
-  if (pb_pack_launch(s, dst, (int)ext.size(), ext.data(), str.data(), src_dtype, dst_dtype, stream) != 0) return -1;
+  if (pb_pack_launch(s, dst, (int)ext.size(), ext.data(), str.data(), src_dtype, dst_dtype, K, kpitch, stream) != 0) return -1;
   launches++;
   return 0;
 }
@@ -299,7 +304,7 @@ void *PbGemmProgram::pack_operand(const void *src, long long off, bool is_a, int
   const long long rowsz = is_a ? M : N;
   void *dst = pb_scratch_alloc((size_t)(nbatch * rowsz * K) * esz);
   if (!dst) return nullptr;
-  if (pack_into(dst, src, off, is_a, src_dtype, dst_dtype, stream) != 0) { pb_scratch_free(dst); return nullptr; }
+  if (pack_into(dst, src, off, is_a, src_dtype, dst_dtype, K, stream) != 0) { pb_scratch_free(dst); return nullptr; }
   return dst;
 }
 

@@ -15,7 +15,7 @@ enum { PB_F32 = 0, PB_BF16 = 1 };
 
 /* dst[i] (dense, axis 0 fastest) = (dst type) src[sum_d x_d * sstride[d]] */
 int pb_pack_launch(const void *src, void *dst, int naxes, const long long *ext, const long long *sstride,
-                   int src_dtype, int dst_dtype, cudaStream_t stream);
+                   int src_dtype, int dst_dtype, long long inner, long long dpitch, cudaStream_t stream);
 
 /* One axis of the contraction: kind m/n/k/b, extent, and the stride it has in
  * the output C, in A, in B and in the addend X (0 where it does not appear). */
@@ -25,6 +25,7 @@ struct PbGemmAxis { char kind; long long ext, sc, sa, sb, sx; };
 struct PbTcOperand {
   void *data = nullptr; size_t bytes = 0;
   const void *src = nullptr; uint64_t version = 0;
+  int misses = 0;      /* conversions done; an operand that changes every call stops being cached */
 };
 
 struct PbGemmProgram : PbAotProgram {
@@ -44,7 +45,8 @@ struct PbGemmProgram : PbAotProgram {
   int launch(void *const *bufs, cudaStream_t stream) override;
 
   /* Dense [batch.., rows.., k..] copy (k fastest) of A or B in dst_dtype into dst. */
-  int pack_into(void *dst, const void *src, long long off, bool is_a, int src_dtype, int dst_dtype, cudaStream_t stream);
+  int pack_into(void *dst, const void *src, long long off, bool is_a, int src_dtype, int dst_dtype,
+                long long kpitch, cudaStream_t stream);
   void *pack_operand(const void *src, long long off, bool is_a, int src_dtype, int dst_dtype, cudaStream_t stream);
 };
 

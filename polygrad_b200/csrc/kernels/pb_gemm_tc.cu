@@ -1,2 +1,394 @@
+/*
+ * pb_gemm_tc.cu -- bf16 x bf16 -> fp32 contraction on the 5th-generation tensor
+ * cores (tcgen05), operands staged by TMA, accumulators in tensor memory.
+ *
+ * Problem: C[b, m, n] = sum_k A[b, m, k] * B[b, n, k] (+ X) (relu), A and B
+ * bfloat16 with k contiguous ("K-major"), C float32 row-major.
+ * polygrad produces this either from bf16 buffers cast to float before the MUL,
+ * or -- under POLY_B200_GEMM=bf16 -- from fp32 buffers whose values are rounded
+ * to bf16 (nearest even) on the way in; products and sums stay fp32.
+ *
+ * One persistent CTA per SM, 6 warps, no clusters and no multicast:
+ *   warp 0     allocates tensor memory; one lane issues the TMA loads
+ *              (cp.async.bulk.tensor, 128-byte swizzle) into a ring of stages;
+ *   warp 1     one lane issues tcgen05.mma (128 x BN x 16 per instruction, 4 per
+ *              64-wide k block) and commits completion to the stage's "empty"
+ *              barrier and, after the last k block, to the tile's "full" barrier;
+ *   warps 2-5  epilogue: tcgen05.ld 32 lanes x 32 columns at a time, transpose
+ *              through shared memory so that global stores are 128-byte rows,
+ *              add the addend, apply relu, store.
+ * Two accumulator buffers in tensor memory let the MMA warp start the next tile
+ * while the epilogue drains the previous one.
+ *
+ * Every wait on an mbarrier is bounded: after a few seconds without progress the
+ * CTA records an error code, stops issuing work, frees its tensor memory and
+ * returns; the host reports the code at the next synchronisation point.
+ */
 #include "pb_gemm.h"
-int pb_gemm_tc_run(PbGemmProgram &, void *const *, cudaStream_t) { return PB_TC_UNSUPPORTED; }
+#include <cuda.h>
+#include <dlfcn.h>
+#include <cstdio>
+#include <cstring>
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define TC_SPIN_LIMIT (1u << 22)
+
+__device__ int pb200_tc_error_flag = 0;
+
+struct TcArgs {
+  float *C; const float *X;
+  int M, N, K;
+  long long c_sm, x_sm, x_sn;
+  int nb; int bext[4]; long long c_sb[4], x_sb[4];
+  int has_x, relu;
+  int tiles_m, tiles_n, n_tiles;   /* n_tiles = nbatch * tiles_m * tiles_n */
+};
+
+/* ── PTX wrappers ────────────────────────────────────────────────────── */
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+/* Bounded wait.  Returns false (after flagging) when the limit is hit or another
+ * role of this CTA has already given up. */
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+  for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicCAS(&pb200_tc_error_flag, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+/* Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 B apart,
+ * 8-row groups 1024 B apart. */
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;                 /* leading byte offset (unused for swizzled K-major) */
+  d |= (uint64_t)(1024 >> 4) << 32;       /* stride byte offset */
+  d |= (uint64_t)1 << 46;                 /* descriptor version */
+  d |= (uint64_t)2 << 61;                 /* 128-byte swizzle */
+  return d;
+}
+
+template <int BN>
+struct TcSmem {
+  static constexpr int STAGE_A = TC_BM * TC_BK * 2;
+  static constexpr int STAGE_B = BN * TC_BK * 2;
+  static constexpr int STAGE = STAGE_A + STAGE_B;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int EPI = 4 * 32 * 33 * 4;
+  static constexpr int BYTES = STAGES * STAGE + EPI + 256 + 1024; /* + barriers + alignment slack */
+};
+
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcArgs g) {
+  using S = TcSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;              /* swizzled tiles need 1024-byte alignment */
+  uint8_t *sm = smem_raw + (base - raw);
+  float *epi = reinterpret_cast<float *>(sm + S::STAGES * S::STAGE);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(sm + S::STAGES * S::STAGE + S::EPI);
+  /* bars: full[STAGES], empty[STAGES], tfull[2], tempty[2] */
+  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * S::STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * S::STAGES, bar_tempty = bar_tfull + 16;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kblocks = (g.K + TC_BK - 1) / TC_BK;
+  constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < S::STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    /* ── TMA producer ── */
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < g.n_tiles && ok; t += gridDim.x) {
+        const int nt = t % g.tiles_n, mt = (t / g.tiles_n) % g.tiles_m, bz = t / (g.tiles_n * g.tiles_m);
+        for (int kb = 0; kb < kblocks; kb++) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, &abort_flag, 1)) { ok = false; break; }
+          mbar_expect_tx(bar_full + 8 * stage, S::STAGE);
+          const uint32_t sa = base + stage * S::STAGE, sb = sa + S::STAGE_A;
+          tma_load_3d(sa, &map_a, bar_full + 8 * stage, kb * TC_BK, mt * TC_BM, bz);
+          tma_load_3d(sb, &map_b, bar_full + 8 * stage, kb * TC_BK, nt * BN, bz);
+          if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    /* ── MMA issuer ── */
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+      uint32_t stage = 0, phase = 0, it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < g.n_tiles && ok; t += gridDim.x, it++) {
+        const uint32_t buf = it & 1u, use = it >> 1;
+        if (!mbar_wait(bar_tempty + 8 * buf, (use & 1u) ^ 1u, &abort_flag, 2)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < kblocks; kb++) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, &abort_flag, 3)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = base + stage * S::STAGE, sb = sa + S::STAGE_A;
+          const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sb);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; k++)
+            tc_mma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+          tc_commit(bar_empty + 8 * stage);          /* frees the stage when these MMAs have read it */
+          if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit(bar_tfull + 8 * buf);      /* accumulator complete */
+      }
+    }
+  } else {
+    /* ── epilogue: warp w owns tensor-memory lanes 32*(w%4) .. +31 ── */
+    const int q = warp & 3;
+    float *stg = epi + (warp - 2) * 32 * 33;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < g.n_tiles && ok; t += gridDim.x, it++) {
+      const int nt = t % g.tiles_n, mt = (t / g.tiles_n) % g.tiles_m;
+      int bz = t / (g.tiles_n * g.tiles_m);
+      long long oc = 0, ox = 0;
+      for (int i = 0; i < g.nb; i++) { const int x = bz % g.bext[i]; bz /= g.bext[i]; oc += x * g.c_sb[i]; ox += x * g.x_sb[i]; }
+      const uint32_t buf = it & 1u, use = it >> 1;
+      if (!mbar_wait(bar_tfull + 8 * buf, use & 1u, &abort_flag, 4)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row0 = mt * TC_BM + q * 32;
+      const int rows = min(32, g.M - row0);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col0 = nt * BN + c0;
+        if (col0 >= g.N) break;
+        uint32_t r[32];
+        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c0, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j++) stg[lane * 33 + j] = __uint_as_float(r[j]);
+        __syncwarp();
+        const int n = col0 + lane;
+        if (n < g.N) {
+          for (int rr = 0; rr < rows; rr++) {
+            const long long m = row0 + rr;
+            float v = stg[rr * 33 + lane];
+            if (g.has_x) v = v + g.X[ox + m * g.x_sm + (long long)n * g.x_sn];
+            if (g.relu) v = (0.0f < v) ? v : 0.0f;
+            g.C[oc + m * g.c_sm + n] = v;
+          }
+        }
+        __syncwarp();
+      }
+      tc_fence_before_sync();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (abort_flag) {
+    /* let copies that were already issued land before the shared memory goes away */
+    for (int i = 0; i < 2000; i++) __nanosleep(1000);
+  }
+  if (warp == 0) {
+    tc_fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+/* ── host side ───────────────────────────────────────────────────────── */
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *lib = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+    if (lib) fn = (EncodeTiledFn)dlsym(lib, "cuTensorMapEncodeTiled");
+  }
+  return fn;
+}
+
+/* rows x K bf16, K contiguous, row pitch `pitch` elements, `nbatch` matrices `bpitch` elements apart */
+static int make_map(CUtensorMap *map, const void *ptr, long long K, long long rows, long long nbatch,
+                    long long pitch, long long bpitch, int box_rows) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) { pb_set_error("gemm: cuTensorMapEncodeTiled not available"); return -1; }
+  cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)nbatch};
+  cuuint64_t strides[2] = {(cuuint64_t)pitch * 2, (cuuint64_t)(nbatch > 1 ? bpitch : rows * pitch) * 2};
+  cuuint32_t box[3] = {TC_BK, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult rc = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) { pb_set_error("gemm: cuTensorMapEncodeTiled failed (%d)", (int)rc); return -1; }
+  return 0;
+}
+
+template <int BN>
+static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, long long nbatch, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(pb200_gemm_tc<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN>::BYTES);
+    if (e != cudaSuccess) { pb_set_error("gemm: cannot reserve %d bytes of shared memory: %s", TcSmem<BN>::BYTES, cudaGetErrorString(e)); return -1; }
+    configured = true;
+  }
+  g.tiles_m = (g.M + TC_BM - 1) / TC_BM;
+  g.tiles_n = (g.N + BN - 1) / BN;
+  long long tiles = (long long)g.tiles_m * g.tiles_n * nbatch;
+  if (tiles > 2147483647LL) { pb_set_error("gemm: too many tiles"); return -1; }
+  g.n_tiles = (int)tiles;
+  static int sms = 0;
+  if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); if (sms <= 0) sms = 148; }
+  int grid = tiles < sms ? (int)tiles : sms;
+  pb200_gemm_tc<BN><<<grid, TC_THREADS, TcSmem<BN>::BYTES, stream>>>(ma, mb, g);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { pb_set_error("tensor-core gemm launch: %s", cudaGetErrorString(e)); return -1; }
+  return 0;
+}
+
+int pb_gemm_tc_error(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, pb200_tc_error_flag, sizeof v) != cudaSuccess) return -1;
+  return v;
+}
+
+/* K-major bf16 copy of operand A or B: [nbatch][rows][Kp], Kp = K rounded up to 8
+ * (TMA wants 16-byte row pitches; the box never reads past K, so the tail is
+ * never used).  An operand whose buffer version did not change since the last
+ * call (weights) is served from the program's cache; one that changes on every
+ * call (activations) is converted into pool scratch that the caller frees. */
+static const void *tc_operand(PbGemmProgram &p, PbTcOperand &cache, const void *src_buf, long long off, bool is_a,
+                              long long rows, long long Kp, cudaStream_t stream, void **scratch) {
+  *scratch = nullptr;
+  const size_t bytes = (size_t)(p.nbatch * rows * Kp) * 2;
+  const uint64_t ver = pb_buffer_version(src_buf);
+  if (cache.data && cache.src == src_buf && cache.version == ver && cache.bytes == bytes && ver != 0) return cache.data;
+  const bool transient = cache.misses >= 2 || ver == 0;
+  void *dst;
+  if (transient) {
+    if (cache.data) { pb_scratch_free(cache.data); cache.data = nullptr; cache.bytes = 0; }
+    dst = pb_scratch_alloc(bytes);
+    if (!dst) return nullptr;
+    *scratch = dst;
+  } else {
+    if (cache.data && cache.bytes != bytes) { pb_scratch_free(cache.data); cache.data = nullptr; }
+    if (!cache.data) { cache.data = pb_scratch_alloc(bytes); cache.bytes = bytes; }
+    if (!cache.data) return nullptr;
+    dst = cache.data;
+    cache.src = src_buf; cache.version = ver; cache.misses++;
+  }
+  if (p.pack_into(dst, src_buf, off, is_a, p.dtype, PB_BF16, Kp, stream) != 0) {
+    if (*scratch) { pb_scratch_free(*scratch); *scratch = nullptr; }
+    return nullptr;
+  }
+  return dst;
+}
+
+int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
+  /* output must be a row-major (or column-major: swap roles) matrix per batch entry */
+  bool swap = false;
+  if (p.c_sn != 1 || p.N == 1) { if (p.c_sm == 1 && p.M > 1) swap = true; else if (p.c_sn != 1) return PB_TC_UNSUPPORTED; }
+  if (p.K < 16) return PB_TC_UNSUPPORTED;
+  const long long Kp = (p.K + 7) & ~7LL;
+  void *scr_a = nullptr, *scr_b = nullptr;
+  const void *A = tc_operand(p, p.tc_a, bufs[p.p_a], p.off_a, true, p.M, Kp, stream, &scr_a);
+  const void *B = A ? tc_operand(p, p.tc_b, bufs[p.p_b], p.off_b, false, p.N, Kp, stream, &scr_b) : nullptr;
+  if (!A || !B) { pb_scratch_free(scr_a); return -1; }
+
+  TcArgs g{};
+  long long rowsA = p.M, rowsB = p.N;
+  if (swap) { std::swap(A, B); std::swap(rowsA, rowsB); }
+  g.M = (int)rowsA; g.N = (int)rowsB; g.K = (int)p.K;
+  g.C = (float *)bufs[p.p_c] + p.off_c;
+  g.c_sm = swap ? p.c_sn : p.c_sm;
+  g.has_x = p.has_x ? 1 : 0; g.relu = p.relu ? 1 : 0;
+  if (p.has_x) { g.X = (const float *)bufs[p.p_x] + p.off_x; g.x_sm = swap ? p.x_sn : p.x_sm; g.x_sn = swap ? p.x_sm : p.x_sn; }
+  g.nb = (int)p.b_ax.size();
+  for (int i = 0; i < g.nb; i++) { g.bext[i] = (int)p.b_ax[i].ext; g.c_sb[i] = p.b_ax[i].sc; g.x_sb[i] = p.b_ax[i].sx; }
+
+  const int BN = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, A, p.K, rowsA, p.nbatch, Kp, rowsA * Kp, TC_BM);
+  if (rc == 0) rc = make_map(&mb, B, p.K, rowsB, p.nbatch, Kp, rowsB * Kp, BN);
+  if (rc != 0) { pb_scratch_free(scr_a); pb_scratch_free(scr_b); return -1; }
+  pb_tc_mark_used();
+  if (BN == 256) rc = tc_launch<256>(ma, mb, g, p.nbatch, stream);
+  else if (BN == 128) rc = tc_launch<128>(ma, mb, g, p.nbatch, stream);
+  else rc = tc_launch<64>(ma, mb, g, p.nbatch, stream);
+  p.launches++;
+  /* stream-ordered pool: later work on this stream may reuse the blocks */
+  pb_scratch_free(scr_a); pb_scratch_free(scr_b);
+  return rc;
+}

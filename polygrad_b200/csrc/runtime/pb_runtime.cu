@@ -199,11 +199,21 @@ static inline bool ready() { return (R.inited || poly_cuda_init() == 0) && R.ok;
 
 extern "C" void *poly_b200_stream(void) { return ready() ? (void *)R.stream : nullptr; }
 
+static bool g_tc_used = false;
+void pb_tc_mark_used(void) { g_tc_used = true; }
+
+static int check_device_flags(void) {
+  if (!g_tc_used) return 0;
+  int code = pb_gemm_tc_error();
+  if (code != 0) { pb_set_error("tensor-core gemm: a barrier wait ran out (code %d); results are invalid", code); return -1; }
+  return 0;
+}
+
 extern "C" int poly_b200_synchronize(void) {
   if (!ready()) return -1;
   if (R.dry) return 0;
   PB_CUDA(cudaStreamSynchronize(R.stream));
-  return 0;
+  return check_device_flags();
 }
 
 extern "C" int poly_cuda_sync(void) {
@@ -377,7 +387,7 @@ extern "C" int poly_cuda_copy_dtoh(void *dst, unsigned long long src, size_t byt
   if (R.dry) { memcpy(dst, p, bytes); return 0; }
   PB_CUDA(cudaMemcpyAsync(dst, p, bytes, cudaMemcpyDeviceToHost, R.stream));
   PB_CUDA(cudaStreamSynchronize(R.stream));
-  return 0;
+  return check_device_flags();
 }
 
 /* ── events ──────────────────────────────────────────────────────────── */

@@ -48,4 +48,9 @@ void  pb_count_launch(bool precompiled, int n = 1);
  * operands (bf16 weights) can be invalidated when the source is written. */
 uint64_t pb_buffer_version(const void *p);      /* changes whenever p's allocation is written */
 
+/* The tensor-core kernel bounds its barrier waits and records a code when one
+ * runs out; the runtime reads it back at synchronisation points. */
+int  pb_gemm_tc_error(void);                    /* 0 = none, >0 = which wait gave up, <0 = cannot read */
+void pb_tc_mark_used(void);
+
 #endif

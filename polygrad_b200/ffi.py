@@ -141,6 +141,8 @@ def _declare_cuda(lib):
     _sig(lib, 'poly_b200_synchronize', ctypes.c_int, [])
     _sig(lib, 'poly_b200_stream', _ptr, [])
     _sig(lib, 'poly_b200_trim', None, [])
+    _sig(lib, 'poly_b200_set_gemm_policy', None, [ctypes.c_int])
+    _sig(lib, 'poly_b200_gemm_policy', ctypes.c_int, [])
     _sig(lib, 'poly_b200_host_alloc', _ptr, [S])
     _sig(lib, 'poly_b200_host_free', None, [_ptr])
     _sig(lib, 'poly_b200_last_dtoh_src', U, [])

@@ -1,0 +1,122 @@
+"""Contractions on the B200 against stock polygrad on the CPU.
+
+fp32 kernel: 1e-5 relative (atol = rtol * rms).  Tensor-core kernel (bf16
+operands, fp32 accumulation): the CPU path computes the same bf16 products and
+sums them in fp32 in k order, so the two differ only in summation order; the
+test allows 1e-4 (the stated bound for bf16 GEMM is 2e-2).  Under the bf16
+compute policy the comparison is against the CPU result on fp32 operands with
+the stated 2e-2 bound, and against the bf16-operand CPU result with 1e-4."""
+import numpy as np
+import pytest
+
+from conftest import assert_close
+from polygrad_b200 import ffi
+from polygrad_b200.tensor import Device
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(128, 256, 64), (300, 200, 100), (129, 65, 17), (64, 10, 512), (1, 384, 96), (512, 512, 512),
+          (257, 1000, 72)]
+
+
+@pytest.fixture(scope='module')
+def devices(ref_lib, gpu):
+    return Device(ref_lib, ffi.DEVICE_CPU), Device(gpu, ffi.DEVICE_CUDA)
+
+
+@pytest.fixture
+def policy(gpu):
+    def set_policy(bf16):
+        gpu.poly_b200_set_gemm_policy(int(bf16))
+    yield set_policy
+    gpu.poly_b200_set_gemm_policy(0)
+
+
+def _ab(shape, seed=0):
+    m, n, k = shape
+    rng = np.random.default_rng([seed, m, n, k])
+    return rng.uniform(-1, 1, (m, k)).astype(np.float32), rng.uniform(-1, 1, (k, n)).astype(np.float32)
+
+
+@pytest.mark.parametrize('shape', SHAPES, ids=str)
+def test_fp32(devices, policy, shape):
+    cpu, cuda = devices
+    policy(False)
+    a, b = _ab(shape)
+    want = cpu.tensor(a).dot(cpu.tensor(b)).numpy()
+    got = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
+    assert_close(got, want, 1e-5, f'fp32 {shape}')
+
+
+@pytest.mark.parametrize('shape', SHAPES, ids=str)
+def test_fp32_transposed_operands(devices, policy, shape):
+    """A read through permute (m contiguous) and B through permute (k contiguous, the lm-head form)."""
+    cpu, cuda = devices
+    policy(False)
+    a, b = _ab(shape, 1)
+    at, bt = np.ascontiguousarray(a.T), np.ascontiguousarray(b.T)
+    want = cpu.tensor(at).permute(1, 0).dot(cpu.tensor(bt).permute(1, 0)).numpy()
+    got = cuda.tensor(at).permute(1, 0).dot(cuda.tensor(bt).permute(1, 0)).numpy()
+    assert_close(got, want, 1e-5, f'fp32 T {shape}')
+
+
+@pytest.mark.parametrize('shape', SHAPES, ids=str)
+def test_bf16_buffers(devices, shape):
+    cpu, cuda = devices
+    a, b = _ab(shape, 2)
+    f = lambda d: d.tensor(a, 'bfloat16').cast('float32').dot(d.tensor(b, 'bfloat16').cast('float32')).numpy()
+    assert_close(f(cuda), f(cpu), 1e-4, f'bf16 {shape}')
+
+
+@pytest.mark.parametrize('shape', SHAPES, ids=str)
+def test_bf16_policy(devices, policy, shape):
+    cpu, cuda = devices
+    a, b = _ab(shape, 3)
+    want32 = cpu.tensor(a).dot(cpu.tensor(b)).numpy()
+    want16 = cpu.tensor(a, 'bfloat16').cast('float32').dot(cpu.tensor(b, 'bfloat16').cast('float32')).numpy()
+    policy(True)
+    got = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
+    assert_close(got, want16, 1e-4, f'policy vs bf16 operands {shape}')
+    assert_close(got, want32, 2e-2, f'policy vs fp32 {shape}')
+
+
+@pytest.mark.parametrize('bf16', [False, True], ids=['fp32', 'bf16'])
+def test_batched_attention_shapes(devices, policy, bf16):
+    """q . k^T and p . v with (batch, head) batch axes read through permuted views."""
+    cpu, cuda = devices
+    policy(bf16)
+    rng = np.random.default_rng(5)
+    B, T, H, hd = 2, 48, 3, 16
+    q = rng.standard_normal((B, T, H, hd)).astype(np.float32)
+    k = rng.standard_normal((B, T, H, hd)).astype(np.float32)
+
+    def scores(d):
+        qq = d.tensor(q).permute(0, 2, 1, 3)
+        kk = d.tensor(k).permute(0, 2, 1, 3).permute(0, 1, 3, 2)
+        s = qq.dot(kk)
+        return s.dot(d.tensor(k).permute(0, 2, 1, 3))
+    policy(False)
+    want = scores(cpu).numpy()
+    policy(bf16)
+    got = scores(cuda).numpy()
+    assert_close(got, want, 2e-2 if bf16 else 1e-5, 'attention contractions')
+
+
+def test_weights_cache_follows_updates(gpu, policy):
+    """A bf16 copy of an operand is reused while its buffer is unchanged and
+    rebuilt after the buffer is rewritten (an instance's weights)."""
+    from polygrad_b200.instance import Instance
+    policy(True)
+    x = np.random.default_rng(0).standard_normal((8, 32)).astype(np.float32)
+    inst = Instance.mlp(gpu, [32, 64, 16], 'relu', True, 8, seed=1)
+    inst.set_device(ffi.DEVICE_CUDA)
+    inst.forward(x=x)
+    y0 = inst.read('output').copy()
+    inst.forward(x=x)
+    assert np.array_equal(inst.read('output'), y0)
+    name = inst.params[0]
+    inst.write(name, np.zeros(inst.shape(name), np.float32))
+    inst.forward(x=x)
+    y1 = inst.read('output')
+    assert not np.array_equal(y1, y0)
+    inst.free()
