@@ -259,6 +259,11 @@ def run_b200(args, cfg, rank, world, local_rank):
     st = lib.stats()
     launches_per_step = st['launches'] // max(args.steps, 1)
 
+    if args.profile:
+        # launch-list / ncu runs: the timed steps only
+        if rank == 0:
+            print(json.dumps(dict(profile=True, ms_per_step=ms_step, launches_per_step=int(launches_per_step))), flush=True)
+        return
     for _ in range(min(args.warmup, 2)):
         forward_e2e()
     ms_e2e = timed(forward_e2e, max(1, min(args.steps, 5)))
@@ -362,6 +367,7 @@ def main():
     ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp32'])
     ap.add_argument('--gather', default='last', choices=['last', 'full'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--profile', action='store_true', help='stop after the timed steps (for ncu launch lists)')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'b200' else max(args.warmup, 1)
     rank = int(os.environ.get('RANK', '0'))

@@ -48,20 +48,119 @@ __global__ void __launch_bounds__(256) pb200_pack(const PackArgs a) {
   }
 }
 
+/* Fast path: the innermost source axis is contiguous and a multiple of 8 long,
+ * so every thread converts 8 consecutive elements: two 128-bit loads, one
+ * 128-bit store.  The remaining (outer) axes are decomposed once per 8 elements. */
+struct PackVecArgs {
+  const float *src; __nv_bfloat16 *dst;
+  int naxes; int ext[PB_PACK_MAX_AXES]; long long sstride[PB_PACK_MAX_AXES]; /* outer axes (axis 0 fastest) */
+  int run8;              /* chunks of 8 in one contiguous source run */
+  long long inner, dpitch; /* destination: element e lives at (e / inner) * dpitch + e % inner */
+  long long total8;
+};
+
+__global__ void __launch_bounds__(256) pb200_pack_f32_bf16_vec8(const PackVecArgs a) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.total8; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % a.run8);
+    const long long rest = i / a.run8;
+    long long rem = rest, o = 0;
+#pragma unroll 4
+    for (int d = 0; d < a.naxes; d++) { const long long x = rem % a.ext[d]; rem /= a.ext[d]; o += x * a.sstride[d]; }
+    const long long e = (rest * a.run8 + c) * 8;
+    const float4 v0 = *reinterpret_cast<const float4 *>(a.src + o + c * 8);
+    const float4 v1 = *reinterpret_cast<const float4 *>(a.src + o + c * 8 + 4);
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v0.x, v0.y), p1 = __floats2bfloat162_rn(v0.z, v0.w);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v1.x, v1.y), p3 = __floats2bfloat162_rn(v1.z, v1.w);
+    uint4 out;
+    out.x = *reinterpret_cast<unsigned *>(&p0); out.y = *reinterpret_cast<unsigned *>(&p1);
+    out.z = *reinterpret_cast<unsigned *>(&p2); out.w = *reinterpret_cast<unsigned *>(&p3);
+    *reinterpret_cast<uint4 *>(a.dst + (e / a.inner) * a.dpitch + (e % a.inner)) = out;
+  }
+}
+
+/* Transposing path: the source is contiguous along a row axis `r` (extent R,
+ * stride 1) while the destination wants k fastest.  32x32 tiles through shared
+ * memory; the other axes are batch.  dst[(b * R + r) * dpitch + k]. */
+struct PackTrArgs {
+  const float *src; __nv_bfloat16 *dst;
+  int R, K; long long s_k;                 /* source: r stride 1, k stride s_k */
+  int naxes; int ext[PB_PACK_MAX_AXES]; long long sstride[PB_PACK_MAX_AXES]; /* batch axes of the source */
+  long long dpitch;
+};
+
+__global__ void __launch_bounds__(256) pb200_pack_f32_bf16_tr(const PackTrArgs a) {
+  __shared__ float tile[32][33];
+  long long rem = blockIdx.z, o = 0;
+  for (int d = 0; d < a.naxes; d++) { const long long x = rem % a.ext[d]; rem /= a.ext[d]; o += x * a.sstride[d]; }
+  const int r0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int j = ty; j < 32; j += 8) {
+    const int k = k0 + j, r = r0 + tx;
+    tile[j][tx] = (k < a.K && r < a.R) ? a.src[o + (long long)k * a.s_k + r] : 0.0f;
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    const int r = r0 + j, k = k0 + tx;
+    if (r < a.R && k < a.K) a.dst[((long long)blockIdx.z * a.R + r) * a.dpitch + k] = __float2bfloat16_rn(tile[tx][j]);
+  }
+}
+
 int pb_pack_launch(const void *src, void *dst, int naxes, const long long *ext, const long long *sstride,
                    int src_dtype, int dst_dtype, long long inner, long long dpitch, cudaStream_t stream) {
-  PackArgs a; a.src = src; a.dst = dst; a.naxes = naxes; a.total = 1;
-  a.inner = inner > 0 ? inner : 1; a.dpitch = inner > 0 ? dpitch : 1;
   if (naxes > PB_PACK_MAX_AXES) { pb_set_error("pack: too many axes"); return -1; }
-  for (int i = 0; i < naxes; i++) { a.ext[i] = ext[i]; a.sstride[i] = sstride[i]; a.total *= ext[i]; }
-  if (a.total == 0) return 0;
+  long long total = 1;
+  for (int i = 0; i < naxes; i++) total *= ext[i];
+  if (total == 0) return 0;
+  cudaError_t e;
+  const bool f2b = src_dtype == PB_F32 && dst_dtype == PB_BF16;
+  /* merge leading axes that are contiguous in the source into one inner run */
+  int lead = 0; long long run = 1;
+  while (lead < naxes && sstride[lead] == run && run < inner) { run *= ext[lead]; lead++; }
+  if (f2b && inner > 0 && run % 8 == 0 && inner % run == 0 && inner % 8 == 0 && dpitch % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(src) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+    bool ok = true;
+    for (int i = lead; i < naxes; i++) if (sstride[i] % 4 != 0 || ext[i] > 2147483647LL) ok = false;
+    if (ok) {
+      PackVecArgs a; a.src = (const float *)src; a.dst = (__nv_bfloat16 *)dst;
+      a.naxes = naxes - lead;
+      for (int i = lead; i < naxes; i++) { a.ext[i - lead] = (int)ext[i]; a.sstride[i - lead] = sstride[i]; }
+      a.run8 = (int)(run / 8); a.inner = inner; a.dpitch = dpitch; a.total8 = total / 8;
+      long long blocks = (a.total8 + 255) / 256;
+      if (blocks > 148LL * 64) blocks = 148LL * 64;
+      pb200_pack_f32_bf16_vec8<<<(unsigned)blocks, 256, 0, stream>>>(a);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) { pb_set_error("pack launch: %s", cudaGetErrorString(e)); return -1; }
+      return 0;
+    }
+  }
+  /* transposing case: exactly one k axis (axis 0, strided) and a row axis with stride 1 right after it */
+  if (f2b && inner > 0 && naxes >= 2 && ext[0] == inner && sstride[1] == 1 && sstride[0] != 1 &&
+      ext[0] <= 2147483647LL && ext[1] <= 2147483647LL) {
+    long long nb = 1;
+    for (int i = 2; i < naxes; i++) nb *= ext[i];
+    if (nb <= 65535 && (ext[0] + 31) / 32 <= 65535) {
+      PackTrArgs a; a.src = (const float *)src; a.dst = (__nv_bfloat16 *)dst;
+      a.K = (int)ext[0]; a.R = (int)ext[1]; a.s_k = sstride[0];
+      a.naxes = naxes - 2;
+      for (int i = 2; i < naxes; i++) { a.ext[i - 2] = (int)ext[i]; a.sstride[i - 2] = sstride[i]; }
+      a.dpitch = dpitch;
+      dim3 grid((unsigned)((a.R + 31) / 32), (unsigned)((a.K + 31) / 32), (unsigned)nb);
+      pb200_pack_f32_bf16_tr<<<grid, 256, 0, stream>>>(a);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) { pb_set_error("pack launch: %s", cudaGetErrorString(e)); return -1; }
+      return 0;
+    }
+  }
+  PackArgs a; a.src = src; a.dst = dst; a.naxes = naxes; a.total = total;
+  a.inner = inner > 0 ? inner : 1; a.dpitch = inner > 0 ? dpitch : 1;
+  for (int i = 0; i < naxes; i++) { a.ext[i] = ext[i]; a.sstride[i] = sstride[i]; }
   long long blocks = (a.total + 255) / 256;
   if (blocks > 148LL * 32) blocks = 148LL * 32;
   if (src_dtype == PB_F32 && dst_dtype == PB_F32) pb200_pack<float, float><<<(unsigned)blocks, 256, 0, stream>>>(a);
   else if (src_dtype == PB_F32 && dst_dtype == PB_BF16) pb200_pack<float, __nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(a);
   else if (src_dtype == PB_BF16 && dst_dtype == PB_BF16) pb200_pack<__nv_bfloat16, __nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(a);
   else { pb_set_error("pack: unsupported dtypes"); return -1; }
-  cudaError_t e = cudaGetLastError();
+  e = cudaGetLastError();
   if (e != cudaSuccess) { pb_set_error("pack launch: %s", cudaGetErrorString(e)); return -1; }
   return 0;
 }
