@@ -1,0 +1,357 @@
+/*
+ * pb_exec_plan.c -- plan compiler and executor for the CUDA device.
+ *
+ * Takes over three entry points of polygrad's src/exec_plan.c for
+ * POLY_DEVICE_CUDA and forwards every other device to the original code, which
+ * is compiled under the names poly_ref_* (see the Makefile):
+ *
+ *   poly_compile_schedule   (reference: src/exec_plan.c:801)
+ *   poly_compiled_plan_run  (reference: src/exec_plan.c:934)
+ *   poly_compiled_plan_free (reference: src/exec_plan.c:1062)
+ *
+ * What changes relative to the reference plan for CUDA:
+ *   - the reference allocates one buffer per intermediate for the life of the
+ *     plan (src/exec_plan.c:860-881) and zeroes all of them before every run
+ *     (:946-963).  Here intermediates live in one arena, placed by live range,
+ *     and only a buffer whose first access is not a whole-buffer overwrite is
+ *     zeroed, right before that access;
+ *   - the reference launches one kernel at a time with two mallocs and a device
+ *     synchronisation each (:584-608).  Here argument blocks are persistent,
+ *     launches are asynchronous, and from the third run on the whole step is
+ *     replayed as one CUDA graph for as long as the bound buffers and the
+ *     converted weight copies stay valid;
+ *   - passes over the step list remove kernels that only re-materialise a
+ *     buffer (the scheduler's CONTIGUOUS barriers, src/modelzoo/models/gpt2.c:38)
+ *     and fuse the softmax chain (pb_fuse.c).
+ *
+ * Kernels with DEFINE_VAR parameters (dynamic shapes) keep the reference plan
+ * path, which drives the same backend symbols one kernel at a time.
+ * POLY_B200_PLAN=ref forces that path for everything (debugging).
+ */
+#include "pb_plan.h"
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* runtime (libpolyb200.so) */
+int poly_b200_program_info(PolyCudaProgram *prog, char *rw, int cap, int *n_params, int *n_vars, int *precompiled);
+int poly_b200_program_stale(PolyCudaProgram *prog, void **args);
+unsigned long long poly_b200_pool_epoch(void);
+int poly_b200_capture_begin(void);
+void *poly_b200_capture_end(int discard);
+int poly_b200_graph_launch(void *exec, unsigned long long n_kernels, unsigned long long n_precompiled);
+void poly_b200_graph_destroy(void *exec);
+int poly_b200_memset_now(unsigned long long ptr, unsigned char val, size_t bytes);
+
+/* the original plan code, compiled under other names */
+PolyCompiledPlan *poly_ref_compile_schedule(PolyCtx *ctx, PolySchedule *schedule, PolyDeviceId device);
+int poly_ref_compiled_plan_run(PolyCompiledPlan *plan, void **slot_data, int n_slots,
+                               struct PolyVarBinding *var_bindings, int n_var_bindings);
+void poly_ref_compiled_plan_free(PolyCompiledPlan *plan);
+
+#define PB_MAX_PLANS 1024
+static PbPlan *g_plans[PB_MAX_PLANS];
+
+static PbPlan *as_pb_plan(PolyCompiledPlan *p) {
+  for (int i = 0; i < PB_MAX_PLANS; i++) if ((PolyCompiledPlan *)g_plans[i] == p) return g_plans[i];
+  return NULL;
+}
+
+static bool env_is(const char *name, const char *val) {
+  const char *e = getenv(name);
+  return e && strcmp(e, val) == 0;
+}
+
+/* ── lowering one item ───────────────────────────────────────────────── */
+static int lower_step(PolyCtx *ctx, PolySchedule *sched, int item_idx, const char *fn_name, PbStep *st) {
+  PolyExecItem *item = &sched->items[item_idx];
+  memset(st, 0, sizeof *st);
+  st->item = item_idx;
+  int n_lin = 0;
+  PolyUOp **lin = poly_linearize_cuda(ctx, item->root, &n_lin);
+  if (!lin) return -1;
+  st->sink = lin[0];
+  char *src = poly_render_cuda(lin, n_lin, fn_name, 256);
+  free(lin);
+  if (!src) return -1;
+  if (getenv("POLY_DUMP_KERNELS")) fprintf(stderr, "=== CUDA KERNEL %s ===\n%s\n=== END ===\n", fn_name, src);
+  st->prog = poly_compile_cuda(src, fn_name);
+  if (!st->prog) { fprintf(stderr, "=== FAILED CUDA KERNEL %s ===\n%s\n=== END ===\n", fn_name, src); free(src); return -1; }
+  st->text = src;
+  int np = 0, nv = 0, pre = 0;
+  poly_b200_program_info(st->prog, st->rw, (int)sizeof st->rw, &np, &nv, &pre);
+  st->precompiled = pre;
+  st->n_vars = nv;
+  if (np > item->n_buf_slots || np > PB_MAX_PARAMS) {
+    fprintf(stderr, "polygrad: cuda: kernel %s has %d parameters, schedule lists %d\n", fn_name, np, item->n_buf_slots);
+    return -1;
+  }
+  st->n_params = np;
+  for (int i = 0; i < np; i++) st->slot[i] = item->buf_slot_indices[i];
+  return 0;
+}
+
+void pb_step_release(PbStep *st) {
+  if (st->prog) poly_cuda_program_destroy(st->prog);
+  free(st->text);
+  st->prog = NULL; st->text = NULL;
+}
+
+/* ── arena placement by live range ───────────────────────────────────── */
+typedef struct { int64_t off, size; } Hole;
+
+static int place_intermediates(PbPlan *p) {
+  int ns = p->n_slots;
+  int *first = malloc(sizeof(int) * (size_t)ns), *last = malloc(sizeof(int) * (size_t)ns);
+  char *first_mode = calloc((size_t)ns, 1);
+  for (int i = 0; i < ns; i++) { first[i] = -1; last[i] = -1; }
+  for (int s = 0; s < p->n_steps; s++) {
+    PbStep *st = &p->steps[s];
+    if (st->dead) continue;
+    for (int a = 0; a < st->n_params; a++) {
+      char m = st->rw[a];
+      if (m == '-' || m == 0) continue;
+      int sl = pb_plan_resolve(p, st->slot[a]);
+      if (first[sl] < 0) { first[sl] = s; first_mode[sl] = m; }
+      else if (first[sl] == s && m != 'W') first_mode[sl] = m;   /* also read in its first step */
+      last[sl] = s;
+    }
+  }
+  /* zero fills: an intermediate whose first access does not overwrite all of it */
+  p->n_zero = 0;
+  for (int i = 0; i < ns; i++) if (p->slot_inter[i] && first[i] >= 0 && first_mode[i] != 'W') p->n_zero++;
+  p->zero_step = malloc(sizeof(int) * (size_t)(p->n_zero + 1));
+  p->zero_slot = malloc(sizeof(int) * (size_t)(p->n_zero + 1));
+  int nz = 0;
+  for (int i = 0; i < ns; i++) if (p->slot_inter[i] && first[i] >= 0 && first_mode[i] != 'W') { p->zero_step[nz] = first[i]; p->zero_slot[nz] = i; nz++; }
+
+  Hole *holes = malloc(sizeof(Hole) * (size_t)(ns + 2));
+  int nh = 0;
+  int64_t top = 0;
+  for (int s = 0; s < p->n_steps; s++) {
+    /* allocate what is first touched here (largest first keeps fragmentation low) */
+    for (;;) {
+      int pick = -1;
+      for (int i = 0; i < ns; i++)
+        if (p->slot_inter[i] && first[i] == s && p->slot_off[i] < 0 && (pick < 0 || p->slot_bytes[i] > p->slot_bytes[pick])) pick = i;
+      if (pick < 0) break;
+      int64_t need = (p->slot_bytes[pick] + 255) & ~(int64_t)255;
+      if (need == 0) need = 256;
+      int best = -1;
+      for (int h = 0; h < nh; h++) if (holes[h].size >= need && (best < 0 || holes[h].size < holes[best].size)) best = h;
+      if (best >= 0) {
+        p->slot_off[pick] = holes[best].off;
+        holes[best].off += need; holes[best].size -= need;
+        if (holes[best].size == 0) { holes[best] = holes[nh - 1]; nh--; }
+      } else {
+        /* grow: extend a hole that ends at the top, else append */
+        int tail = -1;
+        for (int h = 0; h < nh; h++) if (holes[h].off + holes[h].size == top) tail = h;
+        if (tail >= 0) { p->slot_off[pick] = holes[tail].off; top = holes[tail].off + need; holes[tail] = holes[nh - 1]; nh--; }
+        else { p->slot_off[pick] = top; top += need; }
+      }
+    }
+    /* release what is last touched here */
+    for (int i = 0; i < ns; i++) {
+      if (!p->slot_inter[i] || last[i] != s || p->slot_off[i] < 0) continue;
+      int64_t off = p->slot_off[i], size = (p->slot_bytes[i] + 255) & ~(int64_t)255;
+      if (size == 0) size = 256;
+      /* merge with neighbours */
+      for (int h = 0; h < nh;) {
+        if (holes[h].off + holes[h].size == off) { off = holes[h].off; size += holes[h].size; holes[h] = holes[nh - 1]; nh--; h = 0; continue; }
+        if (off + size == holes[h].off) { size += holes[h].size; holes[h] = holes[nh - 1]; nh--; h = 0; continue; }
+        h++;
+      }
+      holes[nh].off = off; holes[nh].size = size; nh++;
+    }
+  }
+  p->arena_bytes = top;
+  free(holes); free(first); free(last); free(first_mode);
+  return 0;
+}
+
+int pb_plan_resolve(const PbPlan *p, int slot) {
+  int guard = 0;
+  while (p->slot_alias[slot] >= 0 && guard++ < 64) slot = p->slot_alias[slot];
+  return slot;
+}
+
+int pb_plan_add_slot(PbPlan *p, int64_t bytes) {
+  int n = p->n_slots + 1;
+  p->slot_bytes = realloc(p->slot_bytes, sizeof(int64_t) * (size_t)n);
+  p->slot_off = realloc(p->slot_off, sizeof(int64_t) * (size_t)n);
+  p->slot_alias = realloc(p->slot_alias, sizeof(int) * (size_t)n);
+  p->slot_inter = realloc(p->slot_inter, (size_t)n);
+  p->slot_ptr = realloc(p->slot_ptr, sizeof(void *) * (size_t)n);
+  p->slot_bytes[n - 1] = bytes; p->slot_off[n - 1] = -1; p->slot_alias[n - 1] = -1; p->slot_inter[n - 1] = 1; p->slot_ptr[n - 1] = NULL;
+  p->n_slots = n;
+  return n - 1;
+}
+
+/* ── compile ─────────────────────────────────────────────────────────── */
+static void plan_destroy(PbPlan *p) {
+  if (!p) return;
+  for (int i = 0; i < PB_MAX_PLANS; i++) if (g_plans[i] == p) g_plans[i] = NULL;
+  if (p->graph) poly_b200_graph_destroy(p->graph);
+  for (int s = 0; s < p->n_steps; s++) pb_step_release(&p->steps[s]);
+  if (p->arena) poly_cuda_free(p->arena);
+  free(p->steps); free(p->slot_bytes); free(p->slot_off); free(p->slot_alias); free(p->slot_inter); free(p->slot_ptr);
+  free(p->zero_step); free(p->zero_slot); free(p->graph_ext);
+  free(p->base.slot_to_data);
+  free(p);
+}
+
+PolyCompiledPlan *poly_compile_schedule(PolyCtx *ctx, PolySchedule *sched, PolyDeviceId device) {
+  if (device != POLY_DEVICE_CUDA || env_is("POLY_B200_PLAN", "ref"))
+    return poly_ref_compile_schedule(ctx, sched, device);
+  if (!ctx || !sched) return NULL;
+  if (poly_cuda_init() != 0) return NULL;
+
+  PbPlan *p = calloc(1, sizeof *p);
+  if (!p) return NULL;
+  p->base.schedule = sched;
+  p->base.device = device;
+  p->base.allocator = &POLY_CUDA_ALLOCATOR;
+  p->ctx = ctx;
+  p->n_steps = sched->n_items;
+  p->steps = calloc((size_t)(sched->n_items > 0 ? sched->n_items : 1), sizeof(PbStep));
+
+  static int plan_counter = 0;
+  bool has_vars = false;
+  for (int s = 0; s < sched->n_items && !has_vars; s++)
+    if (sched->items[sched->exec_order[s]].n_var_uops > 0) has_vars = true;
+  if (has_vars) { plan_destroy(p); return poly_ref_compile_schedule(ctx, sched, device); }
+
+  for (int s = 0; s < sched->n_items; s++) {
+    int k = sched->exec_order[s];
+    if (sched->items[k].kind != POLY_EXEC_COMPUTE) {
+      fprintf(stderr, "polygrad: compile_schedule: non-COMPUTE item %d not supported\n", k);
+      plan_destroy(p); return NULL;
+    }
+    char fn_name[64];
+    snprintf(fn_name, sizeof fn_name, "plan%d_k%d", plan_counter, k);
+    if (lower_step(ctx, sched, k, fn_name, &p->steps[s]) != 0) {
+      fprintf(stderr, "polygrad: compile_schedule: backend 'cuda' failed for kernel %d\n", k);
+      plan_destroy(p); return NULL;
+    }
+  }
+  plan_counter++;
+
+  p->n_slots = 0;
+  for (int i = 0; i < sched->n_buf_slots; i++) {
+    int idx = pb_plan_add_slot(p, sched->buf_slots[i].nbytes > 0 ? sched->buf_slots[i].nbytes : (int64_t)sizeof(float));
+    p->slot_inter[idx] = sched->buf_slots[i].is_intermediate ? 1 : 0;
+  }
+  p->n_sched_slots = sched->n_buf_slots;
+
+  if (!env_is("POLY_B200_FUSE", "0")) pb_plan_fuse(p);
+
+  if (place_intermediates(p) != 0) { plan_destroy(p); return NULL; }
+  if (p->arena_bytes > 0) {
+    p->arena = poly_cuda_alloc((size_t)p->arena_bytes);
+    if (!p->arena) { plan_destroy(p); return NULL; }
+  }
+  for (int i = 0; i < p->n_slots; i++)
+    if (p->slot_inter[i] && p->slot_off[i] >= 0) p->slot_ptr[i] = (void *)(uintptr_t)(p->arena + (unsigned long long)p->slot_off[i]);
+
+  /* fields other polygrad code may look at */
+  p->base.n_slot_to_data = sched->n_buf_slots;
+  p->base.slot_to_data = calloc((size_t)(sched->n_buf_slots > 0 ? sched->n_buf_slots : 1), sizeof(void *));
+
+  if (getenv("POLY_B200_DEBUG")) {
+    int live = 0, dead = 0; int64_t sum = 0;
+    for (int s = 0; s < p->n_steps; s++) { if (p->steps[s].dead) dead++; else live++; }
+    for (int i = 0; i < p->n_slots; i++) if (p->slot_inter[i] && p->slot_off[i] >= 0) sum += p->slot_bytes[i];
+    fprintf(stderr, "pb_plan: %d steps (%d removed), arena %.1f MB for %.1f MB of intermediates, %d zero fills\n",
+            live, dead, p->arena_bytes / 1e6, sum / 1e6, p->n_zero);
+  }
+
+  for (int i = 0; i < PB_MAX_PLANS; i++) if (!g_plans[i]) { g_plans[i] = p; return &p->base; }
+  fprintf(stderr, "polygrad: cuda: too many live plans\n");
+  plan_destroy(p);
+  return NULL;
+}
+
+/* ── run ─────────────────────────────────────────────────────────────── */
+static int run_eager(PbPlan *p) {
+  int zi = 0;
+  for (int s = 0; s < p->n_steps; s++) {
+    for (zi = 0; zi < p->n_zero; zi++)
+      if (p->zero_step[zi] == s) {
+        int sl = p->zero_slot[zi];
+        if (poly_b200_memset_now((unsigned long long)(uintptr_t)p->slot_ptr[sl], 0, (size_t)p->slot_bytes[sl]) != 0) return -1;
+      }
+    PbStep *st = &p->steps[s];
+    if (st->dead) continue;
+    for (int a = 0; a < st->n_params; a++) {
+      int sl = pb_plan_resolve(p, st->slot[a]);
+      st->dptr[a] = (unsigned long long)(uintptr_t)p->slot_ptr[sl];
+      st->argv[a] = &st->dptr[a];
+      if (!st->dptr[a] && st->rw[a] != '-') {
+        fprintf(stderr, "polygrad: plan_run: missing data for param %d (slot %d) in kernel %d\n", a, sl, st->item);
+        return -1;
+      }
+    }
+    if (poly_cuda_launch(st->prog, st->argv, st->n_params, 1, 1, 1, 256, 1, 1) != 0) return -1;
+  }
+  return 0;
+}
+
+static bool graph_valid(PbPlan *p) {
+  if (!p->graph) return false;
+  if (p->graph_epoch != poly_b200_pool_epoch()) return false;
+  for (int i = 0; i < p->n_sched_slots; i++)
+    if (!p->slot_inter[i] && p->graph_ext[i] != p->slot_ptr[i]) return false;
+  for (int s = 0; s < p->n_steps; s++) {
+    PbStep *st = &p->steps[s];
+    if (st->dead || !st->precompiled) continue;
+    if (poly_b200_program_stale(st->prog, st->argv)) return false;
+  }
+  return true;
+}
+
+int poly_compiled_plan_run(PolyCompiledPlan *plan, void **slot_data, int n_slots,
+                           struct PolyVarBinding *var_bindings, int n_var_bindings) {
+  PbPlan *p = plan ? as_pb_plan(plan) : NULL;
+  if (!p) return poly_ref_compiled_plan_run(plan, slot_data, n_slots, var_bindings, n_var_bindings);
+  for (int i = 0; i < p->n_sched_slots; i++) {
+    if (p->slot_inter[i]) continue;
+    p->slot_ptr[i] = (i < n_slots) ? slot_data[i] : NULL;
+    p->base.slot_to_data[i] = p->slot_ptr[i];
+  }
+  p->runs++;
+  const bool graphs = !env_is("POLY_B200_GRAPH", "0") && p->graph_failures < 4 && !getenv("POLY_B200_DRYRUN");
+  if (graphs && graph_valid(p)) {
+    return poly_b200_graph_launch(p->graph, (unsigned long long)p->graph_kernels, (unsigned long long)p->graph_precompiled);
+  }
+  if (p->graph) { poly_b200_graph_destroy(p->graph); p->graph = NULL; p->runs = 1; }
+  if (graphs && p->runs >= 3) {
+    if (poly_b200_capture_begin() == 0) {
+      PolyB200Stats before, after;
+      poly_b200_stats(&before);
+      int rc = run_eager(p);
+      poly_b200_stats(&after);
+      void *g = poly_b200_capture_end(rc != 0);
+      if (g) {
+        p->graph = g;
+        p->graph_epoch = poly_b200_pool_epoch();
+        p->graph_kernels = (long long)(after.launches - before.launches);
+        p->graph_precompiled = (long long)(after.launches_precompiled - before.launches_precompiled);
+        free(p->graph_ext);
+        p->graph_ext = malloc(sizeof(void *) * (size_t)(p->n_sched_slots + 1));
+        for (int i = 0; i < p->n_sched_slots; i++) p->graph_ext[i] = p->slot_ptr[i];
+        /* the captured work has not run yet */
+        return poly_b200_graph_launch(p->graph, 0, 0);
+      }
+      p->graph_failures++;
+      /* fall through: issue the step directly */
+    }
+  }
+  return run_eager(p);
+}
+
+void poly_compiled_plan_free(PolyCompiledPlan *plan) {
+  PbPlan *p = plan ? as_pb_plan(plan) : NULL;
+  if (!p) { poly_ref_compiled_plan_free(plan); return; }
+  plan_destroy(p);
+}

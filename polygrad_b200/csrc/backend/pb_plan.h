@@ -1,0 +1,53 @@
+/*
+ * pb_plan.h -- the CUDA plan: a list of steps over plan slots (pb_exec_plan.c)
+ * and the passes that rewrite that list (pb_fuse.c).
+ */
+#ifndef PB_PLAN_H
+#define PB_PLAN_H
+
+#include "pb_kern.h"
+#include "exec_plan.h"
+#include "frontend.h"
+#include "codegen.h"
+#include "../../../include/poly_b200.h"
+
+/* One launchable step.  Steps start as one per scheduled kernel, in execution
+ * order; passes may mark steps dead or replace their program. */
+typedef struct {
+  int item;                      /* schedule item this step came from (-1: synthesised) */
+  PolyUOp *sink;                 /* the kernel, simplified (what poly_linearize_cuda returned) */
+  PolyCudaProgram *prog;
+  char *text;                    /* program text the program was compiled from */
+  int n_params, n_vars;
+  int slot[PB_MAX_PARAMS];       /* plan slot of each parameter */
+  char rw[PB_MAX_PARAMS + 1];    /* 'r' read, 'w' partly written, 'W' wholly overwritten, 'b' both, '-' unused */
+  int precompiled;
+  bool dead;
+  unsigned long long dptr[PB_MAX_PARAMS];
+  void *argv[PB_MAX_PARAMS];
+} PbStep;
+
+typedef struct {
+  PolyCompiledPlan base;         /* polygrad code reads base.schedule (src/instance.c:158) */
+  PolyCtx *ctx;
+  PbStep *steps; int n_steps;
+  int n_slots, n_sched_slots;    /* schedule slots first, then slots added by passes */
+  int64_t *slot_bytes, *slot_off;
+  int *slot_alias;               /* >= 0: this slot is another slot's storage */
+  char *slot_inter;              /* intermediate (plan-owned) or external */
+  void **slot_ptr;
+  unsigned long long arena; int64_t arena_bytes;
+  int *zero_step, *zero_slot, n_zero;
+  void *graph; unsigned long long graph_epoch; void **graph_ext;
+  long long graph_kernels, graph_precompiled;
+  int runs, graph_failures;
+} PbPlan;
+
+int  pb_plan_resolve(const PbPlan *p, int slot);
+int  pb_plan_add_slot(PbPlan *p, int64_t bytes);
+void pb_step_release(PbStep *st);
+
+/* Rewrites the step list in place (pb_fuse.c). */
+void pb_plan_fuse(PbPlan *p);
+
+#endif

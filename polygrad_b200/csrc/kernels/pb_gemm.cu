@@ -382,6 +382,14 @@ bool pb_gemm_policy_bf16(void) {
 extern "C" void poly_b200_set_gemm_policy(int bf16) { g_policy = bf16 ? 1 : 0; }
 extern "C" int poly_b200_gemm_policy(void) { return pb_gemm_policy_bf16() ? 1 : 0; }
 
+bool PbGemmProgram::stale(void *const *bufs) {
+  if (tc_a.data && tc_a.src == bufs[p_a] && tc_a.version != pb_buffer_version(bufs[p_a])) return true;
+  if (tc_b.data && tc_b.src == bufs[p_b] && tc_b.version != pb_buffer_version(bufs[p_b])) return true;
+  if (tc_a.data && tc_a.src != bufs[p_a]) return true;
+  if (tc_b.data && tc_b.src != bufs[p_b]) return true;
+  return false;
+}
+
 PbGemmProgram::~PbGemmProgram() { pb_scratch_free(tc_a.data); pb_scratch_free(tc_b.data); }
 
 int PbGemmProgram::pack_into(void *dst, const void *src, long long off, bool is_a, int src_dtype, int dst_dtype,

@@ -43,6 +43,7 @@ struct PbGemmProgram : PbAotProgram {
   ~PbGemmProgram() override;
   int n_launches() const override { return launches; }
   int launch(void *const *bufs, cudaStream_t stream) override;
+  bool stale(void *const *bufs) override;
 
   /* Dense [batch.., rows.., k..] copy (k fastest) of A or B in dst_dtype into dst. */
   int pack_into(void *dst, const void *src, long long off, bool is_a, int src_dtype, int dst_dtype,

@@ -71,6 +71,8 @@ struct Runtime {
   uint64_t version_counter = 1;
   int n_pending = 0;
   bool force_sync = false;
+  bool capturing = false, capture_failed = false;
+  uint64_t pool_epoch = 1;       /* bumps when cached blocks go back to the driver */
   PolyB200Stats st{};
 };
 static Runtime R;
@@ -238,6 +240,11 @@ static void *pool_alloc(size_t bytes) {
   auto it = R.free_blocks.find(rs);
   if (it != R.free_blocks.end()) { p = it->second; R.free_blocks.erase(it); }
   else if (R.dry) { p = calloc(1, rs); }
+  else if (R.capturing) {
+    /* no driver allocation inside a stream capture: the caller abandons the capture */
+    R.capture_failed = true;
+    return nullptr;
+  }
   else {
     cudaError_t e = cudaMalloc(&p, rs);
     if (e != cudaSuccess) {
@@ -266,6 +273,7 @@ static void pool_free(void *p) {
 
 extern "C" void poly_b200_trim(void) {
   if (!R.ok) return;
+  R.pool_epoch++;
   if (!R.dry && !R.free_blocks.empty()) cudaStreamSynchronize(R.stream);
   for (auto &kv : R.free_blocks) {
     if (R.dry) free(kv.second); else { cudaFree(kv.second); R.held -= kv.first; }
@@ -696,5 +704,73 @@ extern "C" int poly_cuda_launch(PolyCudaProgram *prog, void **args, int n_args,
                                   (CUstream_)R.stream, kargs, nullptr);
   if (rc != 0) { const char *s = "?"; DRV.GetErrorString(rc, &s); pb_set_error("cuLaunchKernel(%s): %s", prog->name.c_str(), s); return -1; }
   pb_count_launch(false, 1);
+  return 0;
+}
+
+
+/* ── plan support: program facts, stream capture ─────────────────────── */
+extern "C" int poly_b200_program_info(PolyCudaProgram *prog, char *rw, int cap, int *n_params, int *n_vars, int *precompiled) {
+  if (!prog) return -1;
+  if (n_params) *n_params = prog->n_params;
+  if (n_vars) *n_vars = prog->n_vars;
+  if (precompiled) *precompiled = prog->kind == PolyCudaProgram::AOT;
+  if (rw && cap > 0) {
+    int n = (int)prog->rw.size() < cap - 1 ? (int)prog->rw.size() : cap - 1;
+    memcpy(rw, prog->rw.data(), (size_t)n); rw[n] = 0;
+  }
+  return 0;
+}
+
+extern "C" int poly_b200_program_stale(PolyCudaProgram *prog, void **args) {
+  if (!prog || prog->kind != PolyCudaProgram::AOT) return 0;
+  void *bufs[64];
+  for (int i = 0; i < prog->n_params && i < 64; i++) bufs[i] = args[i] ? (void *)(uintptr_t)(*(unsigned long long *)args[i]) : nullptr;
+  return prog->aot->stale(bufs) ? 1 : 0;
+}
+
+extern "C" unsigned long long poly_b200_pool_epoch(void) { return R.pool_epoch; }
+
+extern "C" int poly_b200_capture_begin(void) {
+  if (!ready() || R.dry || R.capturing) return -1;
+  R.capture_failed = false;
+  if (cudaStreamBeginCapture(R.stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { cudaGetLastError(); return -1; }
+  R.capturing = true;
+  return 0;
+}
+
+/* Ends the capture.  Returns an executable graph, or NULL when the capture was
+ * abandoned (the enqueued work is then discarded and must be re-issued). */
+extern "C" void *poly_b200_capture_end(int discard) {
+  if (!R.capturing) return nullptr;
+  R.capturing = false;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(R.stream, &graph);
+  if (e != cudaSuccess || !graph) { cudaGetLastError(); return nullptr; }
+  if (discard || R.capture_failed) { cudaGraphDestroy(graph); return nullptr; }
+  cudaGraphExec_t exec = nullptr;
+  e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  return (void *)exec;
+}
+
+extern "C" int poly_b200_graph_launch(void *exec, unsigned long long n_kernels, unsigned long long n_precompiled) {
+  if (!exec) return -1;
+  PB_CUDA(cudaGraphLaunch((cudaGraphExec_t)exec, R.stream));
+  R.st.launches += n_kernels; R.st.launches_precompiled += n_precompiled; R.st.launches_generated += n_kernels - n_precompiled;
+  return 0;
+}
+
+extern "C" void poly_b200_graph_destroy(void *exec) { if (exec) cudaGraphExecDestroy((cudaGraphExec_t)exec); }
+
+/* Stream-ordered fill used by plans for buffers a kernel only partly writes. */
+extern "C" int poly_b200_memset_now(unsigned long long ptr, unsigned char val, size_t bytes) {
+  if (!ready()) return -1;
+  void *p = (void *)(uintptr_t)ptr;
+  auto it = find_buf(p);
+  if (it != R.live.end()) { if (it->second.pending_zero) { it->second.pending_zero = false; R.n_pending--; } it->second.version = R.version_counter++; }
+  R.st.memsets_executed++;
+  if (R.dry) { memset(p, val, bytes); return 0; }
+  PB_CUDA(cudaMemsetAsync(p, val, bytes, R.stream));
   return 0;
 }

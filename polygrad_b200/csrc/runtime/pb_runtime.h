@@ -30,6 +30,8 @@ struct PbAotProgram {
   int n_params = 0;
   virtual int launch(void *const *bufs, cudaStream_t stream) = 0;
   virtual int n_launches() const { return 1; }
+  /* true when a cached, converted copy of an operand no longer matches its source buffer */
+  virtual bool stale(void *const *bufs) { (void)bufs; return false; }
 };
 
 /* Factories, one per kernel family; return nullptr and set err on bad headers. */
