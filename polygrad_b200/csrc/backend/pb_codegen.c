@@ -34,9 +34,17 @@
 #include <string.h>
 #include <math.h>
 
-typedef struct {
+typedef struct Gen Gen;
+struct Gen {
   PbKern *k;
   PbStr out;
+  PbStr *o;            /* where text goes: &out, or another generator's buffer */
+  const char *pfx;     /* prefix of temp names (several kernels in one function) */
+  char (*range_expr)[40];        /* when set: text that stands for range r */
+  char (*param_expr)[24];        /* when set: name of parameter i */
+  int64_t *param_numel;          /* when set: element count of parameter i as bound in this function */
+  bool (*load_hook)(Gen *g, int id);  /* may emit a LOAD node itself (returns true) */
+  void *ud;
   int *emitted;        /* per node: scope depth of its declaration, -1 = none */
   int *scope_log; int n_log, cap_log;
   int *scope_mark; int depth;   /* scope_mark[d] = n_log when depth d opened */
@@ -48,9 +56,9 @@ typedef struct {
   int vec;             /* >1 while emitting the lane-replicated body of a vector kernel */
   int lane;            /* current lane when vec > 1 */
   uint64_t lane_dep;   /* mask with the bit of the vectorised range */
-} Gen;
+};
 
-static void ind(Gen *g) { for (int i = 0; i < g->indent; i++) pb_str_puts(&g->out, "  "); }
+static void ind(Gen *g) { for (int i = 0; i < g->indent; i++) pb_str_puts(g->o, "  "); }
 
 static bool is_idx_dtype(PolyDType dt) {
   return !dt.is_ptr && (dt.priority == 5 || (dt.priority == -1 && dt.bitsize == 800));
@@ -67,9 +75,9 @@ static bool is_small_float(PolyDType dt) { return dt.priority == 11 || dt.priori
 /* Lane suffix: nodes that depend on the vectorised range get one temp per lane. */
 static void temp_name(Gen *g, int id, char *buf, size_t cap) {
   if (g->vec > 1 && (g->k->nodes[id].deps & g->lane_dep))
-    snprintf(buf, cap, "t%d_%d", id, g->lane);
+    snprintf(buf, cap, "t%s%d_%d", g->pfx, id, g->lane);
   else
-    snprintf(buf, cap, "t%d", id);
+    snprintf(buf, cap, "t%s%d", g->pfx, id);
 }
 
 static void const_literal(Gen *g, PolyUOp *u, char *buf, size_t cap) {
@@ -110,7 +118,11 @@ static void ref(Gen *g, PolyUOp *u, char *buf, size_t cap) {
   case POLY_OP_CONST: const_literal(g, u, buf, cap); return;
   case POLY_OP_RANGE: {
     int r = pb_kern_range_id(g->k, u);
-    if (g->vec > 1 && ((uint64_t)1 << r) == g->lane_dep) snprintf(buf, cap, "(r%d+%d)", r, g->lane);
+    if (g->range_expr) {
+      if (g->vec > 1 && ((uint64_t)1 << r) == g->lane_dep) snprintf(buf, cap, "(%s+%d)", g->range_expr[r], g->lane);
+      else snprintf(buf, cap, "%s", g->range_expr[r]);
+    }
+    else if (g->vec > 1 && ((uint64_t)1 << r) == g->lane_dep) snprintf(buf, cap, "(r%d+%d)", r, g->lane);
     else snprintf(buf, cap, "r%d", r);
     return;
   }
@@ -118,7 +130,10 @@ static void ref(Gen *g, PolyUOp *u, char *buf, size_t cap) {
     for (int v = 0; v < g->k->n_vars; v++)
       if (g->k->vars[v] == u) { snprintf(buf, cap, "((%s)v%d)", g->idx_t, v); return; }
     g->failed = true; snprintf(buf, cap, "0"); return;
-  case POLY_OP_PARAM: snprintf(buf, cap, "p%d", (int)u->arg.i); return;
+  case POLY_OP_PARAM:
+    if (g->param_expr) snprintf(buf, cap, "%s", g->param_expr[u->arg.i]);
+    else snprintf(buf, cap, "p%d", (int)u->arg.i);
+    return;
   default: temp_name(g, pb_kern_node(g->k, u), buf, cap); return;
   }
 }
@@ -206,12 +221,12 @@ static void emit_reduce_serial(Gen *g, int id) {
   char idn[96], name[32];
   temp_name(g, id, name, sizeof name);
   reduce_identity(op, u->dtype, idn, sizeof idn, g);
-  ind(g); pb_str_printf(&g->out, "%s acc_%s = %s;\n", ctype_of(g, u->dtype), name, idn);
+  ind(g); pb_str_printf(g->o, "%s acc_%s = %s;\n", ctype_of(g, u->dtype), name, idn);
   uint64_t saved = g->bound;
   for (int i = 1; i < u->n_src; i++) {
     int r = pb_kern_range_id(g->k, u->src[i]);
     char bs[64]; range_bound_str(g, r, bs, sizeof bs);
-    ind(g); pb_str_printf(&g->out, "for (%s r%d = 0; r%d < %s; ++r%d) {\n", g->idx_t, r, r, bs, r);
+    ind(g); pb_str_printf(g->o, "for (%s r%d = 0; r%d < %s; ++r%d) {\n", g->idx_t, r, r, bs, r);
     g->indent++;
     g->bound |= (uint64_t)1 << r;
   }
@@ -221,11 +236,11 @@ static void emit_reduce_serial(Gen *g, int id) {
   ref(g, u->src[0], v, sizeof v);
   snprintf(acc, sizeof acc, "acc_%s", name);
   combine_expr(op, acc, v, cmb, sizeof cmb);
-  ind(g); pb_str_printf(&g->out, "%s = %s;\n", acc, cmb);
+  ind(g); pb_str_printf(g->o, "%s = %s;\n", acc, cmb);
   close_scope(g);
-  for (int i = 1; i < u->n_src; i++) { g->indent--; ind(g); pb_str_puts(&g->out, "}\n"); }
+  for (int i = 1; i < u->n_src; i++) { g->indent--; ind(g); pb_str_puts(g->o, "}\n"); }
   g->bound = saved;
-  ind(g); pb_str_printf(&g->out, "const %s %s = %s;\n", ctype_of(g, u->dtype), name, acc);
+  ind(g); pb_str_printf(g->o, "const %s %s = %s;\n", ctype_of(g, u->dtype), name, acc);
   log_emit(g, id);
 }
 
@@ -236,19 +251,21 @@ static void emit_load(Gen *g, int id) {
   PolyUOp *p = ix->src[0];
   emit_src(g, ix->src[1]);
   if (ix->n_src > 2) emit_src(g, ix->src[2]);
-  char name[32], is[64], gs[64];
+  char name[40], is[96], gs[96], pn[32];
   temp_name(g, id, name, sizeof name);
   ref(g, ix->src[1], is, sizeof is);
+  ref(g, p, pn, sizeof pn);
   const char *ct = ctype_of(g, u->dtype);
   if (!ct) { g->failed = true; return; }
+  long long numel = g->param_numel ? (long long)g->param_numel[p->arg.i] : (long long)p->dtype.ptr_size;
   ind(g);
   if (ix->n_src > 2) {
     ref(g, ix->src[2], gs, sizeof gs);
-    pb_str_printf(&g->out, "const %s %s = (%s) ? (%s)pb_ld(p%d, %s, %lldLL) : (%s)0;\n",
-                  ct, name, gs, ct, (int)p->arg.i, is, (long long)p->dtype.ptr_size, ct);
+    pb_str_printf(g->o, "const %s %s = (%s) ? (%s)pb_ld(%s, %s, %lldLL) : (%s)0;\n",
+                  ct, name, gs, ct, pn, is, numel, ct);
   } else {
-    pb_str_printf(&g->out, "const %s %s = (%s)pb_ld(p%d, %s, %lldLL);\n",
-                  ct, name, ct, (int)p->arg.i, is, (long long)p->dtype.ptr_size);
+    pb_str_printf(g->o, "const %s %s = (%s)pb_ld(%s, %s, %lldLL);\n",
+                  ct, name, ct, pn, is, numel);
   }
   log_emit(g, id);
 }
@@ -268,11 +285,13 @@ static void emit(Gen *g, int id) {
   case POLY_OP_CONST: case POLY_OP_RANGE: case POLY_OP_DEFINE_VAR: case POLY_OP_PARAM: case POLY_OP_INDEX:
     return;
   case POLY_OP_REDUCE: emit_reduce_serial(g, id); return;
-  case POLY_OP_LOAD: emit_load(g, id); return;
+  case POLY_OP_LOAD:
+    if (g->load_hook && g->load_hook(g, id)) return;
+    emit_load(g, id); return;
   default: break;
   }
   for (int i = 0; i < u->n_src; i++) emit_src(g, u->src[i]);
-  char a[96] = "", b[96] = "", c[96] = "", e[512], name[32];
+  char a[128] = "", b[128] = "", c[128] = "", e[640], name[40];
   if (u->n_src > 0) ref(g, u->src[0], a, sizeof a);
   if (u->n_src > 1) ref(g, u->src[1], b, sizeof b);
   if (u->n_src > 2) ref(g, u->src[2], c, sizeof c);
@@ -340,7 +359,7 @@ static void emit(Gen *g, int id) {
     g->failed = true; return;
   }
   temp_name(g, id, name, sizeof name);
-  ind(g); pb_str_printf(&g->out, "const %s %s = %s;\n", ct, name, e);
+  ind(g); pb_str_printf(g->o, "const %s %s = %s;\n", ct, name, e);
   log_emit(g, id);
 }
 
@@ -386,13 +405,13 @@ static void order_loop_axes(PbKern *k, PbStore *st, int *order, PbAffine *aff_ou
 }
 
 static void emit_decompose(Gen *g, const char *lin, const int *order, int n) {
-  ind(g); pb_str_printf(&g->out, "%s rem_ = %s;\n", g->idx_t, lin);
+  ind(g); pb_str_printf(g->o, "%s rem_ = %s;\n", g->idx_t, lin);
   for (int i = 0; i < n; i++) {
     int r = order[i];
     char bs[64]; range_bound_str(g, r, bs, sizeof bs);
     ind(g);
-    if (i == n - 1) pb_str_printf(&g->out, "const %s r%d = rem_;\n", g->idx_t, r);
-    else pb_str_printf(&g->out, "const %s r%d = rem_ %% %s; rem_ /= %s;\n", g->idx_t, r, bs, bs);
+    if (i == n - 1) pb_str_printf(g->o, "const %s r%d = rem_;\n", g->idx_t, r);
+    else pb_str_printf(g->o, "const %s r%d = rem_ %% %s; rem_ /= %s;\n", g->idx_t, r, bs, bs);
     g->bound |= (uint64_t)1 << r;
   }
 }
@@ -411,10 +430,10 @@ static void emit_store(Gen *g, PbStore *st) {
   ind(g);
   if (ix->n_src > 2) {
     ref(g, ix->src[2], gs, sizeof gs);
-    pb_str_printf(&g->out, "if (%s) pb_st(p%d, %s, %lldLL, (%s)(%s));\n", gs, st->param, is,
+    pb_str_printf(g->o, "if (%s) pb_st(p%d, %s, %lldLL, (%s)(%s));\n", gs, st->param, is,
                   (long long)p->dtype.ptr_size, pt, vs);
   } else {
-    pb_str_printf(&g->out, "pb_st(p%d, %s, %lldLL, (%s)(%s));\n", st->param, is,
+    pb_str_printf(g->o, "pb_st(p%d, %s, %lldLL, (%s)(%s));\n", st->param, is,
                   (long long)p->dtype.ptr_size, pt, vs);
   }
 }
@@ -433,24 +452,24 @@ static const char *PRELUDE =
 
 static void emit_signature(Gen *g, const bool *written, int block) {
   PbKern *k = g->k;
-  pb_str_printf(&g->out, "extern \"C\" __global__ void __launch_bounds__(%d) pb200_kernel(", block);
+  pb_str_printf(g->o, "extern \"C\" __global__ void __launch_bounds__(%d) pb200_kernel(", block);
   bool first = true;
   for (int i = 0; i < k->n_params; i++) {
-    if (!first) pb_str_puts(&g->out, ", ");
+    if (!first) pb_str_puts(g->o, ", ");
     first = false;
-    if (!k->params[i]) { pb_str_printf(&g->out, "const void* __restrict__ p%d", i); continue; }
+    if (!k->params[i]) { pb_str_printf(g->o, "const void* __restrict__ p%d", i); continue; }
     PolyDType base = k->params[i]->dtype; base.is_ptr = false; base.count = 1;
     const char *ct = pb_ctype(base);
     if (!ct) { g->failed = true; ct = "float"; }
-    pb_str_printf(&g->out, "%s%s* __restrict__ p%d", written[i] ? "" : "const ", ct, i);
+    pb_str_printf(g->o, "%s%s* __restrict__ p%d", written[i] ? "" : "const ", ct, i);
   }
   for (int v = 0; v < k->n_vars; v++) {
-    if (!first) pb_str_puts(&g->out, ", ");
+    if (!first) pb_str_puts(g->o, ", ");
     first = false;
-    pb_str_printf(&g->out, "const int v%d", v);
+    pb_str_printf(g->o, "const int v%d", v);
   }
-  if (!first) pb_str_puts(&g->out, ", ");
-  pb_str_puts(&g->out, "const long long n_work)");
+  if (!first) pb_str_puts(g->o, ", ");
+  pb_str_puts(g->o, "const long long n_work)");
 }
 
 /* Which params are read (bit 0) / written (bit 1), and whether the write covers
@@ -597,22 +616,22 @@ static char *render_group_reduce(PbKern *k, const int *usage) {
   for (int i = 0; i < k->n_params; i++)
     if (k->params[i] && k->params[i]->dtype.ptr_size >= ((int64_t)1 << 31)) wide = true;
   g.wide = wide; g.idx_t = wide ? "long long" : "int";
-  pb_str_init(&g.out);
+  pb_str_init(&g.out); g.o = &g.out; g.pfx = "";
 
   bool written[PB_MAX_PARAMS];
   for (int i = 0; i < k->n_params; i++) written[i] = (usage[i] & 2) != 0;
 
   const char *rt = ctype_of(&g, red->dtype);
-  pb_str_puts(&g.out, PRELUDE);
+  pb_str_puts(g.o, PRELUDE);
   emit_signature(&g, written, block);
-  pb_str_puts(&g.out, " {\n");
+  pb_str_puts(g.o, " {\n");
   g.indent = 1;
   int per_block = block / group;
-  ind(&g); pb_str_printf(&g.out, "const int lane_ = threadIdx.x %% %d;\n", group);
-  ind(&g); pb_str_printf(&g.out, "const long long out_ = (long long)blockIdx.x * %d + threadIdx.x / %d;\n", per_block, group);
-  if (group == block) { ind(&g); pb_str_printf(&g.out, "__shared__ %s red_[32];\n", rt); }
+  ind(&g); pb_str_printf(g.o, "const int lane_ = threadIdx.x %% %d;\n", group);
+  ind(&g); pb_str_printf(g.o, "const long long out_ = (long long)blockIdx.x * %d + threadIdx.x / %d;\n", per_block, group);
+  if (group == block) { ind(&g); pb_str_printf(g.o, "__shared__ %s red_[32];\n", rt); }
   /* whole groups leave together, so the shuffles below always see full warps */
-  ind(&g); pb_str_puts(&g.out, "if (out_ >= n_work) return;\n");
+  ind(&g); pb_str_puts(g.o, "if (out_ >= n_work) return;\n");
   int order[PB_MAX_AXES];
   order_loop_axes(k, st, order, NULL);
   if (st->n_loop > 0) emit_decompose(&g, wide ? "out_" : "(int)out_", order, st->n_loop);
@@ -623,17 +642,17 @@ static char *render_group_reduce(PbKern *k, const int *usage) {
 
   char idn[96];
   reduce_identity(op, red->dtype, idn, sizeof idn, &g);
-  ind(&g); pb_str_printf(&g.out, "%s acc_ = %s;\n", rt, idn);
+  ind(&g); pb_str_printf(g.o, "%s acc_ = %s;\n", rt, idn);
   /* reduce axes: the contiguous one fastest */
   int rorder[PB_MAX_AXES]; int n = 0;
   rorder[n++] = fastest;
   for (int j = nr - 1; j >= 0; j--) if (raxes[j] != fastest) rorder[n++] = raxes[j];
-  ind(&g); pb_str_printf(&g.out, "for (%s k_ = lane_; k_ < %lld; k_ += %d) {\n", g.idx_t, (long long)ktot, group);
+  ind(&g); pb_str_printf(g.o, "for (%s k_ = lane_; k_ < %lld; k_ += %d) {\n", g.idx_t, (long long)ktot, group);
   g.indent++;
   uint64_t saved = g.bound;
   open_scope(&g);
   if (nr == 1) {
-    ind(&g); pb_str_printf(&g.out, "const %s r%d = k_;\n", g.idx_t, fastest);
+    ind(&g); pb_str_printf(g.o, "const %s r%d = k_;\n", g.idx_t, fastest);
     g.bound |= (uint64_t)1 << fastest;
   } else {
     emit_decompose(&g, "k_", rorder, nr);
@@ -642,35 +661,35 @@ static char *render_group_reduce(PbKern *k, const int *usage) {
   char v[64], cmb[256];
   ref(&g, red->src[0], v, sizeof v);
   combine_expr(op, "acc_", v, cmb, sizeof cmb);
-  ind(&g); pb_str_printf(&g.out, "acc_ = %s;\n", cmb);
+  ind(&g); pb_str_printf(g.o, "acc_ = %s;\n", cmb);
   close_scope(&g);
   g.bound = saved;
   g.indent--;
-  ind(&g); pb_str_puts(&g.out, "}\n");
+  ind(&g); pb_str_puts(g.o, "}\n");
 
   /* combine across the group */
   char sh[256];
-  ind(&g); pb_str_puts(&g.out, "#pragma unroll\n");
-  ind(&g); pb_str_puts(&g.out, "for (int o_ = 16; o_ > 0; o_ >>= 1) {\n");
-  ind(&g); pb_str_printf(&g.out, "  const %s x_ = __shfl_xor_sync(0xffffffffu, acc_, o_);\n", rt);
+  ind(&g); pb_str_puts(g.o, "#pragma unroll\n");
+  ind(&g); pb_str_puts(g.o, "for (int o_ = 16; o_ > 0; o_ >>= 1) {\n");
+  ind(&g); pb_str_printf(g.o, "  const %s x_ = __shfl_xor_sync(0xffffffffu, acc_, o_);\n", rt);
   combine_expr(op, "acc_", "x_", sh, sizeof sh);
-  ind(&g); pb_str_printf(&g.out, "  acc_ = %s;\n", sh);
-  ind(&g); pb_str_puts(&g.out, "}\n");
+  ind(&g); pb_str_printf(g.o, "  acc_ = %s;\n", sh);
+  ind(&g); pb_str_puts(g.o, "}\n");
   if (group == block) {
     int nw = block / 32;
-    ind(&g); pb_str_puts(&g.out, "if ((threadIdx.x & 31) == 0) red_[threadIdx.x >> 5] = acc_;\n");
-    ind(&g); pb_str_puts(&g.out, "__syncthreads();\n");
-    ind(&g); pb_str_puts(&g.out, "if (threadIdx.x != 0) return;\n");
-    ind(&g); pb_str_puts(&g.out, "acc_ = red_[0];\n");
-    ind(&g); pb_str_printf(&g.out, "for (int w_ = 1; w_ < %d; ++w_) { const %s x_ = red_[w_]; acc_ = %s; }\n", nw, rt, sh);
+    ind(&g); pb_str_puts(g.o, "if ((threadIdx.x & 31) == 0) red_[threadIdx.x >> 5] = acc_;\n");
+    ind(&g); pb_str_puts(g.o, "__syncthreads();\n");
+    ind(&g); pb_str_puts(g.o, "if (threadIdx.x != 0) return;\n");
+    ind(&g); pb_str_puts(g.o, "acc_ = red_[0];\n");
+    ind(&g); pb_str_printf(g.o, "for (int w_ = 1; w_ < %d; ++w_) { const %s x_ = red_[w_]; acc_ = %s; }\n", nw, rt, sh);
   } else {
-    ind(&g); pb_str_puts(&g.out, "if (lane_ != 0) return;\n");
+    ind(&g); pb_str_puts(g.o, "if (lane_ != 0) return;\n");
   }
   char name[32]; temp_name(&g, rid, name, sizeof name);
-  ind(&g); pb_str_printf(&g.out, "const %s %s = acc_;\n", rt, name);
+  ind(&g); pb_str_printf(g.o, "const %s %s = acc_;\n", rt, name);
   log_emit(&g, rid);
   emit_store(&g, st);
-  pb_str_puts(&g.out, "}\n");
+  pb_str_puts(g.o, "}\n");
 
   char *res = NULL;
   if (!g.failed) {
@@ -775,12 +794,12 @@ static char *render_vec_elementwise(PbKern *k, const int *usage) {
   for (int i = 0; i < k->n_params; i++)
     if (k->params[i] && k->params[i]->dtype.ptr_size >= ((int64_t)1 << 31)) wide = true;
   g.wide = wide; g.idx_t = wide ? "long long" : "int";
-  pb_str_init(&g.out);
+  pb_str_init(&g.out); g.o = &g.out; g.pfx = "";
   bool written[PB_MAX_PARAMS];
   for (int i = 0; i < k->n_params; i++) written[i] = (usage[i] & 2) != 0;
 
-  pb_str_puts(&g.out, PRELUDE);
-  pb_str_puts(&g.out,
+  pb_str_puts(g.o, PRELUDE);
+  pb_str_puts(g.o,
     "template <class T> struct pb_v4 { T x, y, z, w; };\n"
     "template <class T> __device__ __forceinline__ void pb_ld4(const T* p, T* o) {\n"
     "  const uint4 v = *reinterpret_cast<const uint4*>(p);\n"
@@ -791,21 +810,21 @@ static char *render_vec_elementwise(PbKern *k, const int *usage) {
     "  *reinterpret_cast<uint4*>(p) = v;\n"
     "}\n");
   emit_signature(&g, written, 256);
-  pb_str_puts(&g.out, " {\n");
+  pb_str_puts(g.o, " {\n");
   g.indent = 1;
-  ind(&g); pb_str_puts(&g.out, "const long long gid_ = (long long)blockIdx.x * blockDim.x + threadIdx.x;\n");
-  ind(&g); pb_str_puts(&g.out, "if (gid_ >= n_work) return;\n");
+  ind(&g); pb_str_puts(g.o, "const long long gid_ = (long long)blockIdx.x * blockDim.x + threadIdx.x;\n");
+  ind(&g); pb_str_puts(g.o, "if (gid_ >= n_work) return;\n");
   /* decompose: x in units of 4 */
-  ind(&g); pb_str_printf(&g.out, "%s rem_ = %s;\n", g.idx_t, wide ? "gid_" : "(int)gid_");
+  ind(&g); pb_str_printf(g.o, "%s rem_ = %s;\n", g.idx_t, wide ? "gid_" : "(int)gid_");
   for (int i = 0; i < st->n_loop; i++) {
     int r = order[i];
     int64_t ext = (r == x) ? k->extent[r] / 4 : k->extent[r];
     ind(&g);
-    if (i == st->n_loop - 1) pb_str_printf(&g.out, "const %s q%d = rem_;\n", g.idx_t, r);
-    else pb_str_printf(&g.out, "const %s q%d = rem_ %% %lld; rem_ /= %lld;\n", g.idx_t, r, (long long)ext, (long long)ext);
+    if (i == st->n_loop - 1) pb_str_printf(g.o, "const %s q%d = rem_;\n", g.idx_t, r);
+    else pb_str_printf(g.o, "const %s q%d = rem_ %% %lld; rem_ /= %lld;\n", g.idx_t, r, (long long)ext, (long long)ext);
     ind(&g);
-    if (r == x) pb_str_printf(&g.out, "const %s r%d = q%d * 4;\n", g.idx_t, r, r);
-    else pb_str_printf(&g.out, "const %s r%d = q%d;\n", g.idx_t, r, r);
+    if (r == x) pb_str_printf(g.o, "const %s r%d = q%d * 4;\n", g.idx_t, r, r);
+    else pb_str_printf(g.o, "const %s r%d = q%d;\n", g.idx_t, r, r);
     g.bound |= (uint64_t)1 << r;
   }
   /* vector loads first (independent, so they are all in flight together) */
@@ -815,16 +834,16 @@ static char *render_vec_elementwise(PbKern *k, const int *usage) {
     PolyUOp *ix = ld->src[0];
     PolyDType base = ix->src[0]->dtype; base.is_ptr = false; base.count = 1;
     const char *pt = pb_ctype(base);
-    ind(&g); pb_str_printf(&g.out, "%s l%d_[4]; { %s o_ = %lld", pt, loads[i].node, g.idx_t, (long long)loads[i].aff.offset);
+    ind(&g); pb_str_printf(g.o, "%s l%d_[4]; { %s o_ = %lld", pt, loads[i].node, g.idx_t, (long long)loads[i].aff.offset);
     for (int j = 0; j < st->n_loop; j++) {
       int64_t s = loads[i].aff.stride[st->loop[j]];
-      if (s) pb_str_printf(&g.out, " + r%d*%lld", st->loop[j], (long long)s);
+      if (s) pb_str_printf(g.o, " + r%d*%lld", st->loop[j], (long long)s);
     }
-    pb_str_printf(&g.out, "; pb_ld4(p%d + o_, l%d_); }\n", (int)ix->src[0]->arg.i, loads[i].node);
+    pb_str_printf(g.o, "; pb_ld4(p%d + o_, l%d_); }\n", (int)ix->src[0]->arg.i, loads[i].node);
   }
   ind(&g); {
     PolyDType base = ob; base.is_ptr = false; base.count = 1;
-    pb_str_printf(&g.out, "%s o4_[4];\n", pb_ctype(base));
+    pb_str_printf(g.o, "%s o4_[4];\n", pb_ctype(base));
   }
   /* lane-independent part once */
   g.vec = 1;
@@ -844,25 +863,25 @@ static char *render_vec_elementwise(PbKern *k, const int *usage) {
       if (!vec_load[i]) continue;
       char nm[32]; temp_name(&g, loads[i].node, nm, sizeof nm);
       PolyUOp *ld = k->nodes[loads[i].node].u;
-      ind(&g); pb_str_printf(&g.out, "const %s %s = (%s)l%d_[%d];\n", ctype_of(&g, ld->dtype), nm,
+      ind(&g); pb_str_printf(g.o, "const %s %s = (%s)l%d_[%d];\n", ctype_of(&g, ld->dtype), nm,
                              ctype_of(&g, ld->dtype), loads[i].node, lane);
       log_emit(&g, loads[i].node);
     }
     emit_src(&g, st->value);
     char vs[96]; ref(&g, st->value, vs, sizeof vs);
     PolyDType base = ob; base.is_ptr = false; base.count = 1;
-    ind(&g); pb_str_printf(&g.out, "o4_[%d] = (%s)(%s);\n", lane, pb_ctype(base), vs);
+    ind(&g); pb_str_printf(g.o, "o4_[%d] = (%s)(%s);\n", lane, pb_ctype(base), vs);
     /* forget lane-dependent temps so the next lane re-emits them under its own names */
     for (int i = 0; i < k->n_nodes; i++)
       if (g.emitted[i] >= 0 && (k->nodes[i].deps & g.lane_dep)) g.emitted[i] = -1;
   }
-  ind(&g); pb_str_printf(&g.out, "{ %s o_ = %lld", g.idx_t, (long long)saff.offset);
+  ind(&g); pb_str_printf(g.o, "{ %s o_ = %lld", g.idx_t, (long long)saff.offset);
   for (int j = 0; j < st->n_loop; j++) {
     int64_t s = saff.stride[st->loop[j]];
-    if (s) pb_str_printf(&g.out, " + r%d*%lld", st->loop[j], (long long)s);
+    if (s) pb_str_printf(g.o, " + r%d*%lld", st->loop[j], (long long)s);
   }
-  pb_str_printf(&g.out, "; pb_st4(p%d + o_, o4_); }\n", st->param);
-  pb_str_puts(&g.out, "}\n");
+  pb_str_printf(g.o, "; pb_st4(p%d + o_, o4_); }\n", st->param);
+  pb_str_puts(g.o, "}\n");
 
   char *res = NULL;
   if (!g.failed) {
@@ -894,15 +913,15 @@ static char *render_flat(PbKern *k, const int *usage) {
     if (t >= ((int64_t)1 << 31)) wide = true;
   }
   g.wide = wide; g.idx_t = wide ? "long long" : "int";
-  pb_str_init(&g.out);
+  pb_str_init(&g.out); g.o = &g.out; g.pfx = "";
   bool written[PB_MAX_PARAMS];
   for (int i = 0; i < k->n_params; i++) written[i] = (usage[i] & 2) != 0;
 
-  pb_str_puts(&g.out, PRELUDE);
+  pb_str_puts(g.o, PRELUDE);
   emit_signature(&g, written, 256);
-  pb_str_puts(&g.out, " {\n");
+  pb_str_puts(g.o, " {\n");
   g.indent = 1;
-  ind(&g); pb_str_puts(&g.out, "const long long gid_ = (long long)blockIdx.x * blockDim.x + threadIdx.x;\n");
+  ind(&g); pb_str_puts(g.o, "const long long gid_ = (long long)blockIdx.x * blockDim.x + threadIdx.x;\n");
 
   PbStr work; pb_str_init(&work);
   /* stores with the same loop set share one section (and their common subexpressions) */
@@ -914,15 +933,15 @@ static char *render_flat(PbKern *k, const int *usage) {
     for (int i = 0; i < st->n_loop; i++) m |= (uint64_t)1 << st->loop[i];
     if (work.n) pb_str_puts(&work, "|");
     size_expr(k, st->loop, st->n_loop, &work);
-    ind(&g); pb_str_puts(&g.out, "{\n"); g.indent++;
+    ind(&g); pb_str_puts(g.o, "{\n"); g.indent++;
     /* section size */
-    ind(&g); pb_str_puts(&g.out, "long long tot_ = 1;");
+    ind(&g); pb_str_puts(g.o, "long long tot_ = 1;");
     for (int i = 0; i < st->n_loop; i++) {
       char bs[64]; range_bound_str(&g, st->loop[i], bs, sizeof bs);
-      pb_str_printf(&g.out, " tot_ *= %s;", bs);
+      pb_str_printf(g.o, " tot_ *= %s;", bs);
     }
-    pb_str_puts(&g.out, "\n");
-    ind(&g); pb_str_puts(&g.out, "if (gid_ < tot_) {\n"); g.indent++;
+    pb_str_puts(g.o, "\n");
+    ind(&g); pb_str_puts(g.o, "if (gid_ < tot_) {\n"); g.indent++;
     open_scope(&g);
     uint64_t saved = g.bound;
     int order[PB_MAX_AXES];
@@ -938,10 +957,10 @@ static char *render_flat(PbKern *k, const int *usage) {
     }
     close_scope(&g);
     g.bound = saved;
-    g.indent--; ind(&g); pb_str_puts(&g.out, "}\n");
-    g.indent--; ind(&g); pb_str_puts(&g.out, "}\n");
+    g.indent--; ind(&g); pb_str_puts(g.o, "}\n");
+    g.indent--; ind(&g); pb_str_puts(g.o, "}\n");
   }
-  pb_str_puts(&g.out, "}\n");
+  pb_str_puts(g.o, "}\n");
 
   char *res = NULL;
   if (!g.failed) {
@@ -975,4 +994,558 @@ char *pb_render_jit(PbKern *k, const char *fn_name) {
     if (r) return r;
   }
   return render_flat(k, usage);
+}
+
+/* ════════════════════════════════════════════════════════════════════════
+ *  Row-fused kernels
+ * ════════════════════════════════════════════════════════════════════════ */
+#define RF_MAX 8
+
+typedef struct {
+  int n;
+  PbFuseIn *in;
+  Gen g[RF_MAX];
+  int wslot[RF_MAX];                 /* slot each kernel writes */
+  int map[RF_MAX][PB_MAX_RANGES];    /* kernel range -> canonical range (a range id of the final kernel), -1 unmapped */
+  int c_range[RF_MAX];               /* the kernel's own range that runs along the row */
+  int usage[RF_MAX][PB_MAX_PARAMS];
+  int fparam[RF_MAX][PB_MAX_PARAMS]; /* fused parameter index of each kernel parameter, -1 internal/unused */
+  char range_expr[RF_MAX][PB_MAX_RANGES][40];
+  char param_expr[RF_MAX][PB_MAX_PARAMS][24];
+  int canon_c;                       /* canonical range along the row */
+  int V, G, NI, RPB; int64_t C;
+  bool final_reduce, out_bf16;
+  int red_node[RF_MAX];              /* REDUCE node of each phase */
+  bool *vec_load[RF_MAX];            /* per node: LOAD served by a 128-bit access */
+} RowFuse;
+
+static RowFuse *rf_of(Gen *g) { return (RowFuse *)g->ud; }
+static int rf_index(RowFuse *rf, Gen *g) { return (int)(g - rf->g); }
+
+static int rf_writer_of(RowFuse *rf, int slot) {
+  for (int i = 0; i < rf->n - 1; i++) if (rf->wslot[i] == slot) return i;
+  return -1;
+}
+
+static void rf_all_open(RowFuse *rf) { for (int i = 0; i < rf->n; i++) open_scope(&rf->g[i]); }
+static void rf_all_close(RowFuse *rf) { for (int i = 0; i < rf->n; i++) close_scope(&rf->g[i]); }
+static void rf_set_indent(RowFuse *rf, int ind_) { for (int i = 0; i < rf->n; i++) rf->g[i].indent = ind_; }
+static void rf_set_lane(RowFuse *rf, int lane) { for (int i = 0; i < rf->n; i++) rf->g[i].lane = lane; }
+static void rf_forget_lane_temps(RowFuse *rf) {
+  for (int i = 0; i < rf->n; i++) {
+    Gen *g = &rf->g[i];
+    if (!g->lane_dep) continue;
+    for (int id = 0; id < g->k->n_nodes; id++)
+      if (g->emitted[id] >= 0 && (g->k->nodes[id].deps & g->lane_dep)) g->emitted[id] = -1;
+  }
+}
+
+/* LOAD nodes of a fused kernel: values that never reach memory come from the
+ * chain itself; contiguous external loads are 128-bit. */
+static bool rf_load_hook(Gen *g, int id) {
+  RowFuse *rf = rf_of(g);
+  int ki = rf_index(rf, g);
+  PolyUOp *u = g->k->nodes[id].u;
+  PolyUOp *ix = u->src[0];
+  if (ix->op != POLY_OP_INDEX || ix->src[0]->op != POLY_OP_PARAM) return false;
+  int pi = (int)ix->src[0]->arg.i;
+  int w = rf_writer_of(rf, rf->in[ki].slot[pi]);
+  char name[40];
+  temp_name(g, id, name, sizeof name);
+  const char *ct = ctype_of(g, u->dtype);
+  if (w >= 0) {
+    if (rf->in[w].role == PB_FUSE_PHASE) {
+      ind(g); pb_str_printf(g->o, "const %s %s = stat%d_;\n", ct, name, w);
+    } else {
+      Gen *pg = &rf->g[w];
+      PbStore *st = &pg->k->stores[0];
+      emit_src(pg, st->value);
+      char v[96]; ref(pg, st->value, v, sizeof v);
+      ind(g); pb_str_printf(g->o, "const %s %s = (%s)(%s);\n", ct, name, ct, v);
+    }
+    log_emit(g, id);
+    return true;
+  }
+  if (rf->V == 4 && rf->vec_load[ki][id]) {
+    if (g->lane == 0) {
+      emit_src(g, ix->src[1]);
+      char is[96], pn[32]; ref(g, ix->src[1], is, sizeof is); ref(g, ix->src[0], pn, sizeof pn);
+      PolyDType base = ix->src[0]->dtype; base.is_ptr = false; base.count = 1;
+      ind(g); pb_str_printf(g->o, "%s lv%s%d_[4]; pb_ld4(%s + %s, lv%s%d_);\n", pb_ctype(base), g->pfx, id, pn, is, g->pfx, id);
+    }
+    ind(g); pb_str_printf(g->o, "const %s %s = (%s)lv%s%d_[%d];\n", ct, name, ct, g->pfx, id, g->lane);
+    log_emit(g, id);
+    return true;
+  }
+  return false;
+}
+
+/* Fit the index of node `ld` (a LOAD) or of a store over all ranges of kernel k. */
+static bool rf_fit(PbKern *k, PolyUOp *index_expr, PbAffine *a) {
+  uint64_t all = 0;
+  for (int r = 0; r < k->n_ranges; r++) all |= (uint64_t)1 << r;
+  pb_fit_affine(k, index_expr, all, a);
+  return a->ok;
+}
+
+/* All loads of parameter `pi` in kernel k share one index?  Returns it fitted. */
+static bool rf_param_load_index(PbKern *k, int pi, PbAffine *a, int *n_loads) {
+  PolyUOp *first = NULL; *n_loads = 0;
+  for (int i = 0; i < k->n_nodes; i++) {
+    PolyUOp *u = k->nodes[i].u;
+    if (u->op != POLY_OP_LOAD || u->src[0]->op != POLY_OP_INDEX || u->src[0]->src[0]->op != POLY_OP_PARAM) continue;
+    if ((int)u->src[0]->src[0]->arg.i != pi) continue;
+    if (u->src[0]->n_src > 2) return false;
+    (*n_loads)++;
+    if (!first) first = u->src[0]->src[1];
+    else if (first != u->src[0]->src[1]) return false;
+  }
+  if (!first) return true;
+  return rf_fit(k, first, a);
+}
+
+static int rf_find_reduce(PbKern *k) {
+  for (int i = 0; i < k->n_nodes; i++) if (k->nodes[i].u->op == POLY_OP_REDUCE) return i;
+  return -1;
+}
+
+/* Map kernel ki's ranges through the buffer it writes, using an already mapped
+ * consumer kj.  Both indices are compared in canonical ranges. */
+static bool rf_map_through(RowFuse *rf, int ki, int kj) {
+  PbKern *kp = rf->in[ki].k, *kc = rf->in[kj].k;
+  PbStore *st = &kp->stores[0];
+  if (st->index->n_src > 2) return false;
+  PbAffine ws, ls;
+  if (!rf_fit(kp, st->index->src[1], &ws)) return false;
+  int pj = -1;
+  for (int a = 0; a < kc->n_params; a++) if (kc->params[a] && rf->in[kj].slot[a] == rf->wslot[ki]) pj = a;
+  if (pj < 0) return true;                      /* kj does not read it */
+  int nl = 0;
+  if (!rf_param_load_index(kc, pj, &ls, &nl)) return false;
+  if (nl == 0) return true;
+  if (ls.offset != ws.offset) return false;
+  /* consumer strides in canonical ranges */
+  int64_t cs[PB_MAX_RANGES] = {0};
+  for (int r = 0; r < kc->n_ranges; r++) {
+    if (ls.stride[r] == 0 || kc->extent[r] <= 1) continue;
+    int cr = rf->map[kj][r];
+    if (cr < 0) return false;
+    if (cs[cr] != 0) return false;
+    cs[cr] = ls.stride[r];
+  }
+  PbKern *kf = rf->in[rf->n - 1].k;
+  bool used[PB_MAX_RANGES] = {0};
+  for (int i = 0; i < st->n_loop; i++) {
+    int q = st->loop[i];
+    if (kp->extent[q] <= 1) { if (rf->map[ki][q] < 0) rf->map[ki][q] = -2; continue; }
+    if (ws.stride[q] == 0) return false;
+    int found = -1;
+    for (int cr = 0; cr < kf->n_ranges; cr++)
+      if (!used[cr] && cs[cr] == ws.stride[q] && kf->extent[cr] == kp->extent[q]) { found = cr; break; }
+    if (found < 0) return false;
+    used[found] = true;
+    if (rf->map[ki][q] >= 0 && rf->map[ki][q] != found) return false;
+    rf->map[ki][q] = found;
+  }
+  for (int cr = 0; cr < kf->n_ranges; cr++) if (cs[cr] != 0 && !used[cr]) return false;
+  return true;
+}
+
+static void rf_free(RowFuse *rf) {
+  for (int i = 0; i < rf->n; i++) {
+    free(rf->g[i].emitted); free(rf->g[i].scope_log); free(rf->g[i].scope_mark); free(rf->vec_load[i]);
+  }
+}
+
+char *pb_render_rowfused(PbFuseIn *in, int n, bool out_bf16, PbFuseOut *out) {
+  if (n < 2 || n > RF_MAX) return NULL;
+  RowFuse *rf = calloc(1, sizeof *rf);
+  rf->n = n; rf->in = in; rf->out_bf16 = out_bf16;
+  char *result = NULL;
+  PbKern *kf = in[n - 1].k;
+  PbStr text; pb_str_init(&text);
+
+  /* shape checks */
+  int n_phase = 0;
+  for (int i = 0; i < n; i++) {
+    PbKern *k = in[i].k;
+    if (k->n_stores != 1 || k->n_vars) goto done;
+    for (int r = 0; r < k->n_ranges; r++) if (k->extent[r] < 0) goto done;
+    rf->wslot[i] = in[i].slot[k->stores[0].param];
+    param_usage(k, rf->usage[i]);
+    rf->red_node[i] = -1;
+    for (int r = 0; r < k->n_ranges; r++) rf->map[i][r] = -1;
+    if (in[i].role == PB_FUSE_PRODUCER) { if (k->n_reduce_nodes != 0) goto done; }
+    else if (in[i].role == PB_FUSE_PHASE) {
+      if (k->n_reduce_nodes != 1) goto done;
+      rf->red_node[i] = rf_find_reduce(k);
+      PolyUOp *red = k->nodes[rf->red_node[i]].u;
+      if (red->n_src != 2 || red->dtype.priority != 13) goto done;
+      PolyOps op = reduce_op(red);
+      if (op != POLY_OP_ADD && op != POLY_OP_MAX) goto done;
+      if (k->nodes[pb_kern_node(k, k->stores[0].index)].has_reduce) goto done;
+      n_phase++;
+    }
+    if (i < n - 1 && !(rf->usage[i][k->stores[0].param] & 4)) goto done;   /* internal buffers are written whole */
+  }
+  if (kf->n_reduce_nodes > 1) goto done;
+  rf->final_reduce = kf->n_reduce_nodes == 1;
+  if (rf->final_reduce) {
+    rf->red_node[n - 1] = rf_find_reduce(kf);
+    PolyUOp *red = kf->nodes[rf->red_node[n - 1]].u;
+    PolyOps op = reduce_op(red);
+    if (red->n_src != 2 || red->dtype.priority != 13 || (op != POLY_OP_ADD && op != POLY_OP_MAX)) goto done;
+    if (out_bf16) goto done;
+  }
+  if (n_phase == 0) goto done;
+  if (kf->stores[0].index->n_src > 2) goto done;
+  for (int i = 0; i < n - 1; i++) for (int j = 0; j < n - 1; j++) if (i != j && rf->wslot[i] == rf->wslot[j]) goto done;
+  for (int i = 0; i < n - 1; i++) if (rf->wslot[i] == rf->wslot[n - 1]) goto done;
+
+  /* candidates for the row axis in the final kernel */
+  int64_t C = -1;
+  for (int i = 0; i < n; i++) if (rf->red_node[i] >= 0) {
+    PbKern *k = in[i].k;
+    int r = pb_kern_range_id(k, k->nodes[rf->red_node[i]].u->src[1]);
+    if (C < 0) C = k->extent[r]; else if (C != k->extent[r]) goto done;
+    rf->c_range[i] = r;
+  }
+  if (C < 32) goto done;
+  PbStore *fst = &kf->stores[0];
+  PbAffine fs;
+  if (!rf_fit(kf, fst->index->src[1], &fs)) goto done;
+  bool mapped = false;
+  for (int cand = 0; cand < kf->n_ranges && !mapped; cand++) {
+    if (rf->final_reduce) { if (cand != rf->c_range[n - 1]) continue; }
+    else {
+      bool is_loop = false;
+      for (int i = 0; i < fst->n_loop; i++) if (fst->loop[i] == cand) is_loop = true;
+      if (!is_loop || kf->extent[cand] != C || fs.stride[cand] == 0) continue;
+    }
+    rf->canon_c = cand;
+    for (int i = 0; i < n; i++) for (int r = 0; r < in[i].k->n_ranges; r++) rf->map[i][r] = -1;
+    for (int r = 0; r < kf->n_ranges; r++) rf->map[n - 1][r] = r;
+    bool ok = true;
+    for (int i = n - 2; i >= 0 && ok; i--) {
+      if (in[i].role == PB_FUSE_PHASE) rf->map[i][rf->c_range[i]] = cand;
+      bool any = false;
+      for (int j = i + 1; j < n && ok; j++) {
+        /* does kj read what ki writes? */
+        PbKern *kc = in[j].k; bool reads = false;
+        for (int a = 0; a < kc->n_params; a++) if (kc->params[a] && in[j].slot[a] == rf->wslot[i] && (rf->usage[j][a] & 1)) reads = true;
+        if (!reads) continue;
+        any = true;
+        ok = rf_map_through(rf, i, j);
+      }
+      if (!any) ok = false;
+      /* every range of the kernel must be placed; a statistic must not vary along the row */
+      PbKern *k = in[i].k;
+      for (int r = 0; r < k->n_ranges && ok; r++) {
+        if (k->extent[r] <= 1) continue;
+        if (rf->map[i][r] < 0) ok = false;
+      }
+      if (ok && in[i].role == PB_FUSE_PHASE)
+        for (int q = 0; q < k->stores[0].n_loop; q++) if (rf->map[i][k->stores[0].loop[q]] == cand) ok = false;
+      if (ok && in[i].role == PB_FUSE_PRODUCER) {
+        /* exactly one of its ranges runs along the row */
+        int cnt = 0;
+        for (int r = 0; r < k->n_ranges; r++) if (rf->map[i][r] == cand) { rf->c_range[i] = r; cnt++; }
+        if (cnt != 1) ok = false;
+      }
+    }
+    /* statistics read by the final kernel must be row-invariant there */
+    if (ok && !rf->final_reduce) rf->c_range[n - 1] = cand;
+    mapped = ok;
+  }
+  if (!mapped) goto done;
+  rf->C = C;
+
+  /* fused parameter list */
+  out->n_params = 0;
+  for (int i = 0; i < n; i++) {
+    PbKern *k = in[i].k;
+    for (int a = 0; a < k->n_params; a++) {
+      rf->fparam[i][a] = -1;
+      if (!k->params[a] || !(rf->usage[i][a] & 3)) continue;
+      int sl = in[i].slot[a];
+      int w = rf_writer_of(rf, sl);
+      if (w >= 0) {
+        /* internal: reads are replaced; the write itself disappears */
+        if ((rf->usage[i][a] & 1) && w >= i) goto done;     /* read before it is produced */
+        continue;
+      }
+      int f = -1;
+      for (int x = 0; x < out->n_params; x++) if (out->slot[x] == sl) f = x;
+      if (f < 0) {
+        if (out->n_params >= PB_MAX_PARAMS) goto done;
+        f = out->n_params++; out->slot[f] = sl; out->rw[f] = 'r';
+      }
+      if (i == n - 1 && a == fst->param) out->rw[f] = (rf->usage[i][a] & 1) ? 'b' : ((rf->usage[i][a] & 4) ? 'W' : 'w');
+      else if (out->slot[f] == rf->wslot[n - 1] && out->rw[f] != 'r') out->rw[f] = 'b';
+      rf->fparam[i][a] = f;
+      /* element type must be 4 bytes wide for every external operand */
+      if (k->params[a]->dtype.bitsize != 32) goto done;
+    }
+  }
+  out->rw[out->n_params] = 0;
+  /* the output buffer may only be read element-for-element, which a row kernel does not guarantee */
+  for (int x = 0; x < out->n_params; x++) if (out->rw[x] == 'b') goto done;
+
+  /* vector width: every row-dependent external access contiguous and aligned */
+  rf->V = (C % 4 == 0) ? 4 : 1;
+  for (int i = 0; i < n; i++) {
+    PbKern *k = in[i].k;
+    rf->vec_load[i] = calloc((size_t)k->n_nodes, 1);
+    uint64_t cbit = (uint64_t)1 << rf->c_range[i];
+    for (int id = 0; id < k->n_nodes; id++) {
+      PolyUOp *u = k->nodes[id].u;
+      if (u->op != POLY_OP_LOAD) continue;
+      PolyUOp *ix = u->src[0];
+      if (ix->op != POLY_OP_INDEX || ix->src[0]->op != POLY_OP_PARAM) goto done;
+      int pi = (int)ix->src[0]->arg.i;
+      if (rf_writer_of(rf, in[i].slot[pi]) >= 0) continue;
+      if (!(k->nodes[id].deps & cbit)) continue;
+      PbAffine a;
+      bool fit = ix->n_src == 2 && rf_fit(k, ix->src[1], &a);
+      bool vec = fit && a.stride[rf->c_range[i]] == 1 && a.offset % 4 == 0;
+      if (vec) {
+        int64_t lo = a.offset, hi = a.offset;
+        for (int r = 0; r < k->n_ranges; r++) {
+          if (r != rf->c_range[i] && a.stride[r] % 4) vec = false;
+          int64_t sp = a.stride[r] * (k->extent[r] - 1);
+          if (sp > 0) hi += sp; else lo += sp;
+        }
+        if (lo < 0 || hi >= ix->src[0]->dtype.ptr_size) vec = false;
+      }
+      rf->vec_load[i][id] = vec;
+      if (!vec && fit && a.stride[rf->c_range[i]] == 0) continue;   /* row-invariant after all */
+      if (!vec) rf->V = 1;
+    }
+  }
+  if (!rf->final_reduce) {
+    if (fs.stride[rf->canon_c] != 1 || fs.offset % 4) rf->V = 1;
+    int64_t lo = fs.offset, hi = fs.offset;
+    for (int r = 0; r < kf->n_ranges; r++) {
+      if (r != rf->canon_c && fs.stride[r] % 4) rf->V = 1;
+      int64_t sp = fs.stride[r] * (kf->extent[r] - 1);
+      if (sp > 0) hi += sp; else lo += sp;
+    }
+    if (lo < 0 || hi >= kf->params[fst->param]->dtype.ptr_size) rf->V = 1;
+    if (out_bf16 && rf->V != 4) goto done;
+  }
+  {
+    int64_t per = (C + rf->V * 8 - 1) / (rf->V * 8);
+    int G = 32; while (G < per && G < 1024) G *= 2;
+    rf->G = G;
+    rf->NI = (int)((C + (int64_t)G * rf->V - 1) / ((int64_t)G * rf->V));
+    if (rf->NI > 32) goto done;
+    rf->RPB = G >= 256 ? 1 : 256 / G;
+  }
+
+  /* rows */
+  int row_axes[PB_MAX_AXES]; int n_row = 0; int64_t n_rows = 1;
+  {
+    int order[PB_MAX_AXES];
+    order_loop_axes(kf, fst, order, NULL);
+    for (int i = 0; i < fst->n_loop; i++) if (order[i] != rf->canon_c) { row_axes[n_row++] = order[i]; n_rows *= kf->extent[order[i]]; }
+  }
+  bool wide = n_rows * rf->G >= ((int64_t)1 << 31);
+  for (int i = 0; i < n; i++) for (int a = 0; a < in[i].k->n_params; a++)
+    if (in[i].k->params[a] && in[i].k->params[a]->dtype.ptr_size >= ((int64_t)1 << 31)) wide = true;
+
+  /* generators */
+  static const char *PFX[RF_MAX] = {"a", "b", "c", "d", "e", "f", "g", "h"};
+  for (int i = 0; i < n; i++) {
+    Gen *g = &rf->g[i];
+    PbKern *k = in[i].k;
+    g->k = k; g->o = &text; g->pfx = PFX[i]; g->ud = rf; g->load_hook = rf_load_hook;
+    g->emitted = malloc(sizeof(int) * (size_t)k->n_nodes);
+    for (int x = 0; x < k->n_nodes; x++) g->emitted[x] = -1;
+    g->scope_mark = calloc(64, sizeof(int));
+    g->wide = wide; g->idx_t = wide ? "long long" : "int";
+    g->range_expr = rf->range_expr[i]; g->param_expr = rf->param_expr[i];
+    for (int r = 0; r < k->n_ranges; r++) {
+      int cr = rf->map[i][r];
+      if (cr == rf->canon_c && r == rf->c_range[i]) snprintf(rf->range_expr[i][r], 40, "c_");
+      else if (cr >= 0) snprintf(rf->range_expr[i][r], 40, "r%d", cr);
+      else snprintf(rf->range_expr[i][r], 40, "0");
+    }
+    for (int a = 0; a < k->n_params; a++) snprintf(rf->param_expr[i][a], 24, "p%d", rf->fparam[i][a]);
+    g->vec = rf->V; g->lane = 0; g->lane_dep = (uint64_t)1 << rf->c_range[i];
+    g->bound = 0;
+    for (int r = 0; r < k->n_ranges; r++) if (r != rf->c_range[i]) g->bound |= (uint64_t)1 << r;
+  }
+
+  /* ── text ── */
+  const int G = rf->G, V = rf->V, NI = rf->NI, RPB = rf->RPB, block = G * RPB;
+  pb_str_puts(&text, PRELUDE);
+  pb_str_puts(&text,
+    "template <class T> __device__ __forceinline__ void pb_ld4(const T* p, T* o) {\n"
+    "  const uint4 v = *reinterpret_cast<const uint4*>(p); memcpy(o, &v, 16);\n}\n"
+    "template <class T> __device__ __forceinline__ void pb_st4(T* p, const T* o) {\n"
+    "  uint4 v; memcpy(&v, o, 16); *reinterpret_cast<uint4*>(p) = v;\n}\n");
+  pb_str_printf(&text, "extern \"C\" __global__ void __launch_bounds__(%d) pb200_kernel(", block);
+  for (int x = 0; x < out->n_params; x++) {
+    /* element type from any kernel parameter bound to this slot */
+    const char *ct = "float";
+    for (int i = 0; i < n; i++) for (int a = 0; a < in[i].k->n_params; a++)
+      if (rf->fparam[i][a] == x) { PolyDType b = in[i].k->params[a]->dtype; b.is_ptr = false; b.count = 1; ct = pb_ctype(b); }
+    bool is_out = out->slot[x] == rf->wslot[n - 1];
+    if (is_out && out_bf16) ct = "__nv_bfloat16";
+    pb_str_printf(&text, "%s%s* __restrict__ p%d, ", is_out ? "" : "const ", ct, x);
+  }
+  pb_str_puts(&text, "const long long n_work) {\n");
+  rf_set_indent(rf, 1);
+  Gen *gf = &rf->g[n - 1];
+  ind(gf); pb_str_printf(&text, "const int lane_ = threadIdx.x %% %d, rib_ = threadIdx.x / %d;\n", G, G);
+  ind(gf); pb_str_printf(&text, "long long row_ = (long long)blockIdx.x * %d + rib_;\n", RPB);
+  ind(gf); pb_str_puts(&text, "const bool live_ = row_ < n_work;\n");
+  ind(gf); pb_str_puts(&text, "if (!live_) row_ = n_work - 1;\n");
+  if (n_row > 0) {
+    ind(gf); pb_str_printf(&text, "%s rem_ = (%s)row_;\n", gf->idx_t, gf->idx_t);
+    for (int i = 0; i < n_row; i++) {
+      int r = row_axes[i];
+      ind(gf);
+      if (i == n_row - 1) pb_str_printf(&text, "const %s r%d = rem_;\n", gf->idx_t, r);
+      else pb_str_printf(&text, "const %s r%d = rem_ %% %lld; rem_ /= %lld;\n", gf->idx_t, r, (long long)kf->extent[r], (long long)kf->extent[r]);
+    }
+  }
+  /* extent-1 ranges of the final kernel */
+  for (int r = 0; r < kf->n_ranges; r++) {
+    bool isrow = false;
+    for (int i = 0; i < n_row; i++) if (row_axes[i] == r) isrow = true;
+    if (!isrow && r != rf->canon_c && !(rf->final_reduce && r == rf->c_range[n - 1])) {
+      ind(gf); pb_str_printf(&text, "const %s r%d = 0;\n", gf->idx_t, r);
+    }
+  }
+
+  for (int i = 0; i < n; i++) {
+    const bool is_final = i == n - 1;
+    if (in[i].role == PB_FUSE_PRODUCER) continue;
+    Gen *g = &rf->g[i];
+    PbKern *k = in[i].k;
+    PbStore *st = &k->stores[0];
+    if (!is_final || rf->final_reduce) {
+      /* ── a reduction phase ── */
+      PolyUOp *red = k->nodes[rf->red_node[i]].u;
+      PolyOps op = reduce_op(red);
+      int vid = pb_kern_node(k, red->src[0]);
+      hoist(g, vid);
+      char idn[96]; reduce_identity(op, red->dtype, idn, sizeof idn, g);
+      ind(g); pb_str_printf(&text, "float acc%d_ = %s;\n", i, idn);
+      ind(g); pb_str_puts(&text, "#pragma unroll\n");
+      ind(g); pb_str_printf(&text, "for (int i_ = 0; i_ < %d; ++i_) {\n", NI);
+      rf_set_indent(rf, 2);
+      ind(g); pb_str_printf(&text, "const %s c_ = (lane_ + i_ * %d) * %d;\n", g->idx_t, G, V);
+      ind(g); pb_str_printf(&text, "if (c_ < %lld) {\n", (long long)C);
+      rf_set_indent(rf, 3);
+      rf_all_open(rf);
+      for (int r = 0; r < rf->n; r++) rf->g[r].bound |= rf->g[r].lane_dep;
+      for (int lane = 0; lane < V; lane++) {
+        rf_set_lane(rf, lane);
+        emit_src(g, red->src[0]);
+        char v[96], acc[24], cmb[256];
+        ref(g, red->src[0], v, sizeof v);
+        snprintf(acc, sizeof acc, "acc%d_", i);
+        combine_expr(op, acc, v, cmb, sizeof cmb);
+        ind(g); pb_str_printf(&text, "%s = %s;\n", acc, cmb);
+        if (V > 1) rf_forget_lane_temps(rf);
+      }
+      rf_set_lane(rf, 0);
+      for (int r = 0; r < rf->n; r++) rf->g[r].bound &= ~rf->g[r].lane_dep;
+      rf_all_close(rf);
+      rf_set_indent(rf, 2); ind(g); pb_str_puts(&text, "}\n");
+      rf_set_indent(rf, 1); ind(g); pb_str_puts(&text, "}\n");
+      /* combine across the group */
+      char sh[256], accn[24]; snprintf(accn, sizeof accn, "acc%d_", i);
+      combine_expr(op, accn, "x_", sh, sizeof sh);
+      ind(g); pb_str_puts(&text, "#pragma unroll\n");
+      ind(g); pb_str_printf(&text, "for (int o_ = 16; o_ > 0; o_ >>= 1) { const float x_ = __shfl_xor_sync(0xffffffffu, %s, o_); %s = %s; }\n", accn, accn, sh);
+      if (G > 32) {
+        int nw = G / 32;
+        ind(g); pb_str_printf(&text, "__shared__ float red%d_[%d][%d];\n", i, RPB, nw);
+        ind(g); pb_str_printf(&text, "if ((lane_ & 31) == 0) red%d_[rib_][lane_ >> 5] = %s;\n", i, accn);
+        ind(g); pb_str_puts(&text, "__syncthreads();\n");
+        ind(g); pb_str_printf(&text, "%s = red%d_[rib_][0];\n", accn, i);
+        ind(g); pb_str_printf(&text, "#pragma unroll\n");
+        ind(g); pb_str_printf(&text, "for (int w_ = 1; w_ < %d; ++w_) { const float x_ = red%d_[rib_][w_]; %s = %s; }\n", nw, i, accn, sh);
+      }
+      /* the kernel's own expression after the reduction */
+      char name[40]; temp_name(g, rf->red_node[i], name, sizeof name);
+      ind(g); pb_str_printf(&text, "const float %s = %s;\n", name, accn);
+      log_emit(g, rf->red_node[i]);
+      emit_src(g, st->value);
+      char sv[96]; ref(g, st->value, sv, sizeof sv);
+      if (!is_final) { ind(g); pb_str_printf(&text, "const float stat%d_ = (float)(%s);\n", i, sv); }
+      else {
+        emit_src(g, st->index->src[1]);
+        char is[96], pn[32]; ref(g, st->index->src[1], is, sizeof is); ref(g, st->index->src[0], pn, sizeof pn);
+        ind(g); pb_str_printf(&text, "if (live_ && lane_ == 0) pb_st(%s, %s, %lldLL, (float)(%s));\n", pn, is,
+                              (long long)k->params[st->param]->dtype.ptr_size, sv);
+      }
+    } else {
+      /* ── the final elementwise pass ── */
+      hoist(g, pb_kern_node(k, st->value));
+      ind(g); pb_str_puts(&text, "#pragma unroll\n");
+      ind(g); pb_str_printf(&text, "for (int i_ = 0; i_ < %d; ++i_) {\n", NI);
+      rf_set_indent(rf, 2);
+      ind(g); pb_str_printf(&text, "const %s c_ = (lane_ + i_ * %d) * %d;\n", g->idx_t, G, V);
+      ind(g); pb_str_printf(&text, "if (c_ < %lld) {\n", (long long)C);
+      rf_set_indent(rf, 3);
+      rf_all_open(rf);
+      for (int r = 0; r < rf->n; r++) rf->g[r].bound |= rf->g[r].lane_dep;
+      char pn[32]; ref(g, st->index->src[0], pn, sizeof pn);
+      if (V == 4) { ind(g); pb_str_puts(&text, "float o4_[4];\n"); }
+      for (int lane = 0; lane < V; lane++) {
+        rf_set_lane(rf, lane);
+        emit_src(g, st->value);
+        char v[96]; ref(g, st->value, v, sizeof v);
+        if (V == 4) { ind(g); pb_str_printf(&text, "o4_[%d] = (float)(%s);\n", lane, v); }
+        else {
+          emit_src(g, st->index->src[1]);
+          char is[96]; ref(g, st->index->src[1], is, sizeof is);
+          ind(g); pb_str_printf(&text, "if (live_) pb_st(%s, %s, %lldLL, (float)(%s));\n", pn, is,
+                                (long long)k->params[st->param]->dtype.ptr_size, v);
+        }
+        if (V > 1 && lane < V - 1) rf_forget_lane_temps(rf);
+      }
+      if (V == 4) {
+        rf_set_lane(rf, 0);
+        rf_forget_lane_temps(rf);
+        emit_src(g, st->index->src[1]);
+        char is[96]; ref(g, st->index->src[1], is, sizeof is);
+        ind(g);
+        if (out_bf16)
+          pb_str_printf(&text, "if (live_) { __nv_bfloat162 q0_ = __floats2bfloat162_rn(o4_[0], o4_[1]), q1_ = __floats2bfloat162_rn(o4_[2], o4_[3]); "
+                               "uint2 w_; w_.x = *reinterpret_cast<unsigned*>(&q0_); w_.y = *reinterpret_cast<unsigned*>(&q1_); "
+                               "*reinterpret_cast<uint2*>(%s + %s) = w_; }\n", pn, is);
+        else pb_str_printf(&text, "if (live_) pb_st4(%s + %s, o4_);\n", pn, is);
+      }
+      rf_set_lane(rf, 0);
+      for (int r = 0; r < rf->n; r++) rf->g[r].bound &= ~rf->g[r].lane_dep;
+      rf_all_close(rf);
+      rf_set_indent(rf, 2); ind(g); pb_str_puts(&text, "}\n");
+      rf_set_indent(rf, 1); ind(g); pb_str_puts(&text, "}\n");
+    }
+  }
+  pb_str_puts(&text, "}\n");
+  bool failed = false;
+  for (int i = 0; i < n; i++) if (rf->g[i].failed) failed = true;
+  if (!failed) {
+    PbStr h; pb_str_init(&h);
+    pb_str_puts(&h, "//PB200 1\n//kind jit\n//entry pb200_kernel\n");
+    pb_str_printf(&h, "//nparams %d\n//nvars 0\n", out->n_params);
+    pb_str_printf(&h, "//launch group block=%d group=%d work=c%lld\n", block, G, (long long)n_rows);
+    pb_str_puts(&h, "//rw");
+    for (int x = 0; x < out->n_params; x++) pb_str_printf(&h, " %s", out->rw[x] == 'W' ? "W" : (out->rw[x] == 'w' ? "w" : "r"));
+    pb_str_printf(&h, "\n//fused %d kernels, row length %lld, %d lanes per row, %d-wide\n", n, (long long)C, G, V);
+    if (out_bf16) pb_str_puts(&h, "#include <cuda_bf16.h>\n");
+    pb_str_puts(&h, text.s);
+    result = pb_str_take(&h);
+  }
+done:
+  pb_str_free(&text);
+  rf_free(rf);
+  free(rf);
+  return result;
 }

@@ -101,6 +101,26 @@ const char *pb_ctype(PolyDType dt);
  * "//PB200" header lines the runtime parses.  Returns malloc'd text or NULL. */
 char *pb_render_jit(PbKern *k, const char *fn_name);
 
+/* Several kernels of one plan rendered as one row-wise kernel: reductions over
+ * the same contiguous axis feed later kernels of the chain through registers
+ * instead of memory (softmax: max, sum of exp, normalise; layernorm: mean,
+ * variance, normalise), and elementwise producers are evaluated in place. */
+enum { PB_FUSE_PRODUCER = 0, PB_FUSE_PHASE = 1, PB_FUSE_FINAL = 2 };
+typedef struct {
+  PbKern *k;
+  const int *slot;     /* plan slot of each kernel parameter */
+  int role;
+} PbFuseIn;
+typedef struct {
+  int n_params;
+  int slot[PB_MAX_PARAMS];
+  char rw[PB_MAX_PARAMS + 1];
+} PbFuseOut;
+/* in[] in execution order, the final kernel last.  out_bf16: store the result as
+ * bfloat16 (for a buffer only tensor-core contractions read).  NULL if the chain
+ * does not have the required shape. */
+char *pb_render_rowfused(PbFuseIn *in, int n, bool out_bf16, PbFuseOut *out);
+
 /* ── pattern lowerings (pb_classify.c) ───────────────────────────────── */
 /* Try to express the kernel as one of the precompiled kernels (GEMM, row
  * gather, strided copy).  Returns malloc'd header-only text, or NULL when the
