@@ -1495,7 +1495,15 @@ char *pb_render_rowfused(PbFuseIn *in, int n, bool out_bf16, PbFuseOut *out) {
       rf_all_open(rf);
       for (int r = 0; r < rf->n; r++) rf->g[r].bound |= rf->g[r].lane_dep;
       char pn[32]; ref(g, st->index->src[0], pn, sizeof pn);
-      if (V == 4) { ind(g); pb_str_puts(&text, "float o4_[4];\n"); }
+      char is0[96] = "";
+      if (V == 4) {
+        /* address of the 4-wide store: the index at lane 0, emitted first so that
+         * lane 0's own use of the same expression finds it declared */
+        ind(g); pb_str_puts(&text, "float o4_[4];\n");
+        rf_set_lane(rf, 0);
+        emit_src(g, st->index->src[1]);
+        ref(g, st->index->src[1], is0, sizeof is0);
+      }
       for (int lane = 0; lane < V; lane++) {
         rf_set_lane(rf, lane);
         emit_src(g, st->value);
@@ -1510,10 +1518,7 @@ char *pb_render_rowfused(PbFuseIn *in, int n, bool out_bf16, PbFuseOut *out) {
         if (V > 1 && lane < V - 1) rf_forget_lane_temps(rf);
       }
       if (V == 4) {
-        rf_set_lane(rf, 0);
-        rf_forget_lane_temps(rf);
-        emit_src(g, st->index->src[1]);
-        char is[96]; ref(g, st->index->src[1], is, sizeof is);
+        const char *is = is0;
         ind(g);
         if (out_bf16)
           pb_str_printf(&text, "if (live_) { __nv_bfloat162 q0_ = __floats2bfloat162_rn(o4_[0], o4_[1]), q1_ = __floats2bfloat162_rn(o4_[2], o4_[3]); "
