@@ -303,58 +303,94 @@ def run_b200(args, cfg, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-def gemm_roofline(lib, args, cfg):
-    """Times the workload's largest projection (tokens x 4d x d) alone through
-    poly_realize and reports it against the tensor-pipe (bf16) peak."""
-    from polygrad_b200 import ffi
-    from polygrad_b200.tensor import Device
-    peaks = read_peaks()
-    M, K, N = cfg['max_batch'] * cfg['max_seq_len'], cfg['n_embd'], 4 * cfg['n_embd']
-    dev = Device(lib, ffi.DEVICE_CUDA)
+def time_gemm(lib, M, N, K, bf16_policy, reps=20, bf16_buffers=False, bias=False):
+    """Device time per call of the contraction kernel(s) through the C-ABI entry
+    poly_b200_gemm, operands resident, CUDA events on the launching stream.
+    B is constant across calls (a weight): its bf16 copy is made once, while A is
+    converted on every call, as in a model's forward."""
+    from polygrad_b200.tensor import f32_to_bf16_bits
     rng = np.random.default_rng(SEED)
     a = rng.uniform(-1, 1, (M, K)).astype(np.float32)
     b = rng.uniform(-1, 1, (K, N)).astype(np.float32)
-    ms = time_realize(lib, dev, a, b, reps=20)
+    if bf16_buffers:
+        a, b = f32_to_bf16_bits(a), f32_to_bf16_bits(b)
+    lib.poly_b200_set_gemm_policy(int(bf16_policy))
+    da, db = lib.poly_cuda_alloc(a.nbytes), lib.poly_cuda_alloc(b.nbytes)
+    dc = lib.poly_cuda_alloc(M * N * 4)
+    dx = lib.poly_cuda_alloc(N * 4) if bias else 0
+    lib.poly_cuda_copy_htod(da, a.ctypes.data, a.nbytes)
+    lib.poly_cuda_copy_htod(db, b.ctypes.data, b.nbytes)
+    if bias:
+        lib.poly_cuda_memset(dx, 0, N * 4)
+
+    def call():
+        rc = lib.poly_b200_gemm(M, N, K, da, K, 1, db, N, 1, dc, N, dx or None, 0, int(bf16_buffers))
+        if rc != 0:
+            raise SystemExit('bench: poly_b200_gemm failed: ' + lib.last_error())
+    for _ in range(3):
+        call()
+    e0, e1 = lib.poly_b200_event_create(), lib.poly_b200_event_create()
+    lib.poly_b200_event_record(e0)
+    for _ in range(reps):
+        call()
+    lib.poly_b200_event_record(e1)
+    ms = lib.poly_b200_event_elapsed_ms(e0, e1) / reps
+    for d in (da, db, dc, dx):
+        if d:
+            lib.poly_cuda_free(d)
+    return ms
+
+
+def gemm_roofline(lib, args, cfg):
+    """The workload's largest projection (tokens x 4d x d) alone, against the
+    tensor-pipe peak (bf16) or the fp32 FMA rate."""
+    peaks = read_peaks()
+    M, K, N = cfg['max_batch'] * cfg['max_seq_len'], cfg['n_embd'], 4 * cfg['n_embd']
+    bf16 = args.dtype == 'bf16'
+    ms = time_gemm(lib, M, N, K, bf16, bias=True)
+    lib.poly_b200_set_gemm_policy(int(bf16))
     flops = 2.0 * M * N * K
     achieved = flops / (ms * 1e-3) / 1e12
-    if args.dtype == 'bf16':
+    if bf16:
         peak, bound = peaks['bf16_tflops'], 'tensor'
     else:
         peak, bound = 75.0, 'fp32-cuda-core'
     return dict(bound=bound, achieved=achieved, peak=peak, unit='TFLOP/s', frac=achieved / peak, traffic=None,
-                kernel=f'gemm {M}x{N}x{K}', peak_source=peaks['source'] if args.dtype == 'bf16' else 'nominal fp32 FMA rate',
+                kernel=f'gemm {M}x{N}x{K} (+ per-call bf16 conversion of the activations)' if bf16 else f'sgemm {M}x{N}x{K}',
+                peak_source=peaks['source'] if bf16 else 'nominal fp32 FMA rate',
                 ms_per_launch=ms)
 
 
-def time_realize(lib, dev, a, b, reps):
-    """Device time of one realize of a @ b with operands resident (events on the launching stream)."""
+def run_gemm_sweep(args):
+    """BASELINE configs[1]: square and model-shaped contractions, fp32 and bf16."""
     from polygrad_b200 import ffi
-    from polygrad_b200.tensor import _i64
-    ta, tb = dev.tensor(a), dev.tensor(b)
-    out = ta.dot(tb)
-    n = out.numel()
-    out_buf = lib.poly_buffer_by_id(dev.ctx, n, ffi.DTYPE_IDS['float32'])
-    store = lib.poly_store_val(dev.ctx, out_buf, lib.poly_reshape(dev.ctx, out.uop, _i64([n]), 1))
-    sink = lib.poly_sink1(dev.ctx, store)
-    pairs = list(out.leaves) + [(out_buf, np.empty(n, np.float32))]
-    binds = (ffi.PolyBufferBinding * len(pairs))()
-    for i, (buf, host) in enumerate(pairs):
-        d = lib.poly_cuda_alloc(host.nbytes)
-        if i < len(pairs) - 1:
-            lib.poly_cuda_copy_htod(d, host.ctypes.data, host.nbytes)
-        binds[i].buffer, binds[i].handle.ptr = buf, d
-        binds[i].handle.nbytes, binds[i].handle.domain = host.nbytes, ffi.DEVICE_CUDA
-    for _ in range(3):
-        assert lib.poly_realize(dev.ctx, sink, binds, len(pairs)) == 0, lib.last_error()
-    e0, e1 = lib.poly_b200_event_create(), lib.poly_b200_event_create()
-    lib.poly_b200_event_record(e0)
-    for _ in range(reps):
-        lib.poly_realize(dev.ctx, sink, binds, len(pairs))
-    lib.poly_b200_event_record(e1)
-    ms = lib.poly_b200_event_elapsed_ms(e0, e1) / reps
-    for i in range(len(pairs)):
-        lib.poly_cuda_free(binds[i].handle.ptr)
-    return ms
+    lib = ffi.product()
+    lib.poly_b200_set_device(int(os.environ.get('LOCAL_RANK', '0')))
+    if lib.poly_cuda_init() != 0:
+        raise SystemExit('bench: no usable B200: ' + lib.last_error())
+    peaks = read_peaks()
+    if args.shape:
+        shapes = [tuple(int(x) for x in args.shape.lower().split('x'))]
+    else:
+        shapes = [(n, n, n) for n in (1024, 2048, 4096, 8192)] + [(8192, 2304, 768), (8192, 3072, 768), (8192, 768, 3072)]
+    rows = []
+    for (M, N, K) in shapes:
+        for mode in (['bf16'] if args.dtype == 'bf16' and args.shape else ['f32', 'bf16-policy', 'bf16-buffers']):
+            if mode == 'f32' and M * N * K > 4096 ** 3 * 4:
+                reps = 3
+            else:
+                reps = max(args.steps, 3)
+            ms = time_gemm(lib, M, N, K, mode in ('bf16-policy', 'bf16'), reps=reps, bf16_buffers=(mode == 'bf16-buffers'))
+            tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+            peak = peaks['bf16_tflops'] if mode != 'f32' else 75.0
+            rows.append(dict(shape=f'{M}x{N}x{K}', mode=mode, us=ms * 1e3, tflops=tf, frac_of_peak=tf / peak))
+    best = max((r for r in rows if r['mode'] != 'f32'), key=lambda r: r['tflops'])
+    print(json.dumps(dict(metric='gemm_tflops', value=best['tflops'], unit='TFLOP/s', n_gpus=1, steps=args.steps,
+                          warmup=3, higher_is_better=True, dtype='bf16', data='synthetic',
+                          config=dict(workload='gemm sweep', best=best['shape']),
+                          roofline=dict(bound='tensor', achieved=best['tflops'], peak=peaks['bf16_tflops'], unit='TFLOP/s',
+                                        frac=best['tflops'] / peaks['bf16_tflops'], traffic=None),
+                          rows=rows)), flush=True)
 
 
 def main():
@@ -363,7 +399,8 @@ def main():
     ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
-    ap.add_argument('--workload', default='gpt2-124m', choices=sorted(WORKLOADS))
+    ap.add_argument('--workload', default='gpt2-124m', choices=sorted(WORKLOADS) + ['gemm'])
+    ap.add_argument('--shape', default='', help='MxNxK for --workload gemm')
     ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp32'])
     ap.add_argument('--gather', default='last', choices=['last', 'full'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
@@ -373,6 +410,8 @@ def main():
     rank = int(os.environ.get('RANK', '0'))
     world = int(os.environ.get('WORLD_SIZE', '1'))
     local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    if args.workload == 'gemm':
+        return run_gemm_sweep(args)
     cfg = WORKLOADS[args.workload]
     if args.impl == 'reference':
         run_reference(args, cfg, rank)

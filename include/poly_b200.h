@@ -94,6 +94,17 @@ int  poly_b200_device(void);
 void poly_b200_set_gemm_policy(int bf16);
 int  poly_b200_gemm_policy(void);
 
+/* The contraction kernels with plain device pointers (what the backend runs for
+ * polygrad's poly_dot, src/frontend.c:1029):
+ *   C[m*c_sm + n] = sum_k A[m*a_sm + k*a_sk] * B[k*b_sk + n*b_sn] (+ bias[n]) (relu)
+ * A and B are float32, or bfloat16 when operands_bf16 != 0; C and bias float32.
+ * float32 operands follow the current policy (poly_b200_set_gemm_policy).
+ * Stream-ordered; 0 / -1. */
+int poly_b200_gemm(long long M, long long N, long long K,
+                   const void *A, long long a_sm, long long a_sk,
+                   const void *B, long long b_sk, long long b_sn,
+                   float *C, long long c_sm, const float *bias, int relu, int operands_bf16);
+
 /* Wait for all enqueued work.  0 / -1. */
 int  poly_b200_synchronize(void);
 

@@ -24,6 +24,7 @@
  */
 #include "../runtime/pb_runtime.h"
 #include "pb_gemm.h"
+#include "../../../include/poly_b200.h"
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
@@ -534,4 +535,44 @@ PbAotProgram *pb_make_gemm(const PbHeader &h, std::string &err) {
   bool x_is_c = p->has_x && p->p_x == p->p_c;
   p->rw[(size_t)p->p_c] = x_is_c ? 'b' : (dense ? 'W' : 'w');
   return p;
+}
+
+/* ── direct entry point ──────────────────────────────────────────────── */
+/* C[m, n] = sum_k A[m*a_sm + k*a_sk] * B[k*b_sk + n*b_sn] (+ bias[n]) (relu), with
+ * plain device pointers.  Programs are kept per argument shape so that bf16
+ * copies of constant operands are reused between calls. */
+#include <tuple>
+static std::map<std::tuple<long long, long long, long long, long long, long long, long long, long long, long long, int, int, int>,
+                PbGemmProgram *> g_direct;
+
+extern "C" int poly_b200_gemm(long long M, long long N, long long K,
+                              const void *A, long long a_sm, long long a_sk,
+                              const void *B, long long b_sk, long long b_sn,
+                              float *C, long long c_sm, const float *bias, int relu, int operands_bf16) {
+  if (poly_cuda_init() != 0) return -1;
+  if (M <= 0 || N <= 0 || K <= 0 || !A || !B || !C) { pb_set_error("poly_b200_gemm: bad arguments"); return -1; }
+  auto key = std::make_tuple(M, N, K, a_sm, a_sk, b_sk, b_sn, c_sm, relu, operands_bf16, bias ? 1 : 0);
+  PbGemmProgram *p = nullptr;
+  auto it = g_direct.find(key);
+  if (it != g_direct.end()) p = it->second;
+  else {
+    p = new PbGemmProgram();
+    p->n_params = 4; p->p_c = 0; p->p_a = 1; p->p_b = 2; p->p_x = bias ? 3 : -1;
+    p->has_x = bias != nullptr; p->relu = relu != 0;
+    p->dtype = operands_bf16 ? PB_BF16 : PB_F32;
+    p->M = M; p->N = N; p->K = K; p->nbatch = 1;
+    p->m_ax.push_back(PbGemmAxis{'m', M, c_sm, a_sm, 0, 0});
+    p->n_ax.push_back(PbGemmAxis{'n', N, 1, 0, b_sn, bias ? 1 : 0});
+    p->k_ax.push_back(PbGemmAxis{'k', K, 0, a_sk, b_sk, 0});
+    p->c_sm = c_sm; p->c_sn = 1; p->x_sm = 0; p->x_sn = 1;
+    p->a_sm = a_sm; p->a_sk = a_sk; p->b_sk = b_sk; p->b_sn = b_sn;
+    p->a_direct = (a_sk == 1 || a_sm == 1) && a_sk > 0 && a_sm >= 0;
+    p->b_direct = (b_sk == 1 || b_sn == 1) && b_sk > 0 && b_sn >= 0;
+    p->rw = "Wrrr";
+    g_direct[key] = p;
+  }
+  void *bufs[4] = {C, const_cast<void *>(A), const_cast<void *>(B), const_cast<float *>(bias)};
+  int rc = p->launch(bufs, (cudaStream_t)poly_b200_stream());
+  if (rc == 0) pb_count_launch(true, p->n_launches());
+  return rc;
 }

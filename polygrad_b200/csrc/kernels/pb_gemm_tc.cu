@@ -8,15 +8,19 @@
  * or -- under POLY_B200_GEMM=bf16 -- from fp32 buffers whose values are rounded
  * to bf16 (nearest even) on the way in; products and sums stay fp32.
  *
- * One persistent CTA per SM, 6 warps, no clusters and no multicast:
+ * One persistent CTA per SM, 10 warps, no clusters and no multicast:
  *   warp 0     allocates tensor memory; one lane issues the TMA loads
  *              (cp.async.bulk.tensor, 128-byte swizzle) into a ring of stages;
  *   warp 1     one lane issues tcgen05.mma (128 x BN x 16 per instruction, 4 per
  *              64-wide k block) and commits completion to the stage's "empty"
  *              barrier and, after the last k block, to the tile's "full" barrier;
- *   warps 2-5  epilogue: tcgen05.ld 32 lanes x 32 columns at a time, transpose
- *              through shared memory so that global stores are 128-byte rows,
- *              add the addend, apply relu, store.
+ *   warps 2-9  epilogue: tcgen05.ld 32 lanes x 32 columns at a time (a thread gets
+ *              32 consecutive values of one row), transposed through swizzled
+ *              shared memory so that a warp writes 128 contiguous bytes of one
+ *              row per store whatever the row pitch (a 50257-wide vocabulary has
+ *              no 16-byte aligned rows); the addend and relu are applied on the
+ *              way out.  Writing each thread's row as 128-bit stores straight
+ *              from registers was measured and is slower (32 rows per store).
  * Two accumulator buffers in tensor memory let the MMA warp start the next tile
  * while the epilogue drains the previous one.
  *
@@ -32,7 +36,7 @@
 
 #define TC_BM 128
 #define TC_BK 64
-#define TC_THREADS 192
+#define TC_THREADS 320
 #define TC_SPIN_LIMIT (1u << 22)
 
 __device__ int pb200_tc_error_flag = 0;
@@ -131,7 +135,7 @@ struct TcSmem {
   static constexpr int STAGE_B = BN * TC_BK * 2;
   static constexpr int STAGE = STAGE_A + STAGE_B;
   static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int EPI = 4 * 32 * 33 * 4;
+  static constexpr int EPI = 8 * 32 * 32 * 4;
   static constexpr int BYTES = STAGES * STAGE + EPI + 256 + 1024; /* + barriers + alignment slack */
 };
 
@@ -158,7 +162,7 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < S::STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-    for (int b = 0; b < 2; b++) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, 4); }
+    for (int b = 0; b < 2; b++) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, 8); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -213,9 +217,10 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       }
     }
   } else {
-    /* ── epilogue: warp w owns tensor-memory lanes 32*(w%4) .. +31 ── */
-    const int q = warp & 3;
-    float *stg = epi + (warp - 2) * 32 * 33;
+    /* ── epilogue: 8 warps; warp w reads tensor-memory lanes 32*(w%4) .. +31 (the
+     * hardware ties a warp to that quarter) and one half of the tile's columns ── */
+    const int q = warp & 3, half = (warp - 2) >> 2;
+    float *stg = epi + (warp - 2) * 32 * 32;
     uint32_t it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < g.n_tiles && ok; t += gridDim.x, it++) {
@@ -228,27 +233,42 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       tc_fence_after_sync();
       const int row0 = mt * TC_BM + q * 32;
       const int rows = min(32, g.M - row0);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        const int col0 = nt * BN + c0;
-        if (col0 >= g.N) break;
-        uint32_t r[32];
-        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c0, r);
-        tc_wait_ld();
+      float *__restrict__ C = g.C + oc;
+      const float *__restrict__ X = g.has_x ? g.X + ox : nullptr;
+      /* chunks of 32 columns; the tensor-memory load of the next chunk is in
+       * flight while this one is transposed and stored */
+      constexpr int NCH = (BN / 2) / 32;
+      const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * (BN / 2);
+      const int colh = nt * BN + half * (BN / 2);
+      const bool x_bcast = X && g.x_sm == 0;       /* bias: one value per column */
+      uint32_t r[2][32];
+      if (colh < g.N) tc_ld32(tbase, r[0]);
 #pragma unroll
-        for (int j = 0; j < 32; j++) stg[lane * 33 + j] = __uint_as_float(r[j]);
-        __syncwarp();
-        const int n = col0 + lane;
-        if (n < g.N) {
-          for (int rr = 0; rr < rows; rr++) {
-            const long long m = row0 + rr;
-            float v = stg[rr * 33 + lane];
-            if (g.has_x) v = v + g.X[ox + m * g.x_sm + (long long)n * g.x_sn];
-            if (g.relu) v = (0.0f < v) ? v : 0.0f;
-            g.C[oc + m * g.c_sm + n] = v;
+      for (int ci = 0; ci < NCH; ci++) {
+        const int col0 = colh + ci * 32;
+        if (col0 < g.N) {
+          tc_wait_ld();
+          if (ci + 1 < NCH && col0 + 32 < g.N) tc_ld32(tbase + (ci + 1) * 32, r[(ci + 1) & 1]);
+#pragma unroll
+          for (int j = 0; j < 32; j++) stg[lane * 32 + (j ^ lane)] = __uint_as_float(r[ci & 1][j]);
+          __syncwarp();
+          const int n = col0 + lane;
+          if (n < g.N) {
+            const float xb = x_bcast ? X[(long long)n * g.x_sn] : 0.0f;
+            float *cp = C + (long long)row0 * g.c_sm + n;
+            const float *xp = (X && !x_bcast) ? X + (long long)row0 * g.x_sm + (long long)n * g.x_sn : nullptr;
+#pragma unroll 8
+            for (int rr = 0; rr < 32; rr++) {
+              if (rr < rows) {
+                float v = stg[rr * 32 + (lane ^ rr)];
+                if (xp) v = v + xp[(long long)rr * g.x_sm]; else v = v + xb;
+                if (g.relu) v = (0.0f < v) ? v : 0.0f;
+                cp[(long long)rr * g.c_sm] = v;
+              }
+            }
           }
+          __syncwarp();
         }
-        __syncwarp();
       }
       tc_fence_before_sync();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
@@ -356,6 +376,24 @@ static const void *tc_operand(PbGemmProgram &p, PbTcOperand &cache, const void *
   return dst;
 }
 
+/* A bf16 operand that is already K-major with 16-byte aligned rows is read in
+ * place by TMA; anything else goes through tc_operand. */
+struct TcView { const void *ptr; long long pitch, bpitch; };
+
+static bool tc_in_place(PbGemmProgram &p, const void *buf, long long off, bool is_a, TcView *v) {
+  if (p.dtype != PB_BF16) return false;
+  const bool direct = is_a ? p.a_direct : p.b_direct;
+  const long long sk = is_a ? p.a_sk : p.b_sk, srow = is_a ? p.a_sm : p.b_sn;
+  const long long rows = is_a ? p.M : p.N;
+  if (!direct || (sk != 1 && p.K > 1) || p.b_ax.size() > 1) return false;
+  long long pitch = rows > 1 ? srow : p.K;
+  long long bp = p.b_ax.empty() ? rows * pitch : (is_a ? p.b_ax[0].sa : p.b_ax[0].sb);
+  const char *ptr = (const char *)buf + off * 2;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || pitch % 8 || pitch < p.K || (p.nbatch > 1 && (bp % 8 || bp <= 0))) return false;
+  v->ptr = ptr; v->pitch = pitch; v->bpitch = bp;
+  return true;
+}
+
 int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
   /* output must be a row-major (or column-major: swap roles) matrix per batch entry */
   bool swap = false;
@@ -363,13 +401,20 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
   if (p.K < 16) return PB_TC_UNSUPPORTED;
   const long long Kp = (p.K + 7) & ~7LL;
   void *scr_a = nullptr, *scr_b = nullptr;
-  const void *A = tc_operand(p, p.tc_a, bufs[p.p_a], p.off_a, true, p.M, Kp, stream, &scr_a);
-  const void *B = A ? tc_operand(p, p.tc_b, bufs[p.p_b], p.off_b, false, p.N, Kp, stream, &scr_b) : nullptr;
-  if (!A || !B) { pb_scratch_free(scr_a); return -1; }
+  TcView va, vb;
+  if (!tc_in_place(p, bufs[p.p_a], p.off_a, true, &va)) {
+    va.ptr = tc_operand(p, p.tc_a, bufs[p.p_a], p.off_a, true, p.M, Kp, stream, &scr_a);
+    va.pitch = Kp; va.bpitch = p.M * Kp;
+  }
+  if (va.ptr && !tc_in_place(p, bufs[p.p_b], p.off_b, false, &vb)) {
+    vb.ptr = tc_operand(p, p.tc_b, bufs[p.p_b], p.off_b, false, p.N, Kp, stream, &scr_b);
+    vb.pitch = Kp; vb.bpitch = p.N * Kp;
+  }
+  if (!va.ptr || !vb.ptr) { pb_scratch_free(scr_a); pb_scratch_free(scr_b); return -1; }
 
   TcArgs g{};
   long long rowsA = p.M, rowsB = p.N;
-  if (swap) { std::swap(A, B); std::swap(rowsA, rowsB); }
+  if (swap) { std::swap(va, vb); std::swap(rowsA, rowsB); }
   g.M = (int)rowsA; g.N = (int)rowsB; g.K = (int)p.K;
   g.C = (float *)bufs[p.p_c] + p.off_c;
   g.c_sm = swap ? p.c_sn : p.c_sm;
@@ -378,10 +423,21 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
   g.nb = (int)p.b_ax.size();
   for (int i = 0; i < g.nb; i++) { g.bext[i] = (int)p.b_ax[i].ext; g.c_sb[i] = p.b_ax[i].sc; g.x_sb[i] = p.b_ax[i].sx; }
 
-  const int BN = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
+  /* tile width: fewest waves of work over the SMs, counting a tile's cost as its width plus a fixed part */
+  int BN = 256;
+  {
+    long long best = -1;
+    const long long tm = (g.M + TC_BM - 1) / TC_BM;
+    for (int bn = 64; bn <= 256; bn *= 2) {
+      if (bn > 64 && g.N <= bn / 2) continue;
+      const long long tiles = tm * ((g.N + bn - 1) / bn) * p.nbatch;
+      const long long cost = ((tiles + 147) / 148) * (bn + 48);
+      if (best < 0 || cost < best || (cost == best && bn > BN)) { best = cost; BN = bn; }
+    }
+  }
   CUtensorMap ma, mb;
-  int rc = make_map(&ma, A, p.K, rowsA, p.nbatch, Kp, rowsA * Kp, TC_BM);
-  if (rc == 0) rc = make_map(&mb, B, p.K, rowsB, p.nbatch, Kp, rowsB * Kp, BN);
+  int rc = make_map(&ma, va.ptr, p.K, rowsA, p.nbatch, va.pitch, va.bpitch, TC_BM);
+  if (rc == 0) rc = make_map(&mb, vb.ptr, p.K, rowsB, p.nbatch, vb.pitch, vb.bpitch, BN);
   if (rc != 0) { pb_scratch_free(scr_a); pb_scratch_free(scr_b); return -1; }
   pb_tc_mark_used();
   if (BN == 256) rc = tc_launch<256>(ma, mb, g, p.nbatch, stream);
