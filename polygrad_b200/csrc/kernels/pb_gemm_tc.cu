@@ -37,7 +37,7 @@
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 320
-#define TC_SPIN_LIMIT (1u << 22)
+#define TC_SPIN_LIMIT (1u << 25)
 
 __device__ int pb200_tc_error_flag = 0;
 
@@ -47,6 +47,7 @@ struct TcArgs {
   long long c_sm, x_sm, x_sn;
   int nb; int bext[4]; long long c_sb[4], x_sb[4];
   int has_x, relu;
+  int vec_io;                      /* C rows (and addend rows) 16-byte aligned, N % 4 == 0 */
   int tiles_m, tiles_n, n_tiles;   /* n_tiles = nbatch * tiles_m * tiles_n */
 };
 
@@ -76,6 +77,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
   for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (i > 8) __nanosleep(32);          /* leave the issue slots to the working warps */
     if ((i & 255u) == 255u && *abort_flag) return false;
   }
   *abort_flag = 1;
@@ -249,6 +251,39 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         if (col0 < g.N) {
           tc_wait_ld();
           if (ci + 1 < NCH && col0 + 32 < g.N) tc_ld32(tbase + (ci + 1) * 32, r[(ci + 1) & 1]);
+          if (g.vec_io) {
+            /* rows of C (and of the addend) are 16-byte aligned: 128-bit shared and
+             * global accesses, 16-byte chunks XOR-swizzled by row so that both the
+             * row-per-thread writes and the 4-rows-per-warp reads are conflict-free */
+            float4 *stg4 = reinterpret_cast<float4 *>(stg);
+#pragma unroll
+            for (int c4 = 0; c4 < 8; c4++)
+              stg4[lane * 8 + (c4 ^ (lane & 7))] = make_float4(__uint_as_float(r[ci & 1][c4 * 4]), __uint_as_float(r[ci & 1][c4 * 4 + 1]),
+                                                               __uint_as_float(r[ci & 1][c4 * 4 + 2]), __uint_as_float(r[ci & 1][c4 * 4 + 3]));
+            __syncwarp();
+            const int c4 = lane & 7, rsub = lane >> 3;
+            const int n = col0 + c4 * 4;
+            if (n < g.N) {
+              float4 xb = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (x_bcast) xb = *reinterpret_cast<const float4 *>(X + n);
+              float *cp = C + (long long)(row0 + rsub) * g.c_sm + n;
+              const float *xp = (X && !x_bcast) ? X + (long long)(row0 + rsub) * g.x_sm + n : nullptr;
+              const long long cstep = 4 * g.c_sm, xstep = 4 * g.x_sm;
+#pragma unroll
+              for (int i8 = 0; i8 < 8; i8++) {
+                const int rr = i8 * 4 + rsub;
+                if (rr < rows) {
+                  float4 v = stg4[rr * 8 + (c4 ^ (rr & 7))];
+                  if (xp) { const float4 x4 = *reinterpret_cast<const float4 *>(xp); v.x += x4.x; v.y += x4.y; v.z += x4.z; v.w += x4.w; }
+                  else { v.x += xb.x; v.y += xb.y; v.z += xb.z; v.w += xb.w; }
+                  if (g.relu) { v.x = (0.f < v.x) ? v.x : 0.f; v.y = (0.f < v.y) ? v.y : 0.f; v.z = (0.f < v.z) ? v.z : 0.f; v.w = (0.f < v.w) ? v.w : 0.f; }
+                  *reinterpret_cast<float4 *>(cp) = v;
+                }
+                cp += cstep;
+                if (xp) xp += xstep;
+              }
+            }
+          } else {
 #pragma unroll
           for (int j = 0; j < 32; j++) stg[lane * 32 + (j ^ lane)] = __uint_as_float(r[ci & 1][j]);
           __syncwarp();
@@ -257,15 +292,13 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             const float xb = x_bcast ? X[(long long)n * g.x_sn] : 0.0f;
             float *cp = C + (long long)row0 * g.c_sm + n;
             const float *xp = (X && !x_bcast) ? X + (long long)row0 * g.x_sm + (long long)n * g.x_sn : nullptr;
-#pragma unroll 8
-            for (int rr = 0; rr < 32; rr++) {
-              if (rr < rows) {
-                float v = stg[rr * 32 + (lane ^ rr)];
-                if (xp) v = v + xp[(long long)rr * g.x_sm]; else v = v + xb;
-                if (g.relu) v = (0.0f < v) ? v : 0.0f;
-                cp[(long long)rr * g.c_sm] = v;
-              }
+            for (int rr = 0; rr < rows; rr++) {
+              float v = stg[rr * 32 + (lane ^ rr)];
+              if (xp) v = v + xp[(long long)rr * g.x_sm]; else v = v + xb;
+              if (g.relu) v = (0.0f < v) ? v : 0.0f;
+              cp[(long long)rr * g.c_sm] = v;
             }
+          }
           }
           __syncwarp();
         }
@@ -423,6 +456,16 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
   g.nb = (int)p.b_ax.size();
   for (int i = 0; i < g.nb; i++) { g.bext[i] = (int)p.b_ax[i].ext; g.c_sb[i] = p.b_ax[i].sc; g.x_sb[i] = p.b_ax[i].sx; }
 
+  {
+    auto al = [](const void *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+    bool v = al(g.C) && (g.c_sm % 4 == 0) && (g.N % 4 == 0);
+    for (int i = 0; i < g.nb; i++) if (g.c_sb[i] % 4) v = false;
+    if (g.has_x) {
+      if (g.x_sn != 1 || g.x_sm % 4 || !al(g.X)) v = false;
+      for (int i = 0; i < g.nb; i++) if (g.x_sb[i] % 4) v = false;
+    }
+    g.vec_io = v ? 1 : 0;
+  }
   /* tile width: fewest waves of work over the SMs, counting a tile's cost as its width plus a fixed part */
   int BN = 256;
   {
