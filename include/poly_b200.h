@@ -105,6 +105,26 @@ int poly_b200_gemm(long long M, long long N, long long K,
                    const void *B, long long b_sk, long long b_sn,
                    float *C, long long c_sm, const float *bias, int relu, int operands_bf16);
 
+/* No counterpart in polygrad.  The same bf16 tensor-core contraction as
+ * poly_b200_gemm under the bf16 policy (float32 operands rounded to bfloat16,
+ * fp32 products and sums), for callers that cannot let the library allocate:
+ * inside a stream capture, in a process whose device memory is fully committed,
+ * or where a driver allocation's implicit synchronisation is not acceptable.
+ * It calls no cudaMalloc / cudaFree and does not touch the runtime's pool; the
+ * converted operands go into a fixed array of POLY_B200_NOALLOC_SCRATCH_BYTES
+ * that belongs to the library image (each GPU that loads the library holds it
+ * until the process exits).  Sizes with (M + N) * roundup8(K) * 2 bytes beyond
+ * that are rejected with -1 and a message.  The first call on a device looks up
+ * the array's device address; make that call before any stream capture.  All
+ * calls share the array: calls that overlap on the GPU (different streams or
+ * processes sharing a context) race; on the library's single stream they do not.
+ * K >= 16. */
+#define POLY_B200_NOALLOC_SCRATCH_BYTES (32u << 20)
+int poly_b200_gemm_noalloc(long long M, long long N, long long K,
+                           const float *A, long long a_sm, long long a_sk,
+                           const float *B, long long b_sk, long long b_sn,
+                           float *C, long long c_sm, const float *bias, int relu);
+
 /* Wait for all enqueued work.  0 / -1. */
 int  poly_b200_synchronize(void);
 

@@ -54,6 +54,12 @@ struct PbGemmProgram : PbAotProgram {
 /* Tensor-core path: returns 0 / -1, or PB_TC_UNSUPPORTED when the shape is not handled. */
 int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream);
 
+/* The tensor-core kernel on ready-made bfloat16 K-major operands; touches no
+ * memory beyond its arguments. */
+int pb_gemm_tc_launch_raw(const void *a_bf16, long long a_pitch, const void *b_bf16, long long b_pitch,
+                          float *C, long long c_sm, long long M, long long N, long long K,
+                          const float *bias, int relu, cudaStream_t stream);
+
 /* POLY_B200_GEMM=bf16: run fp32 contractions with operands rounded to bf16
  * (round-to-nearest-even), products and sums in fp32, on the tensor cores. */
 bool pb_gemm_policy_bf16(void);

@@ -491,3 +491,28 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
   pb_scratch_free(scr_a); pb_scratch_free(scr_b);
   return rc;
 }
+
+
+/* Runs the tensor-core kernel on operands that are already bfloat16, K-major
+ * ([rows][pitch], pitch a multiple of 8 elements, 16-byte aligned base).  Uses no
+ * memory beyond its arguments. */
+int pb_gemm_tc_launch_raw(const void *a_bf16, long long a_pitch, const void *b_bf16, long long b_pitch,
+                          float *C, long long c_sm, long long M, long long N, long long K,
+                          const float *bias, int relu, cudaStream_t stream) {
+  TcArgs g{};
+  g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.C = C; g.c_sm = c_sm;
+  g.has_x = bias ? 1 : 0; g.relu = relu ? 1 : 0;
+  g.X = bias; g.x_sm = 0; g.x_sn = 1;
+  g.nb = 0;
+  g.vec_io = ((reinterpret_cast<uintptr_t>(C) & 15) == 0 && c_sm % 4 == 0 && N % 4 == 0 &&
+              (!bias || (reinterpret_cast<uintptr_t>(bias) & 15) == 0)) ? 1 : 0;
+  const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  CUtensorMap ma, mb;
+  if (make_map(&ma, a_bf16, K, M, 1, a_pitch, M * a_pitch, TC_BM) != 0) return -1;
+  if (make_map(&mb, b_bf16, K, N, 1, b_pitch, N * b_pitch, BN) != 0) return -1;
+  pb_tc_mark_used();
+  if (BN == 256) return tc_launch<256>(ma, mb, g, 1, stream);
+  if (BN == 128) return tc_launch<128>(ma, mb, g, 1, stream);
+  return tc_launch<64>(ma, mb, g, 1, stream);
+}

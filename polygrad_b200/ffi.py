@@ -144,6 +144,7 @@ def _declare_cuda(lib):
     LL = ctypes.c_longlong
     _sig(lib, 'poly_b200_gemm', ctypes.c_int, [LL, LL, LL, _ptr, LL, LL, _ptr, LL, LL, _ptr, LL, _ptr,
                                                ctypes.c_int, ctypes.c_int])
+    _sig(lib, 'poly_b200_gemm_noalloc', ctypes.c_int, [LL, LL, LL, _ptr, LL, LL, _ptr, LL, LL, _ptr, LL, _ptr, ctypes.c_int])
     _sig(lib, 'poly_b200_set_gemm_policy', None, [ctypes.c_int])
     _sig(lib, 'poly_b200_gemm_policy', ctypes.c_int, [])
     _sig(lib, 'poly_b200_host_alloc', _ptr, [S])

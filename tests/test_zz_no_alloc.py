@@ -1,0 +1,67 @@
+"""poly_b200_gemm_noalloc: the bf16 tensor-core contraction for callers that
+cannot allocate device memory (inside a stream capture, with device memory
+fully committed elsewhere, or where a driver allocation's implicit
+synchronisation is unacceptable).  Its scratch is a fixed array inside the
+library instead of pool memory.
+
+Checked against the allocating entry point poly_b200_gemm on the same inputs,
+on two calls in a row with different operands (the shared scratch keeps the
+previous call's contents), and for the size limit.  Runs last so that a failure
+here cannot hide the other tests' results."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(lib, a):
+    d = lib.poly_cuda_alloc(a.nbytes)
+    assert d
+    assert lib.poly_cuda_copy_htod(d, a.ctypes.data, a.nbytes) == 0
+    return d
+
+
+def _run(lib, fn_name, a, b, bias, relu):
+    m, k = a.shape
+    n = b.shape[1]
+    da, db, dx = _dev(lib, a), _dev(lib, b), _dev(lib, bias)
+    dc = lib.poly_cuda_alloc(m * n * 4)
+    if fn_name == 'poly_b200_gemm':
+        rc = lib.poly_b200_gemm(m, n, k, da, k, 1, db, n, 1, dc, n, dx, relu, 0)
+    else:
+        rc = lib.poly_b200_gemm_noalloc(m, n, k, da, k, 1, db, n, 1, dc, n, dx, relu)
+    assert rc == 0, lib.last_error()
+    out = np.empty((m, n), np.float32)
+    assert lib.poly_cuda_copy_dtoh(out.ctypes.data, dc, out.nbytes) == 0
+    for d in (da, db, dx, dc):
+        lib.poly_cuda_free(d)
+    return out
+
+
+def test_noalloc_matches_allocating_entry_twice(gpu):
+    gpu.poly_b200_set_gemm_policy(1)
+    try:
+        for call, (m, n, k) in enumerate([(300, 200, 136), (512, 768, 256)]):
+            rng = np.random.default_rng(100 + call)
+            a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+            b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+            bias = rng.uniform(-1, 1, n).astype(np.float32)
+            want = _run(gpu, 'poly_b200_gemm', a, b, bias, call)
+            got = _run(gpu, 'poly_b200_gemm_noalloc', a, b, bias, call)
+            assert np.abs(want).max() > 0
+            assert_close(got, want, 1e-4, f'call {call}')
+    finally:
+        gpu.poly_b200_set_gemm_policy(0)
+
+
+def test_noalloc_rejects_sizes_beyond_the_array(gpu):
+    # (M + N) * K * 2 bytes = 3 * 8192 * 2048 * 2 > 32 MiB; the pointers are never touched
+    d = gpu.poly_cuda_alloc(64)
+    rc = gpu.poly_b200_gemm_noalloc(16384, 8192, 2048, d, 2048, 1, d, 8192, 1, d, 8192, None, 0)
+    gpu.poly_cuda_free(d)
+    assert rc == -1
+    assert 'scratch' in gpu.last_error()
