@@ -105,6 +105,15 @@ int poly_b200_gemm(long long M, long long N, long long K,
                    const void *B, long long b_sk, long long b_sn,
                    float *C, long long c_sm, const float *bias, int relu, int operands_bf16);
 
+/* out[b,h,t,:] = softmax_k(q[b,t,h,:] . k[b,k,h,:] * scale + mask[t,k]) . v[b,k,h,:]
+ * as one kernel (the T x T scores never reach memory): the arithmetic of the
+ * six-kernel chain polygrad's GPT-2 builder schedules
+ * (src/modelzoo/models/gpt2.c:402-434) under the bf16 contraction policy.
+ * q, k, v float32 [B][T][H][64]; mask float32 [T][T]; out float32 [B][H][T][64].
+ * Head size 64, T a multiple of 128.  Stream-ordered; 0 / -1. */
+int poly_b200_attention(const float *q, const float *k, const float *v, const float *mask, float scale,
+                        float *out, int B, int H, int T);
+
 /* No counterpart in polygrad.  The same bf16 tensor-core contraction as
  * poly_b200_gemm under the bf16 policy (float32 operands rounded to bfloat16,
  * fp32 products and sums), for callers that cannot let the library allocate:

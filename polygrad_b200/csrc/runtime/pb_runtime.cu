@@ -207,7 +207,8 @@ void pb_tc_mark_used(void) { g_tc_used = true; }
 static int check_device_flags(void) {
   if (!g_tc_used) return 0;
   int code = pb_gemm_tc_error();
-  if (code != 0) { pb_set_error("tensor-core gemm: a barrier wait ran out (code %d); results are invalid", code); return -1; }
+  if (code == 0) code = pb_attention_error();
+  if (code != 0) { pb_set_error("tensor-core kernel: a barrier wait ran out (code %d); results are invalid", code); return -1; }
   return 0;
 }
 

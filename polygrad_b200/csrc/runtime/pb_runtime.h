@@ -53,6 +53,7 @@ uint64_t pb_buffer_version(const void *p);      /* changes whenever p's allocati
 /* The tensor-core kernel bounds its barrier waits and records a code when one
  * runs out; the runtime reads it back at synchronisation points. */
 int  pb_gemm_tc_error(void);                    /* 0 = none, >0 = which wait gave up, <0 = cannot read */
+int  pb_attention_error(void);
 void pb_tc_mark_used(void);
 
 #endif

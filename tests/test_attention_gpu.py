@@ -1,0 +1,67 @@
+"""The fused attention kernel (poly_b200_attention) against the arithmetic of
+polygrad's six-kernel attention chain (src/modelzoo/models/gpt2.c:402-434),
+restated in numpy: scores = q.k^T; x = scores*scale + mask; softmax over keys;
+out = p.v.  The kernel rounds q, k, v and p to bf16 for its two contractions
+(the bf16 contraction policy).  Against a reference that rounds q, k, v the same
+way the bound is 1e-2 (what is left is the bf16 rounding of p and summation
+order); against the unrounded fp32 chain it is 4e-2: two chained bf16
+contractions, each within the policy's 2e-2.  The end-to-end bound on logits
+(2e-2) is checked in test_models_gpu.py."""
+import numpy as np
+import pytest
+
+from conftest import assert_close
+from polygrad_b200.tensor import f32_to_bf16_bits
+
+pytestmark = pytest.mark.gpu
+
+
+def bf16(a):
+    return (f32_to_bf16_bits(a).astype(np.uint32) << 16).view(np.float32).reshape(a.shape)
+
+
+def reference(q, k, v, mask, scale):
+    s = np.einsum('bthd,bkhd->bhtk', q.astype(np.float64), k.astype(np.float64)) * scale + mask[None, None]
+    s = s - s.max(-1, keepdims=True)
+    p = np.exp(s)
+    p = p / p.sum(-1, keepdims=True)
+    return np.einsum('bhtk,bkhd->bhtd', p, v.astype(np.float64)).astype(np.float32)
+
+
+def run(lib, q, k, v, mask, scale):
+    B, T, H, hd = q.shape
+    ptrs = []
+    for a in (q, k, v, mask):
+        d = lib.poly_cuda_alloc(a.nbytes)
+        assert lib.poly_cuda_copy_htod(d, a.ctypes.data, a.nbytes) == 0
+        ptrs.append(d)
+    out = np.empty((B, H, T, hd), np.float32)
+    do = lib.poly_cuda_alloc(out.nbytes)
+    rc = lib.poly_b200_attention(ptrs[0], ptrs[1], ptrs[2], ptrs[3], scale, do, B, H, T)
+    assert rc == 0, lib.last_error()
+    assert lib.poly_cuda_copy_dtoh(out.ctypes.data, do, out.nbytes) == 0, lib.last_error()
+    for d in ptrs + [do]:
+        lib.poly_cuda_free(d)
+    return out
+
+
+@pytest.mark.parametrize('B,H,T', [(1, 1, 128), (2, 3, 256), (1, 2, 1024)])
+@pytest.mark.parametrize('causal', [True, False], ids=['causal', 'dense'])
+def test_attention_matches_chain(gpu, B, H, T, causal):
+    rng = np.random.default_rng([B, H, T, int(causal)])
+    q, k, v = (rng.standard_normal((B, T, H, 64)).astype(np.float32) for _ in range(3))
+    ar = np.arange(T, dtype=np.float32)
+    if causal:
+        mask = np.where(ar[:, None] < ar[None, :], np.float32(-1e9), np.float32(0)).astype(np.float32)
+    else:
+        mask = rng.standard_normal((T, T)).astype(np.float32)
+    scale = np.float32(1.0 / 8.0)
+    got = run(gpu, q, k, v, mask, scale)
+    assert_close(got, reference(q, k, v, mask, scale), 4e-2, 'vs fp32 chain')
+    assert_close(got, reference(bf16(q), bf16(k), bf16(v), mask, scale), 1e-2, 'vs chain on bf16-rounded q, k, v')
+
+
+def test_attention_rejects_unsupported_length(gpu):
+    d = gpu.poly_cuda_alloc(64)
+    assert gpu.poly_b200_attention(d, d, d, d, 1.0, d, 1, 1, 100) == -1
+    gpu.poly_cuda_free(d)
