@@ -36,7 +36,7 @@ static void slot_usage(const PbPlan *p, SlotUse *u) {
 /* Is this step `out[i] = in[i]` over all of two equally sized buffers?  Returns
  * the parameter positions of out and in. */
 static bool is_identity_copy(const PbStep *st, int *p_out, int *p_in) {
-  if (st->precompiled || st->n_params != 2 || st->n_vars) return false;
+  if (st->precompiled || st->fused_rows || st->n_params != 2 || st->n_vars) return false;
   PbKern k;
   if (pb_kern_build(&k, st->sink) != 0) { pb_kern_free(&k); return false; }
   bool ok = false;
@@ -94,7 +94,7 @@ static int elide_copies(PbPlan *p) {
  * affine kernel around them that is 3-4 passes over the tensor, here one. */
 #define CHAIN_MAX 8
 
-static bool step_fusable(const PbStep *st) { return !st->dead && !st->precompiled && st->n_vars == 0 && st->sink; }
+static bool step_fusable(const PbStep *st) { return !st->dead && !st->precompiled && !st->fused_rows && st->n_vars == 0 && st->sink; }
 
 static bool step_reads(const PbPlan *p, const PbStep *st, int slot) {
   for (int a = 0; a < st->n_params; a++)
@@ -192,7 +192,9 @@ static int fuse_rows(PbPlan *p) {
     if (!prog) { free(text); continue; }
     PbStep *fs = &p->steps[f];
     poly_cuda_program_destroy(fs->prog); free(fs->text);
-    fs->prog = prog; fs->text = text; fs->sink = NULL;
+    fs->prog = prog; fs->text = text;
+    fs->fused_rows = true; fs->n_chain = no;
+    for (int j = 0; j < no; j++) fs->chain[j] = order[j];
     fs->n_params = fo.n_params;
     for (int a = 0; a < fo.n_params; a++) { fs->slot[a] = fo.slot[a]; fs->rw[a] = fo.rw[a]; }
     fs->rw[fo.n_params] = 0;
@@ -203,10 +205,221 @@ static int fuse_rows(PbPlan *p) {
   return fused;
 }
 
+/* ── attention ───────────────────────────────────────────────────────── */
+/* scores = q.kT  ->  softmax(scores*scale + mask)  ->  out = p.v, where the
+ * middle is a row-fused chain of exactly the four kernels polygrad's GPT-2
+ * builder and poly_softmax produce (reference: src/modelzoo/models/gpt2.c:
+ * 402-434, src/frontend.c:1131-1159), nothing else reads scores or p, and the
+ * bf16 contraction policy is on.  The three steps become one (pb_attention.cu). */
+static const char *hdr_line(const char *text, const char *key, char *buf, size_t cap) {
+  size_t kl = strlen(key);
+  for (const char *p = text; p && p[0] == '/' && p[1] == '/'; ) {
+    const char *eol = strchr(p, '\n');
+    size_t len = eol ? (size_t)(eol - p) : strlen(p);
+    if (len >= 2 + kl && strncmp(p + 2, key, kl) == 0 && (len == 2 + kl || p[2 + kl] == ' ')) {
+      size_t vl = len > 3 + kl ? len - 3 - kl : 0;
+      if (vl >= cap) vl = cap - 1;
+      memcpy(buf, p + 3 + kl, vl); buf[vl] = 0;
+      return buf;
+    }
+    if (!eol) break;
+    p = eol + 1;
+  }
+  return NULL;
+}
+
+typedef struct { char kind; long long ext, sc, sa, sb, sx; } GAxis;
+typedef struct { int params[4]; int relu; char dtype[8]; GAxis ax[16]; int nax; } GHdr;
+
+static bool parse_gemm_hdr(const char *text, GHdr *g) {
+  char buf[256];
+  if (!hdr_line(text, "kind", buf, sizeof buf) || strcmp(buf, "gemm") != 0) return false;
+  if (!hdr_line(text, "params", buf, sizeof buf) || sscanf(buf, "%d %d %d %d", &g->params[0], &g->params[1], &g->params[2], &g->params[3]) != 4) return false;
+  if (!hdr_line(text, "relu", buf, sizeof buf)) return false;
+  g->relu = atoi(buf);
+  if (!hdr_line(text, "dtype", buf, sizeof buf)) return false;
+  snprintf(g->dtype, sizeof g->dtype, "%s", buf);
+  if (!hdr_line(text, "naxes", buf, sizeof buf)) return false;
+  g->nax = atoi(buf);
+  if (g->nax > 16) return false;
+  for (int i = 0; i < g->nax; i++) {
+    char key[16]; snprintf(key, sizeof key, "axis%d", i);
+    if (!hdr_line(text, key, buf, sizeof buf)) return false;
+    if (sscanf(buf, "%c %lld %lld %lld %lld %lld", &g->ax[i].kind, &g->ax[i].ext, &g->ax[i].sc, &g->ax[i].sa, &g->ax[i].sb, &g->ax[i].sx) != 6) return false;
+  }
+  return true;
+}
+
+static bool u_const_near(PolyUOp *u, double v, double rel) {
+  if (u->op != POLY_OP_CONST || u->arg.kind != POLY_ARG_FLOAT) return false;
+  double d = u->arg.f - v; if (d < 0) d = -d;
+  return d <= rel * (v < 0 ? -v : v);
+}
+static bool u_load_of(PolyUOp *u, int param) {
+  return u->op == POLY_OP_LOAD && u->src[0]->op == POLY_OP_INDEX && u->src[0]->n_src == 2 &&
+         u->src[0]->src[0]->op == POLY_OP_PARAM && (int)u->src[0]->src[0]->arg.i == param;
+}
+static int kern_param_of_slot(const PbPlan *p, const PbStep *st, int slot) {
+  for (int a = 0; a < st->n_params; a++) if (pb_plan_resolve(p, st->slot[a]) == slot) return a;
+  return -1;
+}
+/* exp2((x - m) * log2e) with x, m loads of the given parameters */
+static bool u_is_shifted_exp(PolyUOp *u, int px, int pm) {
+  if (u->op != POLY_OP_EXP2) return false;
+  PolyUOp *m = u->src[0];
+  if (m->op != POLY_OP_MUL) return false;
+  PolyUOp *d = NULL;
+  if (u_const_near(m->src[1], 1.4426950408889634, 1e-6)) d = m->src[0];
+  else if (u_const_near(m->src[0], 1.4426950408889634, 1e-6)) d = m->src[1];
+  if (!d || d->op != POLY_OP_SUB) return false;
+  return u_load_of(d->src[0], px) && u_load_of(d->src[1], pm);
+}
+
+#define ABRK { if (getenv("POLY_B200_DEBUG")) fprintf(stderr, "pb_fuse: attention candidate rejected at line %d\n", __LINE__); break; }
+static int fuse_attention(PbPlan *p) {
+  if (!poly_b200_gemm_policy()) return 0;
+  int fused = 0;
+  SlotUse *u = malloc(sizeof(SlotUse) * (size_t)p->n_slots);
+  for (int r = 0; r < p->n_steps; r++) {
+    PbStep *R = &p->steps[r];
+    if (R->dead || !R->fused_rows || R->n_chain != 4) continue;
+    slot_usage(p, u);
+    PbStep *E = &p->steps[R->chain[0]], *MX = &p->steps[R->chain[1]], *SM = &p->steps[R->chain[2]], *NM = R;
+    if (!E->sink || !MX->sink || !SM->sink || !NM->sink) continue;
+    PbKern ke, kmx, ksm, knm;
+    bool b1 = pb_kern_build(&ke, E->sink) == 0, b2 = pb_kern_build(&kmx, MX->sink) == 0;
+    bool b3 = pb_kern_build(&ksm, SM->sink) == 0, b4 = pb_kern_build(&knm, NM->sink) == 0;
+    char *text = NULL; int g1i = -1, g2i = -1;
+    int slots5[5] = {-1, -1, -1, -1, -1}; char outmode = 'w';
+    do {
+      if (!(b1 && b2 && b3 && b4)) ABRK;
+      if (ke.n_stores != 1 || kmx.n_stores != 1 || ksm.n_stores != 1 || knm.n_stores != 1) ABRK;
+      if (ke.n_reduce_nodes != 0 || kmx.n_reduce_nodes != 1 || ksm.n_reduce_nodes != 1 || knm.n_reduce_nodes != 0) ABRK;
+      /* items of the original schedule give the slots of each kernel's own parameters */
+      const PolySchedule *sched = p->base.schedule;
+      const int *se = sched->items[E->item].buf_slot_indices, *smx = sched->items[MX->item].buf_slot_indices;
+      const int *ssm = sched->items[SM->item].buf_slot_indices, *snm = sched->items[NM->item].buf_slot_indices;
+      #define SLOT(arr, i) pb_plan_resolve(p, (arr)[i])
+      int x_slot = SLOT(se, ke.stores[0].param), mx_slot = SLOT(smx, kmx.stores[0].param);
+      int sm_slot = SLOT(ssm, ksm.stores[0].param), p_slot = SLOT(snm, knm.stores[0].param);
+      /* E: x = s * scale + mask */
+      PolyUOp *ev = ke.stores[0].value;
+      if (ev->op != POLY_OP_ADD) ABRK;
+      PolyUOp *mul = NULL, *mload = NULL;
+      if (ev->src[0]->op == POLY_OP_MUL && ev->src[1]->op == POLY_OP_LOAD) { mul = ev->src[0]; mload = ev->src[1]; }
+      else if (ev->src[1]->op == POLY_OP_MUL && ev->src[0]->op == POLY_OP_LOAD) { mul = ev->src[1]; mload = ev->src[0]; }
+      else ABRK;
+      PolyUOp *sload = NULL, *cst = NULL;
+      if (mul->src[0]->op == POLY_OP_LOAD && mul->src[1]->op == POLY_OP_CONST) { sload = mul->src[0]; cst = mul->src[1]; }
+      else if (mul->src[1]->op == POLY_OP_LOAD && mul->src[0]->op == POLY_OP_CONST) { sload = mul->src[1]; cst = mul->src[0]; }
+      else ABRK;
+      if (cst->arg.kind != POLY_ARG_FLOAT || sload->src[0]->n_src != 2 || mload->src[0]->n_src != 2) ABRK;
+      if (sload->src[0]->src[1] != ke.stores[0].index->src[1]) ABRK;          /* s read where x is written */
+      int ps = (int)sload->src[0]->src[0]->arg.i, pmask = (int)mload->src[0]->src[0]->arg.i;
+      int s_slot = SLOT(se, ps), mask_slot = SLOT(se, pmask);
+      if (s_slot == mask_slot || !p->slot_inter[s_slot] || !p->slot_inter[p_slot]) ABRK;
+      /* MAX, SUM, NORM: the softmax of x */
+      PolyUOp *rmx = kmx.stores[0].value, *rsm = ksm.stores[0].value, *nv = knm.stores[0].value;
+      if (rmx->op != POLY_OP_REDUCE || rmx->n_src != 2 || !u_load_of(rmx->src[0], kern_param_of_slot(p, MX, x_slot))) ABRK;
+      if ((rmx->arg.kind == POLY_ARG_OPS ? rmx->arg.ops : (PolyOps)rmx->arg.i) != POLY_OP_MAX) ABRK;
+      if (rsm->op != POLY_OP_REDUCE || rsm->n_src != 2 || (rsm->arg.kind == POLY_ARG_OPS ? rsm->arg.ops : (PolyOps)rsm->arg.i) != POLY_OP_ADD) ABRK;
+      {
+        int px = -1, pm = -1;
+        for (int a = 0; a < ksm.n_params; a++) { if (SLOT(ssm, a) == x_slot) px = a; if (SLOT(ssm, a) == mx_slot) pm = a; }
+        if (px < 0 || pm < 0 || !u_is_shifted_exp(rsm->src[0], px, pm)) ABRK;
+        px = pm = -1; int pz = -1;
+        for (int a = 0; a < knm.n_params; a++) { if (SLOT(snm, a) == x_slot) px = a; if (SLOT(snm, a) == mx_slot) pm = a; if (SLOT(snm, a) == sm_slot) pz = a; }
+        if (px < 0 || pm < 0 || pz < 0 || nv->op != POLY_OP_FDIV || !u_is_shifted_exp(nv->src[0], px, pm) || !u_load_of(nv->src[1], pz)) ABRK;
+      }
+      /* producers and consumers */
+      if (u[s_slot].writers != 1 || u[p_slot].writers != 1) ABRK;
+      g1i = u[s_slot].first_write;
+      int readers_p = 0;
+      for (int s2 = 0; s2 < p->n_steps; s2++) if (!p->steps[s2].dead && step_reads(p, &p->steps[s2], p_slot)) { readers_p++; g2i = s2; }
+      if (readers_p != 1 || g2i <= r || g1i >= R->chain[0]) ABRK;
+      PbStep *G1 = &p->steps[g1i], *G2 = &p->steps[g2i];
+      if (G1->dead || G2->dead || !G1->precompiled || !G2->precompiled) ABRK;
+      GHdr h1, h2;
+      if (!parse_gemm_hdr(G1->text, &h1) || !parse_gemm_hdr(G2->text, &h2)) ABRK;
+      if (strcmp(h1.dtype, "f32") || strcmp(h2.dtype, "f32") || h1.relu || h2.relu || h1.params[3] >= 0 || h2.params[3] >= 0) ABRK;
+      if (pb_plan_resolve(p, G1->slot[h1.params[0]]) != s_slot || pb_plan_resolve(p, G2->slot[h2.params[1]]) != p_slot) ABRK;
+      /* mask strides: E's ranges named by their stride in the scores */
+      uint64_t all = 0;
+      for (int q = 0; q < ke.n_ranges; q++) all |= (uint64_t)1 << q;
+      PbAffine xs, ms;
+      pb_fit_affine(&ke, ke.stores[0].index->src[1], all, &xs);
+      pb_fit_affine(&ke, mload->src[0]->src[1], all, &ms);
+      if (!xs.ok || !ms.ok) ABRK;
+      long long c_sm = -1;
+      for (int i = 0; i < h1.nax; i++) if (h1.ax[i].kind == 'm') c_sm = h1.ax[i].sc;
+      long long msq = 0, msk = 0; bool okm = c_sm > 1;
+      for (int q = 0; q < ke.n_ranges && okm; q++) {
+        if (ke.extent[q] <= 1) continue;
+        if (xs.stride[q] == c_sm) msq = ms.stride[q];
+        else if (xs.stride[q] == 1) msk = ms.stride[q];
+        else if (ms.stride[q] != 0) okm = false;           /* mask varies over batch or head */
+      }
+      if (!okm) ABRK;
+      /* nothing between the first contraction and the second may overwrite q, k or the mask */
+      int q_slot = pb_plan_resolve(p, G1->slot[h1.params[1]]), k_slot = pb_plan_resolve(p, G1->slot[h1.params[2]]);
+      int v_slot = pb_plan_resolve(p, G2->slot[h2.params[2]]), o_slot = pb_plan_resolve(p, G2->slot[h2.params[0]]);
+      bool hazard = false;
+      for (int s2 = g1i + 1; s2 < g2i && !hazard; s2++) {
+        if (p->steps[s2].dead) continue;
+        /* q and k were read at the first contraction, the mask at the scale+mask kernel; all are now read later */
+        if (step_writes(p, &p->steps[s2], q_slot) || step_writes(p, &p->steps[s2], k_slot) ||
+            (s2 > R->chain[0] && step_writes(p, &p->steps[s2], mask_slot)) ||
+            step_reads(p, &p->steps[s2], o_slot) || step_writes(p, &p->steps[s2], o_slot)) hazard = true;
+        if (s2 != R->chain[0] && s2 != r && step_reads(p, &p->steps[s2], s_slot)) hazard = true;
+      }
+      if (hazard || u[s_slot].readers != 1) ABRK;
+      if (o_slot == q_slot || o_slot == k_slot || o_slot == v_slot || o_slot == mask_slot) ABRK;
+      /* program text: both contraction headers under prefixes */
+      PbStr t; pb_str_init(&t);
+      float scale = (float)cst->arg.f; unsigned bits; memcpy(&bits, &scale, 4);
+      outmode = G2->rw[h2.params[0]] == 'W' ? 'W' : 'w';
+      pb_str_printf(&t, "//PB200 1\n//kind attn\n//scale %08x\n//mask %lld %lld %lld\n//outmode %c\n", bits, (long long)ms.offset, msq, msk, outmode);
+      for (int which = 0; which < 2; which++) {
+        const char *src = which ? G2->text : G1->text;
+        for (const char *q = src; q && q[0] == '/' && q[1] == '/'; ) {
+          const char *eol = strchr(q, '\n');
+          size_t len = eol ? (size_t)(eol - q) : strlen(q);
+          if (strncmp(q, "//PB200", 7) != 0 && strncmp(q, "//kind", 6) != 0)
+            pb_str_printf(&t, "//g%d.%.*s\n", which + 1, (int)(len - 2), q + 2);
+          if (!eol) ABRK;
+          q = eol + 1;
+        }
+      }
+      text = pb_str_take(&t);
+      slots5[0] = q_slot; slots5[1] = k_slot; slots5[2] = v_slot; slots5[3] = mask_slot; slots5[4] = o_slot;
+      #undef SLOT
+    } while (0);
+    if (b1) pb_kern_free(&ke); else pb_kern_free(&ke);
+    pb_kern_free(&kmx); pb_kern_free(&ksm); pb_kern_free(&knm);
+    if (!text) continue;
+    char name[64]; snprintf(name, sizeof name, "attention_k%d", p->steps[g2i].item);
+    if (getenv("POLY_DUMP_KERNELS")) fprintf(stderr, "=== CUDA KERNEL %s ===\n%s\n=== END ===\n", name, text);
+    PolyCudaProgram *prog = poly_compile_cuda(text, name);
+    if (!prog) { free(text); continue; }
+    PbStep *G2 = &p->steps[g2i];
+    poly_cuda_program_destroy(G2->prog); free(G2->text);
+    G2->prog = prog; G2->text = text; G2->n_params = 5; G2->precompiled = 1;
+    for (int a = 0; a < 5; a++) G2->slot[a] = slots5[a];
+    memcpy(G2->rw, "rrrr", 4); G2->rw[4] = outmode; G2->rw[5] = 0;
+    p->steps[g1i].dead = true; R->dead = true;
+    fused++;
+  }
+  free(u);
+  return fused;
+}
+
 void pb_plan_fuse(PbPlan *p) {
   int copies = elide_copies(p);
   int rows = 0;
   const char *e = getenv("POLY_B200_FUSE");
   if (!e || strcmp(e, "copies") != 0) rows = fuse_rows(p);
-  if (getenv("POLY_B200_DEBUG")) fprintf(stderr, "pb_fuse: %d copy kernels elided, %d kernels folded into row kernels\n", copies, rows);
+  int attn = 0;
+  if (!e || (strcmp(e, "copies") != 0 && strcmp(e, "rows") != 0)) attn = fuse_attention(p);
+  if (getenv("POLY_B200_DEBUG"))
+    fprintf(stderr, "pb_fuse: %d copy kernels elided, %d kernels folded into row kernels, %d attention chains fused\n", copies, rows, attn);
 }

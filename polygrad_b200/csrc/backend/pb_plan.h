@@ -23,6 +23,8 @@ typedef struct {
   char rw[PB_MAX_PARAMS + 1];    /* 'r' read, 'w' partly written, 'W' wholly overwritten, 'b' both, '-' unused */
   int precompiled;
   bool dead;
+  bool fused_rows;               /* program is a row-fused chain; chain[] lists the member steps, this one last */
+  int chain[8], n_chain;
   unsigned long long dptr[PB_MAX_PARAMS];
   void *argv[PB_MAX_PARAMS];
 } PbStep;

@@ -335,3 +335,63 @@ extern "C" int poly_b200_attention(const float *q, const float *k, const float *
   pb_scratch_free(qb); pb_scratch_free(kb); pb_scratch_free(vb);
   return rc;
 }
+
+
+/* ── plan program: a recognised attention chain ──────────────────────── */
+/* Header: "//kind attn", the two contractions of the chain under the key
+ * prefixes "g1." (scores = q.kᵀ) and "g2." (out = p.v), the scale constant and
+ * the mask's offset and strides.  Parameters: q, k, v, mask, out. */
+struct AttnProgram : PbAotProgram {
+  PbGemmProgram *g1 = nullptr, *g2 = nullptr;
+  float scale = 1.0f;
+  long long mask_off = 0, mask_sq = 0, mask_sk = 0;
+  long long T = 0, BH = 0;
+  ~AttnProgram() override { delete g1; delete g2; }
+  int n_launches() const override { return 4; }
+  int launch(void *const *bufs, cudaStream_t stream) override {
+    const size_t bytes = (size_t)BH * T * AT_HD * 2;
+    void *qb = pb_scratch_alloc(bytes), *kb = pb_scratch_alloc(bytes), *vb = pb_scratch_alloc(bytes);
+    int rc = -1;
+    if (qb && kb && vb) {
+      rc = g1->pack_into(qb, bufs[0], g1->off_a, true, PB_F32, PB_BF16, AT_HD, stream);
+      if (rc == 0) rc = g1->pack_into(kb, bufs[1], g1->off_b, false, PB_F32, PB_BF16, AT_HD, stream);
+      if (rc == 0) rc = g2->pack_into(vb, bufs[2], g2->off_b, false, PB_F32, PB_BF16, T, stream);
+      int bext[4]; long long o_sb[4];
+      const int nb = (int)g2->b_ax.size();
+      for (int i = 0; i < nb; i++) { bext[i] = (int)g2->b_ax[i].ext; o_sb[i] = g2->b_ax[i].sc; }
+      if (rc == 0)
+        rc = pb_attention_launch(qb, kb, vb, (const float *)bufs[3] + mask_off, mask_sq, mask_sk, scale,
+                                 (float *)bufs[4] + g2->off_c, nb, bext, o_sb, g2->c_sm, BH, T, stream);
+    } else pb_set_error("attention: out of scratch memory");
+    pb_scratch_free(qb); pb_scratch_free(kb); pb_scratch_free(vb);
+    return rc;
+  }
+};
+
+PbAotProgram *pb_make_attn(const PbHeader &h, std::string &err) {
+  AttnProgram *p = new AttnProgram();
+  p->g1 = pb_parse_gemm(h, "g1.", err);
+  p->g2 = p->g1 ? pb_parse_gemm(h, "g2.", err) : nullptr;
+  if (!p->g1 || !p->g2) { delete p; return nullptr; }
+  PbGemmProgram &a = *p->g1, &b = *p->g2;
+  bool ok = a.dtype == PB_F32 && b.dtype == PB_F32 && !a.has_x && !b.has_x && !a.relu && !b.relu;
+  ok = ok && a.K == AT_HD && a.M == a.N && b.K == a.N && b.M == a.M && b.N == AT_HD && a.nbatch == b.nbatch;
+  ok = ok && pb_attention_supported(a.M, a.K) && b.c_sn == 1 && b.c_sm % 4 == 0 && a.b_ax.size() == b.b_ax.size() && a.b_ax.size() <= 4;
+  /* the probabilities are read in the layout the scores were written in */
+  ok = ok && a.c_sn == 1 && a.m_ax.size() == 1 && a.n_ax.size() == 1 && b.m_ax.size() == 1 && b.k_ax.size() == 1;
+  if (ok) ok = b.m_ax[0].sa == a.c_sm && b.k_ax[0].sa == 1;
+  for (size_t i = 0; ok && i < a.b_ax.size(); i++)
+    ok = a.b_ax[i].ext == b.b_ax[i].ext && a.b_ax[i].sc == b.b_ax[i].sa && b.b_ax[i].sc % 4 == 0;
+  if (!ok) { err = "attention chain does not have the supported shape"; delete p; return nullptr; }
+  p->T = a.M; p->BH = a.nbatch;
+  const std::string &sc = h.get("scale");
+  unsigned bits = (unsigned)strtoul(sc.c_str(), nullptr, 16);
+  memcpy(&p->scale, &bits, 4);
+  auto m = h.getv("mask");
+  if (m.size() != 3) { err = "malformed attention header"; delete p; return nullptr; }
+  p->mask_off = m[0]; p->mask_sq = m[1]; p->mask_sk = m[2];
+  p->n_params = 5;
+  p->rw = "rrrr";
+  p->rw.push_back(h.get("outmode") == "W" ? 'W' : 'w');
+  return p;
+}

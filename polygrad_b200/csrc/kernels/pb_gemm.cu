@@ -466,7 +466,16 @@ int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
   return rc;
 }
 
-PbAotProgram *pb_make_gemm(const PbHeader &h, std::string &err) {
+PbAotProgram *pb_make_gemm(const PbHeader &h, std::string &err) { return pb_parse_gemm(h, "", err); }
+
+/* Keys are looked up as prefix + name, so a header may carry several contractions. */
+PbGemmProgram *pb_parse_gemm(const PbHeader &h0, const char *prefix, std::string &err) {
+  struct Prefixed {
+    const PbHeader &h; std::string pre;
+    const std::string &get(const char *k) const { return h.get((pre + k).c_str()); }
+    long long geti(const char *k, long long d = 0) const { return h.geti((pre + k).c_str(), d); }
+    std::vector<long long> getv(const char *k) const { return h.getv((pre + k).c_str()); }
+  } h{h0, prefix};
   auto params = h.getv("params"), off = h.getv("offsets");
   if (params.size() != 4 || off.size() != 4) { err = "malformed gemm header"; return nullptr; }
   PbGemmProgram *p = new PbGemmProgram();

@@ -51,6 +51,15 @@ struct PbGemmProgram : PbAotProgram {
   void *pack_operand(const void *src, long long off, bool is_a, int src_dtype, int dst_dtype, cudaStream_t stream);
 };
 
+/* Builds the planned contraction from header lines whose keys start with `prefix`. */
+PbGemmProgram *pb_parse_gemm(const PbHeader &h, const char *prefix, std::string &err);
+
+/* Fused attention (pb_attention.cu). */
+bool pb_attention_supported(long long T, long long hd);
+int pb_attention_launch(const void *qb, const void *kb, const void *vtb, const float *mask, long long mask_sq, long long mask_sk,
+                        float scale, float *out, int nb, const int *bext, const long long *o_sb, long long o_sm,
+                        long long BH, long long T, cudaStream_t stream);
+
 /* Tensor-core path: returns 0 / -1, or PB_TC_UNSUPPORTED when the shape is not handled. */
 int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream);
 

@@ -645,6 +645,7 @@ extern "C" PolyCudaProgram *poly_compile_cuda(const char *source, const char *fn
     if (kind == "gather") p->aot = pb_make_gather(h, err);
     else if (kind == "gemm") p->aot = pb_make_gemm(h, err);
     else if (kind == "copy") p->aot = pb_make_copy(h, err);
+    else if (kind == "attn") p->aot = pb_make_attn(h, err);
     else err = "unknown program kind '" + kind + "'";
     if (!p->aot) { pb_set_error("poly_compile_cuda: %s", err.c_str()); return nullptr; }
     p->n_params = p->aot->n_params;

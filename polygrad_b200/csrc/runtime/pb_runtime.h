@@ -38,6 +38,7 @@ struct PbAotProgram {
 PbAotProgram *pb_make_gather(const PbHeader &h, std::string &err);
 PbAotProgram *pb_make_gemm(const PbHeader &h, std::string &err);
 PbAotProgram *pb_make_copy(const PbHeader &h, std::string &err);
+PbAotProgram *pb_make_attn(const PbHeader &h, std::string &err);
 
 /* Runtime services for kernels that need scratch memory or mode flags. */
 void *pb_scratch_alloc(size_t bytes);          /* pooled; nullptr on failure */

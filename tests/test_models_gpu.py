@@ -59,6 +59,26 @@ def test_gpt2_toy_fp32(ref_lib, gpu, cfg):
         np.mean(got.argmax(-1) == want.argmax(-1)) > 0.99
 
 
+@pytest.mark.parametrize('cfg', [
+    dict(vocab_size=211, n_embd=96, n_head=4, n_layer=2, max_seq_len=48, max_batch=2),     # head size 24: separate kernels
+    dict(vocab_size=307, n_embd=128, n_head=2, n_layer=2, max_seq_len=256, max_batch=2),   # head size 64: fused attention
+], ids=['hd24', 'hd64_fused_attention'])
+def test_gpt2_bf16_policy(ref_lib, gpu, cfg):
+    """bf16 contraction policy (operands rounded to bf16, fp32 accumulation) against the
+    fp32 CPU forward: logits within 2e-2 relative (atol = rtol * rms)."""
+    rng = np.random.default_rng(13)
+    tokens = rng.integers(0, cfg['vocab_size'], (cfg['max_batch'], cfg['max_seq_len']))
+    want = _run_gpt2(ref_lib, ffi.DEVICE_CPU, cfg, tokens)
+    gpu.poly_b200_set_gemm_policy(1)
+    try:
+        gpu.poly_b200_stats_reset()
+        got = _run_gpt2(gpu, ffi.DEVICE_CUDA, cfg, tokens)
+    finally:
+        gpu.poly_b200_set_gemm_policy(0)
+    assert_close(got, want, 2e-2, 'gpt2 logits, bf16 policy')
+    assert np.mean(got.argmax(-1) == want.argmax(-1)) > 0.97
+
+
 def test_gpt2_rows_independent(gpu):
     """Batch rows never interact: row b of a batched forward equals the forward of
     sequence b alone (the property the sharded runs rely on)."""
