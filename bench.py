@@ -397,13 +397,53 @@ def run_gemm_sweep(args):
                           rows=rows)), flush=True)
 
 
+def run_attention(args):
+    """The fused attention kernel alone at the GPT-2 124M layer shape (8 x 12 heads x 1024 x 64)."""
+    from polygrad_b200 import ffi
+    lib = ffi.product()
+    lib.poly_b200_set_device(int(os.environ.get('LOCAL_RANK', '0')))
+    if lib.poly_cuda_init() != 0:
+        raise SystemExit('bench: no usable B200: ' + lib.last_error())
+    B, H, T, hd = 8, 12, 1024, 64
+    rng = np.random.default_rng(SEED)
+    q, k, v = (rng.standard_normal((B, T, H, hd)).astype(np.float32) for _ in range(3))
+    ar = np.arange(T, dtype=np.float32)
+    mask = np.where(ar[:, None] < ar[None, :], np.float32(-1e9), np.float32(0)).astype(np.float32)
+    ptrs = []
+    for a in (q, k, v, mask):
+        d = lib.poly_cuda_alloc(a.nbytes)
+        lib.poly_cuda_copy_htod(d, a.ctypes.data, a.nbytes)
+        ptrs.append(d)
+    do = lib.poly_cuda_alloc(B * H * T * hd * 4)
+
+    def call():
+        if lib.poly_b200_attention(ptrs[0], ptrs[1], ptrs[2], ptrs[3], 0.125, do, B, H, T) != 0:
+            raise SystemExit('bench: poly_b200_attention failed: ' + lib.last_error())
+    for _ in range(3):
+        call()
+    e0, e1 = lib.poly_b200_event_create(), lib.poly_b200_event_create()
+    lib.poly_b200_event_record(e0)
+    for _ in range(args.steps):
+        call()
+    lib.poly_b200_event_record(e1)
+    ms = lib.poly_b200_event_elapsed_ms(e0, e1) / args.steps
+    flops = 4.0 * B * H * T * T * hd
+    peaks = read_peaks()
+    tf = flops / (ms * 1e-3) / 1e12
+    print(json.dumps(dict(metric='attention_tflops', value=tf, unit='TFLOP/s', n_gpus=1, steps=args.steps, warmup=3,
+                          ms_per_step=ms, higher_is_better=True, dtype='bf16', data='synthetic',
+                          config=dict(workload=f'attention {B}x{H}x{T}x{hd}, additive [T,T] mask, incl. bf16 packing of q, k, v'),
+                          roofline=dict(bound='tensor', achieved=tf, peak=peaks['bf16_tflops'], unit='TFLOP/s',
+                                        frac=tf / peaks['bf16_tflops'], traffic=None))), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
-    ap.add_argument('--workload', default='gpt2-124m', choices=sorted(WORKLOADS) + ['gemm'])
+    ap.add_argument('--workload', default='gpt2-124m', choices=sorted(WORKLOADS) + ['gemm', 'attention'])
     ap.add_argument('--shape', default='', help='MxNxK for --workload gemm')
     ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp32'])
     ap.add_argument('--gather', default='last', choices=['last', 'full'])
@@ -416,6 +456,8 @@ def main():
     local_rank = int(os.environ.get('LOCAL_RANK', '0'))
     if args.workload == 'gemm':
         return run_gemm_sweep(args)
+    if args.workload == 'attention':
+        return run_attention(args)
     cfg = WORKLOADS[args.workload]
     if args.impl == 'reference':
         run_reference(args, cfg, rank)

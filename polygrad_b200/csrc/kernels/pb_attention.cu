@@ -16,17 +16,18 @@
  * assumed: the mask is an arbitrary additive [T, T] buffer and every block of
  * keys is processed, as in the reference.
  *
- * One CTA per (batch*head, block of 128 query rows), 5 warps, up to two CTAs
- * per SM:
- *   warp 4   lane 0 issues the TMA loads (Q once; K and Vᵀ blocks, each
+ * One CTA per (batch*head, block of 128 query rows), 9 warps, two CTAs per SM:
+ *   warp 8   lane 0 issues the TMA loads (Q once; K and Vᵀ blocks, each
  *            prefetched as soon as the MMA that read the previous one has
  *            finished) and the tcgen05.mma instructions:
  *            S = Q Kᵀ (128x128x64) into tensor memory, then PV = P Vᵀᵀ
  *            (128x64x128) into another 64 columns;
- *   warps 0-3  one query row per thread: read S from tensor memory in 32-column
- *            chunks (two passes: row max, then exponentials), write P as bf16
- *            into shared memory in the swizzled K-major tile layout the MMA
- *            reads, then add PV to the row's 64 fp32 accumulators in registers.
+ *   warps 0-7  two threads per query row (64 keys and 32 output columns each):
+ *            read S from tensor memory in 32-column chunks (pass 1: x = s*scale
+ *            + mask written back to tensor memory, row max exchanged through
+ *            shared memory; pass 2: exponentials), write P as bf16 into shared
+ *            memory in the swizzled K-major tile layout the MMA reads, then add
+ *            PV to the row's fp32 accumulators in registers.
  * Head size 64, T a multiple of 128.  All barrier waits are bounded.
  */
 #include "pb_gemm.h"
@@ -40,14 +41,23 @@ __device__ int pb200_attn_error_flag = 0;
 #define AT_BQ 128      /* query rows per CTA */
 #define AT_BK 128      /* keys per block */
 #define AT_HD 64
-#define AT_THREADS 160
+#define AT_THREADS 288
 #define AT_SMEM (16384 /*Q*/ + 16384 /*K*/ + 16384 /*Vt: 2 x 8 KB*/ + 32768 /*P: 2 x 16 KB*/ + 256 + 1024)
+
+/* 2^x by the special-function unit (ex2.approx: relative error about 2^-22; the
+ * results are rounded to bfloat16 right after). */
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 struct AttnArgs {
   float *O; const float *mask;
   long long mask_sq, mask_sk;     /* mask[q*mask_sq + k*mask_sk] */
   float scale;
   int mask_vec;                   /* mask rows contiguous and 16-byte aligned */
+  const float *tile_const;        /* per (query block, key block): NaN if the mask tile varies, else its one value */
   int T, n_qblocks;
   int nb; int bext[4]; long long o_sb[4]; long long o_sm;   /* O[batch..][row*o_sm + d] */
 };
@@ -61,9 +71,10 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint8_t *sm = smem_raw + (base - raw);
   const uint32_t s_q = base, s_k = base + 16384, s_v = base + 32768, s_p = base + 49152;
   uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 81920);
-  const uint32_t bar_q = smem_u32(bars), bar_k = bar_q + 8, bar_v = bar_q + 16, bar_s = bar_q + 24, bar_p = bar_q + 32, bar_o = bar_q + 40;
+  const uint32_t bar_q = smem_u32(bars), bar_k = bar_q + 8, bar_v = bar_q + 16, bar_s = bar_q + 24, bar_p = bar_q + 32, bar_o = bar_q + 40, bar_x = bar_q + 48;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ float xchg[2][AT_BQ];     /* per-row exchange between the two threads of a row */
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qb = blockIdx.x % g.n_qblocks, bh = blockIdx.x / g.n_qblocks;
@@ -72,10 +83,10 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   if (threadIdx.x == 0) {
     abort_flag = 0;
     mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1);
-    mbar_init(bar_s, 1); mbar_init(bar_p, 128); mbar_init(bar_o, 1);
+    mbar_init(bar_s, 1); mbar_init(bar_p, 256); mbar_init(bar_o, 1); mbar_init(bar_x, 256);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == 8) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(256u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -85,7 +96,7 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const uint32_t tmem = tmem_slot;
   const uint32_t tmem_s = tmem, tmem_pv = tmem + 128;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       /* instruction descriptors: bf16 x bf16 -> fp32, both operands K-major, M = 128 */
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BK >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
@@ -97,31 +108,37 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_expect_tx(bar_v, 16384);
       tma_load_3d(s_v, &map_vt, bar_v, 0, 0, bh);
       tma_load_3d(s_v + 8192, &map_vt, bar_v, 64, 0, bh);
-      bool ok = mbar_wait(bar_q, 0, &abort_flag, 11);
+      bool ok = mbar_wait(bar_q, 0, &abort_flag, 11) && mbar_wait(bar_k, 0, &abort_flag, 12);
+      const uint64_t dq = make_smem_desc(s_q), dk = make_smem_desc(s_k);
+      if (ok) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < AT_HD / 16; k++) tc_mma_bf16(tmem_s, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, k ? 1u : 0u);
+        tc_commit(bar_s);
+      }
       for (int j = 0; j < nkb && ok; j++) {
         const uint32_t ph = (uint32_t)j & 1u;
-        if (!mbar_wait(bar_k, ph, &abort_flag, 12)) break;
-        tc_fence_after_sync();
-        {
-          const uint64_t da = make_smem_desc(s_q), db = make_smem_desc(s_k);
-#pragma unroll
-          for (int k = 0; k < AT_HD / 16; k++) tc_mma_bf16(tmem_s, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, k ? 1u : 0u);
-          tc_commit(bar_s);
-        }
         /* K is free once S is complete: prefetch the next block of keys */
         if (!mbar_wait(bar_s, ph, &abort_flag, 13)) break;
         if (j + 1 < nkb) { mbar_expect_tx(bar_k, 16384); tma_load_3d(s_k, &map_k, bar_k, 0, (j + 1) * AT_BK, bh); }
-        if (!mbar_wait(bar_p, ph, &abort_flag, 14)) break;     /* P written, previous PV consumed */
+        if (!mbar_wait(bar_p, ph, &abort_flag, 14)) break;     /* P written, S and the previous PV consumed */
         if (!mbar_wait(bar_v, ph, &abort_flag, 15)) break;
         tc_fence_after_sync();
-        {
 #pragma unroll
-          for (int h = 0; h < 2; h++) {
-            const uint64_t da = make_smem_desc(s_p + h * 16384), db = make_smem_desc(s_v + h * 8192);
+        for (int h = 0; h < 2; h++) {
+          const uint64_t da = make_smem_desc(s_p + h * 16384), db = make_smem_desc(s_v + h * 8192);
 #pragma unroll
-            for (int k = 0; k < 4; k++) tc_mma_bf16(tmem_pv, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_o, (h | k) ? 1u : 0u);
-          }
-          tc_commit(bar_o);
+          for (int k = 0; k < 4; k++) tc_mma_bf16(tmem_pv, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_o, (h | k) ? 1u : 0u);
+        }
+        tc_commit(bar_o);
+        /* the next block's scores follow at once: S is free, and the softmax threads find
+         * them ready when they come back from adding this block's PV */
+        if (j + 1 < nkb) {
+          if (!mbar_wait(bar_k, ph ^ 1u, &abort_flag, 12)) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int k = 0; k < AT_HD / 16; k++) tc_mma_bf16(tmem_s, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, k ? 1u : 0u);
+          tc_commit(bar_s);
         }
         if (!mbar_wait(bar_o, ph, &abort_flag, 16)) break;
         if (j + 1 < nkb) {
@@ -132,104 +149,127 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
     }
   } else {
-    /* ── softmax: thread = one query row ── */
-    const int row = warp * 32 + lane;                    /* row within the block = tensor-memory lane */
+    /* ── softmax: two threads per query row (warps w and w+4 share the row's
+     * tensor-memory lanes); each owns 64 of the block's 128 keys and 32 of the
+     * 64 output columns ── */
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = quarter * 32 + lane;                 /* row within the block = tensor-memory lane */
     const long long q = (long long)qb * AT_BQ + row;
     const float *mrow = g.mask + q * g.mask_sq;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t s_cols = tmem_s + lane_addr + half * 64, pv_cols = tmem_pv + lane_addr + half * 32;
     const float LOG2E = 1.44269504088896340736f;
-    float m_run = __int_as_float(0xff800000), l_run = 0.0f;
-    float acc[AT_HD];
+    float m_run = __int_as_float(0xff800000), l_run = 0.0f;   /* l_run: this thread's keys only */
+    float acc[32];
 #pragma unroll
-    for (int d = 0; d < AT_HD; d++) acc[d] = 0.0f;
-    uint8_t *p_row = sm + 49152 + (row >> 3) * 1024 + (row & 7) * 128;
+    for (int d = 0; d < 32; d++) acc[d] = 0.0f;
+    uint8_t *p_row = sm + 49152 + half * 16384 + (row >> 3) * 1024 + (row & 7) * 128;
     bool ok = true;
+    uint32_t xph = 0;
     for (int j = 0; j < nkb && ok; j++) {
       const uint32_t ph = (uint32_t)j & 1u;
+      const float *mj = mrow + ((long long)j * AT_BK + half * 64) * g.mask_sk;
+      const float tile_c = g.tile_const[qb * nkb + j];
+      const bool tile_is_const = (tile_c == tile_c);
       if (!mbar_wait(bar_s, ph, &abort_flag, 17)) { ok = false; break; }
       tc_fence_after_sync();
-      const float *mj = mrow + (long long)j * AT_BK * g.mask_sk;
-      /* pass 1: x = s*scale + mask, written back over S in tensor memory; row max of the block */
-      float m_blk = __int_as_float(0xff800000);
-#pragma unroll 1
-      for (int c = 0; c < AT_BK / 32; c++) {
+      /* pass 1: x = s*scale + mask, written back over S in tensor memory; max over this thread's keys */
+      float m_part = __int_as_float(0xff800000);
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
         uint32_t r[32];
-        tc_ld32(tmem_s + lane_addr + c * 32, r);
+        tc_ld32(s_cols + c * 32, r);
         tc_wait_ld();
-        if (g.mask_vec) {
-          const float4 *m4 = reinterpret_cast<const float4 *>(mj + c * 32);
+        if (tile_is_const) {
+          /* the whole 128 x 128 mask tile holds one value: no loads */
+#pragma unroll
+          for (int i = 0; i < 32; i++) {
+            const float x = __uint_as_float(r[i]) * g.scale + tile_c;
+            r[i] = __float_as_uint(x);
+            m_part = fmaxf(m_part, x);
+          }
+        } else if (g.mask_vec) {
 #pragma unroll
           for (int i = 0; i < 8; i++) {
-            const float4 mv = m4[i];
+            const float4 mv = reinterpret_cast<const float4 *>(mj + c * 32)[i];
             const float x0 = __uint_as_float(r[4 * i]) * g.scale + mv.x, x1 = __uint_as_float(r[4 * i + 1]) * g.scale + mv.y;
             const float x2 = __uint_as_float(r[4 * i + 2]) * g.scale + mv.z, x3 = __uint_as_float(r[4 * i + 3]) * g.scale + mv.w;
             r[4 * i] = __float_as_uint(x0); r[4 * i + 1] = __float_as_uint(x1); r[4 * i + 2] = __float_as_uint(x2); r[4 * i + 3] = __float_as_uint(x3);
-            const float a01 = (x0 > x1) ? x0 : x1, a23 = (x2 > x3) ? x2 : x3;
-            const float a = (a01 > a23) ? a01 : a23;
-            m_blk = (m_blk > a) ? m_blk : a;
+            m_part = fmaxf(m_part, fmaxf(fmaxf(x0, x1), fmaxf(x2, x3)));
           }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; i++) {
             const float x = __uint_as_float(r[i]) * g.scale + mj[(long long)(c * 32 + i) * g.mask_sk];
             r[i] = __float_as_uint(x);
-            m_blk = (m_blk > x) ? m_blk : x;
+            m_part = fmaxf(m_part, x);
           }
         }
-        tc_st32(tmem_s + lane_addr + c * 32, r);
+        tc_st32(s_cols + c * 32, r);
       }
+      xchg[half][row] = m_part;
       tc_wait_st();
-      const float m_new = (m_run > m_blk) ? m_run : m_blk;
-      const float alpha = exp2f((m_run - m_new) * LOG2E);       /* 0 on the first block (m_run = -inf) */
+      /* exchange through an mbarrier rather than bar.sync: its wait is bounded like all others */
+      mbar_arrive(bar_x);
+      if (!mbar_wait(bar_x, xph & 1u, &abort_flag, 19)) { ok = false; break; }
+      xph++;
+      const float m_other = xchg[half ^ 1][row];
+      const float m_new = fmaxf(m_run, fmaxf(m_part, m_other));
+      const float m_scaled = m_new * LOG2E;
+      const float alpha = fast_exp2((m_run - m_new) * LOG2E);   /* 0 on the first block (m_run = -inf) */
       float l_blk = 0.0f;
       /* pass 2: p = exp2((x - m_new) * log2e), written as bf16 into the K-major swizzled tile */
-#pragma unroll 1
-      for (int c = 0; c < AT_BK / 32; c++) {
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
         uint32_t r[32];
-        tc_ld32(tmem_s + lane_addr + c * 32, r);
+        tc_ld32(s_cols + c * 32, r);
         tc_wait_ld();
-        uint8_t *dst = p_row + (c >> 1) * 16384;               /* 64-key half */
 #pragma unroll
         for (int i8 = 0; i8 < 4; i8++) {
           uint32_t w[4];
 #pragma unroll
           for (int i2 = 0; i2 < 4; i2++) {
             const int i = i8 * 8 + i2 * 2;
-            const float p0 = exp2f((__uint_as_float(r[i]) - m_new) * LOG2E), p1 = exp2f((__uint_as_float(r[i + 1]) - m_new) * LOG2E);
+            const float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), LOG2E, -m_scaled)), p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), LOG2E, -m_scaled));
             __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-            /* the sum uses the rounded values, i.e. exactly what the second contraction multiplies */
-            l_blk += __low2float(pb) + __high2float(pb);
+            l_blk += p0 + p1;
             w[i2] = *reinterpret_cast<uint32_t *>(&pb);
           }
-          const int chunk = (c & 1) * 4 + i8;                   /* 16-byte chunk within the 128-byte row */
-          *reinterpret_cast<uint4 *>(dst + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          const int chunk = c * 4 + i8;                         /* 16-byte chunk within the 128-byte row */
+          *reinterpret_cast<uint4 *>(p_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
       l_run = l_run * alpha + l_blk;
       m_run = m_new;
 #pragma unroll
-      for (int d = 0; d < AT_HD; d++) acc[d] *= alpha;
+      for (int d = 0; d < 32; d++) acc[d] *= alpha;
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(bar_p);
       if (!mbar_wait(bar_o, ph, &abort_flag, 18)) { ok = false; break; }
       tc_fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < AT_HD / 32; c++) {
+      {
         uint32_t r[32];
-        tc_ld32(tmem_pv + lane_addr + c * 32, r);
+        tc_ld32(pv_cols, r);
         tc_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; i++) acc[c * 32 + i] += __uint_as_float(r[i]);
+        for (int i = 0; i < 32; i++) acc[i] += __uint_as_float(r[i]);
       }
     }
+    /* total row sum = the two threads' partial sums */
     if (ok) {
+      xchg[half][row] = l_run;
+      mbar_arrive(bar_x);
+      ok = mbar_wait(bar_x, xph & 1u, &abort_flag, 20);
+    }
+    if (ok) {
+      const float l_tot = l_run + xchg[half ^ 1][row];
       int rem = bh; long long ob = 0;
       for (int i = 0; i < g.nb; i++) { const int x = rem % g.bext[i]; rem /= g.bext[i]; ob += x * g.o_sb[i]; }
-      float *o = g.O + ob + q * g.o_sm;
-      const float inv = 1.0f / l_run;
+      float *o = g.O + ob + q * g.o_sm + half * 32;
+      const float inv = 1.0f / l_tot;
 #pragma unroll
-      for (int d = 0; d < AT_HD; d += 4)
+      for (int d = 0; d < 32; d += 4)
         *reinterpret_cast<float4 *>(o + d) = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
     }
   }
@@ -237,10 +277,27 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   tc_fence_before_sync();
   __syncthreads();
   if (abort_flag) { for (int i = 0; i < 2000; i++) __nanosleep(1000); }
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after_sync();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
   }
+}
+
+/* Classifies the mask by 128 x 128 tile: a tile whose entries are all equal (the
+ * zeros below and the -1e9 above the diagonal of a causal mask, for instance) is
+ * recorded by that value, so that the attention kernel adds it without reading
+ * the tile; any other tile is recorded as NaN and read.  Exact for every mask. */
+__global__ void __launch_bounds__(256) pb200_mask_tiles(const float *mask, long long sq, long long sk, int nk, float *out) {
+  const int qi = blockIdx.y, ki = blockIdx.x;
+  const float *t = mask + (long long)qi * AT_BQ * sq + (long long)ki * AT_BK * sk;
+  const float first = t[0];
+  bool same = true;
+  for (int e = threadIdx.x; e < AT_BQ * AT_BK; e += 256) {
+    const float v = t[(long long)(e / AT_BK) * sq + (long long)(e % AT_BK) * sk];
+    same = same && (__float_as_uint(v) == __float_as_uint(first));
+  }
+  const int all = __syncthreads_and(same ? 1 : 0);
+  if (threadIdx.x == 0) out[qi * nk + ki] = (all && first == first) ? first : __int_as_float(0x7fc00000);
 }
 
 /* ── host ────────────────────────────────────────────────────────────── */
@@ -300,6 +357,12 @@ int pb_attention_launch(const void *qb, const void *kb, const void *vtb, const f
   for (int i = 0; i < nb; i++) if (o_sb[i] % 4) { pb_set_error("attention: output batch strides must be 16-byte aligned"); return -1; }
   long long grid = BH * g.n_qblocks;
   if (grid > 2147483647LL) { pb_set_error("attention: grid too large"); return -1; }
+  const int nq = g.n_qblocks, nk = (int)(T / AT_BK);
+  float *tiles = (float *)pb_scratch_alloc((size_t)nq * nk * sizeof(float));
+  if (!tiles) { pb_set_error("attention: out of scratch memory"); return -1; }
+  pb200_mask_tiles<<<dim3((unsigned)nk, (unsigned)nq), 256, 0, stream>>>(mask, mask_sq, mask_sk, nk, tiles);
+  g.tile_const = tiles;
+  pb_scratch_free(tiles);            /* stream-ordered pool: safe to hand back once the work is enqueued */
   pb_tc_mark_used();
   pb200_flash_attn<<<(unsigned)grid, AT_THREADS, AT_SMEM, stream>>>(mq, mk, mv, g);
   cudaError_t e = cudaGetLastError();
