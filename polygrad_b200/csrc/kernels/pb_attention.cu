@@ -175,7 +175,7 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       tc_fence_after_sync();
       /* pass 1: x = s*scale + mask, written back over S in tensor memory; max over this thread's keys */
       float m_part = __int_as_float(0xff800000);
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < 2; c++) {
         uint32_t r[32];
         tc_ld32(s_cols + c * 32, r);
@@ -219,7 +219,7 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const float alpha = fast_exp2((m_run - m_new) * LOG2E);   /* 0 on the first block (m_run = -inf) */
       float l_blk = 0.0f;
       /* pass 2: p = exp2((x - m_new) * log2e), written as bf16 into the K-major swizzled tile */
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < 2; c++) {
         uint32_t r[32];
         tc_ld32(s_cols + c * 32, r);
@@ -410,7 +410,7 @@ struct AttnProgram : PbAotProgram {
   long long mask_off = 0, mask_sq = 0, mask_sk = 0;
   long long T = 0, BH = 0;
   ~AttnProgram() override { delete g1; delete g2; }
-  int n_launches() const override { return 4; }
+  int n_launches() const override { return 5; }
   int launch(void *const *bufs, cudaStream_t stream) override {
     const size_t bytes = (size_t)BH * T * AT_HD * 2;
     void *qb = pb_scratch_alloc(bytes), *kb = pb_scratch_alloc(bytes), *vb = pb_scratch_alloc(bytes);
