@@ -397,6 +397,126 @@ def run_gemm_sweep(args):
                           rows=rows)), flush=True)
 
 
+class ResidentGraph:
+    """A tensor expression realized repeatedly with every buffer resident on the device."""
+
+    def __init__(self, lib, dev, out):
+        from polygrad_b200 import ffi
+        from polygrad_b200.tensor import _i64
+        self.lib, self.dev = lib, dev
+        n = out.numel()
+        out_buf = lib.poly_buffer_by_id(dev.ctx, n, ffi.DTYPE_IDS[out.dtype])
+        self.sink = lib.poly_sink1(dev.ctx, lib.poly_store_val(dev.ctx, out_buf, out.uop))
+        pairs = list(out.leaves) + [(out_buf, np.empty(n, np.float32))]
+        self.binds = (ffi.PolyBufferBinding * len(pairs))()
+        self.n = len(pairs)
+        for i, (buf, host) in enumerate(pairs):
+            d = lib.poly_cuda_alloc(host.nbytes)
+            if i < len(pairs) - 1:
+                lib.poly_cuda_copy_htod(d, host.ctypes.data, host.nbytes)
+            self.binds[i].buffer, self.binds[i].handle.ptr = buf, d
+            self.binds[i].handle.nbytes, self.binds[i].handle.domain = host.nbytes, ffi.DEVICE_CUDA
+
+    def run(self):
+        if self.lib.poly_realize(self.dev.ctx, self.sink, self.binds, self.n) != 0:
+            raise SystemExit('bench: poly_realize failed: ' + self.lib.last_error())
+
+    def kernel_ms(self, reps):
+        """Summed device time of the kernels of one realize (per-launch CUDA events)."""
+        for _ in range(3):
+            self.run()
+        self.lib.poly_b200_timing_begin()
+        for _ in range(reps):
+            self.run()
+        n = ctypes.c_int(0)
+        total = self.lib.poly_b200_timing_end(ctypes.byref(n))
+        return total / reps, n.value // reps
+
+    def free(self):
+        for i in range(self.n):
+            self.lib.poly_cuda_free(self.binds[i].handle.ptr)
+
+
+def run_rowops(args):
+    """BASELINE configs[2]: row ops on a 16384 x 4096 float32 tensor ~N(0,1).  Per op: summed
+    kernel time of one poly_realize, algorithmic bytes (the fused minimum: inputs once,
+    outputs once) and the fraction of the measured HBM copy bandwidth."""
+    from polygrad_b200 import ffi
+    from polygrad_b200.tensor import Device
+    lib = ffi.product()
+    lib.poly_b200_set_device(int(os.environ.get('LOCAL_RANK', '0')))
+    if lib.poly_cuda_init() != 0:
+        raise SystemExit('bench: no usable B200: ' + lib.last_error())
+    peaks = read_peaks()
+    R, C = 16384, 4096
+    x = np.random.default_rng(SEED).standard_normal((R, C)).astype(np.float32)
+    full, red = 2.0 * x.nbytes, x.nbytes + 4.0 * R
+    ops = [
+        ('x*2+1', lambda t: t * 2 + 1, full), ('exp', lambda t: t.exp(), full), ('tanh', lambda t: t.tanh(), full),
+        ('sum', lambda t: t.sum(-1), red), ('max', lambda t: t.max(-1), red), ('mean', lambda t: t.mean(-1), red),
+        ('var', lambda t: t.var(-1), red), ('softmax', lambda t: t.softmax(-1), full),
+        ('layernorm', lambda t: t.layernorm(-1, 1e-5), full), ('permute(1,0)', lambda t: t.permute(1, 0), full),
+        ('[::-1]', lambda t: t[::-1], full), ('[:, ::-1]', lambda t: t[:, ::-1], full),
+    ]
+    rows = []
+    for name, fn, nbytes in ops:
+        dev = Device(lib, ffi.DEVICE_CUDA)
+        g = ResidentGraph(lib, dev, fn(dev.tensor(x)))
+        ms, launches = g.kernel_ms(max(args.steps, 3))
+        g.free()
+        dev.close()
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        rows.append(dict(op=name, us=ms * 1e3, launches=launches, algorithmic_mb=nbytes / 1e6, gbs=gbs,
+                         frac_of_hbm=gbs / peaks['hbm_gbs']))
+    geo = float(np.exp(np.mean([np.log(r['gbs']) for r in rows])))
+    print(json.dumps(dict(metric='rowops_hbm_gbs', value=geo, unit='GB/s (geometric mean over ops)', n_gpus=1,
+                          steps=args.steps, warmup=3, higher_is_better=True, dtype='f32', data='synthetic',
+                          config=dict(workload='row ops 16384x4096 f32', l2='536 MB per op, above the 126 MB L2'),
+                          roofline=dict(bound='hbm', achieved=geo, peak=peaks['hbm_gbs'], unit='GB/s',
+                                        frac=geo / peaks['hbm_gbs'], traffic=None),
+                          rows=rows)), flush=True)
+
+
+def run_mlp(args):
+    """BASELINE configs[0]: MLP 784 -> 512 -> 10 (+ReLU), batch 256, through the instance API."""
+    from polygrad_b200 import ffi
+    from polygrad_b200.instance import Instance
+    lib = ffi.product()
+    lib.poly_b200_set_device(int(os.environ.get('LOCAL_RANK', '0')))
+    if lib.poly_cuda_init() != 0:
+        raise SystemExit('bench: no usable B200: ' + lib.last_error())
+    x = np.random.default_rng(SEED).standard_normal((256, 784)).astype(np.float32)
+    inst = Instance.mlp(lib, [784, 512, 10], 'relu', True, 256, seed=42)
+    inst.set_device(ffi.DEVICE_CUDA)
+    for _ in range(5):
+        inst.forward(x=x)
+    lib.poly_b200_synchronize()
+    lib.poly_b200_stats_reset()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        if lib.poly_instance_forward(inst.h, None, 0) != 0:
+            raise SystemExit('bench: forward failed')
+    lib.poly_b200_synchronize()
+    us = (time.perf_counter() - t0) / args.steps * 1e6
+    st = lib.stats()
+    cpu_us = None
+    ref_path = os.path.join(ROOT, 'oracle', '_ref', 'libpolygrad_ref.so')
+    if os.path.isfile(ref_path) and not args.no_cpu_baseline:
+        ref = ffi.load_reference(ref_path)
+        ci = Instance.mlp(ref, [784, 512, 10], 'relu', True, 256, seed=42)
+        ci.forward(x=x)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            ci.forward(x=x)
+        cpu_us = (time.perf_counter() - t0) / 3 * 1e6
+    print(json.dumps(dict(metric='mlp_forward_us', value=us, unit='us per forward (host wall, device-resident)', n_gpus=1,
+                          steps=args.steps, warmup=5, higher_is_better=False, dtype='f32', data='synthetic',
+                          config=dict(workload='MLP 784-512-10 relu, batch 256'),
+                          launches_per_forward=st['launches'] // max(args.steps, 1),
+                          cpu_baseline=dict(value=cpu_us, unit='us per forward', cores=1, kind='reference',
+                                            sample='full size') if cpu_us else None)), flush=True)
+
+
 def run_attention(args):
     """The fused attention kernel alone at the GPT-2 124M layer shape (8 x 12 heads x 1024 x 64)."""
     from polygrad_b200 import ffi
@@ -443,7 +563,7 @@ def main():
     ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
-    ap.add_argument('--workload', default='gpt2-124m', choices=sorted(WORKLOADS) + ['gemm', 'attention'])
+    ap.add_argument('--workload', default='gpt2-124m', choices=sorted(WORKLOADS) + ['gemm', 'attention', 'rowops', 'mlp'])
     ap.add_argument('--shape', default='', help='MxNxK for --workload gemm')
     ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp32'])
     ap.add_argument('--gather', default='last', choices=['last', 'full'])
@@ -458,6 +578,10 @@ def main():
         return run_gemm_sweep(args)
     if args.workload == 'attention':
         return run_attention(args)
+    if args.workload == 'rowops':
+        return run_rowops(args)
+    if args.workload == 'mlp':
+        return run_mlp(args)
     cfg = WORKLOADS[args.workload]
     if args.impl == 'reference':
         run_reference(args, cfg, rank)

@@ -158,6 +158,13 @@ int   poly_b200_event_record(void *event);
 float poly_b200_event_elapsed_ms(void *start, void *stop); /* waits for stop; <0 on error */
 void  poly_b200_event_destroy(void *event);
 
+/* Per-launch device timing: between begin and end every kernel launch of the
+ * library is bracketed by CUDA events on its stream (plans run launch by launch
+ * instead of as a graph); end waits and returns the summed kernel time in ms. */
+void   poly_b200_timing_begin(void);
+double poly_b200_timing_end(int *n_launches);
+int    poly_b200_timing_active(void);
+
 /* Counters since process start (or since the last reset). */
 typedef struct {
   uint64_t launches;            /* kernels launched by this library */

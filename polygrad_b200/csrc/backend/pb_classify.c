@@ -404,11 +404,69 @@ static char *classify_gemm(PbKern *k) {
   return pb_str_take(&h);
 }
 
+/* ── transposing copy ────────────────────────────────────────────────── */
+static char *classify_transpose(PbKern *k) {
+  if (k->n_stores != 1 || k->n_reduce_nodes != 0 || !all_const_extents(k)) REJECT("shape");
+  PbStore *st = &k->stores[0];
+  if (st->index->n_src != 2 || !is_plain_load(st->value)) REJECT("not a plain copy");
+  PolyUOp *ld = st->value;
+  int po = st->param, pi = load_param(ld);
+  if (po == pi) REJECT("in place");
+  PolyDType a = k->params[po]->dtype, b = k->params[pi]->dtype;
+  if (a.bitsize != 32 || b.bitsize != 32 || a.priority != b.priority) REJECT("element type");
+  uint64_t mask = 0;
+  for (int i = 0; i < st->n_loop; i++) mask |= (uint64_t)1 << st->loop[i];
+  PolyUOp *exprs[2] = { st->index->src[1], load_index(ld) };
+  VAxis va[2 * PB_MAX_AXES]; int nva; VFit fit[2];
+  if (!find_axes(k, mask, exprs, 2, va, &nva, fit)) REJECT("not affine");
+  if (!in_bounds(&fit[0], va, nva, param_numel(k, po)) || !in_bounds(&fit[1], va, nva, param_numel(k, pi))) REJECT("bounds");
+  int x = -1, y = -1;
+  for (int i = 0; i < nva; i++) {
+    if (va[i].extent <= 1) continue;
+    if (fit[0].stride[i] == 1) x = i;
+    if (fit[1].stride[i] == 1) y = i;
+  }
+  if (x < 0 || y < 0 || x == y) REJECT("same contiguous axis");
+  if (va[x].extent < 32 || va[y].extent < 32) REJECT("small");
+  if (fit[1].stride[x] <= 0 || fit[0].stride[y] <= 0) REJECT("negative stride");
+  /* the store must cover distinct elements: every other axis has a non-zero output stride */
+  int64_t total = 1;
+  for (int i = 0; i < nva; i++) { if (va[i].extent > 1 && fit[0].stride[i] == 0) REJECT("broadcast store"); total *= va[i].extent; }
+  PbStr h; pb_str_init(&h);
+  pb_str_puts(&h, "//PB200 1\n//kind copy\n");
+  pb_str_printf(&h, "//nparams %d\n//params %d %d\n", k->n_params, po, pi);
+  pb_str_printf(&h, "//xy %lld %lld %lld %lld\n", (long long)va[x].extent, (long long)va[y].extent,
+                (long long)fit[1].stride[x], (long long)fit[0].stride[y]);
+  pb_str_printf(&h, "//offsets %lld %lld\n", (long long)fit[0].offset, (long long)fit[1].offset);
+  PbStr bt; pb_str_init(&bt); int nb = 0;
+  for (int i = 0; i < nva; i++) {
+    if (i == x || i == y || va[i].extent <= 1) continue;
+    pb_str_printf(&bt, " %lld %lld %lld", (long long)va[i].extent, (long long)fit[0].stride[i], (long long)fit[1].stride[i]);
+    nb++;
+  }
+  if (nb > 6) { pb_str_free(&bt); pb_str_free(&h); REJECT("too many axes"); }
+  pb_str_printf(&h, "//batch%s\n", bt.s ? bt.s : "");
+  pb_str_free(&bt);
+  /* whole-buffer overwrite when the strides tile [0, numel) */
+  bool full = fit[0].offset == 0 && total == param_numel(k, po);
+  if (full) {
+    int ord[2 * PB_MAX_AXES]; int n = 0;
+    for (int i = 0; i < nva; i++) if (va[i].extent > 1) ord[n++] = i;
+    for (int i = 1; i < n; i++) { int v = ord[i], j = i - 1; while (j >= 0 && fit[0].stride[ord[j]] > fit[0].stride[v]) { ord[j + 1] = ord[j]; j--; } ord[j + 1] = v; }
+    int64_t expect = 1;
+    for (int i = 0; i < n; i++) { if (fit[0].stride[ord[i]] != expect) { full = false; break; } expect *= va[ord[i]].extent; }
+  }
+  pb_str_printf(&h, "//full %d\n", full ? 1 : 0);
+  return pb_str_take(&h);
+}
+
 char *pb_classify_aot(PbKern *k, const char *fn_name) {
   (void)fn_name;
   char *r = classify_gather(k);
   if (r) return r;
   r = classify_gemm(k);
+  if (r) return r;
+  r = classify_transpose(k);
   if (r) return r;
   return NULL;
 }

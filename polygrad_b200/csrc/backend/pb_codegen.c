@@ -988,7 +988,24 @@ char *pb_render_jit(PbKern *k, const char *fn_name) {
   param_usage(k, usage);
   const char *force = getenv("POLY_B200_JIT");  /* "flat" forces the general mapping (debugging) */
   if (!force || strcmp(force, "flat") != 0) {
-    char *r = render_group_reduce(k, usage);
+    char *r = NULL;
+    if (k->n_reduce_nodes == 1 && k->n_stores == 1) {
+      /* a lone row reduction: the row-wise renderer gives it 128-bit loads */
+      int ident[PB_MAX_PARAMS]; bool all_used = true;
+      for (int a = 0; a < k->n_params; a++) { ident[a] = a; if (!k->params[a] || !(usage[a] & 3)) all_used = false; }
+      if (all_used) {
+        PbFuseIn in = { k, ident, PB_FUSE_FINAL };
+        PbFuseOut fo;
+        r = pb_render_rowfused(&in, 1, false, &fo);
+        if (r) {
+          bool same = fo.n_params == k->n_params;
+          for (int a = 0; same && a < fo.n_params; a++) if (fo.slot[a] != a) same = false;
+          if (!same) { free(r); r = NULL; }
+        }
+      }
+      if (r) return r;
+    }
+    r = render_group_reduce(k, usage);
     if (r) return r;
     r = render_vec_elementwise(k, usage);
     if (r) return r;
@@ -1158,7 +1175,7 @@ static void rf_free(RowFuse *rf) {
 }
 
 char *pb_render_rowfused(PbFuseIn *in, int n, bool out_bf16, PbFuseOut *out) {
-  if (n < 2 || n > RF_MAX) return NULL;
+  if (n < 1 || n > RF_MAX) return NULL;
   RowFuse *rf = calloc(1, sizeof *rf);
   rf->n = n; rf->in = in; rf->out_bf16 = out_bf16;
   char *result = NULL;
@@ -1197,7 +1214,7 @@ char *pb_render_rowfused(PbFuseIn *in, int n, bool out_bf16, PbFuseOut *out) {
     if (red->n_src != 2 || red->dtype.priority != 13 || (op != POLY_OP_ADD && op != POLY_OP_MAX)) goto done;
     if (out_bf16) goto done;
   }
-  if (n_phase == 0) goto done;
+  if (n_phase == 0 && !rf->final_reduce) goto done;
   if (kf->stores[0].index->n_src > 2) goto done;
   for (int i = 0; i < n - 1; i++) for (int j = 0; j < n - 1; j++) if (i != j && rf->wslot[i] == rf->wslot[j]) goto done;
   for (int i = 0; i < n - 1; i++) if (rf->wslot[i] == rf->wslot[n - 1]) goto done;

@@ -42,6 +42,7 @@ void *poly_b200_capture_end(int discard);
 int poly_b200_graph_launch(void *exec, unsigned long long n_kernels, unsigned long long n_precompiled);
 void poly_b200_graph_destroy(void *exec);
 int poly_b200_memset_now(unsigned long long ptr, unsigned char val, size_t bytes);
+int poly_b200_timing_active(void);
 
 /* the original plan code, compiled under other names */
 PolyCompiledPlan *poly_ref_compile_schedule(PolyCtx *ctx, PolySchedule *schedule, PolyDeviceId device);
@@ -320,7 +321,8 @@ int poly_compiled_plan_run(PolyCompiledPlan *plan, void **slot_data, int n_slots
     p->base.slot_to_data[i] = p->slot_ptr[i];
   }
   p->runs++;
-  const bool graphs = !env_is("POLY_B200_GRAPH", "0") && p->graph_failures < 4 && !getenv("POLY_B200_DRYRUN");
+  const bool graphs = !env_is("POLY_B200_GRAPH", "0") && p->graph_failures < 4 && !getenv("POLY_B200_DRYRUN") &&
+                      !poly_b200_timing_active();      /* per-launch timing needs individual launches */
   if (graphs && graph_valid(p)) {
     return poly_b200_graph_launch(p->graph, (unsigned long long)p->graph_kernels, (unsigned long long)p->graph_precompiled);
   }

@@ -31,6 +31,7 @@
 #include <unordered_map>
 #include <memory>
 #include <sstream>
+#include <vector>
 
 /* ── errors ──────────────────────────────────────────────────────────── */
 static char g_last_error[1024];
@@ -601,6 +602,41 @@ static bool parse_work(const std::string &s, std::vector<WorkTerm> &out) {
   return !out.empty();
 }
 
+/* ── per-launch device timing (measurement aid) ──────────────────────── */
+static bool g_timing = false;
+static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_timing_events;
+
+extern "C" int poly_b200_timing_active(void) { return g_timing ? 1 : 0; }
+extern "C" void poly_b200_timing_begin(void) {
+  for (auto &e : g_timing_events) { cudaEventDestroy(e.first); cudaEventDestroy(e.second); }
+  g_timing_events.clear();
+  g_timing = true;
+}
+/* Stops timing and returns the summed device time of the launches since
+ * poly_b200_timing_begin, in milliseconds; *n_launches receives their count. */
+extern "C" double poly_b200_timing_end(int *n_launches) {
+  g_timing = false;
+  double total = 0.0;
+  if (R.ok && !R.dry) cudaStreamSynchronize(R.stream);
+  for (auto &e : g_timing_events) {
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, e.first, e.second) == cudaSuccess) total += ms;
+    cudaEventDestroy(e.first); cudaEventDestroy(e.second);
+  }
+  if (n_launches) *n_launches = (int)g_timing_events.size();
+  g_timing_events.clear();
+  return total;
+}
+static void timing_mark(bool before) {
+  if (!g_timing || R.dry) return;
+  if (before) {
+    cudaEvent_t a, b;
+    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+    g_timing_events.push_back({a, b});
+    cudaEventRecord(a, R.stream);
+  } else if (!g_timing_events.empty()) cudaEventRecord(g_timing_events.back().second, R.stream);
+}
+
 extern "C" PolyCudaProgram *poly_compile_cuda(const char *source, const char *fn_name) {
   if (!ready()) return nullptr;
   if (!source) { pb_set_error("poly_compile_cuda: null source"); return nullptr; }
@@ -676,7 +712,9 @@ extern "C" int poly_cuda_launch(PolyCudaProgram *prog, void **args, int n_args,
   }
   if (prog->kind == PolyCudaProgram::AOT) {
     if (R.dry) return 0;
+    timing_mark(true);
     int rc = prog->aot->launch(bufs, R.stream);
+    timing_mark(false);
     if (rc == 0) pb_count_launch(true, prog->aot->n_launches());
     return rc;
   }
@@ -702,8 +740,10 @@ extern "C" int poly_cuda_launch(PolyCudaProgram *prog, void **args, int n_args,
   for (int i = 0; i < prog->n_params; i++) kargs[n++] = &bufs[i];
   for (int v = 0; v < prog->n_vars; v++) kargs[n++] = &vars[v];
   kargs[n++] = &work;
+  timing_mark(true);
   CUresult_ rc = DRV.LaunchKernel(prog->module->fn, (unsigned)grid, 1, 1, (unsigned)prog->block, 1, 1, 0,
                                   (CUstream_)R.stream, kargs, nullptr);
+  timing_mark(false);
   if (rc != 0) { const char *s = "?"; DRV.GetErrorString(rc, &s); pb_set_error("cuLaunchKernel(%s): %s", prog->name.c_str(), s); return -1; }
   pb_count_launch(false, 1);
   return 0;

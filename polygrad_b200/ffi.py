@@ -141,6 +141,9 @@ def _declare_cuda(lib):
     _sig(lib, 'poly_b200_synchronize', ctypes.c_int, [])
     _sig(lib, 'poly_b200_stream', _ptr, [])
     _sig(lib, 'poly_b200_trim', None, [])
+    _sig(lib, 'poly_b200_timing_begin', None, [])
+    _sig(lib, 'poly_b200_timing_end', ctypes.c_double, [ctypes.POINTER(ctypes.c_int)])
+    _sig(lib, 'poly_b200_timing_active', ctypes.c_int, [])
     LL = ctypes.c_longlong
     _sig(lib, 'poly_b200_gemm', ctypes.c_int, [LL, LL, LL, _ptr, LL, LL, _ptr, LL, LL, _ptr, LL, _ptr,
                                                ctypes.c_int, ctypes.c_int])

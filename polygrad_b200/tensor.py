@@ -262,10 +262,9 @@ class Tensor:
         np_dt = _NP.get(self.dtype, np.float32)
         out_buf = lib.poly_buffer_by_id(dev.ctx, n, ffi.DTYPE_IDS[self.dtype])
         out = np.zeros(n, dtype=np_dt)
-        uop = self.uop
-        if len(self.shape) != 1:
-            uop = lib.poly_reshape(dev.ctx, uop, _i64([n]), 1)
-        store = lib.poly_store_val(dev.ctx, out_buf, uop)
+        # the value keeps its shape (as in polygrad's Tensor._realize): the scheduler then
+        # emits one range per axis instead of one flat range with div/mod indexing
+        store = lib.poly_store_val(dev.ctx, out_buf, self.uop)
         sink = lib.poly_sink1(dev.ctx, store)
         pairs = list(self.leaves) + [(out_buf, out)]
         binds = (ffi.PolyBufferBinding * len(pairs))()

@@ -80,12 +80,14 @@ def test_gpt2_plan_lowers_in_dry_run():
     r = subprocess.run([sys.executable, '-c', DRY % dict(root=ROOT)], env=env, capture_output=True, text=True,
                        timeout=900)
     assert r.returncode == 0, r.stderr[-4000:]
-    kinds = re.findall(r'^//kind (\w+)', r.stderr, flags=re.M)
+    # one program per scheduled kernel (polygrad's count for GPT-2 is 10 + 26 per layer) ...
     n_layer = 2
-    assert len(kinds) == 10 + 26 * n_layer          # polygrad's kernel count for GPT-2
-    assert kinds.count('gather') == 2               # token and position embeddings
-    assert kinds.count('gemm') == 6 * n_layer + 1   # qkv, scores, attn.v, c_proj, fc, proj per layer + logits
-    launches = re.findall(r'^//launch (\w+)', r.stderr, flags=re.M)
-    assert launches.count('group') >= 4 * n_layer   # LN mean/var and softmax max/sum rows
+    per_kernel = re.findall(r'^=== CUDA KERNEL plan\d+_k\d+ ===\n//PB200 1\n//kind (\w+)', r.stderr, flags=re.M)
+    assert len(per_kernel) == 10 + 26 * n_layer
+    assert per_kernel.count('gather') == 2               # token and position embeddings
+    assert per_kernel.count('gemm') == 6 * n_layer + 1   # qkv, scores, attn.v, c_proj, fc, proj per layer + logits
+    # ... plus the programs the plan passes build from them
+    fused = re.findall(r'^=== CUDA KERNEL rowfused_k\d+ ===', r.stderr, flags=re.M)
+    assert len(fused) >= 3 * n_layer + 1                  # LN1, softmax, LN2 per layer + final LN
     stats = json.loads(r.stdout.strip().splitlines()[-1])
     assert stats['memsets_executed'] <= 4           # zero fills are elided when kernels overwrite whole buffers
