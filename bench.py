@@ -147,7 +147,7 @@ class DevArray:
 
 
 def run_b200(args, cfg, rank, world, local_rank):
-    from polygrad_b200 import ffi
+    from polygrad_b200 import ffi, shard
     from polygrad_b200.instance import Instance, gpt2_init
 
     if args.dtype == 'bf16':
@@ -168,8 +168,7 @@ def run_b200(args, cfg, rank, world, local_rank):
     inst = Instance.gpt2(lib, **cfg)
     inst.init_params(gpt2_init(SEED))          # replicas: same weights on every rank
     inst.set_device(ffi.DEVICE_CUDA)
-    rng = np.random.default_rng([SEED, rank])  # each rank's own shard of the batch
-    tokens = rng.integers(0, V, (B, T)).astype(np.float32)
+    tokens = shard.shard_tokens(SEED, rank, B, T, V)   # each rank's own rows of the global batch
     inputs = inst.gpt2_inputs(tokens)
     out_idx = inst.bufs['output'][0]
     n_logits = B * T * V
@@ -217,7 +216,7 @@ def run_b200(args, cfg, rank, world, local_rank):
             with torch.cuda.stream(ext):
                 if args.gather != 'full':
                     src.copy_(logits[:, -1, :])
-                dist.gather(src, dst, dst=0)
+                shard.gather_to_root(dist, src, dst, rank)
 
     def barrier():
         lib.poly_b200_synchronize()
@@ -245,10 +244,7 @@ def run_b200(args, cfg, rank, world, local_rank):
         lib.poly_b200_event_destroy(e0); lib.poly_b200_event_destroy(e1)
         del wall_ms
         if dist is not None:
-            import torch
-            t = torch.tensor([ms], dtype=torch.float64, device='cuda')
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+            ms = shard.max_over_ranks(dist, ms, device='cuda')
         return ms / steps
 
     for _ in range(args.warmup):

@@ -740,7 +740,7 @@ static char *render_vec_elementwise(PbKern *k, const int *usage) {
   int nl = collect_loads(k, pb_kern_node(k, st->value), loads, 24, 0, seen);
   free(seen);
   if (nl >= 24) return NULL;
-  bool vec_load[24];
+  bool vec_load[24], rev_load[24];
   for (int i = 0; i < nl; i++) {
     PolyUOp *ld = k->nodes[loads[i].node].u;
     PolyUOp *ix = ld->src[0];
@@ -757,11 +757,18 @@ static char *render_vec_elementwise(PbKern *k, const int *usage) {
     pb_fit_affine(k, ix->src[1], m, &loads[i].aff);
     if (!loads[i].aff.ok) return NULL;
     int64_t sx = loads[i].aff.stride[x];
+    rev_load[i] = false;
     if (sx == 1) {
       if (loads[i].aff.offset % 4) return NULL;
       for (int j = 0; j < st->n_loop; j++)
         if (st->loop[j] != x && loads[i].aff.stride[st->loop[j]] % 4) return NULL;
       vec_load[i] = true;
+    } else if (sx == -1) {
+      /* a flipped axis: elements x..x+3 are the 4 words ending at offset - x, reversed */
+      if ((loads[i].aff.offset - 3) % 4) return NULL;
+      for (int j = 0; j < st->n_loop; j++)
+        if (st->loop[j] != x && loads[i].aff.stride[st->loop[j]] % 4) return NULL;
+      vec_load[i] = true; rev_load[i] = true;
     } else if (sx == 0) vec_load[i] = false;
     else return NULL;
     /* bounds: the largest index must stay inside the buffer */
@@ -805,6 +812,10 @@ static char *render_vec_elementwise(PbKern *k, const int *usage) {
     "  const uint4 v = *reinterpret_cast<const uint4*>(p);\n"
     "  memcpy(o, &v, 16);\n"
     "}\n"
+    "template <class T> __device__ __forceinline__ void pb_ld4r(const T* p, T* o) {\n"
+    "  const uint4 v = *reinterpret_cast<const uint4*>(p);\n"
+    "  T t[4]; memcpy(t, &v, 16); o[0] = t[3]; o[1] = t[2]; o[2] = t[1]; o[3] = t[0];\n"
+    "}\n"
     "template <class T> __device__ __forceinline__ void pb_st4(T* p, const T* o) {\n"
     "  uint4 v; memcpy(&v, o, 16);\n"
     "  *reinterpret_cast<uint4*>(p) = v;\n"
@@ -834,12 +845,14 @@ static char *render_vec_elementwise(PbKern *k, const int *usage) {
     PolyUOp *ix = ld->src[0];
     PolyDType base = ix->src[0]->dtype; base.is_ptr = false; base.count = 1;
     const char *pt = pb_ctype(base);
-    ind(&g); pb_str_printf(g.o, "%s l%d_[4]; { %s o_ = %lld", pt, loads[i].node, g.idx_t, (long long)loads[i].aff.offset);
+    ind(&g); pb_str_printf(g.o, "%s l%d_[4]; { %s o_ = %lld", pt, loads[i].node, g.idx_t,
+                           (long long)(loads[i].aff.offset - (rev_load[i] ? 3 : 0)));
     for (int j = 0; j < st->n_loop; j++) {
       int64_t s = loads[i].aff.stride[st->loop[j]];
       if (s) pb_str_printf(g.o, " + r%d*%lld", st->loop[j], (long long)s);
     }
-    pb_str_printf(g.o, "; pb_ld4(p%d + o_, l%d_); }\n", (int)ix->src[0]->arg.i, loads[i].node);
+    if (rev_load[i]) pb_str_printf(g.o, "; pb_ld4r(p%d + o_, l%d_); }\n", (int)ix->src[0]->arg.i, loads[i].node);
+    else pb_str_printf(g.o, "; pb_ld4(p%d + o_, l%d_); }\n", (int)ix->src[0]->arg.i, loads[i].node);
   }
   ind(&g); {
     PolyDType base = ob; base.is_ptr = false; base.count = 1;

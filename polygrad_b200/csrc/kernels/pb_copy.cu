@@ -37,6 +37,34 @@ __global__ void __launch_bounds__(256) pb200_transpose_tiles(const TransposeArgs
   }
 }
 
+/* 64 x 64 tiles, 128-bit global accesses on both sides (X, Y multiples of 4 and
+ * 16-byte aligned rows). */
+__global__ void __launch_bounds__(256) pb200_transpose_tiles_v4(const TransposeArgs a) {
+  __shared__ unsigned tile[64][65];
+  long long rem = blockIdx.z, io = a.i_off, oo = a.o_off;
+  for (int i = 0; i < a.nb; i++) { const long long x = rem % a.bext[i]; rem /= a.bext[i]; io += x * a.i_sb[i]; oo += x * a.o_sb[i]; }
+  const long long x0 = (long long)blockIdx.x * 64, y0 = (long long)blockIdx.y * 64;
+  const int q = threadIdx.x & 15, r = threadIdx.x >> 4;      /* 16 quads per row, 16 rows per pass */
+#pragma unroll
+  for (int j = 0; j < 64; j += 16) {
+    const long long x = x0 + r + j, y = y0 + q * 4;
+    if (x < a.X && y < a.Y) {
+      const uint4 v = *reinterpret_cast<const uint4 *>(a.in + io + x * a.i_sx + y);
+      tile[r + j][q * 4 + 0] = v.x; tile[r + j][q * 4 + 1] = v.y; tile[r + j][q * 4 + 2] = v.z; tile[r + j][q * 4 + 3] = v.w;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 64; j += 16) {
+    const long long y = y0 + r + j, x = x0 + q * 4;
+    if (x < a.X && y < a.Y) {
+      uint4 v;
+      v.x = tile[q * 4 + 0][r + j]; v.y = tile[q * 4 + 1][r + j]; v.z = tile[q * 4 + 2][r + j]; v.w = tile[q * 4 + 3][r + j];
+      *reinterpret_cast<uint4 *>(a.out + oo + x + y * a.o_sy) = v;
+    }
+  }
+}
+
 struct TransposeProgram : PbAotProgram {
   TransposeArgs a{};
   int p_out = 0, p_in = 1;
@@ -44,8 +72,16 @@ struct TransposeProgram : PbAotProgram {
   int launch(void *const *bufs, cudaStream_t stream) override {
     TransposeArgs g = a;
     g.out = (unsigned *)bufs[p_out]; g.in = (const unsigned *)bufs[p_in];
-    dim3 grid((unsigned)((g.X + 31) / 32), (unsigned)((g.Y + 31) / 32), (unsigned)nbatch);
-    pb200_transpose_tiles<<<grid, 256, 0, stream>>>(g);
+    bool v4 = g.X % 4 == 0 && g.Y % 4 == 0 && g.i_sx % 4 == 0 && g.o_sy % 4 == 0 && g.i_off % 4 == 0 && g.o_off % 4 == 0 &&
+              (reinterpret_cast<uintptr_t>(g.in) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.out) & 15) == 0;
+    for (int i = 0; i < g.nb; i++) if (g.i_sb[i] % 4 || g.o_sb[i] % 4) v4 = false;
+    if (v4) {
+      dim3 grid((unsigned)((g.X + 63) / 64), (unsigned)((g.Y + 63) / 64), (unsigned)nbatch);
+      pb200_transpose_tiles_v4<<<grid, 256, 0, stream>>>(g);
+    } else {
+      dim3 grid((unsigned)((g.X + 31) / 32), (unsigned)((g.Y + 31) / 32), (unsigned)nbatch);
+      pb200_transpose_tiles<<<grid, 256, 0, stream>>>(g);
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { pb_set_error("transpose launch: %s", cudaGetErrorString(e)); return -1; }
     return 0;

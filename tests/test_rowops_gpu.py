@@ -63,6 +63,16 @@ def test_movement_bit_exact(devices, name, shape):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), name
 
 
+@pytest.mark.parametrize('shape', [(3, 64, 128), (2, 100, 36), (4, 31, 50)], ids=str)
+def test_batched_transpose_bit_exact(devices, shape):
+    cpu, cuda = devices
+    x = np.random.default_rng(11).standard_normal(shape).astype(np.float32)
+    want = cpu.tensor(x).permute(0, 2, 1).numpy()
+    got = cuda.tensor(x).permute(0, 2, 1).numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert np.array_equal(got, x.transpose(0, 2, 1))
+
+
 def test_matmul_small(devices):
     cpu, cuda = devices
     rng = np.random.default_rng(3)
