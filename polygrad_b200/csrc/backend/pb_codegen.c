@@ -450,6 +450,10 @@ static const char *PRELUDE =
   "  T t; memcpy(&t, &s, sizeof(T)); return t;\n"
   "}\n";
 
+/* Parameter (index + 1) whose buffer holds bfloat16 although the kernel computes
+ * its value as float; 0 = none.  Set around one render call only. */
+static int s_bf16_out_param1 = 0;
+
 static void emit_signature(Gen *g, const bool *written, int block) {
   PbKern *k = g->k;
   pb_str_printf(g->o, "extern \"C\" __global__ void __launch_bounds__(%d) pb200_kernel(", block);
@@ -461,6 +465,7 @@ static void emit_signature(Gen *g, const bool *written, int block) {
     PolyDType base = k->params[i]->dtype; base.is_ptr = false; base.count = 1;
     const char *ct = pb_ctype(base);
     if (!ct) { g->failed = true; ct = "float"; }
+    if (s_bf16_out_param1 == i + 1) ct = "__nv_bfloat16";
     pb_str_printf(g->o, "%s%s* __restrict__ p%d", written[i] ? "" : "const ", ct, i);
   }
   for (int v = 0; v < k->n_vars; v++) {
@@ -732,6 +737,8 @@ static char *render_vec_elementwise(PbKern *k, const int *usage) {
   for (int i = 0; i < st->n_loop; i++) m |= (uint64_t)1 << st->loop[i];
   PolyDType ob = k->params[st->param]->dtype;
   if (ob.bitsize != 32 || (ob.priority != 13 && ob.priority != 5 && ob.priority != 6)) return NULL;
+  const bool out_bf16 = s_bf16_out_param1 == st->param + 1;
+  if (s_bf16_out_param1 && (!out_bf16 || ob.priority != 13)) return NULL;
   if (saff.offset % 4) return NULL;
   for (int i = 0; i < st->n_loop; i++) if (st->loop[i] != x && saff.stride[st->loop[i]] % 4) return NULL;
 
@@ -747,6 +754,7 @@ static char *render_vec_elementwise(PbKern *k, const int *usage) {
     if (ix->op != POLY_OP_INDEX || ix->src[0]->op != POLY_OP_PARAM || ix->n_src > 2) return NULL;
     if (ix->src[0]->dtype.bitsize != 32) return NULL;
     if ((int)ix->src[0]->arg.i == st->param) {
+      if (out_bf16) return NULL;
       /* reading the buffer being written is only safe element-for-element */
       pb_fit_affine(k, ix->src[1], m, &loads[i].aff);
       if (!loads[i].aff.ok) return NULL;
@@ -893,7 +901,11 @@ static char *render_vec_elementwise(PbKern *k, const int *usage) {
     int64_t s = saff.stride[st->loop[j]];
     if (s) pb_str_printf(g.o, " + r%d*%lld", st->loop[j], (long long)s);
   }
-  pb_str_printf(g.o, "; pb_st4(p%d + o_, o4_); }\n", st->param);
+  if (out_bf16)
+    pb_str_printf(g.o, "; __nv_bfloat162 q0_ = __floats2bfloat162_rn(o4_[0], o4_[1]), q1_ = __floats2bfloat162_rn(o4_[2], o4_[3]); "
+                       "uint2 w_; w_.x = *reinterpret_cast<unsigned*>(&q0_); w_.y = *reinterpret_cast<unsigned*>(&q1_); "
+                       "*reinterpret_cast<uint2*>(p%d + o_) = w_; }\n", st->param);
+  else pb_str_printf(g.o, "; pb_st4(p%d + o_, o4_); }\n", st->param);
   pb_str_puts(g.o, "}\n");
 
   char *res = NULL;
@@ -902,6 +914,7 @@ static char *render_vec_elementwise(PbKern *k, const int *usage) {
     char line[256];
     snprintf(line, sizeof line, "//launch flat block=256 work=c%lld", (long long)n_threads);
     emit_header(k, &h, line, usage);
+    if (out_bf16) pb_str_puts(&h, "#include <cuda_bf16.h>\n");
     pb_str_puts(&h, g.out.s);
     res = pb_str_take(&h);
   }
@@ -1024,6 +1037,19 @@ char *pb_render_jit(PbKern *k, const char *fn_name) {
     if (r) return r;
   }
   return render_flat(k, usage);
+}
+
+/* The kernel's one elementwise store rendered so that its float values land in a
+ * bfloat16 buffer of the same element layout (round to nearest even).  NULL when
+ * the kernel is not a vectorisable elementwise kernel with a float output. */
+char *pb_render_elementwise_bf16(PbKern *k) {
+  if (k->n_stores != 1 || k->n_reduce_nodes != 0) return NULL;
+  int usage[PB_MAX_PARAMS];
+  param_usage(k, usage);
+  s_bf16_out_param1 = k->stores[0].param + 1;
+  char *r = render_vec_elementwise(k, usage);
+  s_bf16_out_param1 = 0;
+  return r;
 }
 
 /* ════════════════════════════════════════════════════════════════════════

@@ -112,6 +112,32 @@ static int step_out_slot(const PbPlan *p, const PbStep *st) {
   return -1;
 }
 
+/* Renders the member steps order[0..no) (the last one is the final kernel) as one
+ * row kernel; NULL when the chain does not have a supported form. */
+static char *render_chain(const PbPlan *p, const int *order, int no, bool out_bf16, PbFuseOut *fo) {
+  PbKern kerns[CHAIN_MAX]; PbFuseIn in[CHAIN_MAX]; int slots[CHAIN_MAX][PB_MAX_PARAMS];
+  bool built = true; int n_phase = 0;
+  int nb = 0;
+  for (int j = 0; j < no && built; j++) {
+    const PbStep *m = &p->steps[order[j]];
+    const int *own = m->slot; int n_own = m->n_params;
+    /* a step that already is a fused chain carries the fused parameter list; its
+     * own kernel's parameters are those of the schedule item */
+    if (m->fused_rows) { own = p->base.schedule->items[m->item].buf_slot_indices; n_own = p->base.schedule->items[m->item].n_buf_slots; }
+    if (pb_kern_build(&kerns[j], m->sink) != 0) { pb_kern_free(&kerns[j]); built = false; break; }
+    nb = j + 1;
+    for (int a = 0; a < PB_MAX_PARAMS; a++) slots[j][a] = -1;
+    for (int a = 0; a < n_own && a < PB_MAX_PARAMS; a++) slots[j][a] = pb_plan_resolve(p, own[a]);
+    in[j].k = &kerns[j]; in[j].slot = slots[j];
+    in[j].role = (j == no - 1) ? PB_FUSE_FINAL : (kerns[j].n_reduce_nodes ? PB_FUSE_PHASE : PB_FUSE_PRODUCER);
+    if (in[j].role == PB_FUSE_PHASE) n_phase++;
+  }
+  char *text = NULL;
+  if (built && n_phase > 0) text = pb_render_rowfused(in, no, out_bf16, fo);
+  for (int j = 0; j < nb; j++) pb_kern_free(&kerns[j]);
+  return text;
+}
+
 static int fuse_rows(PbPlan *p) {
   int fused = 0;
   SlotUse *u = malloc(sizeof(SlotUse) * (size_t)p->n_slots);
@@ -169,22 +195,8 @@ static int fuse_rows(PbPlan *p) {
     }
     if (hazard) continue;
 
-    PbKern kerns[CHAIN_MAX]; PbFuseIn in[CHAIN_MAX]; int slots[CHAIN_MAX][PB_MAX_PARAMS];
-    bool built = true; int n_phase = 0;
-    int nb = 0;
-    for (int j = 0; j < no && built; j++) {
-      PbStep *m = &p->steps[order[j]];
-      if (pb_kern_build(&kerns[j], m->sink) != 0) { pb_kern_free(&kerns[j]); built = false; break; }
-      nb = j + 1;
-      for (int a = 0; a < PB_MAX_PARAMS; a++) slots[j][a] = -1;
-      for (int a = 0; a < m->n_params; a++) slots[j][a] = pb_plan_resolve(p, m->slot[a]);
-      in[j].k = &kerns[j]; in[j].slot = slots[j];
-      in[j].role = (j == no - 1) ? PB_FUSE_FINAL : (kerns[j].n_reduce_nodes ? PB_FUSE_PHASE : PB_FUSE_PRODUCER);
-      if (in[j].role == PB_FUSE_PHASE) n_phase++;
-    }
-    char *text = NULL; PbFuseOut fo;
-    if (built && n_phase > 0) text = pb_render_rowfused(in, no, false, &fo);
-    for (int j = 0; j < nb; j++) pb_kern_free(&kerns[j]);
+    PbFuseOut fo;
+    char *text = render_chain(p, order, no, false, &fo);
     if (!text) continue;
     char name[64]; snprintf(name, sizeof name, "rowfused_k%d", p->steps[f].item);
     if (getenv("POLY_DUMP_KERNELS")) fprintf(stderr, "=== CUDA KERNEL %s ===\n%s\n=== END ===\n", name, text);
@@ -413,6 +425,101 @@ static int fuse_attention(PbPlan *p) {
   return fused;
 }
 
+
+/* ── bfloat16 storage for contraction operands ───────────────────────── */
+/* Under the bf16 contraction policy an fp32 operand is rounded to bfloat16 on
+ * its way into the tensor-core kernel.  When the operand is a plan-owned
+ * intermediate that nothing but such contractions reads, its producer can store
+ * the rounded values directly (same element layout, 2-byte elements) and the
+ * contractions read them in place: the values that reach the tensor cores are
+ * bit for bit the same, the conversion pass and half of the producer's write
+ * traffic disappear. */
+static char *hdr_with_line(const char *text, const char *line) {
+  const char *eol = strchr(text, '\n');
+  if (!eol) return NULL;
+  size_t head = (size_t)(eol - text) + 1, ll = strlen(line), tl = strlen(text);
+  char *t = malloc(tl + ll + 2);
+  memcpy(t, text, head); memcpy(t + head, line, ll); t[head + ll] = '\n';
+  memcpy(t + head + ll + 1, text + head, tl - head + 1);
+  return t;
+}
+
+static bool step_is_gemm(const PbStep *st, GHdr *h) {
+  return !st->dead && st->precompiled && st->text && parse_gemm_hdr(st->text, h);
+}
+
+static void step_set_program(PbStep *st, PolyCudaProgram *prog, char *text) {
+  poly_cuda_program_destroy(st->prog); free(st->text);
+  st->prog = prog; st->text = text;
+}
+
+#define RETYPE_MAX_READERS 4
+static int retype_bf16(PbPlan *p) {
+  if (!poly_b200_gemm_policy()) return 0;
+  int done = 0;
+  SlotUse *u = malloc(sizeof(SlotUse) * (size_t)p->n_slots);
+  for (int x = 0; x < p->n_slots; x++) {
+    if (pb_plan_resolve(p, x) != x || !p->slot_inter[x]) continue;
+    slot_usage(p, u);
+    if (u[x].writers != 1 || u[x].readers < 1 || u[x].readers > RETYPE_MAX_READERS) continue;
+    const int w = u[x].first_write;
+    PbStep *W = &p->steps[w];
+    if (W->precompiled || !W->sink || W->n_vars) continue;
+    bool whole = false;
+    for (int a = 0; a < W->n_params; a++) if (pb_plan_resolve(p, W->slot[a]) == x) whole = W->rw[a] == 'W';
+    if (!whole) continue;
+    /* every reader: a contraction that takes the slot as its A operand only */
+    int readers[RETYPE_MAX_READERS]; int nr = 0; bool ok = true;
+    for (int s = 0; s < p->n_steps && ok; s++) {
+      PbStep *R = &p->steps[s];
+      if (R->dead || !step_reads(p, R, x)) continue;
+      GHdr h;
+      if (s <= w || !step_is_gemm(R, &h) || strcmp(h.dtype, "f32") != 0 || hdr_line(R->text, "abf16", (char[8]){0}, 8)) { ok = false; break; }
+      for (int a = 0; a < R->n_params; a++)
+        if (pb_plan_resolve(p, R->slot[a]) == x && a != h.params[1]) ok = false;
+      if (ok && nr < RETYPE_MAX_READERS) readers[nr++] = s; else ok = false;
+    }
+    if (!ok || nr == 0) continue;
+    /* the producer with a bfloat16 store */
+    char *wtext = NULL; PbFuseOut fo; bool w_fused = W->fused_rows;
+    if (w_fused) wtext = render_chain(p, W->chain, W->n_chain, true, &fo);
+    else {
+      PbKern k;
+      if (pb_kern_build(&k, W->sink) == 0 && k.n_stores == 1 &&
+          pb_plan_resolve(p, W->slot[k.stores[0].param]) == x) wtext = pb_render_elementwise_bf16(&k);
+      pb_kern_free(&k);
+    }
+    if (!wtext) continue;
+    if (w_fused) {
+      bool same = fo.n_params == W->n_params;
+      for (int a = 0; same && a < fo.n_params; a++) if (fo.slot[a] != pb_plan_resolve(p, W->slot[a]) || fo.rw[a] != W->rw[a]) same = false;
+      if (!same) { free(wtext); continue; }
+    }
+    char name[64]; snprintf(name, sizeof name, "bf16out_k%d", W->item);
+    PolyCudaProgram *wprog = poly_compile_cuda(wtext, name);
+    PolyCudaProgram *rprog[RETYPE_MAX_READERS] = {0}; char *rtext[RETYPE_MAX_READERS] = {0};
+    bool all = wprog != NULL;
+    for (int i = 0; i < nr && all; i++) {
+      rtext[i] = hdr_with_line(p->steps[readers[i]].text, "//abf16 1");
+      snprintf(name, sizeof name, "gemm_abf16_k%d", p->steps[readers[i]].item);
+      rprog[i] = rtext[i] ? poly_compile_cuda(rtext[i], name) : NULL;
+      if (!rprog[i]) all = false;
+    }
+    if (!all) {
+      if (wprog) poly_cuda_program_destroy(wprog);
+      free(wtext);
+      for (int i = 0; i < nr; i++) { if (rprog[i]) poly_cuda_program_destroy(rprog[i]); free(rtext[i]); }
+      continue;
+    }
+    if (getenv("POLY_DUMP_KERNELS")) fprintf(stderr, "=== CUDA KERNEL bf16out_k%d ===\n%s\n=== END ===\n", W->item, wtext);
+    step_set_program(W, wprog, wtext);
+    for (int i = 0; i < nr; i++) step_set_program(&p->steps[readers[i]], rprog[i], rtext[i]);
+    done++;
+  }
+  free(u);
+  return done;
+}
+
 void pb_plan_fuse(PbPlan *p) {
   int copies = elide_copies(p);
   int rows = 0;
@@ -420,6 +527,9 @@ void pb_plan_fuse(PbPlan *p) {
   if (!e || strcmp(e, "copies") != 0) rows = fuse_rows(p);
   int attn = 0;
   if (!e || (strcmp(e, "copies") != 0 && strcmp(e, "rows") != 0)) attn = fuse_attention(p);
+  int bf16 = 0;
+  if (!e || strcmp(e, "nobf16") != 0) { if (!e || (strcmp(e, "copies") != 0 && strcmp(e, "rows") != 0)) bf16 = retype_bf16(p); }
   if (getenv("POLY_B200_DEBUG"))
-    fprintf(stderr, "pb_fuse: %d copy kernels elided, %d kernels folded into row kernels, %d attention chains fused\n", copies, rows, attn);
+    fprintf(stderr, "pb_fuse: %d copy kernels elided, %d kernels folded into row kernels, %d attention chains fused, "
+                    "%d operands kept in bfloat16\n", copies, rows, attn, bf16);
 }

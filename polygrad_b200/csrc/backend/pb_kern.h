@@ -100,6 +100,7 @@ const char *pb_ctype(PolyDType dt);
 /* Render the kernel as CUDA C for run-time compilation, preceded by the
  * "//PB200" header lines the runtime parses.  Returns malloc'd text or NULL. */
 char *pb_render_jit(PbKern *k, const char *fn_name);
+char *pb_render_elementwise_bf16(PbKern *k);
 
 /* Several kernels of one plan rendered as one row-wise kernel: reductions over
  * the same contiguous axis feed later kernels of the chain through registers

@@ -291,11 +291,21 @@ __global__ void __launch_bounds__(256) pb200_mask_tiles(const float *mask, long 
   const int qi = blockIdx.y, ki = blockIdx.x;
   const float *t = mask + (long long)qi * AT_BQ * sq + (long long)ki * AT_BK * sk;
   const float first = t[0];
-  bool same = true;
-  for (int e = threadIdx.x; e < AT_BQ * AT_BK; e += 256) {
-    const float v = t[(long long)(e / AT_BK) * sq + (long long)(e % AT_BK) * sk];
-    same = same && (__float_as_uint(v) == __float_as_uint(first));
+  /* differences are OR-ed, not tested one by one, so that the loads are independent */
+  unsigned diff = 0;
+  if (sk == 1 && (sq & 3) == 0 && (reinterpret_cast<uintptr_t>(t) & 15) == 0) {
+#pragma unroll 8
+    for (int e = threadIdx.x; e < AT_BQ * AT_BK / 4; e += 256) {
+      const uint4 v = *reinterpret_cast<const uint4 *>(t + (long long)(e / (AT_BK / 4)) * sq + (e % (AT_BK / 4)) * 4);
+      const unsigned f = __float_as_uint(first);
+      diff |= (v.x ^ f) | (v.y ^ f) | (v.z ^ f) | (v.w ^ f);
+    }
+  } else {
+#pragma unroll 8
+    for (int e = threadIdx.x; e < AT_BQ * AT_BK; e += 256)
+      diff |= __float_as_uint(t[(long long)(e / AT_BK) * sq + (long long)(e % AT_BK) * sk]) ^ __float_as_uint(first);
   }
+  const bool same = diff == 0;
   const int all = __syncthreads_and(same ? 1 : 0);
   if (threadIdx.x == 0) out[qi * nk + ki] = (all && first == first) ? first : __int_as_float(0x7fc00000);
 }

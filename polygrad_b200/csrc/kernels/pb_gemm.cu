@@ -418,10 +418,10 @@ void *PbGemmProgram::pack_operand(const void *src, long long off, bool is_a, int
 
 int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
   launches = 0;
-  if (dtype == PB_BF16 || pb_gemm_policy_bf16()) {
+  if (dtype == PB_BF16 || a_bf16 || c_bf16 || pb_gemm_policy_bf16()) {
     int rc = pb_gemm_tc_run(*this, bufs, stream);
     if (rc != PB_TC_UNSUPPORTED) return rc;
-    if (dtype == PB_BF16) { pb_set_error("gemm: bf16 operands need the tensor-core kernel, which rejected this shape"); return -1; }
+    if (dtype == PB_BF16 || a_bf16 || c_bf16) { pb_set_error("gemm: bf16 operands need the tensor-core kernel, which rejected this shape"); return -1; }
   }
   SgemmArgs g{};
   void *pa = nullptr, *pb = nullptr;
@@ -543,6 +543,11 @@ PbGemmProgram *pb_parse_gemm(const PbHeader &h0, const char *prefix, std::string
   }
   bool x_is_c = p->has_x && p->p_x == p->p_c;
   p->rw[(size_t)p->p_c] = x_is_c ? 'b' : (dense ? 'W' : 'w');
+  p->a_bf16 = h.geti("abf16") != 0;
+  p->c_bf16 = h.geti("cbf16") != 0;
+  if ((p->a_bf16 || p->c_bf16) && (p->dtype != PB_F32 || x_is_c || !pb_gemm_tc_static_ok(*p))) {
+    err = "gemm: bfloat16 operand/result storage is not possible for this shape"; delete p; return nullptr;
+  }
   return p;
 }
 

@@ -33,6 +33,8 @@ struct PbGemmProgram : PbAotProgram {
   int dtype = PB_F32;                 /* storage type of A and B */
   long long off_c = 0, off_a = 0, off_b = 0, off_x = 0;
   bool relu = false, has_x = false;
+  bool a_bf16 = false;                /* A's buffer holds bfloat16 (same element layout) although dtype is f32 */
+  bool c_bf16 = false;                /* C is written as bfloat16 (round to nearest even) into the same element layout */
   std::vector<PbGemmAxis> m_ax, n_ax, k_ax, b_ax;   /* m, n by output stride (largest first); k by A stride */
   long long M = 1, N = 1, K = 1, nbatch = 1;
   bool a_direct = false, b_direct = false;          /* strides nest: usable without packing */
@@ -59,6 +61,11 @@ bool pb_attention_supported(long long T, long long hd);
 int pb_attention_launch(const void *qb, const void *kb, const void *vtb, const float *mask, long long mask_sq, long long mask_sk,
                         float scale, float *out, int nb, const int *bext, const long long *o_sb, long long o_sm,
                         long long BH, long long T, cudaStream_t stream);
+
+/* Can the tensor-core kernel run this problem whatever the buffer addresses are
+ * (16-byte aligned bases assumed), reading A in place when a_bf16 and writing
+ * bfloat16 when c_bf16? */
+bool pb_gemm_tc_static_ok(const PbGemmProgram &p);
 
 /* Tensor-core path: returns 0 / -1, or PB_TC_UNSUPPORTED when the shape is not handled. */
 int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream);

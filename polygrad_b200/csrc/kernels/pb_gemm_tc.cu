@@ -47,6 +47,7 @@ struct TcArgs {
   int nb; int bext[4]; long long c_sb[4], x_sb[4];
   int has_x, relu;
   int vec_io;                      /* C rows (and addend rows) 16-byte aligned, N % 4 == 0 */
+  int c_bf16;                      /* C holds bfloat16 (needs vec_io) */
   int tiles_m, tiles_n, n_tiles;   /* n_tiles = nbatch * tiles_m * tiles_n */
 };
 
@@ -199,6 +200,12 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                   if (xp) { const float4 x4 = *reinterpret_cast<const float4 *>(xp); v.x += x4.x; v.y += x4.y; v.z += x4.z; v.w += x4.w; }
                   else { v.x += xb.x; v.y += xb.y; v.z += xb.z; v.w += xb.w; }
                   if (g.relu) { v.x = (0.f < v.x) ? v.x : 0.f; v.y = (0.f < v.y) ? v.y : 0.f; v.z = (0.f < v.z) ? v.z : 0.f; v.w = (0.f < v.w) ? v.w : 0.f; }
+                  if (g.c_bf16) {
+                    /* same element offset, 2-byte elements */
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                    uint2 w; w.x = *reinterpret_cast<const uint32_t *>(&lo); w.y = *reinterpret_cast<const uint32_t *>(&hi);
+                    *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(g.C) + (cp - g.C)) = w;
+                  } else
                   *reinterpret_cast<float4 *>(cp) = v;
                 }
                 cp += cstep;
@@ -335,8 +342,8 @@ static const void *tc_operand(PbGemmProgram &p, PbTcOperand &cache, const void *
  * place by TMA; anything else goes through tc_operand. */
 struct TcView { const void *ptr; long long pitch, bpitch; };
 
-static bool tc_in_place(PbGemmProgram &p, const void *buf, long long off, bool is_a, TcView *v) {
-  if (p.dtype != PB_BF16) return false;
+static bool tc_in_place(const PbGemmProgram &p, const void *buf, long long off, bool is_a, TcView *v) {
+  if (p.dtype != PB_BF16 && !(is_a && p.a_bf16)) return false;
   const bool direct = is_a ? p.a_direct : p.b_direct;
   const long long sk = is_a ? p.a_sk : p.b_sk, srow = is_a ? p.a_sm : p.b_sn;
   const long long rows = is_a ? p.M : p.N;
@@ -349,6 +356,25 @@ static bool tc_in_place(PbGemmProgram &p, const void *buf, long long off, bool i
   return true;
 }
 
+bool pb_gemm_tc_static_ok(const PbGemmProgram &p) {
+  if (p.c_sn != 1 && !(p.c_sm == 1 && p.M > 1)) return false;
+  if (p.K < 16) return false;
+  TcView v;
+  if (p.a_bf16 && !tc_in_place(p, nullptr, p.off_a, true, &v)) return false;
+  if (p.c_bf16) {
+    const bool swap = p.c_sn != 1 || p.N == 1;
+    const long long c_sm = swap ? p.c_sn : p.c_sm, N = swap ? p.M : p.N;
+    if (c_sm % 4 || N % 4 || p.off_c % 4) return false;
+    for (auto &a : p.b_ax) if (a.sc % 4) return false;
+    if (p.has_x) {
+      const long long x_sn = swap ? p.x_sm : p.x_sn, x_sm = swap ? p.x_sn : p.x_sm;
+      if (x_sn != 1 || x_sm % 4 || p.off_x % 4) return false;
+      for (auto &a : p.b_ax) if (a.sx % 4) return false;
+    }
+  }
+  return true;
+}
+
 int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
   /* output must be a row-major (or column-major: swap roles) matrix per batch entry */
   bool swap = false;
@@ -358,6 +384,7 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
   void *scr_a = nullptr, *scr_b = nullptr;
   TcView va, vb;
   if (!tc_in_place(p, bufs[p.p_a], p.off_a, true, &va)) {
+    if (p.a_bf16) { pb_set_error("gemm: bfloat16 A operand is not addressable in place (alignment)"); return -1; }
     va.ptr = tc_operand(p, p.tc_a, bufs[p.p_a], p.off_a, true, p.M, Kp, stream, &scr_a);
     va.pitch = Kp; va.bpitch = p.M * Kp;
   }
@@ -387,6 +414,15 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
       for (int i = 0; i < g.nb; i++) if (g.x_sb[i] % 4) v = false;
     }
     g.vec_io = v ? 1 : 0;
+    g.c_bf16 = p.c_bf16 ? 1 : 0;
+    if (p.c_bf16) {
+      /* the kernel only forms element offsets from this base; elements are 2 bytes */
+      g.C = reinterpret_cast<float *>(reinterpret_cast<__nv_bfloat16 *>(bufs[p.p_c]) + p.off_c);
+      if (!v || (reinterpret_cast<uintptr_t>(bufs[p.p_c]) & 15)) {
+        pb_set_error("gemm: bfloat16 result needs 16-byte aligned rows");
+        pb_scratch_free(scr_a); pb_scratch_free(scr_b); return -1;
+      }
+    }
   }
   /* tile width: fewest waves of work over the SMs, counting a tile's cost as its width plus a fixed part */
   int BN = 256;
