@@ -16,11 +16,16 @@
  * assumed: the mask is an arbitrary additive [T, T] buffer and every block of
  * keys is processed, as in the reference.
  *
+ * Q, K and V are bfloat16 matrices of 64-element rows addressed through strides
+ * (row pitch and up to three batch strides), so the three slices of a fused
+ * qkv projection are read where they lie; V is used as stored ([key][d], the
+ * "MN-major" B operand of the second contraction), nothing is transposed.
+ *
  * One CTA per (batch*head, block of 128 query rows), 9 warps, two CTAs per SM:
- *   warp 8   lane 0 issues the TMA loads (Q once; K and Vᵀ blocks, each
+ *   warp 8   lane 0 issues the TMA loads (Q once; K and V blocks, each
  *            prefetched as soon as the MMA that read the previous one has
  *            finished) and the tcgen05.mma instructions:
- *            S = Q Kᵀ (128x128x64) into tensor memory, then PV = P Vᵀᵀ
+ *            S = Q Kᵀ (128x128x64) into tensor memory, then PV = P V
  *            (128x64x128) into another 64 columns;
  *   warps 0-7  two threads per query row (64 keys and 32 output columns each):
  *            read S from tensor memory in 32-column chunks (pass 1: x = s*scale
@@ -42,7 +47,7 @@ __device__ int pb200_attn_error_flag = 0;
 #define AT_BK 128      /* keys per block */
 #define AT_HD 64
 #define AT_THREADS 288
-#define AT_SMEM (16384 /*Q*/ + 16384 /*K*/ + 16384 /*Vt: 2 x 8 KB*/ + 32768 /*P: 2 x 16 KB*/ + 256 + 1024)
+#define AT_SMEM (16384 /*Q*/ + 16384 /*K*/ + 16384 /*V: 128 keys x 128 B*/ + 32768 /*P: 2 x 16 KB*/ + 256 + 1024)
 
 /* 2^x by the special-function unit (ex2.approx: relative error about 2^-22; the
  * results are rounded to bfloat16 right after). */
@@ -59,12 +64,13 @@ struct AttnArgs {
   int mask_vec;                   /* mask rows contiguous and 16-byte aligned */
   const float *tile_const;        /* per (query block, key block): NaN if the mask tile varies, else its one value */
   int T, n_qblocks;
-  int nb; int bext[4]; long long o_sb[4]; long long o_sm;   /* O[batch..][row*o_sm + d] */
+  int nb; int bext[3]; long long o_sb[3]; long long o_sm;   /* O[batch..][row*o_sm + d] */
+  int out_bf16;                   /* O holds bfloat16 (same element offsets) */
 };
 
 __global__ void __launch_bounds__(AT_THREADS, 2)
 pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                 const __grid_constant__ CUtensorMap map_vt, const AttnArgs g) {
+                 const __grid_constant__ CUtensorMap map_v, const AttnArgs g) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -98,16 +104,23 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
   if (warp == 8) {
     if (lane == 0) {
-      /* instruction descriptors: bf16 x bf16 -> fp32, both operands K-major, M = 128 */
+      /* instruction descriptors: bf16 x bf16 -> fp32, M = 128.  S: both operands K-major.
+       * PV: A (P) K-major, B (V) MN-major (bit 16): V's rows are keys (K), each 64 contiguous d (N). */
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BK >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-      const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_HD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(AT_HD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      int c0 = 0, c1 = 0, c2 = 0;
+      {
+        int rem = bh;
+        if (g.nb > 0) { c0 = rem % g.bext[0]; rem /= g.bext[0]; }
+        if (g.nb > 1) { c1 = rem % g.bext[1]; rem /= g.bext[1]; }
+        if (g.nb > 2) { c2 = rem % g.bext[2]; }
+      }
       mbar_expect_tx(bar_q, 16384);
-      tma_load_3d(s_q, &map_q, bar_q, 0, qb * AT_BQ, bh);
+      tma_load_5d(s_q, &map_q, bar_q, 0, qb * AT_BQ, c0, c1, c2);
       mbar_expect_tx(bar_k, 16384);
-      tma_load_3d(s_k, &map_k, bar_k, 0, 0, bh);
+      tma_load_5d(s_k, &map_k, bar_k, 0, 0, c0, c1, c2);
       mbar_expect_tx(bar_v, 16384);
-      tma_load_3d(s_v, &map_vt, bar_v, 0, 0, bh);
-      tma_load_3d(s_v + 8192, &map_vt, bar_v, 64, 0, bh);
+      tma_load_5d(s_v, &map_v, bar_v, 0, 0, c0, c1, c2);
       bool ok = mbar_wait(bar_q, 0, &abort_flag, 11) && mbar_wait(bar_k, 0, &abort_flag, 12);
       const uint64_t dq = make_smem_desc(s_q), dk = make_smem_desc(s_k);
       if (ok) {
@@ -120,15 +133,18 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const uint32_t ph = (uint32_t)j & 1u;
         /* K is free once S is complete: prefetch the next block of keys */
         if (!mbar_wait(bar_s, ph, &abort_flag, 13)) break;
-        if (j + 1 < nkb) { mbar_expect_tx(bar_k, 16384); tma_load_3d(s_k, &map_k, bar_k, 0, (j + 1) * AT_BK, bh); }
+        if (j + 1 < nkb) { mbar_expect_tx(bar_k, 16384); tma_load_5d(s_k, &map_k, bar_k, 0, (j + 1) * AT_BK, c0, c1, c2); }
         if (!mbar_wait(bar_p, ph, &abort_flag, 14)) break;     /* P written, S and the previous PV consumed */
         if (!mbar_wait(bar_v, ph, &abort_flag, 15)) break;
         tc_fence_after_sync();
+        /* 16 keys per instruction: 32 bytes along a row of P (K-major), two 8-key groups
+         * of 1024 bytes of V (MN-major: the stride between 8-key groups is the descriptor's
+         * stride byte offset, 1024) */
 #pragma unroll
         for (int h = 0; h < 2; h++) {
           const uint64_t da = make_smem_desc(s_p + h * 16384), db = make_smem_desc(s_v + h * 8192);
 #pragma unroll
-          for (int k = 0; k < 4; k++) tc_mma_bf16(tmem_pv, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_o, (h | k) ? 1u : 0u);
+          for (int k = 0; k < 4; k++) tc_mma_bf16(tmem_pv, da + (uint64_t)(k * 2), db + (uint64_t)(k * 128), idesc_o, (h | k) ? 1u : 0u);
         }
         tc_commit(bar_o);
         /* the next block's scores follow at once: S is free, and the softmax threads find
@@ -143,8 +159,7 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (!mbar_wait(bar_o, ph, &abort_flag, 16)) break;
         if (j + 1 < nkb) {
           mbar_expect_tx(bar_v, 16384);
-          tma_load_3d(s_v, &map_vt, bar_v, (j + 1) * AT_BK, 0, bh);
-          tma_load_3d(s_v + 8192, &map_vt, bar_v, (j + 1) * AT_BK + 64, 0, bh);
+          tma_load_5d(s_v, &map_v, bar_v, 0, (j + 1) * AT_BK, c0, c1, c2);
         }
       }
     }
@@ -266,11 +281,26 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const float l_tot = l_run + xchg[half ^ 1][row];
       int rem = bh; long long ob = 0;
       for (int i = 0; i < g.nb; i++) { const int x = rem % g.bext[i]; rem /= g.bext[i]; ob += x * g.o_sb[i]; }
-      float *o = g.O + ob + q * g.o_sm + half * 32;
+      const long long oe = ob + q * g.o_sm + half * 32;
       const float inv = 1.0f / l_tot;
+      if (g.out_bf16) {
+        __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(g.O) + oe;
 #pragma unroll
-      for (int d = 0; d < 32; d += 4)
-        *reinterpret_cast<float4 *>(o + d) = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
+        for (int d = 0; d < 32; d += 8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const __nv_bfloat162 v2 = __floats2bfloat162_rn(acc[d + 2 * i] * inv, acc[d + 2 * i + 1] * inv);
+            w[i] = *reinterpret_cast<const uint32_t *>(&v2);
+          }
+          *reinterpret_cast<uint4 *>(o + d) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else {
+        float *o = g.O + oe;
+#pragma unroll
+        for (int d = 0; d < 32; d += 4)
+          *reinterpret_cast<float4 *>(o + d) = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
+      }
     }
   }
 
@@ -320,14 +350,26 @@ static EncodeTiledFn attn_encode() {
   return fn;
 }
 
-static int attn_map(CUtensorMap *map, const void *ptr, long long inner, long long rows, long long nbatch, int box_inner, int box_rows) {
+/* bf16 rows of 64, `T` rows `row_stride` elements apart, batch axes bext[i] with strides bs[i] */
+static int attn_map(CUtensorMap *map, const PbAttnOperand &op, long long T, int nb, const int *bext, int box_rows) {
   EncodeTiledFn enc = attn_encode();
   if (!enc) { pb_set_error("attention: cuTensorMapEncodeTiled not available"); return -1; }
-  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)nbatch};
-  cuuint64_t strides[2] = {(cuuint64_t)inner * 2, (cuuint64_t)rows * inner * 2};
-  cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult rc = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+  if ((reinterpret_cast<uintptr_t>(op.ptr) & 15) || op.row_stride % 8 || op.row_stride < AT_HD) {
+    pb_set_error("attention: operand rows must be 16-byte aligned"); return -1;
+  }
+  cuuint64_t dims[5] = {AT_HD, (cuuint64_t)T, 1, 1, 1};
+  cuuint64_t strides[4] = {(cuuint64_t)op.row_stride * 2, 0, 0, 0};
+  cuuint64_t span = (cuuint64_t)T * (cuuint64_t)op.row_stride * 2;
+  for (int i = 0; i < 3; i++) {
+    if (i < nb) {
+      if (op.bstride[i] <= 0 || op.bstride[i] % 8) { pb_set_error("attention: operand batch strides must be positive multiples of 8 elements"); return -1; }
+      dims[2 + i] = (cuuint64_t)bext[i]; strides[1 + i] = (cuuint64_t)op.bstride[i] * 2;
+      if (strides[1 + i] * dims[2 + i] > span) span = strides[1 + i] * dims[2 + i];
+    } else strides[1 + i] = span;          /* an axis of extent 1: any 16-byte multiple */
+  }
+  cuuint32_t box[5] = {AT_HD, (cuuint32_t)box_rows, 1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult rc = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void *>(op.ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) { pb_set_error("attention: cuTensorMapEncodeTiled failed (%d)", (int)rc); return -1; }
@@ -342,12 +384,18 @@ int pb_attention_error(void) {
 
 bool pb_attention_supported(long long T, long long hd) { return hd == AT_HD && T >= AT_BK && T % AT_BK == 0; }
 
-/* qb, kb: bf16 [BH][T][64]; vtb: bf16 [BH][64][T]; mask fp32 [T x T] via strides; out fp32. */
-int pb_attention_launch(const void *qb, const void *kb, const void *vtb, const float *mask, long long mask_sq, long long mask_sk,
-                        float scale, float *out, int nb, const int *bext, const long long *o_sb, long long o_sm,
+/* q, k, v: bf16 through strides; mask fp32 [T x T] through strides; out fp32 or bf16 (out_bf16)
+ * at element offsets Σ batch_i*o_sb[i] + row*o_sm + d. */
+int pb_attention_launch(const PbAttnOperand &q, const PbAttnOperand &k, const PbAttnOperand &v,
+                        const float *mask, long long mask_sq, long long mask_sk,
+                        float scale, void *out, bool out_bf16, int nb, const int *bext, const long long *o_sb, long long o_sm,
                         long long BH, long long T, cudaStream_t stream) {
   if (!pb_attention_supported(T, AT_HD)) { pb_set_error("attention: unsupported sequence length %lld", T); return -1; }
-  if ((reinterpret_cast<uintptr_t>(out) & 15) || o_sm % 4) { pb_set_error("attention: output rows must be 16-byte aligned"); return -1; }
+  if (nb > 3) { pb_set_error("attention: more than three batch axes"); return -1; }
+  const int oal = out_bf16 ? 8 : 4;
+  bool o_ok = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && o_sm % oal == 0;
+  for (int i = 0; i < nb; i++) if (o_sb[i] % oal) o_ok = false;
+  if (!o_ok) { pb_set_error("attention: output rows must be 16-byte aligned"); return -1; }
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(pb200_flash_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM);
@@ -355,16 +403,15 @@ int pb_attention_launch(const void *qb, const void *kb, const void *vtb, const f
     configured = true;
   }
   CUtensorMap mq, mk, mv;
-  if (attn_map(&mq, qb, AT_HD, T, BH, 64, AT_BQ) != 0) return -1;
-  if (attn_map(&mk, kb, AT_HD, T, BH, 64, AT_BK) != 0) return -1;
-  if (attn_map(&mv, vtb, T, AT_HD, BH, 64, AT_HD) != 0) return -1;
+  if (attn_map(&mq, q, T, nb, bext, AT_BQ) != 0) return -1;
+  if (attn_map(&mk, k, T, nb, bext, AT_BK) != 0) return -1;
+  if (attn_map(&mv, v, T, nb, bext, AT_BK) != 0) return -1;
   AttnArgs g{};
-  g.O = out; g.mask = mask; g.mask_sq = mask_sq; g.mask_sk = mask_sk; g.scale = scale;
+  g.O = (float *)out; g.out_bf16 = out_bf16 ? 1 : 0; g.mask = mask; g.mask_sq = mask_sq; g.mask_sk = mask_sk; g.scale = scale;
   g.T = (int)T; g.n_qblocks = (int)(T / AT_BQ);
   g.mask_vec = (mask_sk == 1 && mask_sq % 4 == 0 && (reinterpret_cast<uintptr_t>(mask) & 15) == 0) ? 1 : 0;
   g.nb = nb; g.o_sm = o_sm;
-  for (int i = 0; i < nb && i < 4; i++) { g.bext[i] = bext[i]; g.o_sb[i] = o_sb[i]; }
-  for (int i = 0; i < nb; i++) if (o_sb[i] % 4) { pb_set_error("attention: output batch strides must be 16-byte aligned"); return -1; }
+  for (int i = 0; i < nb; i++) { g.bext[i] = bext[i]; g.o_sb[i] = o_sb[i]; }
   long long grid = BH * g.n_qblocks;
   if (grid > 2147483647LL) { pb_set_error("attention: grid too large"); return -1; }
   const int nq = g.n_qblocks, nk = (int)(T / AT_BK);
@@ -393,16 +440,15 @@ extern "C" int poly_b200_attention(const float *q, const float *k, const float *
   void *qb = pb_scratch_alloc(bytes), *kb = pb_scratch_alloc(bytes), *vb = pb_scratch_alloc(bytes);
   int rc = -1;
   if (qb && kb && vb) {
-    /* [b][t][h][d] -> [b*H + h][t][d]: axes d, t, h, b */
-    const long long ext[4] = {AT_HD, T, H, B}, str[4] = {1, D, AT_HD, (long long)T * D};
-    /* Vᵀ: [b*H + h][d][t]: axes t, d, h, b */
-    const long long extv[4] = {T, AT_HD, H, B}, strv[4] = {D, 1, AT_HD, (long long)T * D};
-    rc = pb_pack_launch(q, qb, 4, ext, str, PB_F32, PB_BF16, AT_HD, AT_HD, stream);
-    if (rc == 0) rc = pb_pack_launch(k, kb, 4, ext, str, PB_F32, PB_BF16, AT_HD, AT_HD, stream);
-    if (rc == 0) rc = pb_pack_launch(v, vb, 4, extv, strv, PB_F32, PB_BF16, T, T, stream);
+    /* fp32 [b][t][h][d] -> bf16 in the same layout */
+    const long long ext[2] = {D, (long long)B * T}, str[2] = {1, D};
+    rc = pb_pack_launch(q, qb, 2, ext, str, PB_F32, PB_BF16, D, D, stream);
+    if (rc == 0) rc = pb_pack_launch(k, kb, 2, ext, str, PB_F32, PB_BF16, D, D, stream);
+    if (rc == 0) rc = pb_pack_launch(v, vb, 2, ext, str, PB_F32, PB_BF16, D, D, stream);
     const int bext[2] = {H, B};
     const long long o_sb[2] = {(long long)T * AT_HD, (long long)H * T * AT_HD};
-    if (rc == 0) rc = pb_attention_launch(qb, kb, vb, mask, T, 1, scale, out, 2, bext, o_sb, AT_HD, BH, T, stream);
+    PbAttnOperand oq{qb, D, {AT_HD, (long long)T * D, 0}}, ok{kb, D, {AT_HD, (long long)T * D, 0}}, ov{vb, D, {AT_HD, (long long)T * D, 0}};
+    if (rc == 0) rc = pb_attention_launch(oq, ok, ov, mask, T, 1, scale, out, false, 2, bext, o_sb, AT_HD, BH, T, stream);
     if (rc == 0) pb_count_launch(true, 4);
   } else pb_set_error("poly_b200_attention: out of scratch memory");
   pb_scratch_free(qb); pb_scratch_free(kb); pb_scratch_free(vb);
@@ -419,22 +465,63 @@ struct AttnProgram : PbAotProgram {
   float scale = 1.0f;
   long long mask_off = 0, mask_sq = 0, mask_sk = 0;
   long long T = 0, BH = 0;
+  bool qkv_bf16 = false;     /* q, k, v buffers hold bfloat16 and are read in place */
+  bool out_bf16 = false;     /* out is written as bfloat16 */
   ~AttnProgram() override { delete g1; delete g2; }
-  int n_launches() const override { return 5; }
+  int n_launches() const override { return qkv_bf16 ? 2 : 5; }
+
+  /* q/k/v as the contractions address them: rows of 64 contiguous values */
+  void views(PbAttnOperand *q, PbAttnOperand *k, PbAttnOperand *v, void *const *bufs) const {
+    const int nb = (int)g2->b_ax.size();
+    *q = PbAttnOperand{(const __nv_bfloat16 *)bufs[0] + g1->off_a, g1->m_ax[0].sa, {0, 0, 0}};
+    *k = PbAttnOperand{(const __nv_bfloat16 *)bufs[1] + g1->off_b, g1->n_ax[0].sb, {0, 0, 0}};
+    *v = PbAttnOperand{(const __nv_bfloat16 *)bufs[2] + g2->off_b, g2->k_ax[0].sb, {0, 0, 0}};
+    for (int i = 0; i < nb; i++) { q->bstride[i] = g1->b_ax[i].sa; k->bstride[i] = g1->b_ax[i].sb; v->bstride[i] = g2->b_ax[i].sb; }
+  }
+  bool views_ok() const {
+    if (g1->k_ax.size() != 1 || g1->k_ax[0].sa != 1 || g1->k_ax[0].sb != 1 || g2->n_ax.size() != 1 || g2->n_ax[0].sb != 1) return false;
+    if (g1->off_a % 8 || g1->off_b % 8 || g2->off_b % 8) return false;
+    if (g1->m_ax[0].sa % 8 || g1->n_ax[0].sb % 8 || g2->k_ax[0].sb % 8) return false;
+    if (g1->m_ax[0].sa < AT_HD || g1->n_ax[0].sb < AT_HD || g2->k_ax[0].sb < AT_HD) return false;
+    for (size_t i = 0; i < g2->b_ax.size(); i++) {
+      const long long s[3] = {g1->b_ax[i].sa, g1->b_ax[i].sb, g2->b_ax[i].sb};
+      for (long long x : s) if (x <= 0 || x % 8) return false;
+    }
+    return true;
+  }
+
   int launch(void *const *bufs, cudaStream_t stream) override {
+    int bext[3]; long long o_sb[3];
+    const int nb = (int)g2->b_ax.size();
+    for (int i = 0; i < nb; i++) { bext[i] = (int)g2->b_ax[i].ext; o_sb[i] = g2->b_ax[i].sc; }
+    const float *mask = (const float *)bufs[3] + mask_off;
+    void *out = out_bf16 ? (void *)((__nv_bfloat16 *)bufs[4] + g2->off_c) : (void *)((float *)bufs[4] + g2->off_c);
+    if (qkv_bf16) {
+      PbAttnOperand q, k, v;
+      views(&q, &k, &v, bufs);
+      return pb_attention_launch(q, k, v, mask, mask_sq, mask_sk, scale, out, out_bf16, nb, bext, o_sb, g2->c_sm, BH, T, stream);
+    }
+    /* fp32 operands: dense bf16 copies [batch][row][64] */
     const size_t bytes = (size_t)BH * T * AT_HD * 2;
     void *qb = pb_scratch_alloc(bytes), *kb = pb_scratch_alloc(bytes), *vb = pb_scratch_alloc(bytes);
     int rc = -1;
     if (qb && kb && vb) {
       rc = g1->pack_into(qb, bufs[0], g1->off_a, true, PB_F32, PB_BF16, AT_HD, stream);
       if (rc == 0) rc = g1->pack_into(kb, bufs[1], g1->off_b, false, PB_F32, PB_BF16, AT_HD, stream);
-      if (rc == 0) rc = g2->pack_into(vb, bufs[2], g2->off_b, false, PB_F32, PB_BF16, T, stream);
-      int bext[4]; long long o_sb[4];
-      const int nb = (int)g2->b_ax.size();
-      for (int i = 0; i < nb; i++) { bext[i] = (int)g2->b_ax[i].ext; o_sb[i] = g2->b_ax[i].sc; }
+      if (rc == 0) {
+        /* v as [batch][key][d]: axes d, key, batch (fastest first) */
+        long long ext[PB_PACK_MAX_AXES], str[PB_PACK_MAX_AXES]; int na = 0;
+        ext[na] = AT_HD; str[na++] = g2->n_ax[0].sb;
+        ext[na] = T; str[na++] = g2->k_ax[0].sb;
+        for (int i = 0; i < nb; i++) { ext[na] = g2->b_ax[i].ext; str[na++] = g2->b_ax[i].sb; }
+        rc = pb_pack_launch((const float *)bufs[2] + g2->off_b, vb, na, ext, str, PB_F32, PB_BF16, AT_HD, AT_HD, stream);
+      }
+      /* dense copies: batch index = the same mixed radix as the output's */
+      PbAttnOperand q{qb, AT_HD, {0, 0, 0}}, k{kb, AT_HD, {0, 0, 0}}, v{vb, AT_HD, {0, 0, 0}};
+      long long bs = T * AT_HD;
+      for (int i = 0; i < nb; i++) { q.bstride[i] = k.bstride[i] = v.bstride[i] = bs; bs *= bext[i]; }
       if (rc == 0)
-        rc = pb_attention_launch(qb, kb, vb, (const float *)bufs[3] + mask_off, mask_sq, mask_sk, scale,
-                                 (float *)bufs[4] + g2->off_c, nb, bext, o_sb, g2->c_sm, BH, T, stream);
+        rc = pb_attention_launch(q, k, v, mask, mask_sq, mask_sk, scale, out, out_bf16, nb, bext, o_sb, g2->c_sm, BH, T, stream);
     } else pb_set_error("attention: out of scratch memory");
     pb_scratch_free(qb); pb_scratch_free(kb); pb_scratch_free(vb);
     return rc;
@@ -449,7 +536,8 @@ PbAotProgram *pb_make_attn(const PbHeader &h, std::string &err) {
   PbGemmProgram &a = *p->g1, &b = *p->g2;
   bool ok = a.dtype == PB_F32 && b.dtype == PB_F32 && !a.has_x && !b.has_x && !a.relu && !b.relu;
   ok = ok && a.K == AT_HD && a.M == a.N && b.K == a.N && b.M == a.M && b.N == AT_HD && a.nbatch == b.nbatch;
-  ok = ok && pb_attention_supported(a.M, a.K) && b.c_sn == 1 && b.c_sm % 4 == 0 && a.b_ax.size() == b.b_ax.size() && a.b_ax.size() <= 4;
+  ok = ok && pb_attention_supported(a.M, a.K) && b.c_sn == 1 && b.c_sm % 4 == 0 && a.b_ax.size() == b.b_ax.size() && a.b_ax.size() <= 3;
+  ok = ok && a.k_ax.size() == 1 && b.n_ax.size() == 1;
   /* the probabilities are read in the layout the scores were written in */
   ok = ok && a.c_sn == 1 && a.m_ax.size() == 1 && a.n_ax.size() == 1 && b.m_ax.size() == 1 && b.k_ax.size() == 1;
   if (ok) ok = b.m_ax[0].sa == a.c_sm && b.k_ax[0].sa == 1;
@@ -463,6 +551,14 @@ PbAotProgram *pb_make_attn(const PbHeader &h, std::string &err) {
   auto m = h.getv("mask");
   if (m.size() != 3) { err = "malformed attention header"; delete p; return nullptr; }
   p->mask_off = m[0]; p->mask_sq = m[1]; p->mask_sk = m[2];
+  p->qkv_bf16 = h.geti("qkv16") != 0;
+  p->out_bf16 = h.geti("obf16") != 0;
+  if (p->qkv_bf16 && !p->views_ok()) { err = "attention: operands cannot be read in place"; delete p; return nullptr; }
+  if (p->out_bf16) {
+    bool o8 = b.c_sm % 8 == 0 && b.off_c % 8 == 0;
+    for (auto &ax : b.b_ax) if (ax.sc % 8) o8 = false;
+    if (!o8) { err = "attention: bfloat16 output rows would not be 16-byte aligned"; delete p; return nullptr; }
+  }
   p->n_params = 5;
   p->rw = "rrrr";
   p->rw.push_back(h.get("outmode") == "W" ? 'W' : 'w');

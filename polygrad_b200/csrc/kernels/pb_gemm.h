@@ -58,8 +58,12 @@ PbGemmProgram *pb_parse_gemm(const PbHeader &h, const char *prefix, std::string 
 
 /* Fused attention (pb_attention.cu). */
 bool pb_attention_supported(long long T, long long hd);
-int pb_attention_launch(const void *qb, const void *kb, const void *vtb, const float *mask, long long mask_sq, long long mask_sk,
-                        float scale, float *out, int nb, const int *bext, const long long *o_sb, long long o_sm,
+/* A bfloat16 matrix of 64-element rows: element (batch.., row, d) at
+ * ptr[sum_i batch_i * bstride[i] + row * row_stride + d]. */
+struct PbAttnOperand { const void *ptr; long long row_stride; long long bstride[3]; };
+int pb_attention_launch(const PbAttnOperand &q, const PbAttnOperand &k, const PbAttnOperand &v,
+                        const float *mask, long long mask_sq, long long mask_sk,
+                        float scale, void *out, bool out_bf16, int nb, const int *bext, const long long *o_sb, long long o_sm,
                         long long BH, long long T, cudaStream_t stream);
 
 /* Can the tensor-core kernel run this problem whatever the buffer addresses are
