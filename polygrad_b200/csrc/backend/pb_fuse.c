@@ -17,9 +17,8 @@
 #include <stdlib.h>
 #include <string.h>
 
-typedef struct { int writers, readers, first_write, last_write, last_read; } SlotUse;
 
-static void slot_usage(const PbPlan *p, SlotUse *u) {
+void pb_slot_usage(const PbPlan *p, PbSlotUse *u) {
   for (int i = 0; i < p->n_slots; i++) { u[i].writers = u[i].readers = 0; u[i].first_write = u[i].last_write = u[i].last_read = -1; }
   for (int s = 0; s < p->n_steps; s++) {
     const PbStep *st = &p->steps[s];
@@ -57,13 +56,13 @@ static bool is_identity_copy(const PbStep *st, int *p_out, int *p_in) {
 
 static int elide_copies(PbPlan *p) {
   int removed = 0;
-  SlotUse *u = malloc(sizeof(SlotUse) * (size_t)p->n_slots);
+  PbSlotUse *u = malloc(sizeof(PbSlotUse) * (size_t)p->n_slots);
   for (int s = 0; s < p->n_steps; s++) {
     PbStep *st = &p->steps[s];
     if (st->dead) continue;
     int po, pi;
     if (!is_identity_copy(st, &po, &pi)) continue;
-    slot_usage(p, u);
+    pb_slot_usage(p, u);
     int out = pb_plan_resolve(p, st->slot[po]), in = pb_plan_resolve(p, st->slot[pi]);
     if (out == in || p->slot_bytes[out] != p->slot_bytes[in]) continue;
     if (p->slot_inter[out] && u[out].writers == 1 && u[in].last_write < s) {
@@ -96,12 +95,12 @@ static int elide_copies(PbPlan *p) {
 
 static bool step_fusable(const PbStep *st) { return !st->dead && !st->precompiled && !st->fused_rows && st->n_vars == 0 && st->sink; }
 
-static bool step_reads(const PbPlan *p, const PbStep *st, int slot) {
+bool pb_step_reads(const PbPlan *p, const PbStep *st, int slot) {
   for (int a = 0; a < st->n_params; a++)
     if ((st->rw[a] == 'r' || st->rw[a] == 'b') && pb_plan_resolve(p, st->slot[a]) == slot) return true;
   return false;
 }
-static bool step_writes(const PbPlan *p, const PbStep *st, int slot) {
+bool pb_step_writes(const PbPlan *p, const PbStep *st, int slot) {
   for (int a = 0; a < st->n_params; a++)
     if ((st->rw[a] == 'w' || st->rw[a] == 'W' || st->rw[a] == 'b') && pb_plan_resolve(p, st->slot[a]) == slot) return true;
   return false;
@@ -114,7 +113,7 @@ static int step_out_slot(const PbPlan *p, const PbStep *st) {
 
 /* Renders the member steps order[0..no) (the last one is the final kernel) as one
  * row kernel; NULL when the chain does not have a supported form. */
-static char *render_chain(const PbPlan *p, const int *order, int no, bool out_bf16, PbFuseOut *fo) {
+char *pb_render_chain(const PbPlan *p, const int *order, int no, bool out_bf16, PbFuseOut *fo) {
   PbKern kerns[CHAIN_MAX]; PbFuseIn in[CHAIN_MAX]; int slots[CHAIN_MAX][PB_MAX_PARAMS];
   bool built = true; int n_phase = 0;
   int nb = 0;
@@ -140,10 +139,10 @@ static char *render_chain(const PbPlan *p, const int *order, int no, bool out_bf
 
 static int fuse_rows(PbPlan *p) {
   int fused = 0;
-  SlotUse *u = malloc(sizeof(SlotUse) * (size_t)p->n_slots);
+  PbSlotUse *u = malloc(sizeof(PbSlotUse) * (size_t)p->n_slots);
   for (int f = 0; f < p->n_steps; f++) {
     if (!step_fusable(&p->steps[f])) continue;
-    slot_usage(p, u);
+    pb_slot_usage(p, u);
     int mem[CHAIN_MAX]; int nm = 0;
     mem[nm++] = f;
     /* closure over single-writer intermediates read by members */
@@ -167,7 +166,7 @@ static int fuse_rows(PbPlan *p) {
         int sl = step_out_slot(p, &p->steps[mem[i]]);
         bool outside = sl < 0 || !p->slot_inter[sl];
         for (int s = 0; s < p->n_steps && !outside; s++) {
-          if (p->steps[s].dead || !step_reads(p, &p->steps[s], sl)) continue;
+          if (p->steps[s].dead || !pb_step_reads(p, &p->steps[s], sl)) continue;
           bool in_chain = false;
           for (int j = 0; j < nm; j++) if (mem[j] == s) in_chain = true;
           if (!in_chain) outside = true;
@@ -190,13 +189,13 @@ static int fuse_rows(PbPlan *p) {
       for (int j = 0; j < no && !hazard; j++) {
         const PbStep *m = &p->steps[order[j]];
         for (int a = 0; a < m->n_params; a++)
-          if (m->rw[a] == 'r' && step_writes(p, &p->steps[s], pb_plan_resolve(p, m->slot[a]))) hazard = true;
+          if (m->rw[a] == 'r' && pb_step_writes(p, &p->steps[s], pb_plan_resolve(p, m->slot[a]))) hazard = true;
       }
     }
     if (hazard) continue;
 
     PbFuseOut fo;
-    char *text = render_chain(p, order, no, false, &fo);
+    char *text = pb_render_chain(p, order, no, false, &fo);
     if (!text) continue;
     char name[64]; snprintf(name, sizeof name, "rowfused_k%d", p->steps[f].item);
     if (getenv("POLY_DUMP_KERNELS")) fprintf(stderr, "=== CUDA KERNEL %s ===\n%s\n=== END ===\n", name, text);
@@ -223,7 +222,7 @@ static int fuse_rows(PbPlan *p) {
  * builder and poly_softmax produce (reference: src/modelzoo/models/gpt2.c:
  * 402-434, src/frontend.c:1131-1159), nothing else reads scores or p, and the
  * bf16 contraction policy is on.  The three steps become one (pb_attention.cu). */
-static const char *hdr_line(const char *text, const char *key, char *buf, size_t cap) {
+const char *pb_hdr_line(const char *text, const char *key, char *buf, size_t cap) {
   size_t kl = strlen(key);
   for (const char *p = text; p && p[0] == '/' && p[1] == '/'; ) {
     const char *eol = strchr(p, '\n');
@@ -245,18 +244,18 @@ typedef struct { int params[4]; int relu; char dtype[8]; GAxis ax[16]; int nax; 
 
 static bool parse_gemm_hdr(const char *text, GHdr *g) {
   char buf[256];
-  if (!hdr_line(text, "kind", buf, sizeof buf) || strcmp(buf, "gemm") != 0) return false;
-  if (!hdr_line(text, "params", buf, sizeof buf) || sscanf(buf, "%d %d %d %d", &g->params[0], &g->params[1], &g->params[2], &g->params[3]) != 4) return false;
-  if (!hdr_line(text, "relu", buf, sizeof buf)) return false;
+  if (!pb_hdr_line(text, "kind", buf, sizeof buf) || strcmp(buf, "gemm") != 0) return false;
+  if (!pb_hdr_line(text, "params", buf, sizeof buf) || sscanf(buf, "%d %d %d %d", &g->params[0], &g->params[1], &g->params[2], &g->params[3]) != 4) return false;
+  if (!pb_hdr_line(text, "relu", buf, sizeof buf)) return false;
   g->relu = atoi(buf);
-  if (!hdr_line(text, "dtype", buf, sizeof buf)) return false;
-  snprintf(g->dtype, sizeof g->dtype, "%s", buf);
-  if (!hdr_line(text, "naxes", buf, sizeof buf)) return false;
+  if (!pb_hdr_line(text, "dtype", buf, sizeof buf)) return false;
+  snprintf(g->dtype, sizeof g->dtype, "%.7s", buf);
+  if (!pb_hdr_line(text, "naxes", buf, sizeof buf)) return false;
   g->nax = atoi(buf);
   if (g->nax > 16) return false;
   for (int i = 0; i < g->nax; i++) {
     char key[16]; snprintf(key, sizeof key, "axis%d", i);
-    if (!hdr_line(text, key, buf, sizeof buf)) return false;
+    if (!pb_hdr_line(text, key, buf, sizeof buf)) return false;
     if (sscanf(buf, "%c %lld %lld %lld %lld %lld", &g->ax[i].kind, &g->ax[i].ext, &g->ax[i].sc, &g->ax[i].sa, &g->ax[i].sb, &g->ax[i].sx) != 6) return false;
   }
   return true;
@@ -291,11 +290,11 @@ static bool u_is_shifted_exp(PolyUOp *u, int px, int pm) {
 static int fuse_attention(PbPlan *p) {
   if (!poly_b200_gemm_policy()) return 0;
   int fused = 0;
-  SlotUse *u = malloc(sizeof(SlotUse) * (size_t)p->n_slots);
+  PbSlotUse *u = malloc(sizeof(PbSlotUse) * (size_t)p->n_slots);
   for (int r = 0; r < p->n_steps; r++) {
     PbStep *R = &p->steps[r];
     if (R->dead || !R->fused_rows || R->n_chain != 4) continue;
-    slot_usage(p, u);
+    pb_slot_usage(p, u);
     PbStep *E = &p->steps[R->chain[0]], *MX = &p->steps[R->chain[1]], *SM = &p->steps[R->chain[2]], *NM = R;
     if (!E->sink || !MX->sink || !SM->sink || !NM->sink) continue;
     PbKern ke, kmx, ksm, knm;
@@ -347,7 +346,7 @@ static int fuse_attention(PbPlan *p) {
       if (u[s_slot].writers != 1 || u[p_slot].writers != 1) ABRK;
       g1i = u[s_slot].first_write;
       int readers_p = 0;
-      for (int s2 = 0; s2 < p->n_steps; s2++) if (!p->steps[s2].dead && step_reads(p, &p->steps[s2], p_slot)) { readers_p++; g2i = s2; }
+      for (int s2 = 0; s2 < p->n_steps; s2++) if (!p->steps[s2].dead && pb_step_reads(p, &p->steps[s2], p_slot)) { readers_p++; g2i = s2; }
       if (readers_p != 1 || g2i <= r || g1i >= R->chain[0]) ABRK;
       PbStep *G1 = &p->steps[g1i], *G2 = &p->steps[g2i];
       if (G1->dead || G2->dead || !G1->precompiled || !G2->precompiled) ABRK;
@@ -379,10 +378,10 @@ static int fuse_attention(PbPlan *p) {
       for (int s2 = g1i + 1; s2 < g2i && !hazard; s2++) {
         if (p->steps[s2].dead) continue;
         /* q and k were read at the first contraction, the mask at the scale+mask kernel; all are now read later */
-        if (step_writes(p, &p->steps[s2], q_slot) || step_writes(p, &p->steps[s2], k_slot) ||
-            (s2 > R->chain[0] && step_writes(p, &p->steps[s2], mask_slot)) ||
-            step_reads(p, &p->steps[s2], o_slot) || step_writes(p, &p->steps[s2], o_slot)) hazard = true;
-        if (s2 != R->chain[0] && s2 != r && step_reads(p, &p->steps[s2], s_slot)) hazard = true;
+        if (pb_step_writes(p, &p->steps[s2], q_slot) || pb_step_writes(p, &p->steps[s2], k_slot) ||
+            (s2 > R->chain[0] && pb_step_writes(p, &p->steps[s2], mask_slot)) ||
+            pb_step_reads(p, &p->steps[s2], o_slot) || pb_step_writes(p, &p->steps[s2], o_slot)) hazard = true;
+        if (s2 != R->chain[0] && s2 != r && pb_step_reads(p, &p->steps[s2], s_slot)) hazard = true;
       }
       if (hazard || u[s_slot].readers != 1) ABRK;
       if (o_slot == q_slot || o_slot == k_slot || o_slot == v_slot || o_slot == mask_slot) ABRK;
@@ -426,99 +425,6 @@ static int fuse_attention(PbPlan *p) {
 }
 
 
-/* ── bfloat16 storage for contraction operands ───────────────────────── */
-/* Under the bf16 contraction policy an fp32 operand is rounded to bfloat16 on
- * its way into the tensor-core kernel.  When the operand is a plan-owned
- * intermediate that nothing but such contractions reads, its producer can store
- * the rounded values directly (same element layout, 2-byte elements) and the
- * contractions read them in place: the values that reach the tensor cores are
- * bit for bit the same, the conversion pass and half of the producer's write
- * traffic disappear. */
-static char *hdr_with_line(const char *text, const char *line) {
-  const char *eol = strchr(text, '\n');
-  if (!eol) return NULL;
-  size_t head = (size_t)(eol - text) + 1, ll = strlen(line), tl = strlen(text);
-  char *t = malloc(tl + ll + 2);
-  memcpy(t, text, head); memcpy(t + head, line, ll); t[head + ll] = '\n';
-  memcpy(t + head + ll + 1, text + head, tl - head + 1);
-  return t;
-}
-
-static bool step_is_gemm(const PbStep *st, GHdr *h) {
-  return !st->dead && st->precompiled && st->text && parse_gemm_hdr(st->text, h);
-}
-
-static void step_set_program(PbStep *st, PolyCudaProgram *prog, char *text) {
-  poly_cuda_program_destroy(st->prog); free(st->text);
-  st->prog = prog; st->text = text;
-}
-
-#define RETYPE_MAX_READERS 4
-static int retype_bf16(PbPlan *p) {
-  if (!poly_b200_gemm_policy()) return 0;
-  int done = 0;
-  SlotUse *u = malloc(sizeof(SlotUse) * (size_t)p->n_slots);
-  for (int x = 0; x < p->n_slots; x++) {
-    if (pb_plan_resolve(p, x) != x || !p->slot_inter[x]) continue;
-    slot_usage(p, u);
-    if (u[x].writers != 1 || u[x].readers < 1 || u[x].readers > RETYPE_MAX_READERS) continue;
-    const int w = u[x].first_write;
-    PbStep *W = &p->steps[w];
-    if (W->precompiled || !W->sink || W->n_vars) continue;
-    bool whole = false;
-    for (int a = 0; a < W->n_params; a++) if (pb_plan_resolve(p, W->slot[a]) == x) whole = W->rw[a] == 'W';
-    if (!whole) continue;
-    /* every reader: a contraction that takes the slot as its A operand only */
-    int readers[RETYPE_MAX_READERS]; int nr = 0; bool ok = true;
-    for (int s = 0; s < p->n_steps && ok; s++) {
-      PbStep *R = &p->steps[s];
-      if (R->dead || !step_reads(p, R, x)) continue;
-      GHdr h;
-      if (s <= w || !step_is_gemm(R, &h) || strcmp(h.dtype, "f32") != 0 || hdr_line(R->text, "abf16", (char[8]){0}, 8)) { ok = false; break; }
-      for (int a = 0; a < R->n_params; a++)
-        if (pb_plan_resolve(p, R->slot[a]) == x && a != h.params[1]) ok = false;
-      if (ok && nr < RETYPE_MAX_READERS) readers[nr++] = s; else ok = false;
-    }
-    if (!ok || nr == 0) continue;
-    /* the producer with a bfloat16 store */
-    char *wtext = NULL; PbFuseOut fo; bool w_fused = W->fused_rows;
-    if (w_fused) wtext = render_chain(p, W->chain, W->n_chain, true, &fo);
-    else {
-      PbKern k;
-      if (pb_kern_build(&k, W->sink) == 0 && k.n_stores == 1 &&
-          pb_plan_resolve(p, W->slot[k.stores[0].param]) == x) wtext = pb_render_elementwise_bf16(&k);
-      pb_kern_free(&k);
-    }
-    if (!wtext) continue;
-    if (w_fused) {
-      bool same = fo.n_params == W->n_params;
-      for (int a = 0; same && a < fo.n_params; a++) if (fo.slot[a] != pb_plan_resolve(p, W->slot[a]) || fo.rw[a] != W->rw[a]) same = false;
-      if (!same) { free(wtext); continue; }
-    }
-    char name[64]; snprintf(name, sizeof name, "bf16out_k%d", W->item);
-    PolyCudaProgram *wprog = poly_compile_cuda(wtext, name);
-    PolyCudaProgram *rprog[RETYPE_MAX_READERS] = {0}; char *rtext[RETYPE_MAX_READERS] = {0};
-    bool all = wprog != NULL;
-    for (int i = 0; i < nr && all; i++) {
-      rtext[i] = hdr_with_line(p->steps[readers[i]].text, "//abf16 1");
-      snprintf(name, sizeof name, "gemm_abf16_k%d", p->steps[readers[i]].item);
-      rprog[i] = rtext[i] ? poly_compile_cuda(rtext[i], name) : NULL;
-      if (!rprog[i]) all = false;
-    }
-    if (!all) {
-      if (wprog) poly_cuda_program_destroy(wprog);
-      free(wtext);
-      for (int i = 0; i < nr; i++) { if (rprog[i]) poly_cuda_program_destroy(rprog[i]); free(rtext[i]); }
-      continue;
-    }
-    if (getenv("POLY_DUMP_KERNELS")) fprintf(stderr, "=== CUDA KERNEL bf16out_k%d ===\n%s\n=== END ===\n", W->item, wtext);
-    step_set_program(W, wprog, wtext);
-    for (int i = 0; i < nr; i++) step_set_program(&p->steps[readers[i]], rprog[i], rtext[i]);
-    done++;
-  }
-  free(u);
-  return done;
-}
 
 void pb_plan_fuse(PbPlan *p) {
   int copies = elide_copies(p);
@@ -527,9 +433,7 @@ void pb_plan_fuse(PbPlan *p) {
   if (!e || strcmp(e, "copies") != 0) rows = fuse_rows(p);
   int attn = 0;
   if (!e || (strcmp(e, "copies") != 0 && strcmp(e, "rows") != 0)) attn = fuse_attention(p);
-  int bf16 = 0;
-  if (!e || strcmp(e, "nobf16") != 0) { if (!e || (strcmp(e, "copies") != 0 && strcmp(e, "rows") != 0)) bf16 = retype_bf16(p); }
   if (getenv("POLY_B200_DEBUG"))
-    fprintf(stderr, "pb_fuse: %d copy kernels elided, %d kernels folded into row kernels, %d attention chains fused, "
-                    "%d operands kept in bfloat16\n", copies, rows, attn, bf16);
+    fprintf(stderr, "pb_fuse: %d copy kernels elided, %d kernels folded into row kernels, %d attention chains fused\n", copies, rows, attn);
+  if (!e || (strcmp(e, "copies") != 0 && strcmp(e, "rows") != 0 && strcmp(e, "attn") != 0)) pb_plan_operands(p);
 }

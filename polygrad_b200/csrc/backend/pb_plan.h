@@ -52,4 +52,16 @@ void pb_step_release(PbStep *st);
 /* Rewrites the step list in place (pb_fuse.c). */
 void pb_plan_fuse(PbPlan *p);
 
+/* Helpers shared by the passes. */
+typedef struct { int writers, readers, first_write, last_write, last_read; } PbSlotUse;
+void pb_slot_usage(const PbPlan *p, PbSlotUse *u);
+bool pb_step_reads(const PbPlan *p, const PbStep *st, int slot);
+bool pb_step_writes(const PbPlan *p, const PbStep *st, int slot);
+const char *pb_hdr_line(const char *text, const char *key, char *buf, size_t cap);
+char *pb_render_chain(const PbPlan *p, const int *order, int no, bool out_bf16, PbFuseOut *fo);
+
+/* Passes over the operands of precompiled steps (pb_operands.c): strided copies
+ * folded into the consumer's strides, bfloat16 storage of contraction operands. */
+void pb_plan_operands(PbPlan *p);
+
 #endif

@@ -91,3 +91,40 @@ def test_gpt2_plan_lowers_in_dry_run():
     assert len(fused) >= 3 * n_layer + 1                  # LN1, softmax, LN2 per layer + final LN
     stats = json.loads(r.stdout.strip().splitlines()[-1])
     assert stats['memsets_executed'] <= 4           # zero fills are elided when kernels overwrite whole buffers
+
+
+DRY_BF16 = r'''
+import os, sys
+sys.path.insert(0, %(root)r)
+import numpy as np
+from polygrad_b200 import ffi
+from polygrad_b200.instance import Instance, gpt2_init
+lib = ffi.product()
+assert lib.poly_cuda_init() == 0
+cfg = dict(vocab_size=320, n_embd=128, n_head=2, n_layer=2, max_seq_len=128, max_batch=2)
+inst = Instance.gpt2(lib, **cfg)
+inst.init_params(gpt2_init(1))
+inst.set_device(ffi.DEVICE_CUDA)
+inst.forward(**inst.gpt2_inputs(np.zeros((2, 128))))
+'''
+
+
+def test_bf16_policy_plan_passes_in_dry_run():
+    """Under the bf16 contraction policy, per layer: the attention chain becomes one step, the q/k/v
+    slice copies are folded into its operand strides, and the operands of the four projections (and of
+    the attention) are produced as bfloat16 by the step before them."""
+    env = dict(os.environ, POLY_B200_DRYRUN='1', POLY_B200_DEBUG='1', POLY_B200_CACHE='0', POLY_B200_GEMM='bf16')
+    r = subprocess.run([sys.executable, '-c', DRY_BF16 % dict(root=ROOT)], env=env, capture_output=True, text=True,
+                       timeout=900)
+    assert r.returncode == 0, r.stderr[-4000:]
+    n_layer = 2
+    m = re.search(r'pb_fuse: (\d+) copy kernels elided, (\d+) kernels folded into row kernels, (\d+) attention chains fused', r.stderr)
+    assert m and int(m.group(3)) == n_layer
+    m = re.search(r'pb_operands: (\d+) copies folded into operand strides, (\d+) operands stored as bfloat16, '
+                  r'(\d+) attention outputs written as bfloat16 matrices', r.stderr)
+    assert m, r.stderr[-2000:]
+    assert int(m.group(1)) == 3 * n_layer                 # q, k, v
+    assert int(m.group(2)) == 4 * n_layer + 1             # LN1->qkv, qkv->attention, LN2->fc, GELU->proj; final LN->logits
+    assert int(m.group(3)) == n_layer
+    m = re.search(r'pb_plan: (\d+) steps', r.stderr)
+    assert m and int(m.group(1)) == 5 + 10 * n_layer
