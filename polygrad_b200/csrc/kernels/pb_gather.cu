@@ -11,8 +11,14 @@
  * starting from +0, exactly like the reference accumulation, so a -0.0f table
  * entry comes out as +0.0f there and here.
  *
- * Cost per token: V floats of `arange` (L2-resident: 200 KB at V=50257) plus one
- * table row; HBM traffic is the table rows read plus the output rows written.
+ * A first small kernel checks whether `arange` is strictly increasing (true for
+ * the 0..V-1 buffer the builders make; false for anything with NaNs or
+ * duplicates).  If it is, an id matches at most one v, found by trying v = id
+ * and otherwise by bisection, and the full search is skipped; if not, every
+ * block searches all of `arange` as described above.  Either way the result is
+ * the reference's.
+ *
+ * HBM traffic is the table rows read plus the output rows written.
  */
 #include "../runtime/pb_runtime.h"
 #include <cstdio>
@@ -24,10 +30,19 @@ struct GatherArgs {
   int ntok; long long tok_ext[4], tok_out[4], tok_ids[4];
   int nfeat; long long feat_ext[3], feat_out[3], feat_tab[3];
   long long n_tokens, n_feat;
+  const int *sorted;              /* 1: arange is strictly increasing */
 };
 
 #define GATHER_THREADS 256
 #define GATHER_MAX_MATCH 8
+
+__global__ void __launch_bounds__(1024) pb200_gather_check_sorted(const float *arange, long long vocab, int *flag) {
+  bool ok = true;
+  for (long long v = threadIdx.x; v + 1 < vocab; v += 1024) ok = ok & (arange[v] < arange[v + 1]);
+  if (vocab == 1) ok = arange[0] == arange[0];
+  const int all = __syncthreads_and(ok ? 1 : 0);
+  if (threadIdx.x == 0) *flag = all;
+}
 
 __global__ void __launch_bounds__(GATHER_THREADS) pb200_gather_rows(const GatherArgs a) {
   __shared__ int s_count;
@@ -41,11 +56,29 @@ __global__ void __launch_bounds__(GATHER_THREADS) pb200_gather_rows(const Gather
     if (threadIdx.x == 0) s_count = 0;
     __syncthreads();
     const float id = a.ids[o_ids];
-    /* fast candidate: arange is normally 0..V-1, but nothing relies on it */
-    for (long long v = threadIdx.x; v < a.vocab; v += GATHER_THREADS) {
-      if (a.arange[v] == id) {
-        const int slot = atomicAdd(&s_count, 1);
-        if (slot < GATHER_MAX_MATCH) s_match[slot] = v;
+    if (*a.sorted) {
+      /* strictly increasing: at most one match */
+      if (threadIdx.x == 0 && id == id) {
+        long long v = -1;
+        const long long guess = (id >= 0.0f && id < (float)a.vocab) ? (long long)id : -1;
+        if (guess >= 0 && a.arange[guess] == id) v = guess;
+        else {
+          long long lo = 0, hi = a.vocab - 1;
+          while (lo <= hi) {
+            const long long mid = (lo + hi) >> 1;
+            const float x = a.arange[mid];
+            if (x == id) { v = mid; break; }
+            if (x < id) lo = mid + 1; else hi = mid - 1;
+          }
+        }
+        if (v >= 0) { s_match[0] = v; s_count = 1; }
+      }
+    } else {
+      for (long long v = threadIdx.x; v < a.vocab; v += GATHER_THREADS) {
+        if (a.arange[v] == id) {
+          const int slot = atomicAdd(&s_count, 1);
+          if (slot < GATHER_MAX_MATCH) s_match[slot] = v;
+        }
       }
     }
     __syncthreads();
@@ -81,6 +114,7 @@ __global__ void __launch_bounds__(GATHER_THREADS) pb200_gather_rows(const Gather
 
 struct GatherProgram : PbAotProgram {
   GatherArgs a{};
+  int n_launches() const override { return 2; }
   int p_out, p_ids, p_arange, p_table;
   int launch(void *const *bufs, cudaStream_t stream) override {
     GatherArgs g = a;
@@ -88,7 +122,12 @@ struct GatherProgram : PbAotProgram {
     g.arange = (const float *)bufs[p_arange]; g.table = (const float *)bufs[p_table];
     if (g.n_tokens <= 0 || g.n_feat <= 0) return 0;
     long long grid = g.n_tokens < 148LL * 16 ? g.n_tokens : 148LL * 16;
+    int *flag = (int *)pb_scratch_alloc(sizeof(int));
+    if (!flag) { pb_set_error("gather: out of scratch memory"); return -1; }
+    pb200_gather_check_sorted<<<1, 1024, 0, stream>>>(g.arange, g.vocab, flag);
+    g.sorted = flag;
     pb200_gather_rows<<<(unsigned)grid, GATHER_THREADS, 0, stream>>>(g);
+    pb_scratch_free(flag);            /* stream-ordered pool: safe once the work is enqueued */
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { pb_set_error("gather launch: %s", cudaGetErrorString(e)); return -1; }
     return 0;

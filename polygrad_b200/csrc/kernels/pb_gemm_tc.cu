@@ -49,10 +49,22 @@ struct TcArgs {
   int vec_io;                      /* C rows (and addend rows) 16-byte aligned, N % 4 == 0 */
   int c_bf16;                      /* C holds bfloat16 (needs vec_io) */
   int tiles_m, tiles_n, n_tiles;   /* n_tiles = nbatch * tiles_m * tiles_n */
+  int m_fast;                      /* consecutive tiles differ in the row tile (else in the column tile) */
 };
 
 #define PB_TC_ERROR_FLAG pb200_tc_error_flag
 #include "pb_tc_ptx.cuh"
+
+/* Tile t of a batch entry -> (row tile, column tile).  Consecutive tiles run at the
+ * same time on different SMs; they walk along the axis of the SMALLER operand, so
+ * that the larger one is streamed from memory once while the smaller one stays in
+ * L2 (a 50257 x 768 vocabulary matrix against 8192 x 768 activations: the other
+ * order re-reads the vocabulary once per row tile, 64 times). */
+__device__ __forceinline__ void tile_coords(const TcArgs &g, int t, int *mt, int *nt) {
+  const int in_batch = t % (g.tiles_n * g.tiles_m);
+  if (g.m_fast) { *mt = in_batch % g.tiles_m; *nt = in_batch / g.tiles_m; }
+  else { *nt = in_batch % g.tiles_n; *mt = in_batch / g.tiles_n; }
+}
 
 template <int BN>
 struct TcSmem {
@@ -105,7 +117,8 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < g.n_tiles && ok; t += gridDim.x) {
-        const int nt = t % g.tiles_n, mt = (t / g.tiles_n) % g.tiles_m, bz = t / (g.tiles_n * g.tiles_m);
+        int nt, mt; const int bz = t / (g.tiles_n * g.tiles_m);
+        tile_coords(g, t, &mt, &nt);
         for (int kb = 0; kb < kblocks; kb++) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, &abort_flag, 1)) { ok = false; break; }
           mbar_expect_tx(bar_full + 8 * stage, S::STAGE);
@@ -149,7 +162,8 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     uint32_t it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < g.n_tiles && ok; t += gridDim.x, it++) {
-      const int nt = t % g.tiles_n, mt = (t / g.tiles_n) % g.tiles_m;
+      int nt, mt;
+      tile_coords(g, t, &mt, &nt);
       int bz = t / (g.tiles_n * g.tiles_m);
       long long oc = 0, ox = 0;
       for (int i = 0; i < g.nb; i++) { const int x = bz % g.bext[i]; bz /= g.bext[i]; oc += x * g.c_sb[i]; ox += x * g.x_sb[i]; }
@@ -291,6 +305,7 @@ static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, lo
   long long tiles = (long long)g.tiles_m * g.tiles_n * nbatch;
   if (tiles > 2147483647LL) { pb_set_error("gemm: too many tiles"); return -1; }
   g.n_tiles = (int)tiles;
+  g.m_fast = g.N > g.M ? 1 : 0;
   static int sms = 0;
   if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); if (sms <= 0) sms = 148; }
   int grid = tiles < sms ? (int)tiles : sms;

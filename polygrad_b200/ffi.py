@@ -101,6 +101,7 @@ def _declare_frontend(lib):
     _sig(lib, 'poly_layernorm', P, [P, P, _i64p, I, I, D, _i64p, ctypes.POINTER(I)])
     _sig(lib, 'poly_gather', P, [P, P, _i64p, I, P, _i64p, I, _i64p, ctypes.POINTER(I)])
     _sig(lib, 'poly_where_op', P, [P, P, P, P])
+    _sig(lib, 'poly_eq', P, [P, P, P])
     _sig(lib, 'poly_maximum', P, [P, P, P])
     # instances
     _sig(lib, 'poly_instance_free', None, [P])

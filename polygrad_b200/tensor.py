@@ -130,6 +130,19 @@ class Tensor:
         lib = self.dev.lib
         return self._new(lib.poly_alu1(self.dev.ctx, lib.ops['NEG'], self.uop), self.shape)
 
+    def eq(self, other):
+        """Elementwise equality (a bool tensor), as polygrad's poly_eq."""
+        a, b = self, other
+        if a.shape != b.shape:
+            shape = np.broadcast_shapes(a.shape, b.shape)
+            a, b = a._broadcast_to(shape), b._broadcast_to(shape)
+        return a._new(self.dev.lib.poly_eq(self.dev.ctx, a.uop, b.uop), a.shape, [b], dtype='bool')
+
+    def where(self, a, b):
+        """self ? a : b with a a tensor of self's shape and b a scalar."""
+        lib, ctx = self.dev.lib, self.dev.ctx
+        return a._new(lib.poly_where_op(ctx, self.uop, a.uop, a._const(b)), a.shape, [self], dtype=a.dtype)
+
     def _unary(self, fn):
         return self._new(getattr(self.dev.lib, fn)(self.dev.ctx, self.uop), self.shape)
 
@@ -296,3 +309,16 @@ class Tensor:
             for d in dptrs:
                 lib.poly_cuda_free(d)
         return out.reshape(self.shape)
+
+
+def embedding(ids, arange, table):
+    """table[ids] the way polygrad's model builders write it (reference:
+    src/modelzoo/models/gpt2.c:93-153): a one-hot mask (ids == arange) selects
+    table rows, summed over the vocabulary axis.  ids [...], arange [V],
+    table [V, D] -> [..., D]."""
+    V, D = table.shape
+    lead = ids.shape
+    mask = ids.reshape(*lead, 1).expand(*lead, V).eq(arange.reshape(*((1,) * len(lead)), V).expand(*lead, V))
+    mask = mask.reshape(*lead, V, 1).expand(*lead, V, D)
+    tbl = table.reshape(*((1,) * len(lead)), V, D).expand(*lead, V, D)
+    return mask.where(tbl, 0.0).sum(len(lead))
