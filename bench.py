@@ -53,50 +53,47 @@ def read_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi during the timed region."""
-    Q = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
-         'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+    """Samples the SM clock and the clock event reasons every 10 ms during the timed
+    region (NVML queries only; nothing is set)."""
+    REASONS = (('hw_slowdown', 0x8), ('sw_thermal_slowdown', 0x20), ('hw_thermal_slowdown', 0x40),
+               ('sw_power_cap', 0x4))
 
     def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.sm, self.bits, self.mx, self.stop_flag, self.thread, self.err = index, [], 0, None, False, None, None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(['nvidia-smi', '-i', str(self.index), '--query-gpu=' + self.Q,
-                                          '--format=csv,noheader,nounits', '-lms', '100'],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.mx = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception as e:                       # noqa: BLE001 - any NVML failure just disables sampling
+            self.err = f'NVML unavailable: {e}'
+            return
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+    def _run(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                self.bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+            except Exception as e:                   # noqa: BLE001
+                self.err = str(e)
+                return
+            time.sleep(0.01)
 
     def stop(self):
-        if not self.proc:
-            return dict(sm_mhz=None, sm_max_mhz=None, reasons=['nvidia-smi unavailable'])
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], None, set()
-        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
-        for ln in self.lines:
-            f = [x.strip() for x in ln.split(',')]
-            if len(f) < 6:
-                continue
-            try:
-                sm.append(float(f[0])); mx = float(f[1])
-            except ValueError:
-                continue
-            for n, v in zip(names, f[2:6]):
-                if v.lower().startswith('active'):
-                    reasons.add(n)
-        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=mx, reasons=sorted(reasons),
-                    samples=len(sm))
+        self.stop_flag = True
+        if self.thread:
+            self.thread.join(timeout=2)
+        if not self.sm:
+            return dict(sm_mhz=None, sm_max_mhz=self.mx, reasons=[self.err or 'no samples'], samples=0)
+        reasons = [n for n, bit in self.REASONS if self.bits & bit]
+        return dict(sm_mhz=float(np.median(self.sm)), sm_min_mhz=float(min(self.sm)), sm_max_mhz=self.mx,
+                    reasons=sorted(reasons), samples=len(self.sm))
 
 
 # ── reference arm: stock polygrad on the host cores ────────────────────────
@@ -289,7 +286,7 @@ def run_b200(args, cfg, rank, world, local_rank):
                     data='synthetic',
                     config=dict(workload=args.workload, batch_per_gpu=B, seq_len=T, parallelism=f'dp{world}',
                                 gemm=('bf16 operands, fp32 accumulate (tcgen05)' if args.dtype == 'bf16' else 'fp32 CUDA cores'),
-                                l2='about 16 GB of activations written and read per step, far above the 126 MB L2',
+                                l2='about 5 GB of intermediates written and read per step plus 1.65 GB of logits, far above the 126 MB L2',
                                 gather=(args.gather if world > 1 else 'none'),
                                 model_tflops=flops_per_token(cfg) * value / 1e12),
                     e2e=dict(value=e2e_value, unit='tokens/s', h2d_bytes_per_step=int(tokens.nbytes),
@@ -347,7 +344,7 @@ def gemm_roofline(lib, args, cfg):
     peaks = read_peaks()
     M, K, N = cfg['max_batch'] * cfg['max_seq_len'], cfg['n_embd'], 4 * cfg['n_embd']
     bf16 = args.dtype == 'bf16'
-    ms = time_gemm(lib, M, N, K, bf16, bias=True)
+    ms = time_gemm(lib, M, N, K, bf16, bf16_buffers=bf16, bias=True)
     lib.poly_b200_set_gemm_policy(int(bf16))
     flops = 2.0 * M * N * K
     achieved = flops / (ms * 1e-3) / 1e12
@@ -356,7 +353,8 @@ def gemm_roofline(lib, args, cfg):
     else:
         peak, bound = 75.0, 'fp32-cuda-core'
     return dict(bound=bound, achieved=achieved, peak=peak, unit='TFLOP/s', frac=achieved / peak, traffic=None,
-                kernel=f'gemm {M}x{N}x{K} (+ per-call bf16 conversion of the activations)' if bf16 else f'sgemm {M}x{N}x{K}',
+                kernel=(f'pb200_gemm_tc {M}x{N}x{K}: bf16 activations read in place, bf16 weights, fp32 result + bias'
+                        if bf16 else f'pb200_sgemm {M}x{N}x{K}'),
                 peak_source=peaks['source'] if bf16 else 'nominal fp32 FMA rate',
                 ms_per_launch=ms)
 
