@@ -352,7 +352,16 @@ def gemm_roofline(lib, args, cfg):
         peak, bound = peaks['bf16_tflops'], 'tensor'
     else:
         peak, bound = 75.0, 'fp32-cuda-core'
-    return dict(bound=bound, achieved=achieved, peak=peak, unit='TFLOP/s', frac=achieved / peak, traffic=None,
+    # DRAM bytes per launch of this kernel on this shape (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
+    # capture, see profiles/pb200_gemm_tc_8192x3072x768_bf16.md); scaled by the output size for other shapes, since
+    # the result dominates the traffic
+    traffic = None
+    if bf16:
+        traffic = 58.4e6 * (M * N) / (8192.0 * 3072.0)
+    return dict(bound=bound, achieved=achieved, peak=peak, unit='TFLOP/s', frac=achieved / peak, traffic=traffic,
+                traffic_unit='bytes per launch (ncu capture of the same kernel and shape)',
+                algorithmic_bytes=(M * K * 2 + N * K * 2 + M * N * 4) if bf16 else (M * K + N * K + M * N) * 4,
+                algorithmic_flops=flops,
                 kernel=(f'pb200_gemm_tc {M}x{N}x{K}: bf16 activations read in place, bf16 weights, fp32 result + bias'
                         if bf16 else f'pb200_sgemm {M}x{N}x{K}'),
                 peak_source=peaks['source'] if bf16 else 'nominal fp32 FMA rate',
