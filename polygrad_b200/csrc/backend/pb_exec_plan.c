@@ -259,6 +259,19 @@ PolyCompiledPlan *poly_compile_schedule(PolyCtx *ctx, PolySchedule *sched, PolyD
   p->base.n_slot_to_data = sched->n_buf_slots;
   p->base.slot_to_data = calloc((size_t)(sched->n_buf_slots > 0 ? sched->n_buf_slots : 1), sizeof(void *));
 
+  if (env_is("POLY_B200_DEBUG", "2")) {
+    /* the step list: kind, item, and each parameter's slot with its access */
+    for (int i = 0; i < p->n_steps; i++) {
+      const PbStep *st = &p->steps[i];
+      if (st->dead) continue;
+      char kind[24] = "jit";
+      if (st->precompiled && st->text) pb_hdr_line(st->text, "kind", kind, sizeof kind);
+      else if (st->fused_rows) snprintf(kind, sizeof kind, "rows(%d)", st->n_chain);
+      fprintf(stderr, "pb_plan: step %3d item %3d %-8s", i, st->item, kind);
+      for (int a = 0; a < st->n_params; a++) fprintf(stderr, " %c%d%s", st->rw[a], pb_plan_resolve(p, st->slot[a]), p->slot_inter[pb_plan_resolve(p, st->slot[a])] ? "" : "x");
+      fprintf(stderr, "\n");
+    }
+  }
   if (getenv("POLY_B200_DEBUG")) {
     int live = 0, dead = 0; int64_t sum = 0;
     for (int s = 0; s < p->n_steps; s++) { if (p->steps[s].dead) dead++; else live++; }

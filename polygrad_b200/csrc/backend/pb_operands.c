@@ -38,7 +38,7 @@ typedef struct {
   char dtype[8];
   HAxis ax[16];
 } HGemm;
-typedef struct { char scale[16]; long long mask[3]; char outmode; int qkv16, obf16; HGemm g1, g2; } HAttn;
+typedef struct { char scale[16]; long long mask[3]; char outmode; int qkv16, obf16, tiles; HGemm g1, g2; } HAttn;
 
 static const char *hget(const char *text, const char *pre, const char *key, char *buf, size_t cap) {
   char full[48]; snprintf(full, sizeof full, "%s%s", pre, key);
@@ -102,6 +102,7 @@ static bool hattn_parse(const char *text, HAttn *a) {
   a->outmode = buf[0];
   a->qkv16 = pb_hdr_line(text, "qkv16", buf, sizeof buf) ? atoi(buf) : 0;
   a->obf16 = pb_hdr_line(text, "obf16", buf, sizeof buf) ? atoi(buf) : 0;
+  a->tiles = pb_hdr_line(text, "tiles", buf, sizeof buf) ? atoi(buf) : 0;
   return hgemm_parse(text, "g1.", &a->g1) && hgemm_parse(text, "g2.", &a->g2);
 }
 
@@ -110,6 +111,7 @@ static char *attn_text(const HAttn *a) {
   pb_str_printf(&t, "//PB200 1\n//kind attn\n//scale %s\n//mask %lld %lld %lld\n//outmode %c\n", a->scale, a->mask[0], a->mask[1], a->mask[2], a->outmode);
   if (a->qkv16) pb_str_puts(&t, "//qkv16 1\n");
   if (a->obf16) pb_str_puts(&t, "//obf16 1\n");
+  if (a->tiles) pb_str_printf(&t, "//tiles %d\n", a->tiles);
   hgemm_emit(&t, "g1.", &a->g1);
   hgemm_emit(&t, "g2.", &a->g2);
   return pb_str_take(&t);
@@ -451,6 +453,53 @@ static int relayout_attention_out(PbPlan *p) {
   return done;
 }
 
+
+/* ── one mask classification per mask ────────────────────────────────── */
+/* Every attention step classifies its mask by tile before it runs.  Steps that
+ * read the same mask buffer in the same way, with no write to it in between,
+ * share one classification: the first computes it into a small plan buffer, the
+ * others read that. */
+static int share_mask_tiles(PbPlan *p) {
+  int shared = 0;
+  for (int f = 0; f < p->n_steps; f++) {
+    PbStep *F = &p->steps[f];
+    HAttn fa;
+    if (step_kind(F) != K_ATTN || F->n_params != 5 || !hattn_parse(F->text, &fa) || fa.tiles) continue;
+    const int mslot = pb_plan_resolve(p, F->slot[3]);
+    long long T = 0;
+    for (int i = 0; i < fa.g1.nax; i++) if (fa.g1.ax[i].kind == 'm') T = fa.g1.ax[i].ext;
+    if (T < 128) continue;
+    int members[64]; int nm = 0;
+    for (int s = f + 1; s < p->n_steps && nm < 64; s++) {
+      PbStep *S = &p->steps[s];
+      if (S->dead) continue;
+      if (pb_step_writes(p, S, mslot)) break;
+      HAttn a;
+      if (step_kind(S) != K_ATTN || S->n_params != 5 || !hattn_parse(S->text, &a) || a.tiles) continue;
+      long long Ts = 0;
+      for (int i = 0; i < a.g1.nax; i++) if (a.g1.ax[i].kind == 'm') Ts = a.g1.ax[i].ext;
+      if (pb_plan_resolve(p, S->slot[3]) == mslot && Ts == T && memcmp(a.mask, fa.mask, sizeof a.mask) == 0) members[nm++] = s;
+    }
+    if (nm == 0) continue;
+    const int tslot = pb_plan_add_slot(p, (T / 128) * (T / 128) * (int64_t)sizeof(float));
+    int ok_members = 0;
+    for (int i = -1; i < nm; i++) {
+      PbStep *S = i < 0 ? F : &p->steps[members[i]];
+      HAttn a;
+      hattn_parse(S->text, &a);
+      a.tiles = i < 0 ? 1 : 2;
+      char *text = attn_text(&a);
+      PolyCudaProgram *prog = compile_step_text(S, text, "attn_tiles");
+      if (!prog) { free(text); if (i < 0) break; continue; }
+      step_set_program(S, prog, text);
+      S->slot[5] = tslot; S->rw[5] = i < 0 ? 'W' : 'r'; S->rw[6] = 0; S->n_params = 6;
+      if (i >= 0) ok_members++;
+    }
+    shared += ok_members;
+  }
+  return shared;
+}
+
 void pb_plan_operands(PbPlan *p) {
   const char *e = getenv("POLY_B200_OPERANDS");     /* "0": none, "fold": view folding only */
   if (e && strcmp(e, "0") == 0) return;
@@ -459,7 +508,9 @@ void pb_plan_operands(PbPlan *p) {
     kept = retype_bf16(p);
     outs = relayout_attention_out(p);
   }
+  int tiles = (e && strcmp(e, "notiles") == 0) ? 0 : share_mask_tiles(p);
   if (getenv("POLY_B200_DEBUG"))
     fprintf(stderr, "pb_operands: %d copies folded into operand strides, %d operands stored as bfloat16, "
-                    "%d attention outputs written as bfloat16 matrices\n", folded, kept, outs);
+                    "%d attention outputs written as bfloat16 matrices, "
+                    "%d attention steps reuse a mask classification\n", folded, kept, outs, tiles);
 }

@@ -382,6 +382,8 @@ int pb_attention_error(void) {
   return v;
 }
 
+long long pb_attention_tiles_count(long long T) { return (T / AT_BQ) * (T / AT_BK); }
+
 bool pb_attention_supported(long long T, long long hd) { return hd == AT_HD && T >= AT_BK && T % AT_BK == 0; }
 
 /* q, k, v: bf16 through strides; mask fp32 [T x T] through strides; out fp32 or bf16 (out_bf16)
@@ -389,7 +391,7 @@ bool pb_attention_supported(long long T, long long hd) { return hd == AT_HD && T
 int pb_attention_launch(const PbAttnOperand &q, const PbAttnOperand &k, const PbAttnOperand &v,
                         const float *mask, long long mask_sq, long long mask_sk,
                         float scale, void *out, bool out_bf16, int nb, const int *bext, const long long *o_sb, long long o_sm,
-                        long long BH, long long T, cudaStream_t stream) {
+                        long long BH, long long T, cudaStream_t stream, float *tiles_buf, int tiles_mode) {
   if (!pb_attention_supported(T, AT_HD)) { pb_set_error("attention: unsupported sequence length %lld", T); return -1; }
   if (nb > 3) { pb_set_error("attention: more than three batch axes"); return -1; }
   const int oal = out_bf16 ? 8 : 4;
@@ -415,11 +417,11 @@ int pb_attention_launch(const PbAttnOperand &q, const PbAttnOperand &k, const Pb
   long long grid = BH * g.n_qblocks;
   if (grid > 2147483647LL) { pb_set_error("attention: grid too large"); return -1; }
   const int nq = g.n_qblocks, nk = (int)(T / AT_BK);
-  float *tiles = (float *)pb_scratch_alloc((size_t)nq * nk * sizeof(float));
+  float *tiles = tiles_mode ? tiles_buf : (float *)pb_scratch_alloc((size_t)nq * nk * sizeof(float));
   if (!tiles) { pb_set_error("attention: out of scratch memory"); return -1; }
-  pb200_mask_tiles<<<dim3((unsigned)nk, (unsigned)nq), 256, 0, stream>>>(mask, mask_sq, mask_sk, nk, tiles);
+  if (tiles_mode != 2) pb200_mask_tiles<<<dim3((unsigned)nk, (unsigned)nq), 256, 0, stream>>>(mask, mask_sq, mask_sk, nk, tiles);
   g.tile_const = tiles;
-  pb_scratch_free(tiles);            /* stream-ordered pool: safe to hand back once the work is enqueued */
+  if (!tiles_mode) pb_scratch_free(tiles);   /* stream-ordered pool: safe to hand back once the work is enqueued */
   pb_tc_mark_used();
   pb200_flash_attn<<<(unsigned)grid, AT_THREADS, AT_SMEM, stream>>>(mq, mk, mv, g);
   cudaError_t e = cudaGetLastError();
@@ -467,8 +469,9 @@ struct AttnProgram : PbAotProgram {
   long long T = 0, BH = 0;
   bool qkv_bf16 = false;     /* q, k, v buffers hold bfloat16 and are read in place */
   bool out_bf16 = false;     /* out is written as bfloat16 */
+  int tiles_mode = 0;        /* 1: the mask classification is computed into parameter 5, 2: read from it (same mask) */
   ~AttnProgram() override { delete g1; delete g2; }
-  int n_launches() const override { return qkv_bf16 ? 2 : 5; }
+  int n_launches() const override { return (qkv_bf16 ? 2 : 5) - (tiles_mode == 2 ? 1 : 0); }
 
   /* q/k/v as the contractions address them: rows of 64 contiguous values */
   void views(PbAttnOperand *q, PbAttnOperand *k, PbAttnOperand *v, void *const *bufs) const {
@@ -499,7 +502,8 @@ struct AttnProgram : PbAotProgram {
     if (qkv_bf16) {
       PbAttnOperand q, k, v;
       views(&q, &k, &v, bufs);
-      return pb_attention_launch(q, k, v, mask, mask_sq, mask_sk, scale, out, out_bf16, nb, bext, o_sb, g2->c_sm, BH, T, stream);
+      return pb_attention_launch(q, k, v, mask, mask_sq, mask_sk, scale, out, out_bf16, nb, bext, o_sb, g2->c_sm, BH, T, stream,
+                                 tiles_mode ? (float *)bufs[5] : nullptr, tiles_mode);
     }
     /* fp32 operands: dense bf16 copies [batch][row][64] */
     const size_t bytes = (size_t)BH * T * AT_HD * 2;
@@ -521,7 +525,8 @@ struct AttnProgram : PbAotProgram {
       long long bs = T * AT_HD;
       for (int i = 0; i < nb; i++) { q.bstride[i] = k.bstride[i] = v.bstride[i] = bs; bs *= bext[i]; }
       if (rc == 0)
-        rc = pb_attention_launch(q, k, v, mask, mask_sq, mask_sk, scale, out, out_bf16, nb, bext, o_sb, g2->c_sm, BH, T, stream);
+        rc = pb_attention_launch(q, k, v, mask, mask_sq, mask_sk, scale, out, out_bf16, nb, bext, o_sb, g2->c_sm, BH, T, stream,
+                                 tiles_mode ? (float *)bufs[5] : nullptr, tiles_mode);
     } else pb_set_error("attention: out of scratch memory");
     pb_scratch_free(qb); pb_scratch_free(kb); pb_scratch_free(vb);
     return rc;
@@ -562,5 +567,8 @@ PbAotProgram *pb_make_attn(const PbHeader &h, std::string &err) {
   p->n_params = 5;
   p->rw = "rrrr";
   p->rw.push_back(h.get("outmode") == "W" ? 'W' : 'w');
+  p->tiles_mode = (int)h.geti("tiles");
+  if (p->tiles_mode < 0 || p->tiles_mode > 2) { err = "malformed attention header"; delete p; return nullptr; }
+  if (p->tiles_mode) { p->n_params = 6; p->rw.push_back(p->tiles_mode == 1 ? 'W' : 'r'); }
   return p;
 }

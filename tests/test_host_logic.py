@@ -121,10 +121,11 @@ def test_bf16_policy_plan_passes_in_dry_run():
     m = re.search(r'pb_fuse: (\d+) copy kernels elided, (\d+) kernels folded into row kernels, (\d+) attention chains fused', r.stderr)
     assert m and int(m.group(3)) == n_layer
     m = re.search(r'pb_operands: (\d+) copies folded into operand strides, (\d+) operands stored as bfloat16, '
-                  r'(\d+) attention outputs written as bfloat16 matrices', r.stderr)
+                  r'(\d+) attention outputs written as bfloat16 matrices, (\d+) attention steps reuse a mask classification', r.stderr)
     assert m, r.stderr[-2000:]
     assert int(m.group(1)) == 3 * n_layer                 # q, k, v
     assert int(m.group(2)) == 4 * n_layer + 1             # LN1->qkv, qkv->attention, LN2->fc, GELU->proj; final LN->logits
     assert int(m.group(3)) == n_layer
+    assert int(m.group(4)) == n_layer - 1                 # the mask is classified once
     m = re.search(r'pb_plan: (\d+) steps', r.stderr)
     assert m and int(m.group(1)) == 5 + 10 * n_layer
