@@ -13,8 +13,15 @@
  * rounded to bf16 for the two contractions and fp32 accumulation, the row max
  * and row sum carried across blocks of 128 keys (the usual online form: a new
  * running max rescales what has been accumulated).  No causal structure is
- * assumed: the mask is an arbitrary additive [T, T] buffer and every block of
- * keys is processed, as in the reference.
+ * assumed: the mask is an arbitrary additive [T, T] buffer.  A block of keys is
+ * left out only where that provably changes nothing: its mask tile holds one
+ * value c, and c + S < L - 100, where S bounds |q.k * scale| for the block
+ * (largest row norms of q and k, Cauchy-Schwarz) and L is a lower bound of every
+ * row's running maximum taken from the blocks already processed.  Then each
+ * probability of the block is exp2 of less than -126 -- exactly 0 in this
+ * kernel's arithmetic -- and the running maximum cannot move, so sums and
+ * accumulators are bit for bit what processing the block would leave (for
+ * finite v).  The -1e9 upper triangle of a causal mask goes this way.
  *
  * Q, K and V are bfloat16 matrices of 64-element rows addressed through strides
  * (row pitch and up to three batch strides), so the three slices of a fused
@@ -62,7 +69,9 @@ struct AttnArgs {
   long long mask_sq, mask_sk;     /* mask[q*mask_sq + k*mask_sk] */
   float scale;
   int mask_vec;                   /* mask rows contiguous and 16-byte aligned */
-  const float *tile_const;        /* per (query block, key block): NaN if the mask tile varies, else its one value */
+  const float *tile_const;        /* per (query block, key block) two floats: the tile's one value (NaN if it varies),
+                                     and min over rows of the row's largest mask value in the tile */
+  const float *qn, *kn;           /* per (batch*head, block of 128 rows): upper bound of the largest row 2-norm; null: no skipping */
   int T, n_qblocks;
   int nb; int bext[3]; long long o_sb[3]; long long o_sm;   /* O[batch..][row*o_sm + d] */
   int out_bf16;                   /* O holds bfloat16 (same element offsets) */
@@ -81,12 +90,30 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ float xchg[2][AT_BQ];     /* per-row exchange between the two threads of a row */
+  __shared__ unsigned long long s_live;    /* bit j: key block j is processed */
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = blockIdx.x % g.n_qblocks, bh = blockIdx.x / g.n_qblocks;
+  /* late query blocks first: under a causal mask they process the most key blocks, and the
+   * hardware hands out CTAs in index order, so the short ones fill the tail */
+  const int n_bh = gridDim.x / g.n_qblocks;
+  const int qb = g.n_qblocks - 1 - (int)(blockIdx.x / n_bh), bh = blockIdx.x % n_bh;
   const int nkb = g.T / AT_BK;
 
   if (threadIdx.x == 0) {
+    /* which key blocks to process (see the head of this file) */
+    unsigned long long live = 0;
+    float lrun = __int_as_float(0xff800000);
+    for (int j = 0; j < nkb; j++) {
+      const float c = g.tile_const[2 * (qb * nkb + j)], lmin = g.tile_const[2 * (qb * nkb + j) + 1];
+      float S = 0.0f;
+      bool skip = false;
+      if (g.qn) {
+        S = fabsf(g.scale) * g.qn[bh * g.n_qblocks + qb] * g.kn[bh * nkb + j];
+        skip = (c == c) && (c + S < lrun - 100.0f);
+      }
+      if (!skip) { live |= 1ull << j; lrun = fmaxf(lrun, lmin - S); }
+    }
+    s_live = live;
     abort_flag = 0;
     mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1);
     mbar_init(bar_s, 1); mbar_init(bar_p, 256); mbar_init(bar_o, 1); mbar_init(bar_x, 256);
@@ -117,10 +144,12 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
       mbar_expect_tx(bar_q, 16384);
       tma_load_5d(s_q, &map_q, bar_q, 0, qb * AT_BQ, c0, c1, c2);
+      unsigned long long rem = s_live;
+      const int j0 = __ffsll((long long)rem) - 1;          /* the first block is always processed */
       mbar_expect_tx(bar_k, 16384);
-      tma_load_5d(s_k, &map_k, bar_k, 0, 0, c0, c1, c2);
+      tma_load_5d(s_k, &map_k, bar_k, 0, j0 * AT_BK, c0, c1, c2);
       mbar_expect_tx(bar_v, 16384);
-      tma_load_5d(s_v, &map_v, bar_v, 0, 0, c0, c1, c2);
+      tma_load_5d(s_v, &map_v, bar_v, 0, j0 * AT_BK, c0, c1, c2);
       bool ok = mbar_wait(bar_q, 0, &abort_flag, 11) && mbar_wait(bar_k, 0, &abort_flag, 12);
       const uint64_t dq = make_smem_desc(s_q), dk = make_smem_desc(s_k);
       if (ok) {
@@ -129,11 +158,14 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         for (int k = 0; k < AT_HD / 16; k++) tc_mma_bf16(tmem_s, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, k ? 1u : 0u);
         tc_commit(bar_s);
       }
-      for (int j = 0; j < nkb && ok; j++) {
-        const uint32_t ph = (uint32_t)j & 1u;
+      for (uint32_t it = 0; rem && ok; it++) {
+        rem &= rem - 1;                                    /* this block; what is left are the later ones */
+        const bool more = rem != 0;
+        const int jn = more ? __ffsll((long long)rem) - 1 : 0;
+        const uint32_t ph = it & 1u;
         /* K is free once S is complete: prefetch the next block of keys */
         if (!mbar_wait(bar_s, ph, &abort_flag, 13)) break;
-        if (j + 1 < nkb) { mbar_expect_tx(bar_k, 16384); tma_load_5d(s_k, &map_k, bar_k, 0, (j + 1) * AT_BK, c0, c1, c2); }
+        if (more) { mbar_expect_tx(bar_k, 16384); tma_load_5d(s_k, &map_k, bar_k, 0, jn * AT_BK, c0, c1, c2); }
         if (!mbar_wait(bar_p, ph, &abort_flag, 14)) break;     /* P written, S and the previous PV consumed */
         if (!mbar_wait(bar_v, ph, &abort_flag, 15)) break;
         tc_fence_after_sync();
@@ -149,7 +181,7 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         tc_commit(bar_o);
         /* the next block's scores follow at once: S is free, and the softmax threads find
          * them ready when they come back from adding this block's PV */
-        if (j + 1 < nkb) {
+        if (more) {
           if (!mbar_wait(bar_k, ph ^ 1u, &abort_flag, 12)) break;
           tc_fence_after_sync();
 #pragma unroll
@@ -157,9 +189,9 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           tc_commit(bar_s);
         }
         if (!mbar_wait(bar_o, ph, &abort_flag, 16)) break;
-        if (j + 1 < nkb) {
+        if (more) {
           mbar_expect_tx(bar_v, 16384);
-          tma_load_5d(s_v, &map_v, bar_v, 0, (j + 1) * AT_BK, c0, c1, c2);
+          tma_load_5d(s_v, &map_v, bar_v, 0, jn * AT_BK, c0, c1, c2);
         }
       }
     }
@@ -181,10 +213,12 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     uint8_t *p_row = sm + 49152 + half * 16384 + (row >> 3) * 1024 + (row & 7) * 128;
     bool ok = true;
     uint32_t xph = 0;
-    for (int j = 0; j < nkb && ok; j++) {
-      const uint32_t ph = (uint32_t)j & 1u;
+    uint32_t it = 0;
+    for (unsigned long long rem = s_live; rem && ok; rem &= rem - 1, it++) {
+      const int j = __ffsll((long long)rem) - 1;
+      const uint32_t ph = it & 1u;
       const float *mj = mrow + ((long long)j * AT_BK + half * 64) * g.mask_sk;
-      const float tile_c = g.tile_const[qb * nkb + j];
+      const float tile_c = g.tile_const[2 * (qb * nkb + j)];
       const bool tile_is_const = (tile_c == tile_c);
       if (!mbar_wait(bar_s, ph, &abort_flag, 17)) { ok = false; break; }
       tc_fence_after_sync();
@@ -313,10 +347,13 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   }
 }
 
-/* Classifies the mask by 128 x 128 tile: a tile whose entries are all equal (the
- * zeros below and the -1e9 above the diagonal of a causal mask, for instance) is
- * recorded by that value, so that the attention kernel adds it without reading
- * the tile; any other tile is recorded as NaN and read.  Exact for every mask. */
+/* Classifies the mask by 128 x 128 tile.  out[2*tile]: the tile's value if all its
+ * entries are equal (the zeros below and the -1e9 above the diagonal of a causal
+ * mask, for instance), so that the attention kernel adds it without reading the
+ * tile; NaN for any other tile, which is then read.  out[2*tile + 1]: the smallest,
+ * over the tile's rows, of the row's largest entry (-inf if a row holds a NaN) --
+ * after the tile is processed every row's running maximum is at least that much
+ * minus the bound on |score|.  Exact for every mask. */
 __global__ void __launch_bounds__(256) pb200_mask_tiles(const float *mask, long long sq, long long sk, int nk, float *out) {
   const int qi = blockIdx.y, ki = blockIdx.x;
   const float *t = mask + (long long)qi * AT_BQ * sq + (long long)ki * AT_BK * sk;
@@ -337,7 +374,84 @@ __global__ void __launch_bounds__(256) pb200_mask_tiles(const float *mask, long 
   }
   const bool same = diff == 0;
   const int all = __syncthreads_and(same ? 1 : 0);
-  if (threadIdx.x == 0) out[qi * nk + ki] = (all && first == first) ? first : __int_as_float(0x7fc00000);
+  /* row maxima: a warp per row, 16 rows per warp */
+  const int wid = threadIdx.x >> 5, ln = threadIdx.x & 31;
+  float mx = __int_as_float(0x7f800000);               /* running min over this warp's rows */
+  for (int r = wid; r < AT_BQ; r += 8) {
+    const float *tr = t + (long long)r * sq;
+    float m = __int_as_float(0xff800000); bool nan = false;
+#pragma unroll
+    for (int k = ln; k < AT_BK; k += 32) { const float v = tr[(long long)k * sk]; nan |= !(v == v); m = fmaxf(m, v); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o)); nan |= __shfl_xor_sync(0xffffffffu, nan ? 1 : 0, o) != 0; }
+    if (nan) m = __int_as_float(0xff800000);
+    mx = fminf(mx, m);
+  }
+  /* min over the 128 rows */
+  __shared__ float s_min[8];
+  if (ln == 0) s_min[wid] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = s_min[0];
+    for (int i = 1; i < 8; i++) m = fminf(m, s_min[i]);
+    out[2 * (qi * nk + ki)] = (all && first == first) ? first : __int_as_float(0x7fc00000);
+    out[2 * (qi * nk + ki) + 1] = m;
+  }
+}
+
+/* Per (batch*head, block of 128 rows): an upper bound of the largest 2-norm of a row
+ * of q and of k (bfloat16 rows of 64 through strides). */
+struct BoundsArgs {
+  const __nv_bfloat16 *q, *k; long long q_rs, k_rs, q_bs[3], k_bs[3];
+  int nb, bext[3], nblk;
+  float *qn, *kn;
+};
+__global__ void __launch_bounds__(128) pb200_attn_bounds(const BoundsArgs a) {
+  const int blk = blockIdx.x % a.nblk, bh = blockIdx.x / a.nblk;
+  long long oq = 0, ok = 0; int rem = bh;
+  for (int i = 0; i < a.nb; i++) { const int x = rem % a.bext[i]; rem /= a.bext[i]; oq += x * a.q_bs[i]; ok += x * a.k_bs[i]; }
+  /* 8 threads per row (16 bytes each: a row is one 128-byte line), 16 rows per pass */
+  const int sub = threadIdx.x & 7, grp = threadIdx.x >> 3;
+  float nq = 0.f, nk = 0.f;            /* largest squared norm seen by this thread's row group */
+#pragma unroll 2
+  for (int r = 0; r < 8; r++) {
+    const long long row = (long long)blk * 128 + r * 16 + grp;
+    const uint4 vq = *reinterpret_cast<const uint4 *>(a.q + oq + row * a.q_rs + sub * 8);
+    const uint4 vk = *reinterpret_cast<const uint4 *>(a.k + ok + row * a.k_rs + sub * 8);
+    const uint32_t wq[4] = {vq.x, vq.y, vq.z, vq.w}, wk[4] = {vk.x, vk.y, vk.z, vk.w};
+    float sq_ = 0.f, sk_ = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float q0 = __uint_as_float(wq[j] << 16), q1 = __uint_as_float(wq[j] & 0xffff0000u);
+      const float k0 = __uint_as_float(wk[j] << 16), k1 = __uint_as_float(wk[j] & 0xffff0000u);
+      sq_ = fmaf(q0, q0, fmaf(q1, q1, sq_)); sk_ = fmaf(k0, k0, fmaf(k1, k1, sk_));
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) { sq_ += __shfl_xor_sync(0xffffffffu, sq_, o); sk_ += __shfl_xor_sync(0xffffffffu, sk_, o); }
+    nq = (nq != nq || sq_ != sq_) ? __int_as_float(0x7fc00000) : fmaxf(nq, sq_);
+    nk = (nk != nk || sk_ != sk_) ? __int_as_float(0x7fc00000) : fmaxf(nk, sk_);
+  }
+  /* NaN rows give NaN norms, and a NaN bound never permits a skip */
+  __shared__ float s_q[4], s_k[4];
+  float mq = nq, mk = nk;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float oq2 = __shfl_xor_sync(0xffffffffu, mq, o), ok2 = __shfl_xor_sync(0xffffffffu, mk, o);
+    mq = (mq != mq || oq2 != oq2) ? __int_as_float(0x7fc00000) : fmaxf(mq, oq2);
+    mk = (mk != mk || ok2 != ok2) ? __int_as_float(0x7fc00000) : fmaxf(mk, ok2);
+  }
+  if ((threadIdx.x & 31) == 0) { s_q[threadIdx.x >> 5] = mq; s_k[threadIdx.x >> 5] = mk; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float x = s_q[0], y = s_k[0];
+    for (int i = 1; i < 4; i++) {
+      x = (x != x || s_q[i] != s_q[i]) ? __int_as_float(0x7fc00000) : fmaxf(x, s_q[i]);
+      y = (y != y || s_k[i] != s_k[i]) ? __int_as_float(0x7fc00000) : fmaxf(y, s_k[i]);
+    }
+    /* rounded up: the sums above and the tensor cores' own accumulation round */
+    a.qn[blockIdx.x] = sqrtf(x) * 1.001f;
+    a.kn[blockIdx.x] = sqrtf(y) * 1.001f;
+  }
 }
 
 /* ── host ────────────────────────────────────────────────────────────── */
@@ -382,9 +496,10 @@ int pb_attention_error(void) {
   return v;
 }
 
-long long pb_attention_tiles_count(long long T) { return (T / AT_BQ) * (T / AT_BK); }
+long long pb_attention_tiles_count(long long T) { return 2 * (T / AT_BQ) * (T / AT_BK); }
 
-bool pb_attention_supported(long long T, long long hd) { return hd == AT_HD && T >= AT_BK && T % AT_BK == 0; }
+/* at most 64 key blocks: the set of processed blocks is a 64-bit mask */
+bool pb_attention_supported(long long T, long long hd) { return hd == AT_HD && T >= AT_BK && T % AT_BK == 0 && T / AT_BK <= 64; }
 
 /* q, k, v: bf16 through strides; mask fp32 [T x T] through strides; out fp32 or bf16 (out_bf16)
  * at element offsets Σ batch_i*o_sb[i] + row*o_sm + d. */
@@ -417,11 +532,28 @@ int pb_attention_launch(const PbAttnOperand &q, const PbAttnOperand &k, const Pb
   long long grid = BH * g.n_qblocks;
   if (grid > 2147483647LL) { pb_set_error("attention: grid too large"); return -1; }
   const int nq = g.n_qblocks, nk = (int)(T / AT_BK);
-  float *tiles = tiles_mode ? tiles_buf : (float *)pb_scratch_alloc((size_t)nq * nk * sizeof(float));
+  float *tiles = tiles_mode ? tiles_buf : (float *)pb_scratch_alloc((size_t)2 * nq * nk * sizeof(float));
   if (!tiles) { pb_set_error("attention: out of scratch memory"); return -1; }
+  /* bounds on |q.k| per block, for leaving out key blocks that cannot contribute (POLY_B200_ATTN_SKIP=0: never) */
+  float *norms = nullptr;
+  {
+    const char *e = getenv("POLY_B200_ATTN_SKIP");
+    if (!(e && e[0] == '0')) {
+      norms = (float *)pb_scratch_alloc((size_t)2 * BH * nq * sizeof(float));
+      if (!norms) { if (!tiles_mode) pb_scratch_free(tiles); pb_set_error("attention: out of scratch memory"); return -1; }
+      BoundsArgs ba{};
+      ba.q = (const __nv_bfloat16 *)q.ptr; ba.k = (const __nv_bfloat16 *)k.ptr; ba.q_rs = q.row_stride; ba.k_rs = k.row_stride;
+      ba.nb = nb; ba.nblk = nq;
+      for (int i = 0; i < nb; i++) { ba.bext[i] = bext[i]; ba.q_bs[i] = q.bstride[i]; ba.k_bs[i] = k.bstride[i]; }
+      ba.qn = norms; ba.kn = norms + BH * nq;
+      pb200_attn_bounds<<<(unsigned)(BH * nq), 128, 0, stream>>>(ba);
+      g.qn = ba.qn; g.kn = ba.kn;
+    }
+  }
   if (tiles_mode != 2) pb200_mask_tiles<<<dim3((unsigned)nk, (unsigned)nq), 256, 0, stream>>>(mask, mask_sq, mask_sk, nk, tiles);
   g.tile_const = tiles;
   if (!tiles_mode) pb_scratch_free(tiles);   /* stream-ordered pool: safe to hand back once the work is enqueued */
+  pb_scratch_free(norms);
   pb_tc_mark_used();
   pb200_flash_attn<<<(unsigned)grid, AT_THREADS, AT_SMEM, stream>>>(mq, mk, mv, g);
   cudaError_t e = cudaGetLastError();
@@ -471,7 +603,7 @@ struct AttnProgram : PbAotProgram {
   bool out_bf16 = false;     /* out is written as bfloat16 */
   int tiles_mode = 0;        /* 1: the mask classification is computed into parameter 5, 2: read from it (same mask) */
   ~AttnProgram() override { delete g1; delete g2; }
-  int n_launches() const override { return (qkv_bf16 ? 2 : 5) - (tiles_mode == 2 ? 1 : 0); }
+  int n_launches() const override { return (qkv_bf16 ? 3 : 6) - (tiles_mode == 2 ? 1 : 0); }
 
   /* q/k/v as the contractions address them: rows of 64 contiguous values */
   void views(PbAttnOperand *q, PbAttnOperand *k, PbAttnOperand *v, void *const *bufs) const {

@@ -65,3 +65,64 @@ def test_attention_rejects_unsupported_length(gpu):
     d = gpu.poly_cuda_alloc(64)
     assert gpu.poly_b200_attention(d, d, d, d, 1.0, d, 1, 1, 100) == -1
     gpu.poly_cuda_free(d)
+
+
+def both_ways(gpu, monkeypatch, q, k, v, mask, scale):
+    """The kernel with key-block skipping (the default) and with every block processed."""
+    monkeypatch.delenv('POLY_B200_ATTN_SKIP', raising=False)
+    a = run(gpu, q, k, v, mask, scale)
+    monkeypatch.setenv('POLY_B200_ATTN_SKIP', '0')
+    b = run(gpu, q, k, v, mask, scale)
+    return a, b
+
+
+@pytest.mark.parametrize('T', [256, 1024])
+def test_skipping_masked_blocks_changes_no_bit(gpu, monkeypatch, T):
+    """Key blocks whose mask tile is a constant far below every row's running maximum are left
+    out; the result must be bit for bit that of processing them."""
+    rng = np.random.default_rng(T)
+    q, k, v = (rng.standard_normal((2, T, 3, 64)).astype(np.float32) for _ in range(3))
+    ar = np.arange(T, dtype=np.float32)
+    causal = np.where(ar[:, None] < ar[None, :], np.float32(-1e9), np.float32(0)).astype(np.float32)
+    a, b = both_ways(gpu, monkeypatch, q, k, v, causal, np.float32(0.125))
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    # a banded mask: constant -1e9 tiles on both sides of the diagonal band, first block of keys masked for late rows
+    band = np.where(np.abs(ar[:, None] - ar[None, :]) > 100, np.float32(-1e9), np.float32(0)).astype(np.float32)
+    a, b = both_ways(gpu, monkeypatch, q, k, v, band, np.float32(0.125))
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    assert_close(a, reference(bf16(q), bf16(k), bf16(v), band, np.float32(0.125)), 1e-2, 'banded mask')
+
+
+def test_no_skipping_when_scores_rival_the_mask(gpu, monkeypatch):
+    """Scores as large as the mask constant: the bound on |q.k| forbids skipping, and a mild
+    constant (-30) is never far enough below the running maximum; results must still agree."""
+    T = 256
+    rng = np.random.default_rng(3)
+    q, k, v = (rng.standard_normal((1, T, 2, 64)).astype(np.float32) for _ in range(3))
+    ar = np.arange(T, dtype=np.float32)
+    mild = np.where(ar[:, None] < ar[None, :], np.float32(-30.0), np.float32(0)).astype(np.float32)
+    a, b = both_ways(gpu, monkeypatch, q, k, v, mild, np.float32(0.125))
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    assert_close(a, reference(bf16(q), bf16(k), bf16(v), mild, np.float32(0.125)), 1e-2, 'mild mask')
+    big = np.where(ar[:, None] < ar[None, :], np.float32(-1e4), np.float32(0)).astype(np.float32)
+    a, b = both_ways(gpu, monkeypatch, q * 40, k * 40, v, big, np.float32(0.125))   # |scores| up to ~1e4
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_fully_masked_rows_and_nan_mask_tiles(gpu, monkeypatch):
+    """Rows with nothing but -1e9 (softmax over equal values: the mean of v) and a NaN in the mask."""
+    T = 256
+    rng = np.random.default_rng(4)
+    q, k, v = (rng.standard_normal((1, T, 1, 64)).astype(np.float32) for _ in range(3))
+    ar = np.arange(T, dtype=np.float32)
+    mask = np.where(ar[:, None] < ar[None, :], np.float32(-1e9), np.float32(0)).astype(np.float32)
+    mask[5, :] = -1e9                       # row 5 sees no key at all
+    a, b = both_ways(gpu, monkeypatch, q, k, v, mask, np.float32(0.125))
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    # (row 5 itself is a softmax over values quantised to 64 around -1e9 in fp32: not compared with the fp64 reference)
+    keep = np.arange(T) != 5
+    assert_close(a[:, :, keep], reference(bf16(q), bf16(k), bf16(v), mask, np.float32(0.125))[:, :, keep], 1e-2, 'other rows')
+    assert np.isfinite(a[:, :, 5]).all()
+    mask[200, 7] = np.nan
+    a, b = both_ways(gpu, monkeypatch, q, k, v, mask, np.float32(0.125))
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32), )
