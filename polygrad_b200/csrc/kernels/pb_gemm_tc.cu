@@ -71,7 +71,7 @@ struct TcSmem {
   static constexpr int STAGE_A = TC_BM * TC_BK * 2;
   static constexpr int STAGE_B = BN * TC_BK * 2;
   static constexpr int STAGE = STAGE_A + STAGE_B;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 4 : (BN == 128 ? 6 : 8));
   static constexpr int EPI = 8 * 32 * 32 * 4;
   static constexpr int BYTES = STAGES * STAGE + EPI + 256 + 1024; /* + barriers + alignment slack */
 };
@@ -94,7 +94,8 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kblocks = (g.K + TC_BK - 1) / TC_BK;
-  constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  /* two accumulator buffers; the allocation is a power of two */
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -439,17 +440,24 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
       }
     }
   }
-  /* tile width: fewest waves of work over the SMs, counting a tile's cost as its width plus a fixed part */
+  /* tile width: least estimated time = waves over the 148 SMs x time of one tile, the latter
+   * modelled as K*width (mainloop) plus a fixed 94000 (epilogue and pipeline fill, fitted to
+   * measurements at K = 768 and K = 8192); a wider tile wins ties within 5 % (it moves fewer
+   * operand bytes per flop) */
   int BN = 256;
   {
-    long long best = -1;
+    static const int widths[4] = {64, 128, 192, 256};
+    double best = -1;
     const long long tm = (g.M + TC_BM - 1) / TC_BM;
-    for (int bn = 64; bn <= 256; bn *= 2) {
-      if (bn > 64 && g.N <= bn / 2) continue;
+    for (int wi = 0; wi < 4; wi++) {
+      const int bn = widths[wi];
+      if (bn > 64 && g.N <= widths[wi - 1]) continue;
       const long long tiles = tm * ((g.N + bn - 1) / bn) * p.nbatch;
-      const long long cost = ((tiles + 147) / 148) * (bn + 48);
-      if (best < 0 || cost < best || (cost == best && bn > BN)) { best = cost; BN = bn; }
+      const double cost = (double)((tiles + 147) / 148) * ((double)g.K * bn + 94000.0);
+      if (best < 0 || cost <= best * 1.05) { if (best < 0 || cost < best) best = cost; BN = bn; }
     }
+    const char *f = getenv("POLY_B200_TC_BN");           /* forces a width (measurements) */
+    if (f) { const int v = atoi(f); if (v == 64 || v == 128 || v == 192 || v == 256) BN = v; }
   }
   CUtensorMap ma, mb;
   int rc = make_map(&ma, va.ptr, p.K, rowsA, p.nbatch, va.pitch, va.bpitch, TC_BM);
@@ -457,6 +465,7 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
   if (rc != 0) { pb_scratch_free(scr_a); pb_scratch_free(scr_b); return -1; }
   pb_tc_mark_used();
   if (BN == 256) rc = tc_launch<256>(ma, mb, g, p.nbatch, stream);
+  else if (BN == 192) rc = tc_launch<192>(ma, mb, g, p.nbatch, stream);
   else if (BN == 128) rc = tc_launch<128>(ma, mb, g, p.nbatch, stream);
   else rc = tc_launch<64>(ma, mb, g, p.nbatch, stream);
   p.launches++;

@@ -80,6 +80,20 @@ def test_bf16_policy(devices, policy, shape):
     assert_close(got, want32, 2e-2, f'policy vs fp32 {shape}')
 
 
+@pytest.mark.parametrize('width', [64, 128, 192, 256])
+@pytest.mark.parametrize('shape', [(300, 500, 100), (257, 1000, 72), (512, 768, 256)], ids=str)
+def test_every_tile_width(devices, policy, monkeypatch, width, shape):
+    """The tensor-core kernel picks its tile width per problem; here each width is forced in turn
+    (ragged last tiles in m, n and k included)."""
+    cpu, cuda = devices
+    a, b = _ab(shape, 4)
+    want16 = cpu.tensor(a, 'bfloat16').cast('float32').dot(cpu.tensor(b, 'bfloat16').cast('float32')).numpy()
+    monkeypatch.setenv('POLY_B200_TC_BN', str(width))
+    policy(True)
+    got = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
+    assert_close(got, want16, 1e-4, f'width {width} {shape}')
+
+
 @pytest.mark.parametrize('bf16', [False, True], ids=['fp32', 'bf16'])
 def test_batched_attention_shapes(devices, policy, bf16):
     """q . k^T and p . v with (batch, head) batch axes read through permuted views."""
