@@ -121,7 +121,8 @@ struct GatherProgram : PbAotProgram {
     g.out = (float *)bufs[p_out]; g.ids = (const float *)bufs[p_ids];
     g.arange = (const float *)bufs[p_arange]; g.table = (const float *)bufs[p_table];
     if (g.n_tokens <= 0 || g.n_feat <= 0) return 0;
-    long long grid = g.n_tokens < 148LL * 16 ? g.n_tokens : 148LL * 16;
+    /* a block per token (the blocks are short: one search or bisection, one row copy) */
+    long long grid = g.n_tokens < (1LL << 20) ? g.n_tokens : (1LL << 20);
     int *flag = (int *)pb_scratch_alloc(sizeof(int));
     if (!flag) { pb_set_error("gather: out of scratch memory"); return -1; }
     pb200_gather_check_sorted<<<1, 1024, 0, stream>>>(g.arange, g.vocab, flag);
