@@ -90,3 +90,24 @@ def test_gpt2_rows_independent(gpu):
     for b in (0, 3):
         single = _run_gpt2(gpu, ffi.DEVICE_CUDA, one, tokens[b:b + 1])
         assert_close(full[b], single[0], 1e-5, f'row {b}')
+
+
+def test_plan_passes_change_no_bit_under_bf16_policy(gpu, monkeypatch):
+    """The operand passes (slice copies folded into strides, operands produced as bfloat16 by the
+    step before, attention output relaid, shared mask classification, key-block skipping) only move
+    where a rounding happens or skip work that is exactly zero: the logits must be bit for bit those
+    of the same plan without them."""
+    cfg = dict(vocab_size=307, n_embd=128, n_head=2, n_layer=2, max_seq_len=256, max_batch=2)
+    tokens = np.random.default_rng(21).integers(0, cfg['vocab_size'], (2, 256))
+    gpu.poly_b200_set_gemm_policy(1)
+    try:
+        monkeypatch.delenv('POLY_B200_OPERANDS', raising=False)
+        monkeypatch.delenv('POLY_B200_ATTN_SKIP', raising=False)
+        with_passes = _run_gpt2(gpu, ffi.DEVICE_CUDA, cfg, tokens)
+        monkeypatch.setenv('POLY_B200_OPERANDS', '0')
+        monkeypatch.setenv('POLY_B200_ATTN_SKIP', '0')
+        without = _run_gpt2(gpu, ffi.DEVICE_CUDA, cfg, tokens)
+    finally:
+        gpu.poly_b200_set_gemm_policy(0)
+    assert np.isfinite(with_passes).all()
+    assert np.array_equal(with_passes.view(np.uint32), without.view(np.uint32))
