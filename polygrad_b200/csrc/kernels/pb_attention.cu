@@ -413,11 +413,17 @@ __global__ void __launch_bounds__(128) pb200_attn_bounds(const BoundsArgs a) {
   /* 8 threads per row (16 bytes each: a row is one 128-byte line), 16 rows per pass */
   const int sub = threadIdx.x & 7, grp = threadIdx.x >> 3;
   float nq = 0.f, nk = 0.f;            /* largest squared norm seen by this thread's row group */
-#pragma unroll 2
+  /* all 16 loads of the thread in flight before the arithmetic */
+  uint4 vqs[8], vks[8];
+#pragma unroll
   for (int r = 0; r < 8; r++) {
     const long long row = (long long)blk * 128 + r * 16 + grp;
-    const uint4 vq = *reinterpret_cast<const uint4 *>(a.q + oq + row * a.q_rs + sub * 8);
-    const uint4 vk = *reinterpret_cast<const uint4 *>(a.k + ok + row * a.k_rs + sub * 8);
+    vqs[r] = *reinterpret_cast<const uint4 *>(a.q + oq + row * a.q_rs + sub * 8);
+    vks[r] = *reinterpret_cast<const uint4 *>(a.k + ok + row * a.k_rs + sub * 8);
+  }
+#pragma unroll
+  for (int r = 0; r < 8; r++) {
+    const uint4 vq = vqs[r], vk = vks[r];
     const uint32_t wq[4] = {vq.x, vq.y, vq.z, vq.w}, wk[4] = {vk.x, vk.y, vk.z, vk.w};
     float sq_ = 0.f, sk_ = 0.f;
 #pragma unroll
