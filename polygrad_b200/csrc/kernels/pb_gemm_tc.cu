@@ -24,6 +24,17 @@
  * Two accumulator buffers in tensor memory let the MMA warp start the next tile
  * while the epilogue drains the previous one.
  *
+ * For long K the same kernel runs as CTA pairs (template parameter CTAS = 2, a
+ * cluster of two CTAs on neighbouring SMs): tcgen05.mma.cta_group::2 with M =
+ * 256 computes a 256 x 256 tile, 128 rows in each CTA's tensor memory; each CTA
+ * stages its own 128 rows of A and one half of the tile's B rows (the tensor
+ * cores read both halves), so a stage is 32 KB instead of 48 and six fit.  The
+ * first CTA of the pair issues the MMAs; both CTAs' TMA loads count their bytes
+ * on its "full" barrier (cp.async.bulk.tensor.cta_group::2, no multicast), its
+ * commits arrive on the "empty" and "accumulator full" barriers of both CTAs
+ * (tcgen05.commit ... multicast::cluster), and the epilogue warps of both CTAs
+ * arrive on its "accumulator empty" barrier through mapa / shared::cluster.
+ *
  * Every wait on an mbarrier is bounded: after a few seconds without progress the
  * CTA records an error code, stops issuing work, frees its tensor memory and
  * returns; the host reports the code at the next synchronisation point.
@@ -66,20 +77,25 @@ __device__ __forceinline__ void tile_coords(const TcArgs &g, int t, int *mt, int
   else { *nt = in_batch % g.tiles_n; *mt = in_batch / g.tiles_n; }
 }
 
-template <int BN>
+/* CTAS = 2: two CTAs on neighbouring SMs (a cluster of 2) work on one 256 x BN tile with
+ * cta_group::2 MMAs; each holds its 128 rows of A and half of the tile's B rows. */
+template <int BN, int CTAS>
 struct TcSmem {
   static constexpr int STAGE_A = TC_BM * TC_BK * 2;
-  static constexpr int STAGE_B = BN * TC_BK * 2;
+  static constexpr int STAGE_B = (BN / CTAS) * TC_BK * 2;
   static constexpr int STAGE = STAGE_A + STAGE_B;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 4 : (BN == 128 ? 6 : 8));
+  static constexpr int STAGES = CTAS == 2 ? (BN >= 192 ? 6 : 8) : ((BN == 256) ? 4 : (BN == 192 ? 4 : (BN == 128 ? 6 : 8)));
   static constexpr int EPI = 8 * 32 * 32 * 4;
   static constexpr int BYTES = STAGES * STAGE + EPI + 256 + 1024; /* + barriers + alignment slack */
 };
 
-template <int BN>
+template <int BN, int CTAS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcArgs g) {
-  using S = TcSmem<BN>;
+  using S = TcSmem<BN, CTAS>;
+  /* CTA pair: rank within the pair, the pair's index and count (tiles are handed out per pair) */
+  const uint32_t rank = CTAS == 2 ? cluster_ctarank() : 0u;
+  const int unit = blockIdx.x / CTAS, n_units = gridDim.x / CTAS;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;              /* swizzled tiles need 1024-byte alignment */
@@ -100,15 +116,23 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < S::STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-    for (int b = 0; b < 2; b++) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, 8); }
+    /* the accumulator-empty barrier of the pair's first CTA collects the epilogue warps of both CTAs */
+    for (int b = 0; b < 2; b++) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, 8 * CTAS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (CTAS == 2) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  /* the other CTA's barriers must exist before anything of this CTA signals them */
+  if constexpr (CTAS == 2) cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
 
@@ -117,26 +141,34 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < g.n_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < g.n_tiles && ok; t += n_units) {
         int nt, mt; const int bz = t / (g.tiles_n * g.tiles_m);
         tile_coords(g, t, &mt, &nt);
         for (int kb = 0; kb < kblocks; kb++) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, &abort_flag, 1)) { ok = false; break; }
-          mbar_expect_tx(bar_full + 8 * stage, S::STAGE);
           const uint32_t sa = base + stage * S::STAGE, sb = sa + S::STAGE_A;
-          tma_load_3d(sa, &map_a, bar_full + 8 * stage, kb * TC_BK, mt * TC_BM, bz);
-          tma_load_3d(sb, &map_b, bar_full + 8 * stage, kb * TC_BK, nt * BN, bz);
+          if constexpr (CTAS == 2) {
+            /* both CTAs' bytes are counted on the first CTA's barrier, whose MMA thread waits for them */
+            const uint32_t full0 = mapa_shared(bar_full + 8 * stage, 0);
+            if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * S::STAGE);
+            tma_load_3d_pair(sa, &map_a, full0, kb * TC_BK, (mt * 2 + (int)rank) * TC_BM, bz);
+            tma_load_3d_pair(sb, &map_b, full0, kb * TC_BK, nt * BN + (int)rank * (BN / 2), bz);
+          } else {
+            mbar_expect_tx(bar_full + 8 * stage, S::STAGE);
+            tma_load_3d(sa, &map_a, bar_full + 8 * stage, kb * TC_BK, mt * TC_BM, bz);
+            tma_load_3d(sb, &map_b, bar_full + 8 * stage, kb * TC_BK, nt * BN, bz);
+          }
           if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     /* ── MMA issuer ── */
-    if (lane == 0) {
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((TC_BM * CTAS) >> 4) << 24);
       uint32_t stage = 0, phase = 0, it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < g.n_tiles && ok; t += gridDim.x, it++) {
+      for (int t = unit; t < g.n_tiles && ok; t += n_units, it++) {
         const uint32_t buf = it & 1u, use = it >> 1;
         if (!mbar_wait(bar_tempty + 8 * buf, (use & 1u) ^ 1u, &abort_flag, 2)) { ok = false; break; }
         tc_fence_after_sync();
@@ -147,12 +179,15 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           const uint32_t sa = base + stage * S::STAGE, sb = sa + S::STAGE_A;
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sb);
 #pragma unroll
-          for (int k = 0; k < TC_BK / 16; k++)
-            tc_mma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
-          tc_commit(bar_empty + 8 * stage);          /* frees the stage when these MMAs have read it */
+          for (int k = 0; k < TC_BK / 16; k++) {
+            if constexpr (CTAS == 2) tc_mma_bf16_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+            else tc_mma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+          }
+          /* frees the stage (in both CTAs of a pair) when these MMAs have read it */
+          if constexpr (CTAS == 2) tc_commit_pair(bar_empty + 8 * stage, 3); else tc_commit(bar_empty + 8 * stage);
           if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) tc_commit(bar_tfull + 8 * buf);      /* accumulator complete */
+        if (ok) { if constexpr (CTAS == 2) tc_commit_pair(bar_tfull + 8 * buf, 3); else tc_commit(bar_tfull + 8 * buf); }   /* accumulator complete */
       }
     }
   } else {
@@ -162,7 +197,7 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     float *stg = epi + (warp - 2) * 32 * 32;
     uint32_t it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < g.n_tiles && ok; t += gridDim.x, it++) {
+    for (int t = unit; t < g.n_tiles && ok; t += n_units, it++) {
       int nt, mt;
       tile_coords(g, t, &mt, &nt);
       int bz = t / (g.tiles_n * g.tiles_m);
@@ -171,7 +206,7 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       const uint32_t buf = it & 1u, use = it >> 1;
       if (!mbar_wait(bar_tfull + 8 * buf, use & 1u, &abort_flag, 4)) { ok = false; break; }
       tc_fence_after_sync();
-      const int row0 = mt * TC_BM + q * 32;
+      const int row0 = (mt * CTAS + (int)rank) * TC_BM + q * 32;
       const int rows = min(32, g.M - row0);
       float *__restrict__ C = g.C + oc;
       const float *__restrict__ X = g.has_x ? g.X + ox : nullptr;
@@ -248,7 +283,10 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         }
       }
       tc_fence_before_sync();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+      if (lane == 0) {
+        if constexpr (CTAS == 2) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * buf, 0));
+        else mbar_arrive(bar_tempty + 8 * buf);
+      }
     }
   }
 
@@ -258,9 +296,12 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     /* let copies that were already issued land before the shared memory goes away */
     for (int i = 0; i < 2000; i++) __nanosleep(1000);
   }
+  /* neither CTA of a pair leaves while the other may still signal its barriers or read its tiles */
+  if constexpr (CTAS == 2) cluster_sync_all();
   if (warp == 0) {
     tc_fence_after_sync();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if constexpr (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -293,15 +334,15 @@ static int make_map(CUtensorMap *map, const void *ptr, long long K, long long ro
   return 0;
 }
 
-template <int BN>
+template <int BN, int CTAS>
 static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, long long nbatch, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(pb200_gemm_tc<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN>::BYTES);
-    if (e != cudaSuccess) { pb_set_error("gemm: cannot reserve %d bytes of shared memory: %s", TcSmem<BN>::BYTES, cudaGetErrorString(e)); return -1; }
+    cudaError_t e = cudaFuncSetAttribute(pb200_gemm_tc<BN, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN, CTAS>::BYTES);
+    if (e != cudaSuccess) { pb_set_error("gemm: cannot reserve %d bytes of shared memory: %s", TcSmem<BN, CTAS>::BYTES, cudaGetErrorString(e)); return -1; }
     configured = true;
   }
-  g.tiles_m = (g.M + TC_BM - 1) / TC_BM;
+  g.tiles_m = (g.M + TC_BM * CTAS - 1) / (TC_BM * CTAS);
   g.tiles_n = (g.N + BN - 1) / BN;
   long long tiles = (long long)g.tiles_m * g.tiles_n * nbatch;
   if (tiles > 2147483647LL) { pb_set_error("gemm: too many tiles"); return -1; }
@@ -309,9 +350,21 @@ static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, lo
   g.m_fast = g.N > g.M ? 1 : 0;
   static int sms = 0;
   if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); if (sms <= 0) sms = 148; }
-  int grid = tiles < sms ? (int)tiles : sms;
-  pb200_gemm_tc<BN><<<grid, TC_THREADS, TcSmem<BN>::BYTES, stream>>>(ma, mb, g);
-  cudaError_t e = cudaGetLastError();
+  const int units = sms / CTAS;
+  const int grid = (int)(tiles < units ? tiles : units) * CTAS;
+  cudaError_t e;
+  if (CTAS == 1) {
+    pb200_gemm_tc<BN, CTAS><<<grid, TC_THREADS, TcSmem<BN, CTAS>::BYTES, stream>>>(ma, mb, g);
+    e = cudaGetLastError();
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = TcSmem<BN, CTAS>::BYTES; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, pb200_gemm_tc<BN, CTAS>, ma, mb, g);
+  }
   if (e != cudaSuccess) { pb_set_error("tensor-core gemm launch: %s", cudaGetErrorString(e)); return -1; }
   return 0;
 }
@@ -445,6 +498,7 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
    * measurements at K = 768 and K = 8192); a wider tile wins ties within 5 % (it moves fewer
    * operand bytes per flop) */
   int BN = 256;
+  double best_cost = 0;
   {
     static const int widths[4] = {64, 128, 192, 256};
     double best = -1;
@@ -456,18 +510,34 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
       const double cost = (double)((tiles + 147) / 148) * ((double)g.K * bn + 94000.0);
       if (best < 0 || cost <= best * 1.05) { if (best < 0 || cost < best) best = cost; BN = bn; }
     }
+    best_cost = best;
     const char *f = getenv("POLY_B200_TC_BN");           /* forces a width (measurements) */
     if (f) { const int v = atoi(f); if (v == 64 || v == 128 || v == 192 || v == 256) BN = v; }
   }
+  /* CTA pairs (cta_group::2, one 256 x 256 tile per pair): each CTA stages half as much of B, which
+   * pays where the mainloop is the bound -- long K, and enough tiles to fill the 74 pairs.  With short
+   * K the epilogue is the bound and pairs gain nothing (measured: 8192^3 1235 -> 1384 TFLOP/s,
+   * 8192 x 2304 x 768 802 -> 765).  In the time model a pair's mainloop costs 0.85 of two single
+   * tiles'.  POLY_B200_TC_CTAS=1|2 forces the choice (2 implies the 256-wide tile). */
+  int ctas = 1;
+  if (g.M > TC_BM && g.N > 128) {
+    const long long pair_tiles = ((g.M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((g.N + 255) / 256) * p.nbatch;
+    const double pair_cost = (double)((pair_tiles + 73) / 74) * (0.85 * (double)g.K * 256 + 94000.0);
+    if (g.K >= 2048 && pair_tiles >= 74 && pair_cost <= best_cost && !getenv("POLY_B200_TC_BN")) { ctas = 2; BN = 256; }
+    const char *c = getenv("POLY_B200_TC_CTAS");
+    if (c && atoi(c) == 1) ctas = 1;
+    if (c && atoi(c) == 2) { ctas = 2; BN = 256; }
+  }
   CUtensorMap ma, mb;
   int rc = make_map(&ma, va.ptr, p.K, rowsA, p.nbatch, va.pitch, va.bpitch, TC_BM);
-  if (rc == 0) rc = make_map(&mb, vb.ptr, p.K, rowsB, p.nbatch, vb.pitch, vb.bpitch, BN);
+  if (rc == 0) rc = make_map(&mb, vb.ptr, p.K, rowsB, p.nbatch, vb.pitch, vb.bpitch, BN / ctas);
   if (rc != 0) { pb_scratch_free(scr_a); pb_scratch_free(scr_b); return -1; }
   pb_tc_mark_used();
-  if (BN == 256) rc = tc_launch<256>(ma, mb, g, p.nbatch, stream);
-  else if (BN == 192) rc = tc_launch<192>(ma, mb, g, p.nbatch, stream);
-  else if (BN == 128) rc = tc_launch<128>(ma, mb, g, p.nbatch, stream);
-  else rc = tc_launch<64>(ma, mb, g, p.nbatch, stream);
+  if (ctas == 2) rc = tc_launch<256, 2>(ma, mb, g, p.nbatch, stream);
+  else if (BN == 256) rc = tc_launch<256, 1>(ma, mb, g, p.nbatch, stream);
+  else if (BN == 192) rc = tc_launch<192, 1>(ma, mb, g, p.nbatch, stream);
+  else if (BN == 128) rc = tc_launch<128, 1>(ma, mb, g, p.nbatch, stream);
+  else rc = tc_launch<64, 1>(ma, mb, g, p.nbatch, stream);
   p.launches++;
   /* stream-ordered pool: later work on this stream may reuse the blocks */
   pb_scratch_free(scr_a); pb_scratch_free(scr_b);
@@ -494,7 +564,7 @@ int pb_gemm_tc_launch_raw(const void *a_bf16, long long a_pitch, const void *b_b
   if (make_map(&ma, a_bf16, K, M, 1, a_pitch, M * a_pitch, TC_BM) != 0) return -1;
   if (make_map(&mb, b_bf16, K, N, 1, b_pitch, N * b_pitch, BN) != 0) return -1;
   pb_tc_mark_used();
-  if (BN == 256) return tc_launch<256>(ma, mb, g, 1, stream);
-  if (BN == 128) return tc_launch<128>(ma, mb, g, 1, stream);
-  return tc_launch<64>(ma, mb, g, 1, stream);
+  if (BN == 256) return tc_launch<256, 1>(ma, mb, g, 1, stream);
+  if (BN == 128) return tc_launch<128, 1>(ma, mb, g, 1, stream);
+  return tc_launch<64, 1>(ma, mb, g, 1, stream);
 }

@@ -94,6 +94,20 @@ def test_every_tile_width(devices, policy, monkeypatch, width, shape):
     assert_close(got, want16, 1e-4, f'width {width} {shape}')
 
 
+@pytest.mark.parametrize('shape', [(300, 500, 100), (257, 1000, 72), (512, 768, 256), (129, 65, 17), (1024, 256, 2048)], ids=str)
+def test_cta_pairs(devices, policy, monkeypatch, shape):
+    """The cta_group::2 form of the kernel (two CTAs per 256 x 256 tile), forced for shapes that would
+    not choose it: ragged tiles, a second CTA with a single row or none at all."""
+    cpu, cuda = devices
+    a, b = _ab(shape, 5)
+    want16 = cpu.tensor(a, 'bfloat16').cast('float32').dot(cpu.tensor(b, 'bfloat16').cast('float32')).numpy()
+    monkeypatch.setenv('POLY_B200_TC_BN', '256')
+    monkeypatch.setenv('POLY_B200_TC_CTAS', '2')
+    policy(True)
+    got = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
+    assert_close(got, want16, 1e-4, f'pairs {shape}')
+
+
 @pytest.mark.parametrize('bf16', [False, True], ids=['fp32', 'bf16'])
 def test_batched_attention_shapes(devices, policy, bf16):
     """q . k^T and p . v with (batch, head) batch axes read through permuted views."""
