@@ -159,7 +159,8 @@ int pb_pack_launch(const void *src, void *dst, int naxes, const long long *ext, 
   if (blocks > 148LL * 32) blocks = 148LL * 32;
   if (src_dtype == PB_F32 && dst_dtype == PB_F32) pb200_pack<float, float><<<(unsigned)blocks, 256, 0, stream>>>(a);
   else if (src_dtype == PB_F32 && dst_dtype == PB_BF16) pb200_pack<float, __nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(a);
-  else if (src_dtype == PB_BF16 && dst_dtype == PB_BF16) pb200_pack<__nv_bfloat16, __nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(a);
+  else if ((src_dtype == PB_BF16 && dst_dtype == PB_BF16) || (src_dtype == PB_F16 && dst_dtype == PB_F16))
+    pb200_pack<__nv_bfloat16, __nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(a);     /* a copy of 16-bit elements */
   else { pb_set_error("pack: unsupported dtypes"); return -1; }
   e = cudaGetLastError();
   if (e != cudaSuccess) { pb_set_error("pack launch: %s", cudaGetErrorString(e)); return -1; }
@@ -418,10 +419,10 @@ void *PbGemmProgram::pack_operand(const void *src, long long off, bool is_a, int
 
 int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
   launches = 0;
-  if (dtype == PB_BF16 || a_bf16 || c_bf16 || pb_gemm_policy_bf16()) {
+  if (dtype != PB_F32 || a_bf16 || c_bf16 || pb_gemm_policy_bf16()) {
     int rc = pb_gemm_tc_run(*this, bufs, stream);
     if (rc != PB_TC_UNSUPPORTED) return rc;
-    if (dtype == PB_BF16 || a_bf16 || c_bf16) { pb_set_error("gemm: bf16 operands need the tensor-core kernel, which rejected this shape"); return -1; }
+    if (dtype != PB_F32 || a_bf16 || c_bf16) { pb_set_error("gemm: 16-bit operands need the tensor-core kernel, which rejected this shape"); return -1; }
   }
   SgemmArgs g{};
   void *pa = nullptr, *pb = nullptr;
@@ -484,7 +485,7 @@ PbGemmProgram *pb_parse_gemm(const PbHeader &h0, const char *prefix, std::string
   p->has_x = p->p_x >= 0;
   p->relu = h.geti("relu") != 0;
   const std::string &dt = h.get("dtype");
-  if (dt == "f32") p->dtype = PB_F32; else if (dt == "bf16") p->dtype = PB_BF16;
+  if (dt == "f32") p->dtype = PB_F32; else if (dt == "bf16") p->dtype = PB_BF16; else if (dt == "f16") p->dtype = PB_F16;
   else { err = "gemm operand dtype '" + dt + "' has no kernel"; delete p; return nullptr; }
   p->off_c = off[0]; p->off_a = off[1]; p->off_b = off[2]; p->off_x = off[3];
   p->rw.assign((size_t)p->n_params, '-');

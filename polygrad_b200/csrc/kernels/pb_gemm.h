@@ -9,7 +9,7 @@
 #include <cuda_bf16.h>
 #include <vector>
 
-enum { PB_F32 = 0, PB_BF16 = 1 };
+enum { PB_F32 = 0, PB_BF16 = 1, PB_F16 = 2 };      /* storage type of a contraction's operands */
 #define PB_PACK_MAX_AXES 12
 #define PB_TC_UNSUPPORTED 77
 

@@ -57,6 +57,7 @@ struct TcArgs {
   long long c_sm, x_sm, x_sn;
   int nb; int bext[4]; long long c_sb[4], x_sb[4];
   int has_x, relu;
+  int ab_f16;                      /* A and B hold float16 (else bfloat16) */
   int vec_io;                      /* C rows (and addend rows) 16-byte aligned, N % 4 == 0 */
   int c_bf16;                      /* C holds bfloat16 (needs vec_io) */
   int tiles_m, tiles_n, n_tiles;   /* n_tiles = nbatch * tiles_m * tiles_n */
@@ -165,7 +166,9 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
   } else if (warp == 1) {
     /* ── MMA issuer ── */
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((TC_BM * CTAS) >> 4) << 24);
+      /* D float32; A and B bfloat16 (format 1) or float16 (format 0), both K-major */
+      const uint32_t fmt = g.ab_f16 ? 0u : 1u;
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((TC_BM * CTAS) >> 4) << 24);
       uint32_t stage = 0, phase = 0, it = 0;
       bool ok = true;
       for (int t = unit; t < g.n_tiles && ok; t += n_units, it++) {
@@ -320,16 +323,16 @@ static EncodeTiledFn encode_tiled() {
 
 /* rows x K bf16, K contiguous, row pitch `pitch` elements, `nbatch` matrices `bpitch` elements apart */
 static int make_map(CUtensorMap *map, const void *ptr, long long K, long long rows, long long nbatch,
-                    long long pitch, long long bpitch, int box_rows) {
+                    long long pitch, long long bpitch, int box_rows, bool f16 = false) {
   EncodeTiledFn enc = encode_tiled();
   if (!enc) { pb_set_error("gemm: cuTensorMapEncodeTiled not available"); return -1; }
   cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)nbatch};
   cuuint64_t strides[2] = {(cuuint64_t)pitch * 2, (cuuint64_t)(nbatch > 1 ? bpitch : rows * pitch) * 2};
   cuuint32_t box[3] = {TC_BK, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult rc = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult rc = enc(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr),
+                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) { pb_set_error("gemm: cuTensorMapEncodeTiled failed (%d)", (int)rc); return -1; }
   return 0;
 }
@@ -400,7 +403,7 @@ static const void *tc_operand(PbGemmProgram &p, PbTcOperand &cache, const void *
     dst = cache.data;
     cache.src = src_buf; cache.version = ver; cache.misses++;
   }
-  if (p.pack_into(dst, src_buf, off, is_a, p.dtype, PB_BF16, Kp, stream) != 0) {
+  if (p.pack_into(dst, src_buf, off, is_a, p.dtype, p.dtype == PB_F16 ? PB_F16 : PB_BF16, Kp, stream) != 0) {
     if (*scratch) { pb_scratch_free(*scratch); *scratch = nullptr; }
     return nullptr;
   }
@@ -412,7 +415,7 @@ static const void *tc_operand(PbGemmProgram &p, PbTcOperand &cache, const void *
 struct TcView { const void *ptr; long long pitch, bpitch; };
 
 static bool tc_in_place(const PbGemmProgram &p, const void *buf, long long off, bool is_a, TcView *v) {
-  if (p.dtype != PB_BF16 && !(is_a && p.a_bf16)) return false;
+  if (p.dtype == PB_F32 && !(is_a && p.a_bf16)) return false;
   const bool direct = is_a ? p.a_direct : p.b_direct;
   const long long sk = is_a ? p.a_sk : p.b_sk, srow = is_a ? p.a_sm : p.b_sn;
   const long long rows = is_a ? p.M : p.N;
@@ -470,6 +473,7 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
   g.C = (float *)bufs[p.p_c] + p.off_c;
   g.c_sm = swap ? p.c_sn : p.c_sm;
   g.has_x = p.has_x ? 1 : 0; g.relu = p.relu ? 1 : 0;
+  g.ab_f16 = p.dtype == PB_F16 ? 1 : 0;
   if (p.has_x) { g.X = (const float *)bufs[p.p_x] + p.off_x; g.x_sm = swap ? p.x_sn : p.x_sm; g.x_sn = swap ? p.x_sm : p.x_sn; }
   g.nb = (int)p.b_ax.size();
   for (int i = 0; i < g.nb; i++) { g.bext[i] = (int)p.b_ax[i].ext; g.c_sb[i] = p.b_ax[i].sc; g.x_sb[i] = p.b_ax[i].sx; }
@@ -529,8 +533,8 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
     if (c && atoi(c) == 2) { ctas = 2; BN = 256; }
   }
   CUtensorMap ma, mb;
-  int rc = make_map(&ma, va.ptr, p.K, rowsA, p.nbatch, va.pitch, va.bpitch, TC_BM);
-  if (rc == 0) rc = make_map(&mb, vb.ptr, p.K, rowsB, p.nbatch, vb.pitch, vb.bpitch, BN / ctas);
+  int rc = make_map(&ma, va.ptr, p.K, rowsA, p.nbatch, va.pitch, va.bpitch, TC_BM, p.dtype == PB_F16);
+  if (rc == 0) rc = make_map(&mb, vb.ptr, p.K, rowsB, p.nbatch, vb.pitch, vb.bpitch, BN / ctas, p.dtype == PB_F16);
   if (rc != 0) { pb_scratch_free(scr_a); pb_scratch_free(scr_b); return -1; }
   pb_tc_mark_used();
   if (ctas == 2) rc = tc_launch<256, 2>(ma, mb, g, p.nbatch, stream);

@@ -69,6 +69,22 @@ def test_bf16_buffers(devices, shape):
 
 
 @pytest.mark.parametrize('shape', SHAPES, ids=str)
+def test_fp16_buffers(devices, gpu, shape):
+    """float16 operands, fp32 accumulation.  Stock polygrad cannot run this graph on the CPU here
+    (its C renderer's __fp16 does not compile with gcc on x86), so the reference is numpy on the
+    same float16-rounded operands, accumulated in float64."""
+    _, cuda = devices
+    a, b = _ab(shape, 6)
+    a16, b16 = a.astype(np.float16), b.astype(np.float16)
+    want = (a16.astype(np.float64) @ b16.astype(np.float64)).astype(np.float32)
+    gpu.poly_b200_stats_reset()
+    got = cuda.tensor(a16).cast('float32').dot(cuda.tensor(b16).cast('float32')).numpy()
+    assert_close(got, want, 1e-4, f'fp16 {shape}')
+    if shape[2] >= 16 and shape[0] * shape[1] >= 64:
+        assert gpu.stats()['launches_precompiled'] >= 1      # the tensor-core kernel, not the general renderer
+
+
+@pytest.mark.parametrize('shape', SHAPES, ids=str)
 def test_bf16_policy(devices, policy, shape):
     cpu, cuda = devices
     a, b = _ab(shape, 3)
