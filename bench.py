@@ -458,7 +458,9 @@ def run_rowops(args):
         ('x*2+1', lambda t: t * 2 + 1, full), ('exp', lambda t: t.exp(), full), ('tanh', lambda t: t.tanh(), full),
         ('sum', lambda t: t.sum(-1), red), ('max', lambda t: t.max(-1), red), ('mean', lambda t: t.mean(-1), red),
         ('var', lambda t: t.var(-1), red), ('softmax', lambda t: t.softmax(-1), full),
-        ('layernorm', lambda t: t.layernorm(-1, 1e-5), full), ('permute(1,0)', lambda t: t.permute(1, 0), full),
+        ('layernorm', lambda t: t.layernorm(-1, 1e-5), full),
+        ('rmsnorm', lambda t: t / ((t * t).mean(-1, keepdim=True) + 1e-6).sqrt(), full),
+        ('permute(1,0)', lambda t: t.permute(1, 0), full),
         ('[::-1]', lambda t: t[::-1], full), ('[:, ::-1]', lambda t: t[:, ::-1], full),
     ]
     rows = []

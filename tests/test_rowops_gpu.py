@@ -25,6 +25,8 @@ OPS = {
     'sum0': lambda t: t.sum(0),
     'softmax': lambda t: t.softmax(-1),
     'layernorm': lambda t: t.layernorm(-1, 1e-5),
+    # polygrad has no RMSNorm builder; this is the composition a caller writes
+    'rmsnorm': lambda t: t / ((t * t).mean(-1, keepdim=True) + 1e-6).sqrt(),
 }
 EXACT = {
     'permute': lambda t: t.permute(1, 0),
