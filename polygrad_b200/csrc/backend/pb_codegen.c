@@ -1020,7 +1020,7 @@ char *pb_render_jit(PbKern *k, const char *fn_name) {
       int ident[PB_MAX_PARAMS]; bool all_used = true;
       for (int a = 0; a < k->n_params; a++) { ident[a] = a; if (!k->params[a] || !(usage[a] & 3)) all_used = false; }
       if (all_used) {
-        PbFuseIn in = { k, ident, PB_FUSE_FINAL };
+        PbFuseIn in = { k, ident, PB_FUSE_FINAL, false };
         PbFuseOut fo;
         r = pb_render_rowfused(&in, 1, false, &fo);
         if (r) {
@@ -1232,6 +1232,7 @@ char *pb_render_rowfused(PbFuseIn *in, int n, bool out_bf16, PbFuseOut *out) {
     rf->red_node[i] = -1;
     for (int r = 0; r < k->n_ranges; r++) rf->map[i][r] = -1;
     if (in[i].role == PB_FUSE_PRODUCER) { if (k->n_reduce_nodes != 0) goto done; }
+    else if (in[i].keep_out) goto done;
     else if (in[i].role == PB_FUSE_PHASE) {
       if (k->n_reduce_nodes != 1) goto done;
       rf->red_node[i] = rf_find_reduce(k);
@@ -1325,6 +1326,13 @@ char *pb_render_rowfused(PbFuseIn *in, int n, bool out_bf16, PbFuseOut *out) {
       if (!k->params[a] || !(rf->usage[i][a] & 3)) continue;
       int sl = in[i].slot[a];
       int w = rf_writer_of(rf, sl);
+      if (w >= 0 && w == i && in[i].keep_out && a == k->stores[0].param && !(rf->usage[i][a] & 1)) {
+        /* a producer whose result lives on: written by the final pass next to the final result */
+        if (out->n_params >= PB_MAX_PARAMS || k->params[a]->dtype.bitsize != 32 || k->params[a]->dtype.priority != 13) goto done;
+        int f = out->n_params++; out->slot[f] = sl; out->rw[f] = (rf->usage[i][a] & 4) ? 'W' : 'w';
+        rf->fparam[i][a] = f;
+        continue;
+      }
       if (w >= 0) {
         /* internal: reads are replaced; the write itself disappears */
         if ((rf->usage[i][a] & 1) && w >= i) goto done;     /* read before it is produced */
@@ -1377,6 +1385,21 @@ char *pb_render_rowfused(PbFuseIn *in, int n, bool out_bf16, PbFuseOut *out) {
       if (!vec && fit && a.stride[rf->c_range[i]] == 0) continue;   /* row-invariant after all */
       if (!vec) rf->V = 1;
     }
+  }
+  for (int i = 0; i < n - 1; i++) {
+    if (!in[i].keep_out) continue;
+    if (rf->final_reduce) goto done;                 /* there is no elementwise final pass to store from */
+    PbKern *k = in[i].k;
+    PbAffine ps;
+    if (k->stores[0].index->n_src > 2 || !rf_fit(k, k->stores[0].index->src[1], &ps)) goto done;
+    if (ps.stride[rf->c_range[i]] != 1 || ps.offset % 4) rf->V = 1;
+    int64_t lo = ps.offset, hi = ps.offset;
+    for (int r = 0; r < k->n_ranges; r++) {
+      if (r != rf->c_range[i] && ps.stride[r] % 4) rf->V = 1;
+      int64_t sp = ps.stride[r] * (k->extent[r] - 1);
+      if (sp > 0) hi += sp; else lo += sp;
+    }
+    if (lo < 0 || hi >= k->params[k->stores[0].param]->dtype.ptr_size) rf->V = 1;
   }
   if (!rf->final_reduce) {
     if (fs.stride[rf->canon_c] != 1 || fs.offset % 4) rf->V = 1;
@@ -1448,7 +1471,7 @@ char *pb_render_rowfused(PbFuseIn *in, int n, bool out_bf16, PbFuseOut *out) {
       if (rf->fparam[i][a] == x) { PolyDType b = in[i].k->params[a]->dtype; b.is_ptr = false; b.count = 1; ct = pb_ctype(b); }
     bool is_out = out->slot[x] == rf->wslot[n - 1];
     if (is_out && out_bf16) ct = "__nv_bfloat16";
-    pb_str_printf(&text, "%s%s* __restrict__ p%d, ", is_out ? "" : "const ", ct, x);
+    pb_str_printf(&text, "%s%s* __restrict__ p%d, ", (is_out || out->rw[x] != 'r') ? "" : "const ", ct, x);
   }
   pb_str_puts(&text, "const long long n_work) {\n");
   rf_set_indent(rf, 1);
@@ -1560,8 +1583,36 @@ char *pb_render_rowfused(PbFuseIn *in, int n, bool out_bf16, PbFuseOut *out) {
         emit_src(g, st->index->src[1]);
         ref(g, st->index->src[1], is0, sizeof is0);
       }
+      /* producers whose result is kept: their store index (lane 0) and a 4-wide buffer */
+      char kis[RF_MAX][96];
+      for (int w = 0; w < n - 1; w++) {
+        kis[w][0] = 0;
+        if (!in[w].keep_out) continue;
+        Gen *pg = &rf->g[w];
+        PbStore *pst = &pg->k->stores[0];
+        if (V == 4) {
+          ind(g); pb_str_printf(&text, "float k4_%d_[4];\n", w);
+          rf_set_lane(rf, 0);
+          emit_src(pg, pst->index->src[1]);
+          ref(pg, pst->index->src[1], kis[w], sizeof kis[w]);
+        }
+      }
       for (int lane = 0; lane < V; lane++) {
         rf_set_lane(rf, lane);
+        for (int w = 0; w < n - 1; w++) {
+          if (!in[w].keep_out) continue;
+          Gen *pg = &rf->g[w];
+          PbStore *pst = &pg->k->stores[0];
+          emit_src(pg, pst->value);
+          char kv[96]; ref(pg, pst->value, kv, sizeof kv);
+          if (V == 4) { ind(g); pb_str_printf(&text, "k4_%d_[%d] = (float)(%s);\n", w, lane, kv); }
+          else {
+            emit_src(pg, pst->index->src[1]);
+            char kidx[96], kpn[32]; ref(pg, pst->index->src[1], kidx, sizeof kidx); ref(pg, pst->index->src[0], kpn, sizeof kpn);
+            ind(g); pb_str_printf(&text, "if (live_) pb_st(%s, %s, %lldLL, (float)(%s));\n", kpn, kidx,
+                                  (long long)pg->k->params[pst->param]->dtype.ptr_size, kv);
+          }
+        }
         emit_src(g, st->value);
         char v[96]; ref(g, st->value, v, sizeof v);
         if (V == 4) { ind(g); pb_str_printf(&text, "o4_[%d] = (float)(%s);\n", lane, v); }
@@ -1581,6 +1632,12 @@ char *pb_render_rowfused(PbFuseIn *in, int n, bool out_bf16, PbFuseOut *out) {
                                "uint2 w_; w_.x = *reinterpret_cast<unsigned*>(&q0_); w_.y = *reinterpret_cast<unsigned*>(&q1_); "
                                "*reinterpret_cast<uint2*>(%s + %s) = w_; }\n", pn, is);
         else pb_str_printf(&text, "if (live_) pb_st4(%s + %s, o4_);\n", pn, is);
+        for (int w = 0; w < n - 1; w++) {
+          if (!in[w].keep_out) continue;
+          Gen *pg = &rf->g[w];
+          char kpn[32]; ref(pg, pg->k->stores[0].index->src[0], kpn, sizeof kpn);
+          ind(g); pb_str_printf(&text, "if (live_) pb_st4(%s + %s, k4_%d_);\n", kpn, kis[w], w);
+        }
       }
       rf_set_lane(rf, 0);
       for (int r = 0; r < rf->n; r++) rf->g[r].bound &= ~rf->g[r].lane_dep;

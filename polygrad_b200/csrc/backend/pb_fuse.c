@@ -113,7 +113,7 @@ static int step_out_slot(const PbPlan *p, const PbStep *st) {
 
 /* Renders the member steps order[0..no) (the last one is the final kernel) as one
  * row kernel; NULL when the chain does not have a supported form. */
-char *pb_render_chain(const PbPlan *p, const int *order, int no, bool out_bf16, PbFuseOut *fo) {
+char *pb_render_chain(const PbPlan *p, const int *order, const bool *keep, int no, bool out_bf16, PbFuseOut *fo) {
   PbKern kerns[CHAIN_MAX]; PbFuseIn in[CHAIN_MAX]; int slots[CHAIN_MAX][PB_MAX_PARAMS];
   bool built = true; int n_phase = 0;
   int nb = 0;
@@ -129,6 +129,7 @@ char *pb_render_chain(const PbPlan *p, const int *order, int no, bool out_bf16, 
     for (int a = 0; a < n_own && a < PB_MAX_PARAMS; a++) slots[j][a] = pb_plan_resolve(p, own[a]);
     in[j].k = &kerns[j]; in[j].slot = slots[j];
     in[j].role = (j == no - 1) ? PB_FUSE_FINAL : (kerns[j].n_reduce_nodes ? PB_FUSE_PHASE : PB_FUSE_PRODUCER);
+    in[j].keep_out = keep && keep[j];
     if (in[j].role == PB_FUSE_PHASE) n_phase++;
   }
   char *text = NULL;
@@ -136,6 +137,8 @@ char *pb_render_chain(const PbPlan *p, const int *order, int no, bool out_bf16, 
   for (int j = 0; j < nb; j++) pb_kern_free(&kerns[j]);
   return text;
 }
+
+static bool env_no_keep(void) { const char *e = getenv("POLY_B200_FUSE_KEEP"); return e && e[0] == '0'; }
 
 static int fuse_rows(PbPlan *p) {
   int fused = 0;
@@ -159,27 +162,43 @@ static int fuse_rows(PbPlan *p) {
         if (!have && nm < CHAIN_MAX) mem[nm++] = w;
       }
     }
-    /* drop members whose result is also needed outside the chain */
+    /* a member whose result is also needed outside the chain is dropped -- unless it is an elementwise
+     * producer (the fused kernel can store its value as well) whose outside readers all run after F */
+    bool keep_m[CHAIN_MAX] = {false};
     for (bool changed = true; changed;) {
       changed = false;
       for (int i = 1; i < nm; i++) {
         int sl = step_out_slot(p, &p->steps[mem[i]]);
-        bool outside = sl < 0 || !p->slot_inter[sl];
-        for (int s = 0; s < p->n_steps && !outside; s++) {
+        bool outside = sl < 0 || !p->slot_inter[sl], early = false;
+        for (int s = 0; s < p->n_steps; s++) {
           if (p->steps[s].dead || !pb_step_reads(p, &p->steps[s], sl)) continue;
           bool in_chain = false;
           for (int j = 0; j < nm; j++) if (mem[j] == s) in_chain = true;
-          if (!in_chain) outside = true;
+          if (!in_chain) { outside = true; if (s < f) early = true; }
         }
-        if (outside) { mem[i] = mem[nm - 1]; nm--; changed = true; break; }
+        keep_m[i] = false;
+        /* (its result must be as large as the final one: a broadcast operand such as a mask would be
+         * stored once per row block) */
+        const int fsl = step_out_slot(p, &p->steps[f]);
+        if (outside && sl >= 0 && p->slot_inter[sl] && !early && !env_no_keep() && fsl >= 0 &&
+            p->slot_bytes[sl] == p->slot_bytes[fsl]) {
+          PbKern kk;
+          bool elementwise = pb_kern_build(&kk, p->steps[mem[i]].sink) == 0 && kk.n_reduce_nodes == 0 && kk.n_stores == 1;
+          pb_kern_free(&kk);
+          if (elementwise) { keep_m[i] = true; outside = false; }
+        }
+        if (outside) { mem[i] = mem[nm - 1]; keep_m[i] = keep_m[nm - 1]; nm--; changed = true; break; }
       }
     }
     if (nm < 2) continue;
     /* order by step, final last */
-    for (int i = 1; i < nm; i++) for (int j = i; j > 1 && mem[j] < mem[j - 1]; j--) { int t = mem[j]; mem[j] = mem[j - 1]; mem[j - 1] = t; }
-    int order[CHAIN_MAX]; int no = 0;
-    for (int i = 1; i < nm; i++) order[no++] = mem[i];
-    order[no++] = f;
+    for (int i = 1; i < nm; i++) for (int j = i; j > 1 && mem[j] < mem[j - 1]; j--) {
+      int t = mem[j]; mem[j] = mem[j - 1]; mem[j - 1] = t;
+      bool tk = keep_m[j]; keep_m[j] = keep_m[j - 1]; keep_m[j - 1] = tk;
+    }
+    int order[CHAIN_MAX]; bool keep[CHAIN_MAX]; int no = 0;
+    for (int i = 1; i < nm; i++) { keep[no] = keep_m[i]; order[no++] = mem[i]; }
+    keep[no] = false; order[no++] = f;
     /* nothing outside the chain may overwrite what the chain reads, between its first member and F */
     bool hazard = false;
     for (int s = order[0]; s < f && !hazard; s++) {
@@ -195,7 +214,7 @@ static int fuse_rows(PbPlan *p) {
     if (hazard) continue;
 
     PbFuseOut fo;
-    char *text = pb_render_chain(p, order, no, false, &fo);
+    char *text = pb_render_chain(p, order, keep, no, false, &fo);
     if (!text) continue;
     char name[64]; snprintf(name, sizeof name, "rowfused_k%d", p->steps[f].item);
     if (getenv("POLY_DUMP_KERNELS")) fprintf(stderr, "=== CUDA KERNEL %s ===\n%s\n=== END ===\n", name, text);
@@ -205,7 +224,7 @@ static int fuse_rows(PbPlan *p) {
     poly_cuda_program_destroy(fs->prog); free(fs->text);
     fs->prog = prog; fs->text = text;
     fs->fused_rows = true; fs->n_chain = no;
-    for (int j = 0; j < no; j++) fs->chain[j] = order[j];
+    for (int j = 0; j < no; j++) { fs->chain[j] = order[j]; fs->chain_keep[j] = keep[j]; }
     fs->n_params = fo.n_params;
     for (int a = 0; a < fo.n_params; a++) { fs->slot[a] = fo.slot[a]; fs->rw[a] = fo.rw[a]; }
     fs->rw[fo.n_params] = 0;

@@ -111,6 +111,7 @@ typedef struct {
   PbKern *k;
   const int *slot;     /* plan slot of each kernel parameter */
   int role;
+  bool keep_out;       /* a producer whose result is also read outside the chain: it is stored as well */
 } PbFuseIn;
 typedef struct {
   int n_params;

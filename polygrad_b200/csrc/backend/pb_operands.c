@@ -355,7 +355,7 @@ static int retype_bf16(PbPlan *p) {
           pb_plan_resolve(p, W->slot[g.params[OP_C]]) == x && g.params[OP_X] != g.params[OP_C]) { g.cbf16 = 1; wtext = gemm_text(&g); }
     } else if (W->fused_rows) {
       PbFuseOut fo;
-      wtext = pb_render_chain(p, W->chain, W->n_chain, true, &fo);
+      wtext = pb_render_chain(p, W->chain, W->chain_keep, W->n_chain, true, &fo);
       if (wtext) {
         bool same = fo.n_params == W->n_params;
         for (int a = 0; same && a < fo.n_params; a++) if (fo.slot[a] != pb_plan_resolve(p, W->slot[a]) || fo.rw[a] != W->rw[a]) same = false;

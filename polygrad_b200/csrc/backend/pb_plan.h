@@ -25,6 +25,7 @@ typedef struct {
   bool dead;
   bool fused_rows;               /* program is a row-fused chain; chain[] lists the member steps, this one last */
   int chain[8], n_chain;
+  bool chain_keep[8];            /* member whose own result is still stored by the fused kernel (read outside the chain) */
   unsigned long long dptr[PB_MAX_PARAMS];
   void *argv[PB_MAX_PARAMS];
 } PbStep;
@@ -58,7 +59,7 @@ void pb_slot_usage(const PbPlan *p, PbSlotUse *u);
 bool pb_step_reads(const PbPlan *p, const PbStep *st, int slot);
 bool pb_step_writes(const PbPlan *p, const PbStep *st, int slot);
 const char *pb_hdr_line(const char *text, const char *key, char *buf, size_t cap);
-char *pb_render_chain(const PbPlan *p, const int *order, int no, bool out_bf16, PbFuseOut *fo);
+char *pb_render_chain(const PbPlan *p, const int *order, const bool *keep, int no, bool out_bf16, PbFuseOut *fo);
 
 /* Passes over the operands of precompiled steps (pb_operands.c): strided copies
  * folded into the consumer's strides, bfloat16 storage of contraction operands. */

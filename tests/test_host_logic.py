@@ -128,4 +128,6 @@ def test_bf16_policy_plan_passes_in_dry_run():
     assert int(m.group(3)) == n_layer
     assert int(m.group(4)) == n_layer - 1                 # the mask is classified once
     m = re.search(r'pb_plan: (\d+) steps', r.stderr)
-    assert m and int(m.group(1)) == 5 + 10 * n_layer
+    # per layer: LN1 (with the residual add before it), qkv, attention, c_proj, LN2 (with its add), fc, GELU, proj;
+    # around them: two gathers, the mask generator, final LN (with the last add), logits
+    assert m and int(m.group(1)) == 5 + 8 * n_layer
