@@ -502,8 +502,6 @@ int pb_attention_error(void) {
   return v;
 }
 
-long long pb_attention_tiles_count(long long T) { return 2 * (T / AT_BQ) * (T / AT_BK); }
-
 /* at most 64 key blocks: the set of processed blocks is a 64-bit mask */
 bool pb_attention_supported(long long T, long long hd) { return hd == AT_HD && T >= AT_BK && T % AT_BK == 0 && T / AT_BK <= 64; }
 
