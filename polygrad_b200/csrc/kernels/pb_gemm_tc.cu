@@ -519,15 +519,15 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
     if (f) { const int v = atoi(f); if (v == 64 || v == 128 || v == 192 || v == 256) BN = v; }
   }
   /* CTA pairs (cta_group::2, one 256 x 256 tile per pair): each CTA stages half as much of B, which
-   * pays where the mainloop is the bound -- long K, and enough tiles to fill the 74 pairs.  With short
-   * K the epilogue is the bound and pairs gain nothing (measured: 8192^3 1235 -> 1384 TFLOP/s,
-   * 8192 x 2304 x 768 802 -> 765).  In the time model a pair's mainloop costs 0.85 of two single
+   * pays where the mainloop is the bound -- K of 1024 or more, and enough tiles to fill the 74 pairs.
+   * With short K the epilogue is the bound and pairs gain nothing (measured: 8192^3 1235 -> 1384 TFLOP/s,
+   * 8192 x 3072 x 1024 915 -> 999, 8192 x 2304 x 768 802 -> 765).  In the time model a pair's mainloop costs 0.85 of two single
    * tiles'.  POLY_B200_TC_CTAS=1|2 forces the choice (2 implies the 256-wide tile). */
   int ctas = 1;
   if (g.M > TC_BM && g.N > 128) {
     const long long pair_tiles = ((g.M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((g.N + 255) / 256) * p.nbatch;
     const double pair_cost = (double)((pair_tiles + 73) / 74) * (0.85 * (double)g.K * 256 + 94000.0);
-    if (g.K >= 2048 && pair_tiles >= 74 && pair_cost <= best_cost && !getenv("POLY_B200_TC_BN")) { ctas = 2; BN = 256; }
+    if (g.K >= 1024 && pair_tiles >= 74 && pair_cost <= best_cost && !getenv("POLY_B200_TC_BN")) { ctas = 2; BN = 256; }
     const char *c = getenv("POLY_B200_TC_CTAS");
     if (c && atoi(c) == 1) ctas = 1;
     if (c && atoi(c) == 2) { ctas = 2; BN = 256; }
