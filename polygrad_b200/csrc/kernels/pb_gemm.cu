@@ -338,7 +338,100 @@ static SgemmFn pick_vec(bool va, bool vb) {
   return pb200_sgemm<AK, BKm, false, false>;
 }
 
+/* Small problems: a 128 x 128 tiling would leave most SMs idle (the 256 x 784 x 512 and
+ * 256 x 512 x 10 layers of an MLP are 8 and 2 such tiles).  32 x 32 tiles, 256 threads,
+ * 2 x 2 results per thread, any strides; same accumulation as the large kernel
+ * (k ascending, one fused multiply-add per product). */
+#define SB 32
+__global__ void __launch_bounds__(256) pb200_sgemm_small(const SgemmArgs g) {
+  __shared__ float As[2][SB][SB + 1];      /* [k][m] */
+  __shared__ float Bs[2][SB][SB + 1];      /* [k][n] */
+  long long oa = 0, ob = 0, oc = 0, ox = 0;
+  {
+    int rem = blockIdx.z;
+    for (int i = 0; i < g.nb; i++) {
+      const int x = rem % g.bext[i]; rem /= g.bext[i];
+      oa += x * g.a_sb[i]; ob += x * g.b_sb[i]; oc += x * g.c_sb[i]; ox += x * g.x_sb[i];
+    }
+  }
+  const float *__restrict__ A = g.A + oa;
+  const float *__restrict__ B = g.B + ob;
+  const int m0 = blockIdx.y * SB, n0 = blockIdx.x * SB;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  /* element e of a 32 x 32 tile: consecutive threads along the operand's contiguous axis */
+  const bool a_kfast = g.a_sk == 1, b_kfast = g.b_sk == 1 && g.b_sn != 1;
+  float ra[4], rb[4];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int e = tid + i * 256;
+      const int ka = a_kfast ? (e & 31) : (e >> 5), ma = a_kfast ? (e >> 5) : (e & 31);
+      const int kb = b_kfast ? (e & 31) : (e >> 5), nb = b_kfast ? (e >> 5) : (e & 31);
+      ra[i] = (m0 + ma < g.M && k0 + ka < g.K) ? A[(long long)(m0 + ma) * g.a_sm + (long long)(k0 + ka) * g.a_sk] : 0.0f;
+      rb[i] = (n0 + nb < g.N && k0 + kb < g.K) ? B[(long long)(k0 + kb) * g.b_sk + (long long)(n0 + nb) * g.b_sn] : 0.0f;
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int e = tid + i * 256;
+      const int ka = a_kfast ? (e & 31) : (e >> 5), ma = a_kfast ? (e >> 5) : (e & 31);
+      const int kb = b_kfast ? (e & 31) : (e >> 5), nb = b_kfast ? (e >> 5) : (e & 31);
+      As[buf][ka][ma] = ra[i];
+      Bs[buf][kb][nb] = rb[i];
+    }
+  };
+  float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  const int nk = (g.K + SB - 1) / SB;
+  for (int kt = 0; kt < nk; kt++) {
+    const int cur = kt & 1;
+    if (kt + 1 < nk) fetch((kt + 1) * SB);
+#pragma unroll
+    for (int k = 0; k < SB; k++) {
+      const float a0 = As[cur][k][ty * 2], a1 = As[cur][k][ty * 2 + 1];
+      const float b0 = Bs[cur][k][tx * 2], b1 = Bs[cur][k][tx * 2 + 1];
+      acc[0][0] = fmaf(a0, b0, acc[0][0]); acc[0][1] = fmaf(a0, b1, acc[0][1]);
+      acc[1][0] = fmaf(a1, b0, acc[1][0]); acc[1][1] = fmaf(a1, b1, acc[1][1]);
+    }
+    if (kt + 1 < nk) stash(cur ^ 1);
+    __syncthreads();
+  }
+  float *__restrict__ C = g.C + oc;
+  const float *__restrict__ X = g.has_x ? g.X + ox : nullptr;
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    const int m = m0 + ty * 2 + i;
+    if (m >= g.M) continue;
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+      const int n = n0 + tx * 2 + j;
+      if (n >= g.N) continue;
+      float t = acc[i][j];
+      if (X) t = t + X[(long long)m * g.x_sm + (long long)n * g.x_sn];
+      if (g.relu) t = (0.0f < t) ? t : 0.0f;
+      C[(long long)m * g.c_sm + (long long)n * g.c_sn] = t;
+    }
+  }
+}
+
 static int sgemm_launch(const SgemmArgs &g, long long nbatch, cudaStream_t stream) {
+  /* fewer large tiles than SMs: the small-tile kernel spreads the work */
+  {
+    const long long big = (long long)((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN) * nbatch;
+    const long long small = (long long)((g.M + SB - 1) / SB) * ((g.N + SB - 1) / SB) * nbatch;
+    if (big < 74 && small <= 65535LL * 16 && nbatch <= 65535) {
+      dim3 grid((unsigned)((g.N + SB - 1) / SB), (unsigned)((g.M + SB - 1) / SB), (unsigned)nbatch);
+      if (grid.y <= 65535) {
+        pb200_sgemm_small<<<grid, 256, 0, stream>>>(g);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { pb_set_error("sgemm launch: %s", cudaGetErrorString(e)); return -1; }
+        return 0;
+      }
+    }
+  }
   /* operand layout: contiguous along k, or along the row/column axis */
   const bool a_k = (g.a_sk == 1) || g.K == 1, b_k = (g.b_sk == 1 && g.b_sn != 1);
   const bool a_ok = a_k ? true : (g.a_sm == 1), b_ok = b_k ? true : (g.b_sn == 1);
