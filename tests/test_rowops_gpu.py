@@ -36,7 +36,7 @@ EXACT = {
     'shrink': lambda t: t.shrink(((1, t.shape[0] - 1), (3, t.shape[1] - 2))),
     'pad': lambda t: t.pad(((1, 2), (0, 3))),
 }
-SHAPES = [(64, 128), (33, 257), (5, 4096), (256, 1000), (1, 7)]
+SHAPES = [(64, 128), (33, 257), (5, 4096), (256, 1000), (1, 7), (256, 10)]   # (256, 10): the MLP's class scores
 
 
 @pytest.fixture(scope='module')
