@@ -110,7 +110,11 @@ int poly_b200_gemm(long long M, long long N, long long K,
  * six-kernel chain polygrad's GPT-2 builder schedules
  * (src/modelzoo/models/gpt2.c:402-434) under the bf16 contraction policy.
  * q, k, v float32 [B][T][H][64]; mask float32 [T][T]; out float32 [B][H][T][64].
- * Head size 64, T a multiple of 128.  Stream-ordered; 0 / -1. */
+ * Head size 64, T a multiple of 128 up to 8192.  Blocks of 128 keys whose mask
+ * tile is one value far enough below every row's running maximum to contribute
+ * exactly nothing (the -1e9 triangle of a causal mask) are left out; the result
+ * is bit for bit that of processing them (POLY_B200_ATTN_SKIP=0 processes all).
+ * Stream-ordered; 0 / -1. */
 int poly_b200_attention(const float *q, const float *k, const float *v, const float *mask, float scale,
                         float *out, int B, int H, int T);
 
