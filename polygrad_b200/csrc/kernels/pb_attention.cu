@@ -116,7 +116,7 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     s_live = live;
     abort_flag = 0;
     mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1);
-    mbar_init(bar_s, 1); mbar_init(bar_p, 256); mbar_init(bar_o, 1); mbar_init(bar_x, 256);
+    mbar_init(bar_s, 1); mbar_init(bar_p, 8); mbar_init(bar_o, 1); mbar_init(bar_x, 8);   /* one arrival per softmax warp */
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 8) {
@@ -220,7 +220,7 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const float *mj = mrow + ((long long)j * AT_BK + half * 64) * g.mask_sk;
       const float tile_c = g.tile_const[2 * (qb * nkb + j)];
       const bool tile_is_const = (tile_c == tile_c);
-      if (!mbar_wait(bar_s, ph, &abort_flag, 17)) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, ph, &abort_flag, 17))) { ok = false; break; }
       tc_fence_after_sync();
       /* pass 1: x = s*scale + mask, written back over S in tensor memory; max over this thread's keys */
       float m_part = __int_as_float(0xff800000);
@@ -258,9 +258,11 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
       xchg[half][row] = m_part;
       tc_wait_st();
-      /* exchange through an mbarrier rather than bar.sync: its wait is bounded like all others */
-      mbar_arrive(bar_x);
-      if (!mbar_wait(bar_x, xph & 1u, &abort_flag, 19)) { ok = false; break; }
+      /* exchange through an mbarrier rather than bar.sync: its wait is bounded like all others.
+       * One arrival per warp (256 arrivals on one shared-memory word serialise). */
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_x);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_x, xph & 1u, &abort_flag, 19))) { ok = false; break; }
       xph++;
       const float m_other = xchg[half ^ 1][row];
       const float m_new = fmaxf(m_run, fmaxf(m_part, m_other));
@@ -294,8 +296,9 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       for (int d = 0; d < 32; d++) acc[d] *= alpha;
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(bar_p);
-      if (!mbar_wait(bar_o, ph, &abort_flag, 18)) { ok = false; break; }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_o, ph, &abort_flag, 18))) { ok = false; break; }
       tc_fence_after_sync();
       {
         uint32_t r[32];
@@ -308,8 +311,9 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     /* total row sum = the two threads' partial sums */
     if (ok) {
       xchg[half][row] = l_run;
-      mbar_arrive(bar_x);
-      ok = mbar_wait(bar_x, xph & 1u, &abort_flag, 20);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_x);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_x, xph & 1u, &abort_flag, 20));
     }
     if (ok) {
       const float l_tot = l_run + xchg[half ^ 1][row];
