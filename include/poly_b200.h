@@ -105,6 +105,13 @@ int poly_b200_gemm(long long M, long long N, long long K,
                    const void *B, long long b_sk, long long b_sn,
                    float *C, long long c_sm, const float *bias, int relu, int operands_bf16);
 
+/* Diagnostics: runs a one-thread kernel that waits, with a short limit, on a barrier nothing
+ * arrives at -- the situation every barrier wait of the tensor-core kernels is bounded
+ * against -- and checks that the wait gives up, records its code in the device error word
+ * and returns, leaving the context usable.  Clears the error word again.  0 = as designed.
+ * (No counterpart in polygrad.) */
+int poly_b200_selftest_bounded_wait(void);
+
 /* out[b,h,t,:] = softmax_k(q[b,t,h,:] . k[b,k,h,:] * scale + mask[t,k]) . v[b,k,h,:]
  * as one kernel (the T x T scores never reach memory): the arithmetic of the
  * six-kernel chain polygrad's GPT-2 builder schedules

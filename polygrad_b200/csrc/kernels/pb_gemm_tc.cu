@@ -40,6 +40,7 @@
  * returns; the host reports the code at the next synchronisation point.
  */
 #include "pb_gemm.h"
+#include "../../../include/poly_b200.h"
 #include <cuda.h>
 #include <dlfcn.h>
 #include <cstdio>
@@ -306,6 +307,40 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     if constexpr (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
+}
+
+/* Self-test of the bounded wait: one thread waits on a barrier that nothing ever arrives at,
+ * with a short limit; it must give up, record its code in the error word and return. */
+#define TC_PROBE_CODE 90
+__global__ void pb200_wait_probe(int *gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_flag, TC_PROBE_CODE, 1u << 14);
+    *gave_up = ok ? 0 : 1;
+  }
+}
+
+extern "C" int poly_b200_selftest_bounded_wait(void) {
+  if (poly_cuda_init() != 0) return -1;
+  cudaStream_t stream = (cudaStream_t)poly_b200_stream();
+  int *flag = (int *)pb_scratch_alloc(sizeof(int));
+  if (!flag) { pb_set_error("selftest: out of scratch memory"); return -1; }
+  int zero = 0, gave_up = -1, code = -1;
+  cudaError_t e = cudaMemcpyAsync(flag, &zero, sizeof zero, cudaMemcpyHostToDevice, stream);
+  if (e == cudaSuccess) { pb200_wait_probe<<<1, 32, 0, stream>>>(flag); e = cudaGetLastError(); }
+  if (e == cudaSuccess) e = cudaMemcpyAsync(&gave_up, flag, sizeof gave_up, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  pb_scratch_free(flag);
+  if (e != cudaSuccess) { pb_set_error("selftest: %s", cudaGetErrorString(e)); return -1; }
+  /* the wait's code must be in the error word; clear it again so that later work is not reported as failed */
+  if (cudaMemcpyFromSymbol(&code, pb200_tc_error_flag, sizeof code) != cudaSuccess) { pb_set_error("selftest: cannot read the error word"); return -1; }
+  if (cudaMemcpyToSymbol(pb200_tc_error_flag, &zero, sizeof zero) != cudaSuccess) { pb_set_error("selftest: cannot clear the error word"); return -1; }
+  if (gave_up != 1 || code != TC_PROBE_CODE) { pb_set_error("selftest: bounded wait did not report (gave_up %d, code %d)", gave_up, code); return -1; }
+  return 0;
 }
 
 /* ── host side ───────────────────────────────────────────────────────── */

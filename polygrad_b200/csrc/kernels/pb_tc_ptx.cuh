@@ -35,8 +35,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 /* Bounded wait.  Returns false (after flagging) when the limit is hit or another
  * role of this CTA has already given up. */
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
-  for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code,
+                                          uint32_t limit = TC_SPIN_LIMIT) {
+  for (uint32_t i = 0; i < limit; i++) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 8) __nanosleep(32);          /* leave the issue slots to the working warps */
     if ((i & 255u) == 255u && *abort_flag) return false;

@@ -149,6 +149,7 @@ def _declare_cuda(lib):
     _sig(lib, 'poly_b200_gemm', ctypes.c_int, [LL, LL, LL, _ptr, LL, LL, _ptr, LL, LL, _ptr, LL, _ptr,
                                                ctypes.c_int, ctypes.c_int])
     _sig(lib, 'poly_b200_gemm_noalloc', ctypes.c_int, [LL, LL, LL, _ptr, LL, LL, _ptr, LL, LL, _ptr, LL, _ptr, ctypes.c_int])
+    _sig(lib, 'poly_b200_selftest_bounded_wait', ctypes.c_int, [])
     _sig(lib, 'poly_b200_attention', ctypes.c_int, [_ptr, _ptr, _ptr, _ptr, ctypes.c_float, _ptr, ctypes.c_int, ctypes.c_int, ctypes.c_int])
     _sig(lib, 'poly_b200_set_gemm_policy', None, [ctypes.c_int])
     _sig(lib, 'poly_b200_gemm_policy', ctypes.c_int, [])
