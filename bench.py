@@ -1,17 +1,25 @@
 #!/usr/bin/env python
 """GPT-2 forward throughput through polygrad's instance API on the B200 backend.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype bf16|fp32]
-                    [--workload gpt2-124m|gpt2-1.5b] [--impl b200|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype bf16|fp32] [--impl b200|reference]
+                    [--workload gpt2-124m|gpt2-1.5b|gemm|attention|rowops|mlp] [--shape MxNxK]
+                    [--gather last|full] [--profile] [--no-cpu-baseline]
 
-One step = one forward pass of the workload's batch (8 x 1024 token ids) on every
-rank.  Ranks hold independent replicas (weights replicated, batch rows sharded),
-so the data path has no collective; the last-position logits of every rank are
-gathered to rank 0 with NCCL inside the timed region (the full logits can be
-gathered with --gather full).  Prints one JSON line on rank 0.
+Default workload: GPT-2 124M, one step = one forward pass of 8 x 1024 token ids on every
+rank.  Ranks hold independent replicas (weights replicated, batch rows sharded), so the data
+path has no collective; the last-position logits of every rank are gathered to rank 0 with
+NCCL inside the timed region (--gather full gathers all logits).  Rank 0 prints one JSON
+line: `value` with inputs resident, `e2e` with token ids coming from pinned host memory and
+the logits read back, `roofline` for the dominant kernel (the largest projection's
+contraction, timed alone), `cpu_baseline` (stock polygrad on one host core, bounded sample),
+`clocks` sampled through NVML during the timed region.
 
---impl reference times stock polygrad's CPU backend (oracle/_ref, built from
-polygrad's own sources) on a bounded sample of the same workload.
+The other workloads time one kernel family each: the contraction kernels on one shape or the
+square sweep (gemm), the fused attention kernel (attention), the row-op kernels on a
+16384 x 4096 tensor (rowops), the 784-512-10 MLP (mlp).
+
+--impl reference times stock polygrad's CPU backend (oracle/_ref, built from polygrad's own
+sources) on a bounded sample of the same workload.
 """
 import argparse
 import ctypes

@@ -111,3 +111,37 @@ def test_plan_passes_change_no_bit_under_bf16_policy(gpu, monkeypatch):
         gpu.poly_b200_set_gemm_policy(0)
     assert np.isfinite(with_passes).all()
     assert np.array_equal(with_passes.view(np.uint32), without.view(np.uint32))
+
+
+def test_gpt2_124m_full_width_properties(gpu):
+    """GPT-2 124M at full depth, width, vocabulary and context under the bf16 policy (the oracle
+    cannot run this size in test time): properties that do not depend on a reference.  A sequence's
+    logits do not depend on what else is in the batch (bit for bit), a repeated forward is bit for
+    bit the same, a sequence's logits at position t do not depend on later tokens (causal mask),
+    and everything is finite."""
+    cfg = dict(vocab_size=50257, n_embd=768, n_head=12, n_layer=12, max_seq_len=1024, max_batch=2)
+    rng = np.random.default_rng(77)
+    tokens = rng.integers(0, 50257, (2, 1024))
+    gpu.poly_b200_set_gemm_policy(1)
+    try:
+        inst = Instance.gpt2(gpu, **cfg)
+        inst.init_params(gpt2_init(3))
+        inst.set_device(ffi.DEVICE_CUDA)
+        inst.forward(**inst.gpt2_inputs(tokens))
+        both = inst.read('output').copy()
+        inst.forward(**inst.gpt2_inputs(tokens))
+        again = inst.read('output').copy()
+        changed = tokens.copy()
+        changed[0, 700:] = rng.integers(0, 50257, 324)         # the future of sequence 0 changes
+        inst.forward(**inst.gpt2_inputs(changed))
+        future = inst.read('output').copy()
+        inst.free()
+        one = _run_gpt2(gpu, ffi.DEVICE_CUDA, dict(cfg, max_batch=1), tokens[1:2], seed=3)
+    finally:
+        gpu.poly_b200_set_gemm_policy(0)
+    assert np.isfinite(both).all()
+    assert np.array_equal(both.view(np.uint32), again.view(np.uint32))
+    assert np.array_equal(both[1].view(np.uint32), one[0].view(np.uint32))
+    assert np.array_equal(future[0, :700].view(np.uint32), both[0, :700].view(np.uint32))
+    assert not np.array_equal(future[0, 700:], both[0, 700:])
+    assert np.array_equal(future[1].view(np.uint32), both[1].view(np.uint32))
