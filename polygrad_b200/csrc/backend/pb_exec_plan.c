@@ -43,6 +43,7 @@ int poly_b200_graph_launch(void *exec, unsigned long long n_kernels, unsigned lo
 void poly_b200_graph_destroy(void *exec);
 int poly_b200_memset_now(unsigned long long ptr, unsigned char val, size_t bytes);
 int poly_b200_timing_active(void);
+int poly_b200_ptr_on_host(const void *p);
 
 /* the original plan code, compiled under other names */
 PolyCompiledPlan *poly_ref_compile_schedule(PolyCtx *ctx, PolySchedule *schedule, PolyDeviceId device);
@@ -198,6 +199,8 @@ static void plan_destroy(PbPlan *p) {
   if (p->arena) poly_cuda_free(p->arena);
   free(p->steps); free(p->slot_bytes); free(p->slot_off); free(p->slot_alias); free(p->slot_inter); free(p->slot_ptr);
   free(p->zero_step); free(p->zero_slot); free(p->graph_ext);
+  if (p->stage) for (int i = 0; i < p->n_sched_slots; i++) if (p->stage[i]) poly_cuda_free(p->stage[i]);
+  free(p->stage); free(p->slot_acc); free(p->ext_seen); free(p->ext_host);
   free(p->base.slot_to_data);
   free(p);
 }
@@ -254,6 +257,25 @@ PolyCompiledPlan *poly_compile_schedule(PolyCtx *ctx, PolySchedule *sched, PolyD
   }
   for (int i = 0; i < p->n_slots; i++)
     if (p->slot_inter[i] && p->slot_off[i] >= 0) p->slot_ptr[i] = (void *)(uintptr_t)(p->arena + (unsigned long long)p->slot_off[i]);
+
+  /* how the live steps use each bound buffer (decides the copies around a run
+   * when the buffer turns out to be host memory) */
+  {
+    size_t n = (size_t)(sched->n_buf_slots > 0 ? sched->n_buf_slots : 1);
+    p->slot_acc = calloc(n, 1); p->ext_host = calloc(n, 1);
+    p->ext_seen = calloc(n, sizeof(void *)); p->stage = calloc(n, sizeof(unsigned long long));
+    for (int s = 0; s < p->n_steps; s++) {
+      const PbStep *st = &p->steps[s];
+      if (st->dead) continue;
+      for (int a = 0; a < st->n_params; a++) {
+        int sl = pb_plan_resolve(p, st->slot[a]);
+        if (sl < 0 || sl >= sched->n_buf_slots) continue;
+        char m = st->rw[a];
+        if (m == 'r' || m == 'b' || m == 'w') p->slot_acc[sl] |= PB_ACC_READ;      /* a partial write keeps the rest */
+        if (m == 'w' || m == 'W' || m == 'b') p->slot_acc[sl] |= PB_ACC_WRITE;
+      }
+    }
+  }
 
   /* fields other polygrad code may look at */
   p->base.n_slot_to_data = sched->n_buf_slots;
@@ -324,15 +346,58 @@ static bool graph_valid(PbPlan *p) {
   return true;
 }
 
+/* Bound buffers in pageable host memory.  polygrad binds a few that way even
+ * when everything else is on the device: the loss scalar, the gradient outputs
+ * of value_and_grad and the optimizer's moments and bias corrections
+ * (reference: src/instance.c:1028-1043, 1298-1311, all CPU-domain pointers in a
+ * CUDA plan's slot table).  A kernel cannot address them, so each runs from a
+ * device copy of its own: filled before the steps when a step reads it, copied
+ * back after them when a step wrote it.  Pinned and managed memory is device
+ * addressable and is used in place. */
+static int bind_slots(PbPlan *p, void **slot_data, int n_slots, int *n_staged) {
+  *n_staged = 0;
+  for (int i = 0; i < p->n_sched_slots; i++) {
+    if (p->slot_inter[i]) continue;
+    void *h = (i < n_slots) ? slot_data[i] : NULL;
+    p->base.slot_to_data[i] = h;
+    p->slot_ptr[i] = h;
+    if (!h || !p->slot_acc[i]) continue;
+    if (h != p->ext_seen[i]) { p->ext_seen[i] = h; p->ext_host[i] = (char)(poly_b200_ptr_on_host(h) ? 1 : 0); }
+    if (!p->ext_host[i]) continue;
+    if (!p->stage[i]) {
+      p->stage[i] = poly_cuda_alloc((size_t)p->slot_bytes[i]);
+      if (!p->stage[i]) return -1;
+    }
+    if ((p->slot_acc[i] & PB_ACC_READ) && poly_cuda_copy_htod(p->stage[i], h, (size_t)p->slot_bytes[i]) != 0) return -1;
+    p->slot_ptr[i] = (void *)(uintptr_t)p->stage[i];
+    (*n_staged)++;
+  }
+  return 0;
+}
+
+static int return_slots(PbPlan *p) {
+  for (int i = 0; i < p->n_sched_slots; i++) {
+    if (p->slot_inter[i] || !p->ext_host[i] || !p->stage[i] || !p->base.slot_to_data[i]) continue;
+    if (p->slot_ptr[i] != (void *)(uintptr_t)p->stage[i] || !(p->slot_acc[i] & PB_ACC_WRITE)) continue;
+    if (poly_cuda_copy_dtoh(p->base.slot_to_data[i], p->stage[i], (size_t)p->slot_bytes[i]) != 0) return -1;
+  }
+  return 0;
+}
+
+static int run_steps(PbPlan *p);
+
 int poly_compiled_plan_run(PolyCompiledPlan *plan, void **slot_data, int n_slots,
                            struct PolyVarBinding *var_bindings, int n_var_bindings) {
   PbPlan *p = plan ? as_pb_plan(plan) : NULL;
   if (!p) return poly_ref_compiled_plan_run(plan, slot_data, n_slots, var_bindings, n_var_bindings);
-  for (int i = 0; i < p->n_sched_slots; i++) {
-    if (p->slot_inter[i]) continue;
-    p->slot_ptr[i] = (i < n_slots) ? slot_data[i] : NULL;
-    p->base.slot_to_data[i] = p->slot_ptr[i];
-  }
+  int n_staged = 0;
+  if (bind_slots(p, slot_data, n_slots, &n_staged) != 0) return -1;
+  int rc = run_steps(p);
+  if (rc == 0 && n_staged > 0) rc = return_slots(p);
+  return rc;
+}
+
+static int run_steps(PbPlan *p) {
   p->runs++;
   const bool graphs = !env_is("POLY_B200_GRAPH", "0") && p->graph_failures < 4 && !getenv("POLY_B200_DRYRUN") &&
                       !poly_b200_timing_active();      /* per-launch timing needs individual launches */

@@ -445,7 +445,28 @@ static int fuse_attention(PbPlan *p) {
 
 
 
+/* Does the plan update a bound buffer in place -- read it in one step and
+ * write it in another?  An optimizer step does (reference: the ASSIGN nodes of
+ * src/instance.c:1155-1212; the scheduler orders every reader of the old value
+ * before the writer, src/sched/rangeify.c:3099-3152).  The passes below move
+ * work later in the list (a producer into the chain that consumes it, a copy
+ * into the strides of its readers) on the assumption that a buffer written once
+ * keeps its value; such a plan therefore runs its steps as scheduled. */
+static bool updates_in_place(const PbPlan *p) {
+  PbSlotUse *u = malloc(sizeof(PbSlotUse) * (size_t)p->n_slots);
+  pb_slot_usage(p, u);
+  bool found = false;
+  for (int i = 0; i < p->n_sched_slots && !found; i++)
+    if (!p->slot_inter[i] && u[i].writers > 0 && u[i].readers > 0) found = true;
+  free(u);
+  return found;
+}
+
 void pb_plan_fuse(PbPlan *p) {
+  if (updates_in_place(p)) {
+    if (getenv("POLY_B200_DEBUG")) fprintf(stderr, "pb_fuse: plan updates bound buffers in place; steps run as scheduled\n");
+    return;
+  }
   int copies = elide_copies(p);
   int rows = 0;
   const char *e = getenv("POLY_B200_FUSE");

@@ -39,12 +39,18 @@ typedef struct {
   int *slot_alias;               /* >= 0: this slot is another slot's storage */
   char *slot_inter;              /* intermediate (plan-owned) or external */
   void **slot_ptr;
+  /* bound buffers that live in pageable host memory are run from a device copy */
+  char *slot_acc;                /* per schedule slot: PB_ACC_READ | PB_ACC_WRITE over all live steps */
+  void **ext_seen; char *ext_host;   /* last pointer bound to an external slot and whether it was host memory */
+  unsigned long long *stage;     /* the device copy, allocated on first use */
   unsigned long long arena; int64_t arena_bytes;
   int *zero_step, *zero_slot, n_zero;
   void *graph; unsigned long long graph_epoch; void **graph_ext;
   long long graph_kernels, graph_precompiled;
   int runs, graph_failures;
 } PbPlan;
+
+enum { PB_ACC_READ = 1, PB_ACC_WRITE = 2 };
 
 int  pb_plan_resolve(const PbPlan *p, int slot);
 int  pb_plan_add_slot(PbPlan *p, int64_t bytes);

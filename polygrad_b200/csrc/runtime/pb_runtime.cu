@@ -371,6 +371,18 @@ extern "C" int poly_cuda_copy_htod(unsigned long long dst, const void *src, size
   return 0;
 }
 
+/* Is p ordinary (pageable) host memory, which a kernel cannot address?  Memory
+ * of this library's pool, other device allocations, pinned and managed memory
+ * all answer no. */
+extern "C" int poly_b200_ptr_on_host(const void *p) {
+  if (!p || !ready()) return 0;
+  if (find_buf(p) != R.live.end()) return 0;
+  if (R.dry) return 1;
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) { cudaGetLastError(); return 1; }
+  return attr.type == cudaMemoryTypeUnregistered ? 1 : 0;
+}
+
 static unsigned long long g_last_dtoh_src = 0;
 extern "C" unsigned long long poly_b200_last_dtoh_src(void) { return g_last_dtoh_src; }
 

@@ -20,6 +20,7 @@ _i64p = ctypes.POINTER(ctypes.c_int64)
 
 # polygrad PolyDeviceId (src/exec_plan.h:28-36)
 DEVICE_AUTO, DEVICE_CPU, DEVICE_INTERP, DEVICE_CUDA = 0, 1, 2, 3
+OPTIM_NONE, OPTIM_SGD, OPTIM_ADAM, OPTIM_ADAMW = 0, 1, 2, 3      # src/instance.h:39-42
 
 # polygrad instance buffer roles (src/instance.h:33-37)
 ROLE_PARAM, ROLE_INPUT, ROLE_TARGET, ROLE_OUTPUT, ROLE_AUX = 0, 1, 2, 3, 4
@@ -120,6 +121,10 @@ def _declare_frontend(lib):
     _sig(lib, 'poly_instance_upload_param', I, [P, I, P, ctypes.c_size_t])
     _sig(lib, 'poly_instance_forward', I, [P, ctypes.POINTER(PolyIOBinding), I])
     _sig(lib, 'poly_instance_call', I, [P, ctypes.c_char_p, ctypes.POINTER(PolyIOBinding), I])
+    _sig(lib, 'poly_instance_readback_param', I, [P, I, P, ctypes.c_size_t])
+    _sig(lib, 'poly_instance_set_optimizer', I, [P, I, ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_float])
+    _sig(lib, 'poly_instance_train_step', I, [P, ctypes.POINTER(PolyIOBinding), I, ctypes.POINTER(ctypes.c_float)])
+    _sig(lib, 'poly_instance_value_and_grad', I, [P, ctypes.c_char_p, ctypes.POINTER(PolyIOBinding), I, ctypes.POINTER(ctypes.c_float)])
     _sig(lib, 'poly_mlp_instance', P, [ctypes.c_char_p, I])
     _sig(lib, 'poly_gpt2_build', P, [ctypes.POINTER(GPT2Config), I])
 

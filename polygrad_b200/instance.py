@@ -59,9 +59,9 @@ class Instance:
         return inst
 
     @classmethod
-    def mlp(cls, lib, layers, activation='relu', bias=True, batch_size=1, seed=42):
+    def mlp(cls, lib, layers, activation='relu', bias=True, batch_size=1, seed=42, loss='none'):
         spec = json.dumps({'layers': list(layers), 'activation': activation, 'bias': bool(bias),
-                           'loss': 'none', 'batch_size': int(batch_size), 'seed': int(seed)}).encode()
+                           'loss': loss, 'batch_size': int(batch_size), 'seed': int(seed)}).encode()
         return cls(lib, lib.poly_mlp_instance(spec, len(spec)))
 
     # ---- data ----
@@ -123,6 +123,44 @@ class Instance:
         if rc != 0:
             msg = self.lib.last_error() if self.lib.has_cuda else ''
             raise RuntimeError(f'poly_instance_forward failed ({rc}) {msg}')
+
+    def _bind(self, inputs):
+        n = len(inputs)
+        io = (ffi.PolyIOBinding * max(n, 1))()
+        keep = []
+        for i, (name, arr) in enumerate(inputs.items()):
+            a = np.ascontiguousarray(arr, dtype=np.float32)
+            keep.append(a)
+            io[i].name = name.encode()
+            io[i].data = a.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+        return io, n, keep
+
+    def set_optimizer(self, kind, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0):
+        """poly_instance_set_optimizer (src/instance.h:147); call before the first train_step."""
+        if self.lib.poly_instance_set_optimizer(self.h, kind, lr, beta1, beta2, eps, weight_decay) != 0:
+            raise RuntimeError('poly_instance_set_optimizer failed')
+
+    def train_step(self, **io_arrays):
+        """One forward + backward + optimizer update of the 'loss' entrypoint
+        (poly_instance_train_step, src/instance.c:1242); returns the loss."""
+        io, n, keep = self._bind(io_arrays)
+        loss = ctypes.c_float(0)
+        rc = self.lib.poly_instance_train_step(self.h, io, n, ctypes.byref(loss))
+        if rc != 0:
+            msg = self.lib.last_error() if self.lib.has_cuda else ''
+            raise RuntimeError(f'poly_instance_train_step failed ({rc}) {msg}')
+        return loss.value
+
+    def value_and_grad(self, entrypoint='loss', **io_arrays):
+        """Loss of a differentiable entrypoint; gradients stay inside the instance
+        (poly_instance_value_and_grad, src/instance.c:1003)."""
+        io, n, keep = self._bind(io_arrays)
+        loss = ctypes.c_float(0)
+        rc = self.lib.poly_instance_value_and_grad(self.h, entrypoint.encode(), io, n, ctypes.byref(loss))
+        if rc != 0:
+            msg = self.lib.last_error() if self.lib.has_cuda else ''
+            raise RuntimeError(f'poly_instance_value_and_grad failed ({rc}) {msg}')
+        return loss.value
 
     def gpt2_inputs(self, tokens):
         """Input buffers for a GPT-2 instance: token ids (as float32, which is how

@@ -1,0 +1,97 @@
+"""Training steps on the B200 against stock polygrad on the CPU.
+
+poly_instance_train_step (src/instance.c:1242) runs forward, backward and the
+optimizer update as one plan whose parameters are updated in place; the loss
+scalar, the optimizer moments and the bias corrections are bound as host
+pointers even when the instance lives on the device (src/instance.c:1298-1311),
+and poly_instance_value_and_grad binds the loss and every gradient that way
+(src/instance.c:1028-1043).  The plan executor runs such buffers from device
+copies, so the same calls work after poly_instance_set_device(CUDA).
+
+polygrad's MLP builder supports a loss only at batch size 1 (the target buffer
+is not reshaped, src/model_mlp.c:258-274), which is also how its own training
+tests run (test/test_mlp.c:248-370): the cases here use batch size 1 at the
+widths of the benchmark MLP.
+
+Tolerance: 1e-5 relative per step for the loss and 1e-5 (SGD) / 1e-4 (Adam,
+AdamW: a division by sqrt(v)+eps follows the gradients) for the parameters
+after five steps, atol = rtol * rms.
+"""
+import numpy as np
+import pytest
+
+from conftest import assert_close
+from polygrad_b200 import ffi
+from polygrad_b200.instance import Instance
+
+pytestmark = pytest.mark.gpu
+
+LAYERS = [784, 512, 10]
+STEPS = 5
+
+
+def _data(loss):
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((1, LAYERS[0])).astype(np.float32)
+    if loss == 'cross_entropy':
+        y = np.zeros((1, LAYERS[-1]), dtype=np.float32)
+        y[0, 3] = 1.0
+    else:
+        y = rng.standard_normal((1, LAYERS[-1])).astype(np.float32)
+    return x, y
+
+
+def _train(lib, device, loss, optim, lr):
+    inst = Instance.mlp(lib, LAYERS, 'relu', True, 1, seed=42, loss=loss)
+    x, y = _data(loss)
+    if device != ffi.DEVICE_CPU:
+        inst.set_device(device)          # before the first step: the moments are created afterwards
+    inst.set_optimizer(optim, lr, weight_decay=0.01 if optim == ffi.OPTIM_ADAMW else 0.0)
+    losses = [inst.train_step(x=x, y=y) for _ in range(STEPS)]
+    params = {n: inst.read(n).copy() for n in inst.params}
+    inst.free()
+    return np.array(losses), params
+
+
+@pytest.mark.parametrize('loss', ['mse', 'cross_entropy'])
+@pytest.mark.parametrize('optim,lr,ptol', [(ffi.OPTIM_SGD, 0.001, 1e-5), (ffi.OPTIM_ADAM, 0.0001, 1e-4),
+                                           (ffi.OPTIM_ADAMW, 0.0001, 1e-4)])
+def test_mlp_train_steps_match_cpu(ref_lib, gpu, loss, optim, lr, ptol):
+    want_l, want_p = _train(ref_lib, ffi.DEVICE_CPU, loss, optim, lr)
+    got_l, got_p = _train(gpu, ffi.DEVICE_CUDA, loss, optim, lr)
+    assert want_l[-1] < want_l[0], 'the reference run itself must learn'
+    np.testing.assert_allclose(got_l, want_l, rtol=1e-5 * STEPS, atol=1e-7)
+    for name in want_p:
+        assert_close(got_p[name], want_p[name], ptol, f'{name} after {STEPS} steps')
+
+
+def test_parameters_change_on_the_device(gpu):
+    """The update happens in the device-resident parameters (nothing is trained
+    on the host and copied over): read back before and after one step."""
+    inst = Instance.mlp(gpu, LAYERS, 'relu', True, 1, seed=42, loss='mse')
+    x, y = _data('mse')
+    inst.set_device(ffi.DEVICE_CUDA)
+    inst.set_optimizer(ffi.OPTIM_SGD, 0.05)
+    before = {n: inst.read(n).copy() for n in inst.params}
+    gpu.poly_b200_stats_reset()
+    inst.train_step(x=x, y=y)
+    st = ffi.PolyB200Stats()
+    gpu.poly_b200_stats(st)
+    assert st.launches > 0
+    after = {n: inst.read(n) for n in inst.params}
+    assert any(np.abs(after[n] - before[n]).max() > 0 for n in inst.params)
+    inst.free()
+
+
+@pytest.mark.parametrize('loss', ['mse', 'cross_entropy'])
+def test_value_and_grad_loss_matches_cpu(ref_lib, gpu, loss):
+    x, y = _data(loss)
+    vals = []
+    for lib, dev in ((ref_lib, ffi.DEVICE_CPU), (gpu, ffi.DEVICE_CUDA)):
+        inst = Instance.mlp(lib, LAYERS, 'relu', True, 1, seed=42, loss=loss)
+        if dev != ffi.DEVICE_CPU:
+            inst.set_device(dev)
+        vals.append([inst.value_and_grad('loss', x=x, y=y) for _ in range(2)])
+        inst.free()
+    np.testing.assert_allclose(vals[1], vals[0], rtol=1e-5, atol=1e-7)
+    assert vals[1][0] == vals[1][1], 'value_and_grad does not update anything'
