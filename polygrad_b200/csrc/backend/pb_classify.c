@@ -164,6 +164,23 @@ static bool const_is(PolyUOp *u, double v) {
   return false;
 }
 
+static bool const_f32(PolyUOp *u, float *out) {
+  if (u->op != POLY_OP_CONST || !is_f32(u->dtype)) return false;
+  if (u->arg.kind == POLY_ARG_FLOAT) { *out = (float)u->arg.f; return true; }
+  if (u->arg.kind == POLY_ARG_INT) { *out = (float)u->arg.i; return true; }
+  return false;
+}
+
+/* u as scale * red: red itself, -red, c * red or red * c. */
+static bool scaled_by_const(PolyUOp *u, PolyUOp *red, float *scale) {
+  float c;
+  if (u == red) { *scale = 1.0f; return true; }
+  if (u->op == POLY_OP_NEG && u->src[0] == red) { *scale = -1.0f; return true; }
+  if (u->op == POLY_OP_MUL && u->src[1] == red && const_f32(u->src[0], &c)) { *scale = c; return true; }
+  if (u->op == POLY_OP_MUL && u->src[0] == red && const_f32(u->src[1], &c)) { *scale = c; return true; }
+  return false;
+}
+
 static bool is_plain_load(PolyUOp *u) {
   return u->op == POLY_OP_LOAD && u->src[0]->op == POLY_OP_INDEX && u->src[0]->n_src == 2 &&
          u->src[0]->src[0]->op == POLY_OP_PARAM;
@@ -292,9 +309,12 @@ static char *classify_gemm(PbKern *k) {
   if (!dta || !dtb || strcmp(dta, dtb) != 0) REJECT("pattern");
   if (k->params[st->param]->dtype.priority != 13) REJECT("output is not fp32");
 
-  /* epilogue: REDUCE | REDUCE + load | max(REDUCE + load, 0) | max(REDUCE, 0) */
+  /* epilogue: REDUCE | REDUCE + load | max(REDUCE + load, 0) | max(REDUCE, 0), and with
+   * the sum scaled by a constant: load + c * REDUCE | load - c * REDUCE (the update of
+   * a parameter by its gradient, reference src/instance.c:1158-1162) */
   PolyUOp *v = st->value, *addend = NULL;
   bool relu = false;
+  float alpha = 1.0f;
   if (v->op == POLY_OP_MAX && const_is(v->src[1], 0.0)) {
     /* (x>0)?x:0 */
     relu = true; v = v->src[0];
@@ -304,12 +324,17 @@ static char *classify_gemm(PbKern *k) {
     relu = true; v = v->src[1];
   }
   if (v->op == POLY_OP_ADD) {
-    if (v->src[0] == red && is_plain_load(v->src[1])) addend = v->src[1];
-    else if (v->src[1] == red && is_plain_load(v->src[0])) addend = v->src[0];
+    if (is_plain_load(v->src[1]) && scaled_by_const(v->src[0], red, &alpha)) addend = v->src[1];
+    else if (is_plain_load(v->src[0]) && scaled_by_const(v->src[1], red, &alpha)) addend = v->src[0];
     else REJECT("pattern");
+    v = red;
+  } else if (v->op == POLY_OP_SUB) {
+    if (!is_plain_load(v->src[0]) || !scaled_by_const(v->src[1], red, &alpha)) REJECT("pattern");
+    addend = v->src[0]; alpha = -alpha;
     v = red;
   }
   if (v != red) REJECT("pattern");
+  if (alpha != 1.0f && strcmp(dta, "f32") != 0) REJECT("scaled sum of 16-bit operands");
   if (addend && !is_f32(addend->dtype)) REJECT("addend dtype");
   if (addend && (k->nodes[pb_kern_node(k, addend)].deps & ~k->nodes[pb_kern_node(k, st->u)].deps)) REJECT("pattern");
 
@@ -387,6 +412,7 @@ static char *classify_gemm(PbKern *k) {
   pb_str_printf(&h, "//offsets %lld %lld %lld %lld\n", (long long)fit[0].offset, (long long)fit[1].offset,
                 (long long)fit[2].offset, (long long)(addend ? fit[3].offset : 0));
   pb_str_printf(&h, "//relu %d\n", relu ? 1 : 0);
+  if (alpha != 1.0f) { uint32_t bits; memcpy(&bits, &alpha, 4); pb_str_printf(&h, "//alpha %lld\n", (long long)bits); }
   pb_str_printf(&h, "//numel %lld %lld %lld %lld\n", (long long)param_numel(k, params[0]), (long long)param_numel(k, params[1]),
                 (long long)param_numel(k, params[2]), (long long)(addend ? param_numel(k, params[3]) : 0));
   /* several "//axis" lines share a key; number them */

@@ -34,6 +34,7 @@ enum { OP_C = 0, OP_A = 1, OP_B = 2, OP_X = 3 };
 typedef struct { char kind; long long ext, s[4]; } HAxis;          /* strides in C, A, B, X */
 typedef struct {
   int nparams, params[4], relu, nax, abf16, cbf16;
+  long long alpha; int has_alpha;      /* bits of the float32 scale of the sum, when it is not 1 */
   long long off[4], numel[4];
   char dtype[8];
   HAxis ax[16];
@@ -68,6 +69,8 @@ static bool hgemm_parse(const char *text, const char *pre, HGemm *g) {
   }
   g->abf16 = hget(text, pre, "abf16", buf, sizeof buf) ? atoi(buf) : 0;
   g->cbf16 = hget(text, pre, "cbf16", buf, sizeof buf) ? atoi(buf) : 0;
+  g->has_alpha = hget(text, pre, "alpha", buf, sizeof buf) ? 1 : 0;
+  if (g->has_alpha) g->alpha = atoll(buf);
   return true;
 }
 
@@ -82,6 +85,7 @@ static void hgemm_emit(PbStr *t, const char *pre, const HGemm *g) {
   pb_str_printf(t, "//%snaxes %d\n", pre, g->nax);
   if (g->abf16) pb_str_printf(t, "//%sabf16 1\n", pre);
   if (g->cbf16) pb_str_printf(t, "//%scbf16 1\n", pre);
+  if (g->has_alpha) pb_str_printf(t, "//%salpha %lld\n", pre, g->alpha);
 }
 
 static char *gemm_text(const HGemm *g) {
@@ -332,7 +336,7 @@ static int retype_bf16(PbPlan *p) {
       if (s <= w || kind == K_OTHER || nr >= RETYPE_MAX_READERS) { ok = false; break; }
       if (kind == K_GEMM) {
         HGemm g;
-        if (!hgemm_parse(R->text, "", &g) || strcmp(g.dtype, "f32") != 0 || g.abf16) { ok = false; break; }
+        if (!hgemm_parse(R->text, "", &g) || strcmp(g.dtype, "f32") != 0 || g.abf16 || g.has_alpha) { ok = false; break; }
         for (int a = 0; a < R->n_params; a++) if (pb_plan_resolve(p, R->slot[a]) == x && a != g.params[OP_A]) ok = false;
         g.abf16 = 1;
         if (ok) rtext[nr] = gemm_text(&g);
@@ -351,7 +355,7 @@ static int retype_bf16(PbPlan *p) {
     char *wtext = NULL;
     if (wkind == K_GEMM) {
       HGemm g;
-      if (hgemm_parse(W->text, "", &g) && strcmp(g.dtype, "f32") == 0 && !g.cbf16 &&
+      if (hgemm_parse(W->text, "", &g) && strcmp(g.dtype, "f32") == 0 && !g.cbf16 && !g.has_alpha &&
           pb_plan_resolve(p, W->slot[g.params[OP_C]]) == x && g.params[OP_X] != g.params[OP_C]) { g.cbf16 = 1; wtext = gemm_text(&g); }
     } else if (W->fused_rows) {
       PbFuseOut fo;

@@ -178,6 +178,7 @@ struct SgemmArgs {
   long long a_sm, a_sk, b_sk, b_sn, c_sm, c_sn, x_sm, x_sn;
   int nb; int bext[4]; long long a_sb[4], b_sb[4], c_sb[4], x_sb[4];
   int relu; int has_x;
+  float alpha;          /* the sum is scaled by alpha before the addend: X + alpha * (A.B) */
 };
 
 /* Load a BMxBK tile of an operand whose "row" axis has stride s_row and whose k
@@ -313,7 +314,7 @@ __global__ void __launch_bounds__(256, 2) pb200_sgemm(const SgemmArgs g) {
       float v[4];
 #pragma unroll
       for (int j = 0; j < 4; j++) {
-        float t = acc[i][jh * 4 + j];
+        float t = __fmul_rn(acc[i][jh * 4 + j], g.alpha);
         if (X && n + j < g.N) t = t + X[(long long)m * g.x_sm + (long long)(n + j) * g.x_sn];
         if (g.relu) t = (0.0f < t) ? t : 0.0f;
         v[j] = t;
@@ -409,7 +410,7 @@ __global__ void __launch_bounds__(256) pb200_sgemm_small(const SgemmArgs g) {
     for (int j = 0; j < 2; j++) {
       const int n = n0 + tx * 2 + j;
       if (n >= g.N) continue;
-      float t = acc[i][j];
+      float t = __fmul_rn(acc[i][j], g.alpha);
       if (X) t = t + X[(long long)m * g.x_sm + (long long)n * g.x_sn];
       if (g.relu) t = (0.0f < t) ? t : 0.0f;
       C[(long long)m * g.c_sm + (long long)n * g.c_sn] = t;
@@ -512,7 +513,8 @@ void *PbGemmProgram::pack_operand(const void *src, long long off, bool is_a, int
 
 int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
   launches = 0;
-  if (dtype != PB_F32 || a_bf16 || c_bf16 || pb_gemm_policy_bf16()) {
+  /* a scaled sum (an optimizer update fused behind a weight gradient) runs on the fp32 kernel */
+  if (dtype != PB_F32 || a_bf16 || c_bf16 || (pb_gemm_policy_bf16() && alpha == 1.0f)) {
     int rc = pb_gemm_tc_run(*this, bufs, stream);
     if (rc != PB_TC_UNSUPPORTED) return rc;
     if (dtype != PB_F32 || a_bf16 || c_bf16) { pb_set_error("gemm: 16-bit operands need the tensor-core kernel, which rejected this shape"); return -1; }
@@ -542,7 +544,7 @@ int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
     for (int i = 0; i < g.nb; i++) { g.b_sb[i] = s; s *= b_ax[i].ext; }
   }
   g.C = (float *)bufs[p_c] + off_c; g.c_sm = c_sm; g.c_sn = c_sn;
-  g.has_x = has_x ? 1 : 0; g.relu = relu ? 1 : 0;
+  g.has_x = has_x ? 1 : 0; g.relu = relu ? 1 : 0; g.alpha = alpha;
   if (has_x) { g.X = (const float *)bufs[p_x] + off_x; g.x_sm = x_sm; g.x_sn = x_sn; }
   int rc;
   if (g.c_sn != 1 && g.c_sm == 1) {
@@ -577,6 +579,7 @@ PbGemmProgram *pb_parse_gemm(const PbHeader &h0, const char *prefix, std::string
   p->p_c = (int)params[0]; p->p_a = (int)params[1]; p->p_b = (int)params[2]; p->p_x = (int)params[3];
   p->has_x = p->p_x >= 0;
   p->relu = h.geti("relu") != 0;
+  if (!h.get("alpha").empty()) { uint32_t bits = (uint32_t)h.geti("alpha"); memcpy(&p->alpha, &bits, 4); }
   const std::string &dt = h.get("dtype");
   if (dt == "f32") p->dtype = PB_F32; else if (dt == "bf16") p->dtype = PB_BF16; else if (dt == "f16") p->dtype = PB_F16;
   else { err = "gemm operand dtype '" + dt + "' has no kernel"; delete p; return nullptr; }
@@ -639,7 +642,8 @@ PbGemmProgram *pb_parse_gemm(const PbHeader &h0, const char *prefix, std::string
   p->rw[(size_t)p->p_c] = x_is_c ? 'b' : (dense ? 'W' : 'w');
   p->a_bf16 = h.geti("abf16") != 0;
   p->c_bf16 = h.geti("cbf16") != 0;
-  if ((p->a_bf16 || p->c_bf16) && (p->dtype != PB_F32 || x_is_c || !pb_gemm_tc_static_ok(*p))) {
+  if (p->alpha != 1.0f && p->dtype != PB_F32) { err = "gemm: a scaled sum needs fp32 operands"; delete p; return nullptr; }
+  if ((p->a_bf16 || p->c_bf16) && (p->dtype != PB_F32 || x_is_c || p->alpha != 1.0f || !pb_gemm_tc_static_ok(*p))) {
     err = "gemm: bfloat16 operand/result storage is not possible for this shape"; delete p; return nullptr;
   }
   return p;

@@ -33,6 +33,7 @@ struct PbGemmProgram : PbAotProgram {
   int dtype = PB_F32;                 /* storage type of A and B */
   long long off_c = 0, off_a = 0, off_b = 0, off_x = 0;
   bool relu = false, has_x = false;
+  float alpha = 1.0f;                 /* C = X + alpha * sum (relu); 1 except for fused optimizer updates */
   bool a_bf16 = false;                /* A's buffer holds bfloat16 (same element layout) although dtype is f32 */
   bool c_bf16 = false;                /* C is written as bfloat16 (round to nearest even) into the same element layout */
   std::vector<PbGemmAxis> m_ax, n_ax, k_ax, b_ax;   /* m, n by output stride (largest first); k by A stride */

@@ -164,3 +164,22 @@ def test_weights_cache_follows_updates(gpu, policy):
     y1 = inst.read('output')
     assert not np.array_equal(y1, y0)
     inst.free()
+
+
+@pytest.mark.parametrize('bf16_policy', [False, True], ids=['fp32_policy', 'bf16_policy'])
+@pytest.mark.parametrize('shape', [(128, 256, 64), (300, 200, 100), (257, 1000, 72)], ids=str)
+def test_scaled_sum_behind_an_addend(devices, policy, gpu, shape, bf16_policy):
+    """p - lr * (a @ b): the update of a parameter by a gradient that is itself a
+    contraction (reference src/instance.c:1158-1162) schedules as one kernel and
+    runs on the fp32 contraction kernel with the scale in its epilogue, under
+    either policy (a scaled sum is never rounded to bf16)."""
+    cpu, cuda = devices
+    policy(bf16_policy)
+    a, b = _ab(shape, 9)
+    p = np.random.default_rng(5).standard_normal((shape[0], shape[1])).astype(np.float32)
+    want = (cpu.tensor(p) - cpu.tensor(a).dot(cpu.tensor(b)) * 0.01).numpy()
+    gpu.poly_b200_stats_reset()
+    got = (cuda.tensor(p) - cuda.tensor(a).dot(cuda.tensor(b)) * 0.01).numpy()
+    assert_close(got, want, 1e-5, f'scaled sum {shape}')
+    st = gpu.stats()
+    assert st['launches'] == 1 and st['launches_precompiled'] == 1
