@@ -131,3 +131,37 @@ def test_bf16_policy_plan_passes_in_dry_run():
     # per layer: LN1 (with the residual add before it), qkv, attention, c_proj, LN2 (with its add), fc, GELU, proj;
     # around them: two gathers, the mask generator, final LN (with the last add), logits
     assert m and int(m.group(1)) == 5 + 8 * n_layer
+
+
+DRY_TRAIN = '''
+import sys
+sys.path.insert(0, %(root)r)
+import numpy as np
+from polygrad_b200 import ffi
+from polygrad_b200.instance import Instance, gpt2_init
+lib = ffi.product()
+inst = Instance.gpt2(lib, 64, 48, 4, 1, 16, 2)
+inst.init_params(gpt2_init(3))
+inst.set_device(ffi.DEVICE_CUDA)
+inst.set_optimizer(ffi.OPTIM_SGD, 1e-3)
+inst.train_step(**inst.gpt2_inputs(np.zeros((2, 16))))
+inst.train_step(**inst.gpt2_inputs(np.zeros((2, 16))))
+'''
+
+
+def test_training_plan_in_dry_run():
+    """A training step's plan updates the bound parameters in place: it is run as scheduled (no pass
+    moves work across the update), its weight-gradient contractions with plain operands carry the
+    learning-rate scale, and the loss scalar -- a host pointer in a device plan -- is accepted."""
+    env = dict(os.environ, POLY_B200_DRYRUN='1', POLY_B200_DEBUG='2', POLY_B200_CACHE='0')
+    r = subprocess.run([sys.executable, '-c', DRY_TRAIN % dict(root=ROOT)], env=env, capture_output=True, text=True,
+                       timeout=900)
+    assert r.returncode == 0, r.stderr[-4000:]
+    assert 'plan updates bound buffers in place' in r.stderr
+    assert 'kernels folded into row kernels' not in r.stderr
+    steps = re.findall(r'pb_plan: step +\d+ item +\d+ (\S+) +(.*)', r.stderr)
+    kinds = [k for k, _ in steps]
+    assert kinds.count('gather') == 2 and kinds.count('gemm') >= 13
+    # every bound buffer that is written (parameters, logits are not part of this plan, loss) has one writer
+    written = [a for _, args in steps for a in args.split() if a[0] in 'Wwb' and a.endswith('x')]
+    assert len(written) == len(set(written)) and len(written) >= 17
