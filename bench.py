@@ -530,6 +530,59 @@ def run_mlp(args):
                                             sample='full size') if cpu_us else None)), flush=True)
 
 
+TRAIN_CFG = dict(vocab_size=2048, n_embd=256, n_head=4, n_layer=4, max_seq_len=128, max_batch=4)
+
+
+def run_train(args):
+    """One optimizer step (forward, backward, SGD update in one plan) of a small GPT-2 through
+    poly_instance_train_step on the device, with the CPU reference timed on the same configuration."""
+    from polygrad_b200 import ffi
+    from polygrad_b200.instance import Instance, gpt2_init
+    lib = ffi.product()
+    lib.poly_b200_set_device(int(os.environ.get('LOCAL_RANK', '0')))
+    if lib.poly_cuda_init() != 0:
+        raise SystemExit('bench: no usable B200: ' + lib.last_error())
+    cfg = TRAIN_CFG
+    tokens = np.random.default_rng(SEED).integers(0, cfg['vocab_size'], (cfg['max_batch'], cfg['max_seq_len']))
+    n_tok = cfg['max_batch'] * cfg['max_seq_len']
+
+    def steps_of(library, device, warmup, steps):
+        inst = Instance.gpt2(library, **cfg)
+        inst.init_params(gpt2_init(SEED))
+        if device != ffi.DEVICE_CPU:
+            inst.set_device(device)
+        inst.set_optimizer(ffi.OPTIM_SGD, 1e-6)
+        io = inst.gpt2_inputs(tokens)
+        losses = [inst.train_step(**io) for _ in range(warmup)]
+        if device != ffi.DEVICE_CPU:
+            library.poly_b200_synchronize()
+            library.poly_b200_stats_reset()
+        t0 = time.perf_counter()
+        losses += [inst.train_step(**io) for _ in range(steps)]
+        ms = (time.perf_counter() - t0) / steps * 1e3
+        inst.free()
+        return ms, losses
+
+    warm = max(args.warmup, 3)
+    ms, losses = steps_of(lib, ffi.DEVICE_CUDA, warm, args.steps)
+    st = lib.stats()
+    cpu = None
+    ref_path = os.path.join(ROOT, 'oracle', '_ref', 'libpolygrad_ref.so')
+    if os.path.isfile(ref_path) and not args.no_cpu_baseline:
+        cms, closses = steps_of(ffi.load_reference(ref_path), ffi.DEVICE_CPU, 1, 2)
+        cpu = dict(value=n_tok / (cms * 1e-3), unit='tokens/s', cores=1, kind='reference', ms_per_step=cms,
+                   sample='same configuration, 2 steps after 1 warm-up',
+                   loss_rel_diff_step0=abs(losses[0] - closses[0]) / abs(closses[0]))
+    print(json.dumps(dict(metric='train_tokens_per_s', value=n_tok / (ms * 1e-3), unit='tokens/s', n_gpus=1,
+                          steps=args.steps, warmup=warm, ms_per_step=ms, higher_is_better=True, dtype='f32',
+                          data='synthetic',
+                          config=dict(workload='GPT-2 train step (SGD), V=2048 D=256 H=4 L=4, batch 4x128', **cfg),
+                          timing='host wall around poly_instance_train_step (each step ends with the loss read back)',
+                          launches_per_step=st['launches'] // max(args.steps, 1),
+                          precompiled_per_step=st['launches_precompiled'] // max(args.steps, 1),
+                          cpu_baseline=cpu)), flush=True)
+
+
 def run_attention(args):
     """The fused attention kernel alone at the GPT-2 124M layer shape (8 x 12 heads x 1024 x 64)."""
     from polygrad_b200 import ffi
@@ -576,7 +629,7 @@ def main():
     ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
-    ap.add_argument('--workload', default='gpt2-124m', choices=sorted(WORKLOADS) + ['gemm', 'attention', 'rowops', 'mlp'])
+    ap.add_argument('--workload', default='gpt2-124m', choices=sorted(WORKLOADS) + ['gemm', 'attention', 'rowops', 'mlp', 'train'])
     ap.add_argument('--shape', default='', help='MxNxK for --workload gemm')
     ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp32'])
     ap.add_argument('--gather', default='last', choices=['last', 'full'])
@@ -595,6 +648,8 @@ def main():
         return run_rowops(args)
     if args.workload == 'mlp':
         return run_mlp(args)
+    if args.workload == 'train':
+        return run_train(args)
     cfg = WORKLOADS[args.workload]
     if args.impl == 'reference':
         run_reference(args, cfg, rank)
