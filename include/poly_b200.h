@@ -190,6 +190,21 @@ typedef struct {
 void poly_b200_stats(PolyB200Stats *out);
 void poly_b200_stats_reset(void);
 
+/* Safetensors weights into an instance wherever its buffers live (exported by
+ * libpolygrad_b200.so, which contains polygrad's instance code).  Replaces
+ * poly_instance_import_weights (polygrad src/instance.c:522-550), which fills
+ * the host arrays only -- stale once poly_instance_set_device(CUDA) has moved
+ * the buffers -- and takes float32 files only.  Here F32, BF16 and F16 tensors
+ * are accepted (16-bit ones are widened to the instance's float32 buffers),
+ * float32 tensors of a device-resident instance go from the file bytes to the
+ * device in one copy each, and len may exceed 2 GB.  Tensors are matched by
+ * buffer name; unknown names are reported and skipped; a size mismatch or an
+ * integer dtype is an error (-1).  *bytes_to_device (may be NULL) receives the
+ * bytes copied to device buffers. */
+struct PolyInstance;
+int poly_b200_instance_import_weights(struct PolyInstance *inst, const unsigned char *data, long long len,
+                                      long long *bytes_to_device);
+
 /* Text of the last error reported by this library ("" if none). */
 const char *poly_b200_last_error(void);
 

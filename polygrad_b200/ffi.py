@@ -125,6 +125,8 @@ def _declare_frontend(lib):
     _sig(lib, 'poly_instance_set_optimizer', I, [P, I, ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_float])
     _sig(lib, 'poly_instance_train_step', I, [P, ctypes.POINTER(PolyIOBinding), I, ctypes.POINTER(ctypes.c_float)])
     _sig(lib, 'poly_instance_value_and_grad', I, [P, ctypes.c_char_p, ctypes.POINTER(PolyIOBinding), I, ctypes.POINTER(ctypes.c_float)])
+    _sig(lib, 'poly_instance_export_weights', ctypes.POINTER(ctypes.c_ubyte), [P, ctypes.POINTER(I)])
+    _sig(lib, 'poly_instance_import_weights', I, [P, ctypes.c_char_p, I])
     _sig(lib, 'poly_mlp_instance', P, [ctypes.c_char_p, I])
     _sig(lib, 'poly_gpt2_build', P, [ctypes.POINTER(GPT2Config), I])
 
@@ -155,6 +157,8 @@ def _declare_cuda(lib):
                                                ctypes.c_int, ctypes.c_int])
     _sig(lib, 'poly_b200_gemm_noalloc', ctypes.c_int, [LL, LL, LL, _ptr, LL, LL, _ptr, LL, LL, _ptr, LL, _ptr, ctypes.c_int])
     _sig(lib, 'poly_b200_selftest_bounded_wait', ctypes.c_int, [])
+    _sig(lib, 'poly_b200_instance_import_weights', ctypes.c_int,
+         [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_longlong, ctypes.POINTER(ctypes.c_longlong)])
     _sig(lib, 'poly_b200_attention', ctypes.c_int, [_ptr, _ptr, _ptr, _ptr, ctypes.c_float, _ptr, ctypes.c_int, ctypes.c_int, ctypes.c_int])
     _sig(lib, 'poly_b200_set_gemm_policy', None, [ctypes.c_int])
     _sig(lib, 'poly_b200_gemm_policy', ctypes.c_int, [])

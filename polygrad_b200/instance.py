@@ -96,6 +96,22 @@ class Instance:
             ctypes.memmove(out.ctypes.data, p, out.nbytes)
         return out.reshape(shape)
 
+    def export_weights(self):
+        """All parameters as safetensors bytes (poly_instance_export_weights, src/instance.h:86)."""
+        n = ctypes.c_int(0)
+        p = self.lib.poly_instance_export_weights(self.h, ctypes.byref(n))
+        if not p:
+            raise RuntimeError('poly_instance_export_weights failed')
+        return ctypes.string_at(p, n.value)      # the C buffer is left to the process (no matching free is exported)
+
+    def import_weights(self, blob):
+        """Safetensors bytes into the instance's buffers wherever they live; returns the
+        bytes that went to device buffers."""
+        moved = ctypes.c_longlong(0)
+        if self.lib.poly_b200_instance_import_weights(self.h, blob, len(blob), ctypes.byref(moved)) != 0:
+            raise RuntimeError('poly_b200_instance_import_weights failed: ' + self.lib.last_error())
+        return moved.value
+
     def init_params(self, fn):
         for name in self.params:
             self.write(name, fn(name, self.shape(name)))
