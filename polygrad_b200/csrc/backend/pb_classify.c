@@ -112,7 +112,8 @@ static void collect_divisors(PolyUOp *e, int64_t *out, int *n, int cap, int dept
 }
 
 /* Build virtual axes for the ranges in `mask` such that every expression in
- * exprs[] is affine; tries no split, then one split, then two. */
+ * exprs[] is affine; tries no split, one split, two splits of different
+ * ranges, then one range split in three. */
 static bool find_axes(const PbKern *k, uint64_t mask, PolyUOp **exprs, int n_exprs,
                       VAxis *va, int *nva, VFit *fits) {
   int ids[PB_MAX_RANGES]; int n = 0;
@@ -146,6 +147,31 @@ static bool find_axes(const PbKern *k, uint64_t mask, PolyUOp **exprs, int n_exp
       for (int i = 0; i < n_exprs && all; i++) { vfit(k, exprs[i], va, m, &fits[i]); all = fits[i].ok; }
       if (all) { *nva = m; return true; }
     }
+  }
+  /* one range in three parts (a flat [out][head][dim] index read through a head permutation) */
+  int64_t outer[16 + 16 * 16]; int no = 0;          /* the outer factor may be a product of two divisors */
+  for (int i = 0; i < nc; i++) outer[no++] = cands[i];
+  for (int i = 0; i < nc; i++) for (int j = i; j < nc; j++) {
+    const int64_t pr = cands[i] * cands[j];
+    bool have = false;
+    for (int q = 0; q < no; q++) if (outer[q] == pr) have = true;
+    if (!have && pr < ((int64_t)1 << 40)) outer[no++] = pr;
+  }
+  for (int a = 0; a < n; a++) for (int ca = 0; ca < no; ca++) for (int cb = 0; cb < nc; cb++) {
+    const int64_t fa = outer[ca], fb = cands[cb], ext = k->extent[ids[a]];
+    if (fb >= fa || fa % fb || fa >= ext || ext % fa) continue;
+    int m = 0;
+    for (int i = 0; i < n; i++) {
+      int r = ids[i];
+      if (i == a) {
+        va[m++] = (VAxis){r, ext / fa, fa, k->is_reduce[r]};
+        va[m++] = (VAxis){r, fa / fb, fb, k->is_reduce[r]};
+        va[m++] = (VAxis){r, fb, 1, k->is_reduce[r]};
+      } else va[m++] = (VAxis){r, k->extent[r], 1, k->is_reduce[r]};
+    }
+    bool all = true;
+    for (int i = 0; i < n_exprs && all; i++) { vfit(k, exprs[i], va, m, &fits[i]); all = fits[i].ok; }
+    if (all) { *nva = m; return true; }
   }
   return false;
 }
