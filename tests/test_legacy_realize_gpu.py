@@ -1,7 +1,11 @@
-"""polygrad's older eager path, poly_realize_cuda (src/frontend.c:2450): it schedules on every call,
-keeps its own host-pointer-keyed device buffers and a program cache, and drives the device only
-through the 13 backend symbols (linearize, render, compile, launch with its own grid numbers, alloc,
-copies).  polygrad's Python Tensor uses it.  It must keep working on top of this backend unchanged."""
+"""polygrad's older eager entry point, poly_realize_cuda (src/frontend.c:2450), which polygrad's
+Python Tensor uses: host pointers in the bindings, results fetched with poly_cuda_copyback.
+
+The reference code schedules on every call, keeps its own host-pointer-keyed device buffers and a
+program cache, and drives the device only through the 13 backend symbols (linearize, render,
+compile, launch with its own grid numbers, alloc, copies); it still runs unchanged on this backend
+(POLY_B200_LEGACY=ref).  By default the entry point compiles the schedule into a plan instead, so
+the eager API gets the fused kernels, and runs it on the host pointers directly."""
 import ctypes
 
 import numpy as np
@@ -35,7 +39,12 @@ def realize_legacy(lib, dev, tensor):
     return out.reshape(tensor.shape)
 
 
-def test_legacy_path_runs_on_the_backend(ref_lib, gpu):
+@pytest.mark.parametrize('route', ['plan', 'ref'])
+def test_legacy_path_runs_on_the_backend(ref_lib, gpu, monkeypatch, route):
+    if route == 'ref':
+        monkeypatch.setenv('POLY_B200_LEGACY', 'ref')
+    else:
+        monkeypatch.delenv('POLY_B200_LEGACY', raising=False)
     cpu, cuda = Device(ref_lib, ffi.DEVICE_CPU), Device(gpu, ffi.DEVICE_CUDA)
     rng = np.random.default_rng(12)
     x = rng.standard_normal((96, 320)).astype(np.float32)
@@ -48,5 +57,32 @@ def test_legacy_path_runs_on_the_backend(ref_lib, gpu):
     # a second call with the same graph shape goes through the path's program cache
     got = realize_legacy(gpu, cuda, (cuda.tensor(x) * 2 + 1).exp())
     assert_close(got, np.exp(x * 2 + 1), 1e-5, 'legacy realize, cached programs')
+    gpu.poly_cuda_flush_buffers()
+    gpu.poly_cuda_prog_cache_flush()
+
+
+def test_eager_entry_runs_fused_kernels(gpu, monkeypatch):
+    """softmax is three scheduled kernels; through the plan route it is one launch, through the
+    reference route three.  Repeated calls (a new SINK each, as polygrad's Tensor makes them) reuse the
+    compiled programs and leave no plan behind."""
+    cuda = Device(gpu, ffi.DEVICE_CUDA)
+    x = np.random.default_rng(4).standard_normal((512, 1024)).astype(np.float32)
+    e = np.exp(x - x.max(-1, keepdims=True))
+    want = e / e.sum(-1, keepdims=True)
+    monkeypatch.delenv('POLY_B200_LEGACY', raising=False)
+    realize_legacy(gpu, cuda, cuda.tensor(x).softmax(-1))          # compiles
+    held = gpu.stats()['bytes_allocated']
+    gpu.poly_b200_stats_reset()
+    for _ in range(20):
+        got = realize_legacy(gpu, cuda, cuda.tensor(x).softmax(-1))
+    st = gpu.stats()
+    assert_close(got, want, 1e-5, 'softmax through the eager entry')
+    assert st['launches'] == 20 and st['programs_compiled'] == 0
+    assert st['bytes_allocated'] <= held + (1 << 20)
+    monkeypatch.setenv('POLY_B200_LEGACY', 'ref')
+    gpu.poly_b200_stats_reset()
+    got = realize_legacy(gpu, cuda, cuda.tensor(x).softmax(-1))
+    assert_close(got, want, 1e-5, 'softmax through the reference route')
+    assert gpu.stats()['launches'] == 3
     gpu.poly_cuda_flush_buffers()
     gpu.poly_cuda_prog_cache_flush()
