@@ -206,3 +206,51 @@ def gpt2_forward(cfg, init, tokens, bf16=False):
         h = (h + pr).astype(F32)
     hf = (layernorm(h) * p('ln_f.weight', D) + p('ln_f.bias', D)).astype(F32)
     return mm(hf.reshape(B * T, D), wte.T).reshape(B, T, V)
+
+
+def mlp_train_sgd(weights, biases, x, y, lr, steps, loss='mse'):
+    """poly_instance_train_step with POLY_OPTIM_SGD on a ReLU MLP built by
+    poly_mlp_instance: forward, the loss of src/model_mlp.c:269-304 as it
+    evaluates (MSE: see the note in the code; cross-entropy: -mean over the batch of
+    sum(target * log_softmax)), polygrad's autograd through it (src/autograd.c:
+    relu passes the gradient where 0 < x) and p <- p - lr * grad
+    (src/instance.c:1158-1162).  Returns the loss before each update and the
+    final parameters.  float32 arithmetic; sums in numpy's order, which differs
+    from the kernels' by rounding only."""
+    ws = [np.array(w, dtype=F32) for w in weights]
+    bs = [np.array(b, dtype=F32) for b in biases]
+    x = np.asarray(x, dtype=F32)
+    y = np.asarray(y, dtype=F32)
+    lr = F32(lr)
+    losses = []
+    for _ in range(steps):
+        acts, pre = [x], []
+        for i, (w, b) in enumerate(zip(ws, bs)):
+            z = (acts[-1] @ w.T + b).astype(F32)
+            pre.append(z)
+            acts.append(np.where(z > 0, z, F32(0)).astype(F32) if i + 1 < len(ws) else z)
+        out = acts[-1]
+        if loss == 'mse':
+            # src/model_mlp.c:276-285 reduces axis 0 twice; a reduction keeps its axis (size 1), so
+            # both run over the batch axis and the class axis is never summed.  The [1, out] result
+            # is stored into the one-element loss buffer, which takes class 0: the loss polygrad
+            # reports is sum_b (out[b, 0] - y[b, 0])^2 / (batch * out).  Autograd seeds every element
+            # of that [1, out] value, so the gradient is the one of the full mean squared error.
+            d = (out - y).astype(F32)
+            losses.append(F32(np.sum(d[:, 0] * d[:, 0], dtype=F32) * F32(1.0 / d.size)))
+            g = (d * F32(2.0) * F32(1.0 / d.size)).astype(F32)
+        else:
+            m = out.max(-1, keepdims=True)
+            e = np.exp(out - m).astype(F32)
+            s = e.sum(-1, keepdims=True, dtype=F32)
+            logp = (out - m - np.log(s)).astype(F32)
+            losses.append(F32(-np.sum(y * logp, dtype=F32) / F32(out.shape[0])))
+            g = ((e / s) * y.sum(-1, keepdims=True) - y).astype(F32) / F32(out.shape[0])
+        for i in range(len(ws) - 1, -1, -1):
+            gw = (g.T @ acts[i]).astype(F32)
+            gb = g.sum(0, dtype=F32)
+            if i > 0:
+                g = ((g @ ws[i]) * (pre[i - 1] > 0)).astype(F32)
+            ws[i] = (ws[i] - lr * gw).astype(F32)
+            bs[i] = (bs[i] - lr * gb).astype(F32)
+    return np.array(losses, dtype=F32), ws, bs

@@ -1,7 +1,8 @@
 """Regenerates tests/golden/*.npz by running STOCK polygrad (CPU backend, built
 by `make -C oracle ref` from its own sources) on seeded inputs.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py            # everything
+    python tests/golden/make_golden.py train      # train.npz only
 
 Needs the polygrad checkout; the committed .npz files are what travels.  Every
 case stores its inputs and polygrad's output, so tests need neither the
@@ -25,6 +26,9 @@ OUT = os.path.dirname(os.path.abspath(__file__))
 
 def main():
     ref = ffi.load_reference(os.path.join(ROOT, 'oracle', '_ref', 'libpolygrad_ref.so'))
+    if sys.argv[1:] == ['train']:          # only the training fixture
+        make_training(ref)
+        return
     cpu = Device(ref, ffi.DEVICE_CPU)
     rng = np.random.default_rng(20240607)
 
@@ -66,7 +70,43 @@ def main():
                         cfg=np.array([cfg[k] for k in ('vocab_size', 'n_embd', 'n_head', 'n_layer', 'max_seq_len', 'max_batch')]),
                         seed=np.array(7))
     inst.free()
+    make_training(ref)
     print('golden fixtures written to', OUT)
+
+
+def make_training(ref):
+    """train.npz: poly_instance_train_step on the CPU backend.  A small MLP (batch 1: polygrad's MLP
+    builder supports a loss at that batch size only) under SGD with both losses, and a two-layer GPT-2 under SGD: inputs, initial parameters, the loss of every step and
+    every parameter after the last one."""
+    rng = np.random.default_rng(20240608)
+    out = {}
+    x = rng.standard_normal((1, 96)).astype(np.float32)
+    for loss in ('mse', 'cross_entropy'):
+        y = rng.standard_normal((1, 10)).astype(np.float32)
+        if loss == 'cross_entropy':
+            y = np.zeros((1, 10), np.float32)
+            y[0, 7] = 1.0
+        inst = Instance.mlp(ref, [96, 64, 10], 'relu', True, 1, seed=42, loss=loss)
+        for n in inst.params:
+            out[f'mlp_{loss}:init:{n}'] = inst.read(n).copy()
+        inst.set_optimizer(ffi.OPTIM_SGD, 0.01)
+        out[f'mlp_{loss}:x'], out[f'mlp_{loss}:y'] = x, y
+        out[f'mlp_{loss}:losses'] = np.array([inst.train_step(x=x, y=y) for _ in range(5)], np.float32)
+        for n in inst.params:
+            out[f'mlp_{loss}:final:{n}'] = inst.read(n).copy()
+        inst.free()
+    cfg = dict(vocab_size=64, n_embd=48, n_head=4, n_layer=2, max_seq_len=16, max_batch=2)
+    tokens = rng.integers(0, cfg['vocab_size'], (2, 16))
+    inst = Instance.gpt2(ref, **cfg)
+    inst.init_params(gpt2_init(7))
+    inst.set_optimizer(ffi.OPTIM_SGD, 1e-5)
+    out['gpt2:tokens'] = tokens
+    out['gpt2:cfg'] = np.array([cfg[k] for k in ('vocab_size', 'n_embd', 'n_head', 'n_layer', 'max_seq_len', 'max_batch')])
+    out['gpt2:losses'] = np.array([inst.train_step(**inst.gpt2_inputs(tokens)) for _ in range(3)], np.float32)
+    for n in inst.params:
+        out[f'gpt2:final:{n}'] = inst.read(n).copy()
+    inst.free()
+    np.savez_compressed(os.path.join(OUT, 'train.npz'), **out)
 
 
 if __name__ == '__main__':

@@ -102,3 +102,45 @@ def test_against_stock_polygrad(ref_lib):
     assert_close(polyref.layernorm(x), t.layernorm(-1, 1e-5).numpy(), 2e-6, 'layernorm')
     w = np.random.default_rng(98).uniform(-1, 1, (70, 13)).astype(np.float32)
     assert np.array_equal(polyref.matmul(x, w), t.dot(cpu.tensor(w)).numpy())
+
+
+# ── training steps ──────────────────────────────────────────────────────────
+def _mlp_case(g, loss):
+    names = sorted(k.split(':', 2)[2] for k in g.files if k.startswith(f'mlp_{loss}:init:'))
+    init = {n: g[f'mlp_{loss}:init:{n}'] for n in names}
+    final = {n: g[f'mlp_{loss}:final:{n}'] for n in names}
+    return names, init, final
+
+
+@pytest.mark.parametrize('loss', ['mse', 'cross_entropy'])
+def test_mlp_training_restatement_against_polygrad_fixture(loss):
+    """polyref.mlp_train_sgd against five poly_instance_train_step calls of stock polygrad
+    (tests/golden/train.npz): loss of every step and every parameter afterwards within 1e-5."""
+    g = np.load(os.path.join(G, 'train.npz'))
+    names, init, final = _mlp_case(g, loss)
+    ws = [init[n] for n in names if n.endswith('weight')]
+    bs = [init[n] for n in names if n.endswith('bias')]
+    losses, ws2, bs2 = polyref.mlp_train_sgd(ws, bs, g[f'mlp_{loss}:x'], g[f'mlp_{loss}:y'], 0.01, 5, loss)
+    np.testing.assert_allclose(losses, g[f'mlp_{loss}:losses'], rtol=2e-5)
+    for got, n in zip(ws2, [n for n in names if n.endswith('weight')]):
+        assert_close(got, final[n], 1e-5, n)
+    for got, n in zip(bs2, [n for n in names if n.endswith('bias')]):
+        assert_close(got, final[n], 1e-5, n)
+    assert losses[-1] < losses[0]
+
+
+def test_training_fixture_reproduced_by_polygrad(ref_lib):
+    """Where stock polygrad is built, it reproduces its own training fixture."""
+    from polygrad_b200 import ffi
+    from polygrad_b200.instance import Instance
+    g = np.load(os.path.join(G, 'train.npz'))
+    names, init, final = _mlp_case(g, 'mse')
+    inst = Instance.mlp(ref_lib, [96, 64, 10], 'relu', True, 1, seed=42, loss='mse')
+    for n in names:
+        inst.write(n, init[n])
+    inst.set_optimizer(ffi.OPTIM_SGD, 0.01)
+    losses = [inst.train_step(x=g['mlp_mse:x'], y=g['mlp_mse:y']) for _ in range(5)]
+    np.testing.assert_allclose(losses, g['mlp_mse:losses'], rtol=1e-6)
+    for n in names:
+        assert_close(inst.read(n), final[n], 1e-6, n)
+    inst.free()

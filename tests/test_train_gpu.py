@@ -17,6 +17,8 @@ Tolerance: 1e-5 relative per step for the loss and 1e-5 (SGD) / 1e-4 (Adam,
 AdamW: a division by sqrt(v)+eps follows the gradients) for the parameters
 after five steps, atol = rtol * rms.
 """
+import os
+
 import numpy as np
 import pytest
 
@@ -134,3 +136,34 @@ def test_gpt2_train_steps_match_cpu(ref_lib, gpu, optim, lr):
             assert np.abs(got[d:2 * d] - want[d:2 * d]).max() <= 2 * 3 * lr * 1.01
             got, want = np.delete(got, np.s_[d:2 * d]), np.delete(want, np.s_[d:2 * d])
         assert_close(got, want, ptol, f'{name} after 3 steps')
+
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'golden', 'train.npz')
+
+
+@pytest.mark.parametrize('loss', ['mse', 'cross_entropy'])
+def test_mlp_training_against_committed_fixture(gpu, loss):
+    """Five SGD steps from the fixture's initial parameters against what stock polygrad produced
+    (tests/golden/train.npz): needs neither polygrad's CPU library nor its sources."""
+    g = np.load(GOLDEN)
+    names = sorted(k.split(':', 2)[2] for k in g.files if k.startswith(f'mlp_{loss}:init:'))
+    inst = Instance.mlp(gpu, [96, 64, 10], 'relu', True, 1, seed=42, loss=loss)
+    inst.set_device(ffi.DEVICE_CUDA)
+    for n in names:
+        inst.write(n, g[f'mlp_{loss}:init:{n}'])
+    inst.set_optimizer(ffi.OPTIM_SGD, 0.01)
+    losses = [inst.train_step(x=g[f'mlp_{loss}:x'], y=g[f'mlp_{loss}:y']) for _ in range(5)]
+    np.testing.assert_allclose(losses, g[f'mlp_{loss}:losses'], rtol=5e-5)
+    for n in names:
+        assert_close(inst.read(n), g[f'mlp_{loss}:final:{n}'], 1e-5, n)
+    inst.free()
+
+
+def test_gpt2_training_against_committed_fixture(gpu):
+    g = np.load(GOLDEN)
+    keys = ('vocab_size', 'n_embd', 'n_head', 'n_layer', 'max_seq_len', 'max_batch')
+    cfg = {k: int(v) for k, v in zip(keys, g['gpt2:cfg'])}
+    losses, params = _train_gpt2(gpu, ffi.DEVICE_CUDA, cfg, g['gpt2:tokens'], ffi.OPTIM_SGD, 1e-5, 3)
+    np.testing.assert_allclose(losses, g['gpt2:losses'], rtol=1e-4)
+    for n, got in params.items():
+        assert_close(got, g[f'gpt2:final:{n}'], 1e-4, n)
