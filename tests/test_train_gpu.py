@@ -167,3 +167,24 @@ def test_gpt2_training_against_committed_fixture(gpu):
     np.testing.assert_allclose(losses, g['gpt2:losses'], rtol=1e-4)
     for n, got in params.items():
         assert_close(got, g[f'gpt2:final:{n}'], 1e-4, n)
+
+
+def test_gpt2_training_under_bf16_policy(ref_lib, gpu):
+    """Five SGD steps with the contractions of the forward and backward pass on the tensor cores
+    (operands rounded to bfloat16, fp32 accumulation): every step's loss within 2e-2 of the fp32 CPU
+    run.  From the third step on the plan replays as a CUDA graph, and the bfloat16 copies of the
+    weights must follow the in-place updates -- a stale copy would leave the loss where it was."""
+    cfg = dict(vocab_size=64, n_embd=48, n_head=4, n_layer=2, max_seq_len=16, max_batch=2)
+    tokens = np.random.default_rng(17).integers(0, cfg['vocab_size'], (cfg['max_batch'], cfg['max_seq_len']))
+    want_l, want_p = _train_gpt2(ref_lib, ffi.DEVICE_CPU, cfg, tokens, ffi.OPTIM_SGD, 1e-5, 5)
+    gpu.poly_b200_set_gemm_policy(1)
+    try:
+        gpu.poly_b200_stats_reset()
+        got_l, got_p = _train_gpt2(gpu, ffi.DEVICE_CUDA, cfg, tokens, ffi.OPTIM_SGD, 1e-5, 5)
+        assert gpu.stats()['launches_precompiled'] > 0
+    finally:
+        gpu.poly_b200_set_gemm_policy(0)
+    assert want_l[-1] < 0.9 * want_l[0]
+    np.testing.assert_allclose(got_l, want_l, rtol=2e-2)
+    for name in want_p:
+        assert_close(got_p[name], want_p[name], 2e-2, f'{name} after 5 steps, bf16 policy')
