@@ -586,14 +586,35 @@ static char *render_group_reduce(PbKern *k, const int *usage) {
   for (int r = 0; r < k->n_ranges; r++) all |= (uint64_t)1 << r;
   int fastest = -1; int64_t best = INT64_MAX;
   int64_t loop_best = INT64_MAX;      /* smallest stride any loop axis has in a reduce-dependent load */
+  int64_t mat_best = INT64_MAX;       /* smallest reduce-axis stride among loads that also walk an output axis */
   for (int i = 0; i < nl; i++) {
     PolyUOp *ld = k->nodes[loads[i].node].u;
     if (!(k->nodes[loads[i].node].deps & rmask)) continue;
     pb_fit_affine(k, ld->src[0]->src[1], all, &loads[i].aff);
-    if (!loads[i].aff.ok) continue;
+    if (!loads[i].aff.ok) {
+      /* an index with div/mod of a flattened output range is not affine; what decides
+       * coalescing is how far the address moves for one step of each axis, so take the
+       * unit-step differences at the origin in place of strides (static extents only) */
+      int64_t v0[PB_MAX_RANGES] = {0}, base;
+      if (k->n_vars != 0 || !pb_eval_int(k, ld->src[0]->src[1], v0, NULL, &base)) continue;
+      bool probed = true;
+      for (int r = 0; r < k->n_ranges && probed; r++) {
+        loads[i].aff.stride[r] = 0;
+        if (!(all >> r & 1) || k->extent[r] < 2) continue;
+        int64_t v1[PB_MAX_RANGES] = {0}, at;
+        v1[r] = 1;
+        if (!pb_eval_int(k, ld->src[0]->src[1], v1, NULL, &at)) probed = false;
+        else loads[i].aff.stride[r] = at - base;
+      }
+      if (!probed) continue;
+    }
+    bool matrix = false;          /* walks an output axis as well: a matrix operand, not a per-row vector */
+    for (int j = 0; j < st->n_loop; j++)
+      if (loads[i].aff.stride[st->loop[j]] != 0 && range_max(k, st->loop[j]) > 1) matrix = true;
     for (int j = 0; j < nr; j++) {
       int64_t s = llabs(loads[i].aff.stride[raxes[j]]);
       if (s != 0 && k->extent[raxes[j]] > 1 && s < best) { best = s; fastest = raxes[j]; }
+      if (matrix && s != 0 && k->extent[raxes[j]] > 1 && s < mat_best) mat_best = s;
     }
     for (int j = 0; j < st->n_loop; j++) {
       int64_t s = llabs(loads[i].aff.stride[st->loop[j]]);
@@ -601,6 +622,10 @@ static char *render_group_reduce(PbKern *k, const int *usage) {
     }
   }
   if (fastest < 0) return NULL;
+  /* vectors indexed by the reduce axes alone (per-row statistics) are contiguous along them but
+   * small; when every matrix operand is strided along the reduce axes and contiguous along an
+   * output axis, a thread per output is the coalesced mapping */
+  if (mat_best != INT64_MAX && mat_best != 1 && loop_best == 1) return NULL;
   /* when an output axis is the memory-contiguous one, a thread per output is
    * already coalesced and this mapping would not be */
   if (best != 1 && loop_best == 1) return NULL;
