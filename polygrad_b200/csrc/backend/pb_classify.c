@@ -207,6 +207,15 @@ static bool scaled_by_const(PolyUOp *u, PolyUOp *red, float *scale) {
   return false;
 }
 
+/* u without a float32 constant factor; the factor is multiplied into *scale. */
+static PolyUOp *strip_const_scale(PolyUOp *u, float *scale) {
+  float c;
+  if (u->op != POLY_OP_MUL) return u;
+  if (const_f32(u->src[1], &c)) { *scale *= c; return u->src[0]; }
+  if (const_f32(u->src[0], &c)) { *scale *= c; return u->src[1]; }
+  return u;
+}
+
 static bool is_plain_load(PolyUOp *u) {
   return u->op == POLY_OP_LOAD && u->src[0]->op == POLY_OP_INDEX && u->src[0]->n_src == 2 &&
          u->src[0]->src[0]->op == POLY_OP_PARAM;
@@ -328,8 +337,11 @@ static char *classify_gemm(PbKern *k) {
   PolyOps rop = red->arg.kind == POLY_ARG_OPS ? red->arg.ops : (PolyOps)red->arg.i;
   if (rop != POLY_OP_ADD || !is_f32(red->dtype)) REJECT("not an fp32 sum");
   if (red->src[0]->op != POLY_OP_MUL) REJECT("pattern");
-  PolyUOp *la = strip_cast_to_f32(red->src[0]->src[0]);
-  PolyUOp *lb = strip_cast_to_f32(red->src[0]->src[1]);
+  /* an operand multiplied by a constant (the 2 of d(x^2)/dx in front of a backward
+   * contraction) scales the whole sum: sum((c*a)*b) = c * sum(a*b) up to rounding */
+  float operand_scale = 1.0f;
+  PolyUOp *la = strip_cast_to_f32(strip_const_scale(red->src[0]->src[0], &operand_scale));
+  PolyUOp *lb = strip_cast_to_f32(strip_const_scale(red->src[0]->src[1], &operand_scale));
   if (!is_plain_load(la) || !is_plain_load(lb)) REJECT("pattern");
   const char *dta = operand_dtype(la), *dtb = operand_dtype(lb);
   if (!dta || !dtb || strcmp(dta, dtb) != 0) REJECT("pattern");
@@ -360,6 +372,7 @@ static char *classify_gemm(PbKern *k) {
     v = red;
   }
   if (v != red) REJECT("pattern");
+  alpha *= operand_scale;
   if (alpha != 1.0f && strcmp(dta, "f32") != 0) REJECT("scaled sum of 16-bit operands");
   if (addend && !is_f32(addend->dtype)) REJECT("addend dtype");
   if (addend && (k->nodes[pb_kern_node(k, addend)].deps & ~k->nodes[pb_kern_node(k, st->u)].deps)) REJECT("pattern");

@@ -625,13 +625,15 @@ static char *render_group_reduce(PbKern *k, const int *usage) {
   /* vectors indexed by the reduce axes alone (per-row statistics) are contiguous along them but
    * small; when every matrix operand is strided along the reduce axes and contiguous along an
    * output axis, a thread per output is the coalesced mapping */
-  if (mat_best != INT64_MAX && mat_best != 1 && loop_best == 1) return NULL;
-  /* when an output axis is the memory-contiguous one, a thread per output is
-   * already coalesced and this mapping would not be */
-  if (best != 1 && loop_best == 1) return NULL;
-
   int64_t n_out_max = 1;
   for (int i = 0; i < st->n_loop; i++) n_out_max *= range_max(k, st->loop[i]);
+  /* A thread per output is the coalesced mapping when an output axis is the memory-contiguous
+   * one and no reduce axis is -- but only with enough outputs to fill the machine: a bias
+   * gradient (a few hundred outputs, each a sum over every token) is a handful of blocks walking
+   * long serial loops there, and far faster with a warp per output even though its loads stride. */
+  const bool enough_outputs = n_out_max >= 32768;
+  if (enough_outputs && best != 1 && loop_best == 1) return NULL;
+  if (enough_outputs && mat_best != INT64_MAX && mat_best != 1 && loop_best == 1) return NULL;
 
   int group, block;
   if (ktot >= 2048 || n_out_max < 2048) { group = ktot >= 8192 ? 512 : 256; if (ktot < 512) group = 128; block = group; }
