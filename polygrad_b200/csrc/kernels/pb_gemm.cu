@@ -519,6 +519,17 @@ int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
     if (rc != PB_TC_UNSUPPORTED) return rc;
     if (dtype != PB_F32 || a_bf16 || c_bf16) { pb_set_error("gemm: 16-bit operands need the tensor-core kernel, which rejected this shape"); return -1; }
   }
+  /* float32 contractions large enough to fill the machine run on the tensor cores as three tf32
+   * products; small ones (and scaled sums) stay on the CUDA-core kernels.  POLY_B200_FP32=simt keeps
+   * everything there, POLY_B200_FP32=tc sends every shape the tensor-core kernel accepts. */
+  if (alpha == 1.0f) {
+    const char *m = getenv("POLY_B200_FP32");
+    const bool never = m && strcmp(m, "simt") == 0, always = m && strcmp(m, "tc") == 0;
+    if (!never && (always || (double)M * (double)N * (double)K * (double)nbatch >= 268435456.0)) {
+      int rc = pb_gemm_tc_run(*this, bufs, stream, true);
+      if (rc != PB_TC_UNSUPPORTED) return rc;
+    }
+  }
   SgemmArgs g{};
   void *pa = nullptr, *pb = nullptr;
   g.M = (int)M; g.N = (int)N; g.K = (int)K;

@@ -58,7 +58,7 @@ struct TcArgs {
   long long c_sm, x_sm, x_sn;
   int nb; int bext[4]; long long c_sb[4], x_sb[4];
   int has_x, relu;
-  int ab_f16;                      /* A and B hold float16 (else bfloat16) */
+  int ab_fmt;                      /* operand format: 0 float16, 1 bfloat16 (64 per 128-byte tile row), 2 tf32 (32 per row) */
   int vec_io;                      /* C rows (and addend rows) 16-byte aligned, N % 4 == 0 */
   int c_bf16;                      /* C holds bfloat16 (needs vec_io) */
   int tiles_m, tiles_n, n_tiles;   /* n_tiles = nbatch * tiles_m * tiles_n */
@@ -111,7 +111,8 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kblocks = (g.K + TC_BK - 1) / TC_BK;
+  const int bk = g.ab_fmt == 2 ? TC_BK / 2 : TC_BK;      /* elements along k in one 128-byte tile row */
+  const int kblocks = (g.K + bk - 1) / bk;
   /* two accumulator buffers; the allocation is a power of two */
   constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
 
@@ -153,12 +154,12 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             /* both CTAs' bytes are counted on the first CTA's barrier, whose MMA thread waits for them */
             const uint32_t full0 = mapa_shared(bar_full + 8 * stage, 0);
             if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * S::STAGE);
-            tma_load_3d_pair(sa, &map_a, full0, kb * TC_BK, (mt * 2 + (int)rank) * TC_BM, bz);
-            tma_load_3d_pair(sb, &map_b, full0, kb * TC_BK, nt * BN + (int)rank * (BN / 2), bz);
+            tma_load_3d_pair(sa, &map_a, full0, kb * bk, (mt * 2 + (int)rank) * TC_BM, bz);
+            tma_load_3d_pair(sb, &map_b, full0, kb * bk, nt * BN + (int)rank * (BN / 2), bz);
           } else {
             mbar_expect_tx(bar_full + 8 * stage, S::STAGE);
-            tma_load_3d(sa, &map_a, bar_full + 8 * stage, kb * TC_BK, mt * TC_BM, bz);
-            tma_load_3d(sb, &map_b, bar_full + 8 * stage, kb * TC_BK, nt * BN, bz);
+            tma_load_3d(sa, &map_a, bar_full + 8 * stage, kb * bk, mt * TC_BM, bz);
+            tma_load_3d(sb, &map_b, bar_full + 8 * stage, kb * bk, nt * BN, bz);
           }
           if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -167,8 +168,10 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
   } else if (warp == 1) {
     /* ── MMA issuer ── */
     if (lane == 0 && rank == 0) {
-      /* D float32; A and B bfloat16 (format 1) or float16 (format 0), both K-major */
-      const uint32_t fmt = g.ab_f16 ? 0u : 1u;
+      /* D float32; A and B float16 (format 0), bfloat16 (1) or tf32 (2), both K-major.  A tile row is
+       * 128 bytes in every format and one instruction consumes 32 of them (16 or 8 elements). */
+      const uint32_t fmt = (uint32_t)g.ab_fmt;
+      const bool tf32 = g.ab_fmt == 2;
       const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((TC_BM * CTAS) >> 4) << 24);
       uint32_t stage = 0, phase = 0, it = 0;
       bool ok = true;
@@ -184,8 +187,13 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sb);
 #pragma unroll
           for (int k = 0; k < TC_BK / 16; k++) {
-            if constexpr (CTAS == 2) tc_mma_bf16_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
-            else tc_mma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+            if constexpr (CTAS == 2) {
+              if (tf32) tc_mma_tf32_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+              else tc_mma_bf16_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+            } else {
+              if (tf32) tc_mma_tf32(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+              else tc_mma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+            }
           }
           /* frees the stage (in both CTAs of a pair) when these MMAs have read it */
           if constexpr (CTAS == 2) tc_commit_pair(bar_empty + 8 * stage, 3); else tc_commit(bar_empty + 8 * stage);
@@ -358,14 +366,16 @@ static EncodeTiledFn encode_tiled() {
 
 /* rows x K bf16, K contiguous, row pitch `pitch` elements, `nbatch` matrices `bpitch` elements apart */
 static int make_map(CUtensorMap *map, const void *ptr, long long K, long long rows, long long nbatch,
-                    long long pitch, long long bpitch, int box_rows, bool f16 = false) {
+                    long long pitch, long long bpitch, int box_rows, int fmt = 1) {
   EncodeTiledFn enc = encode_tiled();
   if (!enc) { pb_set_error("gemm: cuTensorMapEncodeTiled not available"); return -1; }
   cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)nbatch};
-  cuuint64_t strides[2] = {(cuuint64_t)pitch * 2, (cuuint64_t)(nbatch > 1 ? bpitch : rows * pitch) * 2};
-  cuuint32_t box[3] = {TC_BK, (cuuint32_t)box_rows, 1};
+  const cuuint64_t esz = fmt == 2 ? 4 : 2;
+  cuuint64_t strides[2] = {(cuuint64_t)pitch * esz, (cuuint64_t)(nbatch > 1 ? bpitch : rows * pitch) * esz};
+  cuuint32_t box[3] = {(cuuint32_t)(fmt == 2 ? TC_BK / 2 : TC_BK), (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult rc = enc(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr),
+  const CUtensorMapDataType dt = fmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : fmt == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUresult rc = enc(map, dt, 3, const_cast<void *>(ptr),
                     dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) { pb_set_error("gemm: cuTensorMapEncodeTiled failed (%d)", (int)rc); return -1; }
@@ -445,6 +455,72 @@ static const void *tc_operand(PbGemmProgram &p, PbTcOperand &cache, const void *
   return dst;
 }
 
+/* ── fp32 contractions on the tensor cores: three tf32 products ─────────
+ * a = hi + lo with hi = tf32(a), lo = tf32(a - hi) carries 22 bits of a's
+ * mantissa; a.b ~ hi.hi + hi.lo + lo.hi leaves out terms of relative size
+ * 2^-22.  The three products are one contraction over a k axis three times as
+ * long: A' = [hi | hi | lo], B' = [hi | lo | hi], each segment Kp = K rounded up
+ * to 4 elements (16-byte rows) and zero-filled past K.  Accumulation is fp32 in
+ * TMEM, so the result is a float32 contraction to within a few 1e-7. */
+__device__ __forceinline__ float tf32_rna(float a) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(a));
+  return __uint_as_float(u);
+}
+
+__global__ void __launch_bounds__(256) pb200_split_tf32x3(const float *__restrict__ src, float *__restrict__ dst,
+                                                          long long total, int K, int Kp, int is_b) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / Kp; const int k = (int)(i % Kp);
+    const float a = k < K ? src[row * Kp + k] : 0.0f;
+    const float hi = tf32_rna(a);
+    const float d = a - hi;
+    const float lo = (d == d && fabsf(hi) <= 3.0e38f) ? tf32_rna(d) : 0.0f;     /* infinities and NaNs stay in hi */
+    float *o = dst + row * 3 * Kp;
+    o[k] = hi; o[Kp + k] = is_b ? lo : hi; o[2 * Kp + k] = is_b ? hi : lo;
+  }
+}
+
+/* [nbatch][rows][3 * Kp] float32 copy of A or B in the split form; cached like the bf16 copies. */
+static const void *tc_operand_x3(PbGemmProgram &p, PbTcOperand &cache, const void *src_buf, long long off, bool is_a,
+                                 long long rows, long long Kp, cudaStream_t stream, void **scratch) {
+  *scratch = nullptr;
+  const size_t bytes = (size_t)(p.nbatch * rows * 3 * Kp) * 4;
+  const uint64_t ver = pb_buffer_version(src_buf);
+  if (cache.data && cache.src == src_buf && cache.version == ver && cache.bytes == bytes && ver != 0) return cache.data;
+  const bool transient = cache.misses >= 2 || ver == 0;
+  void *dst;
+  if (transient) {
+    if (cache.data) { pb_scratch_free(cache.data); cache.data = nullptr; cache.bytes = 0; }
+    dst = pb_scratch_alloc(bytes);
+    if (!dst) return nullptr;
+    *scratch = dst;
+  } else {
+    if (cache.data && cache.bytes != bytes) { pb_scratch_free(cache.data); cache.data = nullptr; }
+    if (!cache.data) { cache.data = pb_scratch_alloc(bytes); cache.bytes = bytes; }
+    if (!cache.data) return nullptr;
+    dst = cache.data;
+    cache.src = src_buf; cache.version = ver; cache.misses++;
+  }
+  void *dense = pb_scratch_alloc((size_t)(p.nbatch * rows * Kp) * 4);
+  bool ok = dense != nullptr && p.pack_into(dense, src_buf, off, is_a, PB_F32, PB_F32, Kp, stream) == 0;
+  if (ok) {
+    const long long total = p.nbatch * rows * Kp;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148LL * 32) blocks = 148LL * 32;
+    pb200_split_tf32x3<<<(unsigned)blocks, 256, 0, stream>>>((const float *)dense, (float *)dst, total, (int)p.K, (int)Kp, is_a ? 0 : 1);
+    ok = cudaGetLastError() == cudaSuccess;
+    p.launches++;
+  }
+  pb_scratch_free(dense);           /* stream-ordered pool: reusable by later work on this stream */
+  if (!ok) {
+    if (*scratch) { pb_scratch_free(*scratch); *scratch = nullptr; }
+    else cache.version = 0;
+    return nullptr;
+  }
+  return dst;
+}
+
 /* A bf16 operand that is already K-major with 16-byte aligned rows is read in
  * place by TMA; anything else goes through tc_operand. */
 struct TcView { const void *ptr; long long pitch, bpitch; };
@@ -482,20 +558,26 @@ bool pb_gemm_tc_static_ok(const PbGemmProgram &p) {
   return true;
 }
 
-int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
+int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, bool fp32x3) {
   /* output must be a row-major (or column-major: swap roles) matrix per batch entry */
   bool swap = false;
   if (p.c_sn != 1 || p.N == 1) { if (p.c_sm == 1 && p.M > 1) swap = true; else if (p.c_sn != 1) return PB_TC_UNSUPPORTED; }
   if (p.K < 16) return PB_TC_UNSUPPORTED;
-  const long long Kp = (p.K + 7) & ~7LL;
+  const long long Kp = fp32x3 ? ((p.K + 3) & ~3LL) : ((p.K + 7) & ~7LL);
   void *scr_a = nullptr, *scr_b = nullptr;
   TcView va, vb;
-  if (!tc_in_place(p, bufs[p.p_a], p.off_a, true, &va)) {
+  if (fp32x3) {
+    if (p.dtype != PB_F32 || p.a_bf16 || p.c_bf16 || 3 * Kp > 2147483647LL) return PB_TC_UNSUPPORTED;
+    va.ptr = tc_operand_x3(p, p.tc_a, bufs[p.p_a], p.off_a, true, p.M, Kp, stream, &scr_a);
+    va.pitch = 3 * Kp; va.bpitch = p.M * 3 * Kp;
+    vb.ptr = va.ptr ? tc_operand_x3(p, p.tc_b, bufs[p.p_b], p.off_b, false, p.N, Kp, stream, &scr_b) : nullptr;
+    vb.pitch = 3 * Kp; vb.bpitch = p.N * 3 * Kp;
+  } else if (!tc_in_place(p, bufs[p.p_a], p.off_a, true, &va)) {
     if (p.a_bf16) { pb_set_error("gemm: bfloat16 A operand is not addressable in place (alignment)"); return -1; }
     va.ptr = tc_operand(p, p.tc_a, bufs[p.p_a], p.off_a, true, p.M, Kp, stream, &scr_a);
     va.pitch = Kp; va.bpitch = p.M * Kp;
   }
-  if (va.ptr && !tc_in_place(p, bufs[p.p_b], p.off_b, false, &vb)) {
+  if (!fp32x3 && va.ptr && !tc_in_place(p, bufs[p.p_b], p.off_b, false, &vb)) {
     vb.ptr = tc_operand(p, p.tc_b, bufs[p.p_b], p.off_b, false, p.N, Kp, stream, &scr_b);
     vb.pitch = Kp; vb.bpitch = p.N * Kp;
   }
@@ -504,11 +586,11 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
   TcArgs g{};
   long long rowsA = p.M, rowsB = p.N;
   if (swap) { std::swap(va, vb); std::swap(rowsA, rowsB); }
-  g.M = (int)rowsA; g.N = (int)rowsB; g.K = (int)p.K;
+  g.M = (int)rowsA; g.N = (int)rowsB; g.K = fp32x3 ? (int)(3 * Kp) : (int)p.K;
   g.C = (float *)bufs[p.p_c] + p.off_c;
   g.c_sm = swap ? p.c_sn : p.c_sm;
   g.has_x = p.has_x ? 1 : 0; g.relu = p.relu ? 1 : 0;
-  g.ab_f16 = p.dtype == PB_F16 ? 1 : 0;
+  g.ab_fmt = fp32x3 ? 2 : (p.dtype == PB_F16 ? 0 : 1);
   if (p.has_x) { g.X = (const float *)bufs[p.p_x] + p.off_x; g.x_sm = swap ? p.x_sn : p.x_sm; g.x_sn = swap ? p.x_sm : p.x_sn; }
   g.nb = (int)p.b_ax.size();
   for (int i = 0; i < g.nb; i++) { g.bext[i] = (int)p.b_ax[i].ext; g.c_sb[i] = p.b_ax[i].sc; g.x_sb[i] = p.b_ax[i].sx; }
@@ -538,6 +620,7 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
    * operand bytes per flop) */
   int BN = 256;
   double best_cost = 0;
+  const double k_model = fp32x3 ? 2.0 * g.K : (double)g.K;      /* in 2-byte elements: a tf32 tile row holds half as many */
   {
     static const int widths[4] = {64, 128, 192, 256};
     double best = -1;
@@ -546,7 +629,7 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
       const int bn = widths[wi];
       if (bn > 64 && g.N <= widths[wi - 1]) continue;
       const long long tiles = tm * ((g.N + bn - 1) / bn) * p.nbatch;
-      const double cost = (double)((tiles + 147) / 148) * ((double)g.K * bn + 94000.0);
+      const double cost = (double)((tiles + 147) / 148) * (k_model * bn + 94000.0);
       if (best < 0 || cost <= best * 1.05) { if (best < 0 || cost < best) best = cost; BN = bn; }
     }
     best_cost = best;
@@ -561,15 +644,15 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream) {
   int ctas = 1;
   if (g.M > TC_BM && g.N > 128) {
     const long long pair_tiles = ((g.M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((g.N + 255) / 256) * p.nbatch;
-    const double pair_cost = (double)((pair_tiles + 73) / 74) * (0.85 * (double)g.K * 256 + 94000.0);
-    if (g.K >= 1024 && pair_tiles >= 74 && pair_cost <= best_cost && !getenv("POLY_B200_TC_BN")) { ctas = 2; BN = 256; }
+    const double pair_cost = (double)((pair_tiles + 73) / 74) * (0.85 * k_model * 256 + 94000.0);
+    if (k_model >= 1024 && pair_tiles >= 74 && pair_cost <= best_cost && !getenv("POLY_B200_TC_BN")) { ctas = 2; BN = 256; }
     const char *c = getenv("POLY_B200_TC_CTAS");
     if (c && atoi(c) == 1) ctas = 1;
     if (c && atoi(c) == 2) { ctas = 2; BN = 256; }
   }
   CUtensorMap ma, mb;
-  int rc = make_map(&ma, va.ptr, p.K, rowsA, p.nbatch, va.pitch, va.bpitch, TC_BM, p.dtype == PB_F16);
-  if (rc == 0) rc = make_map(&mb, vb.ptr, p.K, rowsB, p.nbatch, vb.pitch, vb.bpitch, BN / ctas, p.dtype == PB_F16);
+  int rc = make_map(&ma, va.ptr, g.K, rowsA, p.nbatch, va.pitch, va.bpitch, TC_BM, g.ab_fmt);
+  if (rc == 0) rc = make_map(&mb, vb.ptr, g.K, rowsB, p.nbatch, vb.pitch, vb.bpitch, BN / ctas, g.ab_fmt);
   if (rc != 0) { pb_scratch_free(scr_a); pb_scratch_free(scr_b); return -1; }
   pb_tc_mark_used();
   if (ctas == 2) rc = tc_launch<256, 2>(ma, mb, g, p.nbatch, stream);
@@ -594,6 +677,7 @@ int pb_gemm_tc_launch_raw(const void *a_bf16, long long a_pitch, const void *b_b
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
   g.C = C; g.c_sm = c_sm;
   g.has_x = bias ? 1 : 0; g.relu = relu ? 1 : 0;
+  g.ab_fmt = 1;
   g.X = bias; g.x_sm = 0; g.x_sn = 1;
   g.nb = 0;
   g.vec_io = ((reinterpret_cast<uintptr_t>(C) & 15) == 0 && c_sm % 4 == 0 && N % 4 == 0 &&
