@@ -461,7 +461,8 @@ static const void *tc_operand(PbGemmProgram &p, PbTcOperand &cache, const void *
  * 2^-22.  The three products are one contraction over a k axis three times as
  * long: A' = [hi | hi | lo], B' = [hi | lo | hi], each segment Kp = K rounded up
  * to 4 elements (16-byte rows) and zero-filled past K.  Accumulation is fp32 in
- * TMEM, so the result is a float32 contraction to within a few 1e-7. */
+ * TMEM; measured against a float64 product the result is within about 1e-6 of
+ * its rms (a CPU float32 sum: about 2e-7). */
 __device__ __forceinline__ float tf32_rna(float a) {
   uint32_t u;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(a));
