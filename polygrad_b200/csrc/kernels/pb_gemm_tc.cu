@@ -461,8 +461,9 @@ static const void *tc_operand(PbGemmProgram &p, PbTcOperand &cache, const void *
  * 2^-22.  The three products are one contraction over a k axis three times as
  * long: A' = [hi | hi | lo], B' = [hi | lo | hi], each segment Kp = K rounded up
  * to 4 elements (16-byte rows) and zero-filled past K.  Accumulation is fp32 in
- * TMEM; measured against a float64 product the result is within about 1e-6 of
- * its rms (a CPU float32 sum: about 2e-7). */
+ * TMEM, which truncates: measured against a float64 product the error is about
+ * 1e-8 * K of the result's rms (a CPU float32 sum: 2e-7 to 4e-7), so this route
+ * is opt-in (POLY_B200_FP32=tc) and not the float32 default. */
 __device__ __forceinline__ float tf32_rna(float a) {
   uint32_t u;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(a));
@@ -474,10 +475,16 @@ __global__ void __launch_bounds__(256) pb200_split_tf32x3(const float *__restric
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long row = i / Kp; const int k = (int)(i % Kp);
     const float a = k < K ? src[row * Kp + k] : 0.0f;
-    const float hi = tf32_rna(a);
-    const float d = a - hi;
-    const float lo = (d == d && fabsf(hi) <= 3.0e38f) ? tf32_rna(d) : 0.0f;     /* infinities and NaNs stay in hi */
     float *o = dst + row * 3 * Kp;
+    if (!(fabsf(a) <= 3.4028235e38f)) {
+      /* an infinity or a NaN meets only the other operand's hi part, once: inf * b keeps b's sign
+       * (and inf * 0 is NaN) as in the plain product, instead of meeting lo parts of either sign */
+      o[k] = a; o[Kp + k] = 0.0f; o[2 * Kp + k] = 0.0f;
+      continue;
+    }
+    float hi = tf32_rna(a);
+    if (!(fabsf(hi) <= 3.4028235e38f)) hi = __uint_as_float(__float_as_uint(a) & 0xffffe000u);   /* rounding overflowed: truncate */
+    const float lo = tf32_rna(a - hi);
     o[k] = hi; o[Kp + k] = is_b ? lo : hi; o[2 * Kp + k] = is_b ? hi : lo;
   }
 }

@@ -185,12 +185,13 @@ def test_scaled_sum_behind_an_addend(devices, policy, gpu, shape, bf16_policy):
     assert st['launches'] == 1 and st['launches_precompiled'] == 1
 
 
-@pytest.mark.parametrize('shape', SHAPES + [(1024, 1024, 512), (1000, 900, 333)], ids=str)
+@pytest.mark.parametrize('shape', SHAPES + [(1024, 1024, 512), (1000, 900, 333), (512, 256, 3072)], ids=str)
 def test_fp32_as_three_tf32_products(devices, policy, gpu, monkeypatch, shape):
-    """float32 contractions on the tensor cores: a = hi + lo in tf32, a.b = hi.hi + hi.lo + lo.hi with
-    fp32 accumulation.  Same 1e-5 bound against the CPU as the CUDA-core kernel; measured against a
-    float64 product the error is about 1e-6 of the result's rms (the tensor cores' fp32 accumulation
-    truncates where the CPU rounds; the CPU's own float32 error is about 2e-7), bounded here by 3e-6."""
+    """POLY_B200_FP32=tc: float32 contractions on the tensor cores, a = hi + lo in tf32 and
+    a.b = hi.hi + hi.lo + lo.hi with fp32 accumulation in TMEM.  That accumulation truncates: against a
+    float64 product the error grows linearly with K (about 1e-8 * K of the result's rms; a CPU float32
+    sum stays at 2e-7 to 4e-7), which is why this route is opt-in and its bound against the CPU is 1e-4
+    here, between the float32 kernel's 1e-5 and the bf16 policy's 2e-2."""
     cpu, cuda = devices
     policy(False)
     monkeypatch.setenv('POLY_B200_FP32', 'tc')
@@ -198,28 +199,27 @@ def test_fp32_as_three_tf32_products(devices, policy, gpu, monkeypatch, shape):
     want = cpu.tensor(a).dot(cpu.tensor(b)).numpy()
     gpu.poly_b200_stats_reset()
     got = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
-    assert_close(got, want, 1e-5, f'fp32 via tf32x3 {shape}')
+    assert_close(got, want, 1e-4, f'fp32 via tf32x3 {shape}')
     exact = a.astype(np.float64) @ b.astype(np.float64)
     rms = np.sqrt(np.mean(exact ** 2))
     err_tc = np.sqrt(np.mean((got - exact) ** 2)) / rms
-    err_cpu = np.sqrt(np.mean((want - exact) ** 2)) / rms
-    assert err_tc <= max(4 * err_cpu, 3e-6), (err_tc, err_cpu)
+    assert err_tc <= 1e-6 + 2e-8 * shape[2], err_tc
     if shape[2] >= 16:
         assert gpu.stats()['launches_precompiled'] >= 3          # two splits and the contraction, not the CUDA-core kernel
 
 
-def test_fp32_tensor_core_route_is_the_default_for_large_problems(devices, policy, gpu, monkeypatch):
+def test_fp32_default_route_is_the_cuda_core_kernel(devices, policy, gpu, monkeypatch):
     cpu, cuda = devices
     policy(False)
     a, b = _ab((1024, 768, 512), 8)
     want = cpu.tensor(a).dot(cpu.tensor(b)).numpy()
     monkeypatch.delenv('POLY_B200_FP32', raising=False)
     got = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
-    monkeypatch.setenv('POLY_B200_FP32', 'simt')
-    simt = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
+    monkeypatch.setenv('POLY_B200_FP32', 'tc')
+    tc = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
     assert_close(got, want, 1e-5, 'fp32 default route')
-    assert_close(simt, want, 1e-5, 'fp32 CUDA-core route')
-    assert not np.array_equal(got, simt)         # two different kernels ran
+    assert_close(tc, want, 1e-4, 'fp32 tensor-core route')
+    assert not np.array_equal(got, tc)         # two different kernels ran
 
 
 def test_fp32_tensor_core_route_keeps_infinities(devices, policy, monkeypatch):
@@ -235,4 +235,4 @@ def test_fp32_tensor_core_route_keeps_infinities(devices, policy, monkeypatch):
     assert np.array_equal(np.isinf(got), np.isinf(want)) and np.array_equal(np.isnan(got), np.isnan(want))
     assert np.array_equal(np.sign(got[np.isinf(want)]), np.sign(want[np.isinf(want)]))
     fin = np.isfinite(want)
-    assert_close(got[fin], want[fin], 1e-5, 'finite rows')
+    assert_close(got[fin], want[fin], 1e-4, 'finite rows')
