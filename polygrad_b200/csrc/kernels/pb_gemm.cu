@@ -519,15 +519,15 @@ int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
     if (rc != PB_TC_UNSUPPORTED) return rc;
     if (dtype != PB_F32 || a_bf16 || c_bf16) { pb_set_error("gemm: 16-bit operands need the tensor-core kernel, which rejected this shape"); return -1; }
   }
-  /* POLY_B200_FP32=tc: float32 contractions on the tensor cores as three tf32 products.  Off by
-   * default: the tensor cores' fp32 accumulation truncates, and the error against an exact product
-   * grows linearly with K (measured: about 1e-8 * K of the result's rms, 5e-6 at K = 512), which
-   * leaves the 1e-5 bound of the float32 path beyond K of a few hundred.  It is a middle setting
-   * between the CUDA-core kernel and the bf16 policy (1e-4 at the K of a GPT-2 layer). */
+  /* float32 contractions on the tensor cores as three tf32 products.  POLY_B200_FP32=tcp: partial
+   * sums over two k-blocks are added up in registers (float32-accurate); =tc: the whole k axis is
+   * summed in tensor memory, whose accumulation truncates (error about 1e-8 * K of the result's rms).
+   * Default: the CUDA-core kernel. */
   if (alpha == 1.0f) {
     const char *m = getenv("POLY_B200_FP32");
-    if (m && strcmp(m, "tc") == 0) {
-      int rc = pb_gemm_tc_run(*this, bufs, stream, true);
+    const int mode = !m ? 0 : strcmp(m, "tc") == 0 ? 1 : strcmp(m, "tcp") == 0 ? 2 : 0;
+    if (mode) {
+      int rc = pb_gemm_tc_run(*this, bufs, stream, mode);
       if (rc != PB_TC_UNSUPPORTED) return rc;
     }
   }

@@ -75,8 +75,9 @@ int pb_attention_launch(const PbAttnOperand &q, const PbAttnOperand &k, const Pb
 bool pb_gemm_tc_static_ok(const PbGemmProgram &p);
 
 /* Tensor-core path: returns 0 / -1, or PB_TC_UNSUPPORTED when the shape is not handled. */
-/* fp32x3: float32 operands as three tf32 products (float32-accurate) instead of 16-bit operands */
-int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, bool fp32x3 = false);
+/* fp32_mode 0: 16-bit operands.  1: float32 operands as three tf32 products, summed in tensor memory.
+ * 2: the same with the partial sums moved to registers every few k-blocks (float32-accurate). */
+int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, int fp32_mode = 0);
 
 /* The tensor-core kernel on ready-made bfloat16 K-major operands; touches no
  * memory beyond its arguments. */

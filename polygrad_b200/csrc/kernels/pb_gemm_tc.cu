@@ -63,6 +63,7 @@ struct TcArgs {
   int c_bf16;                      /* C holds bfloat16 (needs vec_io) */
   int tiles_m, tiles_n, n_tiles;   /* n_tiles = nbatch * tiles_m * tiles_n */
   int m_fast;                      /* consecutive tiles differ in the row tile (else in the column tile) */
+  int kchunk;                      /* PROMOTE kernels: k-blocks summed in tensor memory before the partial sum moves to registers */
 };
 
 #define PB_TC_ERROR_FLAG pb200_tc_error_flag
@@ -91,10 +92,11 @@ struct TcSmem {
   static constexpr int BYTES = STAGES * STAGE + EPI + 256 + 1024; /* + barriers + alignment slack */
 };
 
-template <int BN, int CTAS>
+template <int BN, int CTAS, bool PROMOTE = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcArgs g) {
   using S = TcSmem<BN, CTAS>;
+  static_assert(!PROMOTE || (CTAS == 1 && BN <= 128), "partial sums in registers: single CTAs, tiles up to 128 wide");
   /* CTA pair: rank within the pair, the pair's index and count (tiles are handed out per pair) */
   const uint32_t rank = CTAS == 2 ? cluster_ctarank() : 0u;
   const int unit = blockIdx.x / CTAS, n_units = gridDim.x / CTAS;
@@ -175,31 +177,39 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((TC_BM * CTAS) >> 4) << 24);
       uint32_t stage = 0, phase = 0, it = 0;
       bool ok = true;
-      for (int t = unit; t < g.n_tiles && ok; t += n_units, it++) {
-        const uint32_t buf = it & 1u, use = it >> 1;
-        if (!mbar_wait(bar_tempty + 8 * buf, (use & 1u) ^ 1u, &abort_flag, 2)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + buf * BN;
-        for (int kb = 0; kb < kblocks; kb++) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, &abort_flag, 3)) { ok = false; break; }
+      /* one accumulator buffer per tile -- or, in a PROMOTE kernel, per chunk of g.kchunk k-blocks:
+       * the epilogue warps add each chunk's sum to registers (rounded float32 adds), because the
+       * tensor cores' own accumulation truncates and would drift over a long k axis */
+      const int kstep = PROMOTE ? g.kchunk : kblocks;
+      for (int t = unit; t < g.n_tiles && ok; t += n_units) {
+        for (int kb0 = 0; kb0 < kblocks && ok; kb0 += kstep, it++) {
+          const uint32_t buf = it & 1u, use = it >> 1;
+          if (!mbar_wait(bar_tempty + 8 * buf, (use & 1u) ^ 1u, &abort_flag, 2)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t sa = base + stage * S::STAGE, sb = sa + S::STAGE_A;
-          const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sb);
+          const uint32_t tmem_d = tmem_base + buf * BN;
+          const int kend = min(kb0 + kstep, kblocks);
+          for (int kb = kb0; kb < kend; kb++) {
+            if (!mbar_wait(bar_full + 8 * stage, phase, &abort_flag, 3)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t sa = base + stage * S::STAGE, sb = sa + S::STAGE_A;
+            const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sb);
 #pragma unroll
-          for (int k = 0; k < TC_BK / 16; k++) {
-            if constexpr (CTAS == 2) {
-              if (tf32) tc_mma_tf32_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
-              else tc_mma_bf16_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
-            } else {
-              if (tf32) tc_mma_tf32(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
-              else tc_mma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+            for (int k = 0; k < TC_BK / 16; k++) {
+              const uint32_t accum = ((kb - kb0) | k) ? 1u : 0u;
+              if constexpr (CTAS == 2) {
+                if (tf32) tc_mma_tf32_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
+                else tc_mma_bf16_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
+              } else {
+                if (tf32) tc_mma_tf32(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
+                else tc_mma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
+              }
             }
+            /* frees the stage (in both CTAs of a pair) when these MMAs have read it */
+            if constexpr (CTAS == 2) tc_commit_pair(bar_empty + 8 * stage, 3); else tc_commit(bar_empty + 8 * stage);
+            if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
           }
-          /* frees the stage (in both CTAs of a pair) when these MMAs have read it */
-          if constexpr (CTAS == 2) tc_commit_pair(bar_empty + 8 * stage, 3); else tc_commit(bar_empty + 8 * stage);
-          if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
+          if (ok) { if constexpr (CTAS == 2) tc_commit_pair(bar_tfull + 8 * buf, 3); else tc_commit(bar_tfull + 8 * buf); }   /* accumulator complete */
         }
-        if (ok) { if constexpr (CTAS == 2) tc_commit_pair(bar_tfull + 8 * buf, 3); else tc_commit(bar_tfull + 8 * buf); }   /* accumulator complete */
       }
     }
   } else {
@@ -209,33 +219,70 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     float *stg = epi + (warp - 2) * 32 * 32;
     uint32_t it = 0;
     bool ok = true;
-    for (int t = unit; t < g.n_tiles && ok; t += n_units, it++) {
+    for (int t = unit; t < g.n_tiles && ok; t += n_units) {
       int nt, mt;
       tile_coords(g, t, &mt, &nt);
       int bz = t / (g.tiles_n * g.tiles_m);
       long long oc = 0, ox = 0;
       for (int i = 0; i < g.nb; i++) { const int x = bz % g.bext[i]; bz /= g.bext[i]; oc += x * g.c_sb[i]; ox += x * g.x_sb[i]; }
-      const uint32_t buf = it & 1u, use = it >> 1;
-      if (!mbar_wait(bar_tfull + 8 * buf, use & 1u, &abort_flag, 4)) { ok = false; break; }
-      tc_fence_after_sync();
+      constexpr int NCH = (BN / 2) / 32;
+      const int colh = nt * BN + half * (BN / 2);
+      uint32_t buf = 0;
+      [[maybe_unused]] float acc[PROMOTE ? NCH : 1][32];
+      if constexpr (PROMOTE) {
+        /* the tile arrives as partial sums over g.kchunk k-blocks each; add them up here */
+#pragma unroll
+        for (int ci = 0; ci < NCH; ci++)
+#pragma unroll
+          for (int j = 0; j < 32; j++) acc[ci][j] = 0.0f;
+        for (int kb0 = 0; kb0 < kblocks && ok; kb0 += g.kchunk, it++) {
+          buf = it & 1u;
+          if (!mbar_wait(bar_tfull + 8 * buf, (it >> 1) & 1u, &abort_flag, 4)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t tb = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * (BN / 2);
+#pragma unroll
+          for (int ci = 0; ci < NCH; ci++) {
+            if (colh + ci * 32 < g.N) {
+              uint32_t part[32];
+              tc_ld32(tb + ci * 32, part);
+              tc_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 32; j++) acc[ci][j] += __uint_as_float(part[j]);
+            }
+          }
+          tc_fence_before_sync();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+        }
+        if (!ok) break;
+      } else {
+        buf = it & 1u;
+        const uint32_t use = it >> 1;
+        it++;
+        if (!mbar_wait(bar_tfull + 8 * buf, use & 1u, &abort_flag, 4)) { ok = false; break; }
+        tc_fence_after_sync();
+      }
       const int row0 = (mt * CTAS + (int)rank) * TC_BM + q * 32;
       const int rows = min(32, g.M - row0);
       float *__restrict__ C = g.C + oc;
       const float *__restrict__ X = g.has_x ? g.X + ox : nullptr;
       /* chunks of 32 columns; the tensor-memory load of the next chunk is in
        * flight while this one is transposed and stored */
-      constexpr int NCH = (BN / 2) / 32;
       const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * (BN / 2);
-      const int colh = nt * BN + half * (BN / 2);
       const bool x_bcast = X && g.x_sm == 0;       /* bias: one value per column */
-      uint32_t r[2][32];
-      if (colh < g.N) tc_ld32(tbase, r[0]);
+      [[maybe_unused]] uint32_t r[PROMOTE ? 1 : 2][32];
+      /* the value of column j of chunk ci: from registers (PROMOTE) or from the load in flight */
+      auto val = [&](int ci, int j) -> float {
+        if constexpr (PROMOTE) return acc[ci][j]; else return __uint_as_float(r[ci & 1][j]);
+      };
+      if constexpr (!PROMOTE) { if (colh < g.N) tc_ld32(tbase, r[0]); }
 #pragma unroll
       for (int ci = 0; ci < NCH; ci++) {
         const int col0 = colh + ci * 32;
         if (col0 < g.N) {
-          tc_wait_ld();
-          if (ci + 1 < NCH && col0 + 32 < g.N) tc_ld32(tbase + (ci + 1) * 32, r[(ci + 1) & 1]);
+          if constexpr (!PROMOTE) {
+            tc_wait_ld();
+            if (ci + 1 < NCH && col0 + 32 < g.N) tc_ld32(tbase + (ci + 1) * 32, r[(ci + 1) & 1]);
+          }
           if (g.vec_io) {
             /* rows of C (and of the addend) are 16-byte aligned: 128-bit shared and
              * global accesses, 16-byte chunks XOR-swizzled by row so that both the
@@ -243,8 +290,7 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             float4 *stg4 = reinterpret_cast<float4 *>(stg);
 #pragma unroll
             for (int c4 = 0; c4 < 8; c4++)
-              stg4[lane * 8 + (c4 ^ (lane & 7))] = make_float4(__uint_as_float(r[ci & 1][c4 * 4]), __uint_as_float(r[ci & 1][c4 * 4 + 1]),
-                                                               __uint_as_float(r[ci & 1][c4 * 4 + 2]), __uint_as_float(r[ci & 1][c4 * 4 + 3]));
+              stg4[lane * 8 + (c4 ^ (lane & 7))] = make_float4(val(ci, c4 * 4), val(ci, c4 * 4 + 1), val(ci, c4 * 4 + 2), val(ci, c4 * 4 + 3));
             __syncwarp();
             const int c4 = lane & 7, rsub = lane >> 3;
             const int n = col0 + c4 * 4;
@@ -276,7 +322,7 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             }
           } else {
 #pragma unroll
-          for (int j = 0; j < 32; j++) stg[lane * 32 + (j ^ lane)] = __uint_as_float(r[ci & 1][j]);
+          for (int j = 0; j < 32; j++) stg[lane * 32 + (j ^ lane)] = val(ci, j);
           __syncwarp();
           const int n = col0 + lane;
           if (n < g.N) {
@@ -294,10 +340,12 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
           __syncwarp();
         }
       }
-      tc_fence_before_sync();
-      if (lane == 0) {
-        if constexpr (CTAS == 2) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * buf, 0));
-        else mbar_arrive(bar_tempty + 8 * buf);
+      if constexpr (!PROMOTE) {
+        tc_fence_before_sync();
+        if (lane == 0) {
+          if constexpr (CTAS == 2) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * buf, 0));
+          else mbar_arrive(bar_tempty + 8 * buf);
+        }
       }
     }
   }
@@ -382,11 +430,11 @@ static int make_map(CUtensorMap *map, const void *ptr, long long K, long long ro
   return 0;
 }
 
-template <int BN, int CTAS>
+template <int BN, int CTAS, bool PROMOTE = false>
 static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, long long nbatch, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(pb200_gemm_tc<BN, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN, CTAS>::BYTES);
+    cudaError_t e = cudaFuncSetAttribute(pb200_gemm_tc<BN, CTAS, PROMOTE>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN, CTAS>::BYTES);
     if (e != cudaSuccess) { pb_set_error("gemm: cannot reserve %d bytes of shared memory: %s", TcSmem<BN, CTAS>::BYTES, cudaGetErrorString(e)); return -1; }
     configured = true;
   }
@@ -402,7 +450,7 @@ static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, lo
   const int grid = (int)(tiles < units ? tiles : units) * CTAS;
   cudaError_t e;
   if (CTAS == 1) {
-    pb200_gemm_tc<BN, CTAS><<<grid, TC_THREADS, TcSmem<BN, CTAS>::BYTES, stream>>>(ma, mb, g);
+    pb200_gemm_tc<BN, CTAS, PROMOTE><<<grid, TC_THREADS, TcSmem<BN, CTAS>::BYTES, stream>>>(ma, mb, g);
     e = cudaGetLastError();
   } else {
     cudaLaunchConfig_t cfg = {};
@@ -411,7 +459,7 @@ static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, lo
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, pb200_gemm_tc<BN, CTAS>, ma, mb, g);
+    e = cudaLaunchKernelEx(&cfg, pb200_gemm_tc<BN, CTAS, PROMOTE>, ma, mb, g);
   }
   if (e != cudaSuccess) { pb_set_error("tensor-core gemm launch: %s", cudaGetErrorString(e)); return -1; }
   return 0;
@@ -566,7 +614,8 @@ bool pb_gemm_tc_static_ok(const PbGemmProgram &p) {
   return true;
 }
 
-int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, bool fp32x3) {
+int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, int fp32_mode) {
+  const bool fp32x3 = fp32_mode != 0, promote = fp32_mode == 2;
   /* output must be a row-major (or column-major: swap roles) matrix per batch entry */
   bool swap = false;
   if (p.c_sn != 1 || p.N == 1) { if (p.c_sm == 1 && p.M > 1) swap = true; else if (p.c_sn != 1) return PB_TC_UNSUPPORTED; }
@@ -633,7 +682,7 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, boo
     static const int widths[4] = {64, 128, 192, 256};
     double best = -1;
     const long long tm = (g.M + TC_BM - 1) / TC_BM;
-    for (int wi = 0; wi < 4; wi++) {
+    for (int wi = 0; wi < (promote ? 2 : 4); wi++) {      /* partial sums in registers: tiles up to 128 wide */
       const int bn = widths[wi];
       if (bn > 64 && g.N <= widths[wi - 1]) continue;
       const long long tiles = tm * ((g.N + bn - 1) / bn) * p.nbatch;
@@ -642,7 +691,7 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, boo
     }
     best_cost = best;
     const char *f = getenv("POLY_B200_TC_BN");           /* forces a width (measurements) */
-    if (f) { const int v = atoi(f); if (v == 64 || v == 128 || v == 192 || v == 256) BN = v; }
+    if (f) { const int v = atoi(f); if (v == 64 || v == 128 || ((v == 192 || v == 256) && !promote)) BN = v; }
   }
   /* CTA pairs (cta_group::2, one 256 x 256 tile per pair): each CTA stages half as much of B, which
    * pays where the mainloop is the bound -- K of 1024 or more, and enough tiles to fill the 74 pairs.
@@ -650,7 +699,7 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, boo
    * 8192 x 3072 x 1024 915 -> 999, 8192 x 2304 x 768 802 -> 765).  In the time model a pair's mainloop costs 0.85 of two single
    * tiles'.  POLY_B200_TC_CTAS=1|2 forces the choice (2 implies the 256-wide tile). */
   int ctas = 1;
-  if (g.M > TC_BM && g.N > 128) {
+  if (!promote && g.M > TC_BM && g.N > 128) {
     const long long pair_tiles = ((g.M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((g.N + 255) / 256) * p.nbatch;
     const double pair_cost = (double)((pair_tiles + 73) / 74) * (0.85 * k_model * 256 + 94000.0);
     if (k_model >= 1024 && pair_tiles >= 74 && pair_cost <= best_cost && !getenv("POLY_B200_TC_BN")) { ctas = 2; BN = 256; }
@@ -663,7 +712,13 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, boo
   if (rc == 0) rc = make_map(&mb, vb.ptr, g.K, rowsB, p.nbatch, vb.pitch, vb.bpitch, BN / ctas, g.ab_fmt);
   if (rc != 0) { pb_scratch_free(scr_a); pb_scratch_free(scr_b); return -1; }
   pb_tc_mark_used();
-  if (ctas == 2) rc = tc_launch<256, 2>(ma, mb, g, p.nbatch, stream);
+  if (promote) {
+    /* two 128-byte k-blocks (eight instructions) per partial sum; POLY_B200_TC_KCHUNK overrides (measurements) */
+    const char *kc = getenv("POLY_B200_TC_KCHUNK");
+    g.kchunk = kc && atoi(kc) > 0 ? atoi(kc) : 2;
+    rc = BN == 128 ? tc_launch<128, 1, true>(ma, mb, g, p.nbatch, stream) : tc_launch<64, 1, true>(ma, mb, g, p.nbatch, stream);
+  }
+  else if (ctas == 2) rc = tc_launch<256, 2>(ma, mb, g, p.nbatch, stream);
   else if (BN == 256) rc = tc_launch<256, 1>(ma, mb, g, p.nbatch, stream);
   else if (BN == 192) rc = tc_launch<192, 1>(ma, mb, g, p.nbatch, stream);
   else if (BN == 128) rc = tc_launch<128, 1>(ma, mb, g, p.nbatch, stream);

@@ -208,6 +208,29 @@ def test_fp32_as_three_tf32_products(devices, policy, gpu, monkeypatch, shape):
         assert gpu.stats()['launches_precompiled'] >= 3          # two splits and the contraction, not the CUDA-core kernel
 
 
+@pytest.mark.parametrize('shape', SHAPES + [(1024, 1024, 512), (1000, 900, 333), (512, 256, 3072), (256, 512, 8192)], ids=str)
+def test_fp32_tf32_products_with_promoted_partial_sums(devices, policy, gpu, monkeypatch, shape):
+    """POLY_B200_FP32=tcp: the three-product scheme with the partial sum of every two k-blocks (eight
+    instructions) moved from tensor memory to registers and added there with rounded float32 adds.
+    The error against a float64 product no longer grows with K: the float32 bound of 1e-5 against the
+    CPU holds at every K, and the error stays within a small multiple of the CPU's own rounding."""
+    cpu, cuda = devices
+    policy(False)
+    monkeypatch.setenv('POLY_B200_FP32', 'tcp')
+    a, b = _ab(shape, 4)
+    want = cpu.tensor(a).dot(cpu.tensor(b)).numpy()
+    gpu.poly_b200_stats_reset()
+    got = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
+    assert_close(got, want, 1e-5, f'fp32 via promoted tf32x3 {shape}')
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    rms = np.sqrt(np.mean(exact ** 2))
+    err_tc = np.sqrt(np.mean((got - exact) ** 2)) / rms
+    err_cpu = np.sqrt(np.mean((want - exact) ** 2)) / rms
+    assert err_tc <= max(4 * err_cpu, 1.5e-6), (err_tc, err_cpu)
+    if shape[2] >= 16:
+        assert gpu.stats()['launches_precompiled'] >= 3
+
+
 def test_fp32_default_route_is_the_cuda_core_kernel(devices, policy, gpu, monkeypatch):
     cpu, cuda = devices
     policy(False)
