@@ -92,7 +92,7 @@ struct TcSmem {
   static constexpr int BYTES = STAGES * STAGE + EPI + 256 + 1024; /* + barriers + alignment slack */
 };
 
-template <int BN, int CTAS, bool PROMOTE = false>
+template <int BN, int CTAS, bool PROMOTE = false, bool TF32 = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcArgs g) {
   using S = TcSmem<BN, CTAS>;
@@ -113,7 +113,7 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bk = g.ab_fmt == 2 ? TC_BK / 2 : TC_BK;      /* elements along k in one 128-byte tile row */
+  constexpr int bk = TF32 ? TC_BK / 2 : TC_BK;           /* elements along k in one 128-byte tile row */
   const int kblocks = (g.K + bk - 1) / bk;
   /* two accumulator buffers; the allocation is a power of two */
   constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
@@ -170,45 +170,64 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
   } else if (warp == 1) {
     /* ── MMA issuer ── */
     if (lane == 0 && rank == 0) {
-      /* D float32; A and B float16 (format 0), bfloat16 (1) or tf32 (2), both K-major.  A tile row is
-       * 128 bytes in every format and one instruction consumes 32 of them (16 or 8 elements). */
-      const uint32_t fmt = (uint32_t)g.ab_fmt;
-      const bool tf32 = g.ab_fmt == 2;
+      /* D float32; A and B float16 (format 0), bfloat16 (1) or tf32 (2, a compile-time variant), both
+       * K-major.  A tile row is 128 bytes in every format and one instruction consumes 32 of them
+       * (16 or 8 elements). */
+      const uint32_t fmt = TF32 ? 2u : (uint32_t)g.ab_fmt;
       const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((TC_BM * CTAS) >> 4) << 24);
       uint32_t stage = 0, phase = 0, it = 0;
       bool ok = true;
-      /* one accumulator buffer per tile -- or, in a PROMOTE kernel, per chunk of g.kchunk k-blocks:
-       * the epilogue warps add each chunk's sum to registers (rounded float32 adds), because the
-       * tensor cores' own accumulation truncates and would drift over a long k axis */
-      const int kstep = PROMOTE ? g.kchunk : kblocks;
-      for (int t = unit; t < g.n_tiles && ok; t += n_units) {
-        for (int kb0 = 0; kb0 < kblocks && ok; kb0 += kstep, it++) {
+      /* the four instructions of one k-block; `first` clears the accumulator */
+      auto issue_block = [&](uint32_t tmem_d, bool first) {
+        const uint32_t sa = base + stage * S::STAGE, sb = sa + S::STAGE_A;
+        const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sb);
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; k++) {
+          const uint32_t accum = (!first || k) ? 1u : 0u;
+          if constexpr (CTAS == 2) {
+            if constexpr (TF32) tc_mma_tf32_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
+            else tc_mma_bf16_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
+          } else {
+            if constexpr (TF32) tc_mma_tf32(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
+            else tc_mma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
+          }
+        }
+        /* frees the stage (in both CTAs of a pair) when these MMAs have read it */
+        if constexpr (CTAS == 2) tc_commit_pair(bar_empty + 8 * stage, 3); else tc_commit(bar_empty + 8 * stage);
+        if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
+      };
+      if constexpr (!PROMOTE) {
+        /* one accumulator buffer per tile */
+        for (int t = unit; t < g.n_tiles && ok; t += n_units, it++) {
           const uint32_t buf = it & 1u, use = it >> 1;
           if (!mbar_wait(bar_tempty + 8 * buf, (use & 1u) ^ 1u, &abort_flag, 2)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t tmem_d = tmem_base + buf * BN;
-          const int kend = min(kb0 + kstep, kblocks);
-          for (int kb = kb0; kb < kend; kb++) {
+          for (int kb = 0; kb < kblocks; kb++) {
             if (!mbar_wait(bar_full + 8 * stage, phase, &abort_flag, 3)) { ok = false; break; }
             tc_fence_after_sync();
-            const uint32_t sa = base + stage * S::STAGE, sb = sa + S::STAGE_A;
-            const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sb);
-#pragma unroll
-            for (int k = 0; k < TC_BK / 16; k++) {
-              const uint32_t accum = ((kb - kb0) | k) ? 1u : 0u;
-              if constexpr (CTAS == 2) {
-                if (tf32) tc_mma_tf32_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
-                else tc_mma_bf16_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
-              } else {
-                if (tf32) tc_mma_tf32(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
-                else tc_mma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
-              }
-            }
-            /* frees the stage (in both CTAs of a pair) when these MMAs have read it */
-            if constexpr (CTAS == 2) tc_commit_pair(bar_empty + 8 * stage, 3); else tc_commit(bar_empty + 8 * stage);
-            if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
+            issue_block(tmem_d, kb == 0);
           }
           if (ok) { if constexpr (CTAS == 2) tc_commit_pair(bar_tfull + 8 * buf, 3); else tc_commit(bar_tfull + 8 * buf); }   /* accumulator complete */
+        }
+      } else {
+        /* one accumulator buffer per chunk of g.kchunk k-blocks: the epilogue warps add each chunk's
+         * sum to registers (rounded float32 adds), because the tensor cores' own accumulation
+         * truncates and would drift over a long k axis */
+        for (int t = unit; t < g.n_tiles && ok; t += n_units) {
+          for (int kb0 = 0; kb0 < kblocks && ok; kb0 += g.kchunk, it++) {
+            const uint32_t buf = it & 1u, use = it >> 1;
+            if (!mbar_wait(bar_tempty + 8 * buf, (use & 1u) ^ 1u, &abort_flag, 2)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t tmem_d = tmem_base + buf * BN;
+            const int kend = min(kb0 + g.kchunk, kblocks);
+            for (int kb = kb0; kb < kend; kb++) {
+              if (!mbar_wait(bar_full + 8 * stage, phase, &abort_flag, 3)) { ok = false; break; }
+              tc_fence_after_sync();
+              issue_block(tmem_d, kb == kb0);
+            }
+            if (ok) tc_commit(bar_tfull + 8 * buf);
+          }
         }
       }
     }
@@ -430,11 +449,11 @@ static int make_map(CUtensorMap *map, const void *ptr, long long K, long long ro
   return 0;
 }
 
-template <int BN, int CTAS, bool PROMOTE = false>
+template <int BN, int CTAS, bool PROMOTE = false, bool TF32 = false>
 static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, long long nbatch, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(pb200_gemm_tc<BN, CTAS, PROMOTE>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN, CTAS>::BYTES);
+    cudaError_t e = cudaFuncSetAttribute(pb200_gemm_tc<BN, CTAS, PROMOTE, TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN, CTAS>::BYTES);
     if (e != cudaSuccess) { pb_set_error("gemm: cannot reserve %d bytes of shared memory: %s", TcSmem<BN, CTAS>::BYTES, cudaGetErrorString(e)); return -1; }
     configured = true;
   }
@@ -450,7 +469,7 @@ static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, lo
   const int grid = (int)(tiles < units ? tiles : units) * CTAS;
   cudaError_t e;
   if (CTAS == 1) {
-    pb200_gemm_tc<BN, CTAS, PROMOTE><<<grid, TC_THREADS, TcSmem<BN, CTAS>::BYTES, stream>>>(ma, mb, g);
+    pb200_gemm_tc<BN, CTAS, PROMOTE, TF32><<<grid, TC_THREADS, TcSmem<BN, CTAS>::BYTES, stream>>>(ma, mb, g);
     e = cudaGetLastError();
   } else {
     cudaLaunchConfig_t cfg = {};
@@ -459,7 +478,7 @@ static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, lo
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, pb200_gemm_tc<BN, CTAS, PROMOTE>, ma, mb, g);
+    e = cudaLaunchKernelEx(&cfg, pb200_gemm_tc<BN, CTAS, PROMOTE, TF32>, ma, mb, g);
   }
   if (e != cudaSuccess) { pb_set_error("tensor-core gemm launch: %s", cudaGetErrorString(e)); return -1; }
   return 0;
@@ -716,7 +735,13 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, int
     /* two 128-byte k-blocks (eight instructions) per partial sum; POLY_B200_TC_KCHUNK overrides (measurements) */
     const char *kc = getenv("POLY_B200_TC_KCHUNK");
     g.kchunk = kc && atoi(kc) > 0 ? atoi(kc) : 2;
-    rc = BN == 128 ? tc_launch<128, 1, true>(ma, mb, g, p.nbatch, stream) : tc_launch<64, 1, true>(ma, mb, g, p.nbatch, stream);
+    rc = BN == 128 ? tc_launch<128, 1, true, true>(ma, mb, g, p.nbatch, stream) : tc_launch<64, 1, true, true>(ma, mb, g, p.nbatch, stream);
+  } else if (fp32x3) {
+    if (ctas == 2) rc = tc_launch<256, 2, false, true>(ma, mb, g, p.nbatch, stream);
+    else if (BN == 256) rc = tc_launch<256, 1, false, true>(ma, mb, g, p.nbatch, stream);
+    else if (BN == 192) rc = tc_launch<192, 1, false, true>(ma, mb, g, p.nbatch, stream);
+    else if (BN == 128) rc = tc_launch<128, 1, false, true>(ma, mb, g, p.nbatch, stream);
+    else rc = tc_launch<64, 1, false, true>(ma, mb, g, p.nbatch, stream);
   }
   else if (ctas == 2) rc = tc_launch<256, 2>(ma, mb, g, p.nbatch, stream);
   else if (BN == 256) rc = tc_launch<256, 1>(ma, mb, g, p.nbatch, stream);
