@@ -390,19 +390,21 @@ def run_gemm_sweep(args):
         shapes = [(n, n, n) for n in (1024, 2048, 4096, 8192)] + [(8192, 2304, 768), (8192, 3072, 768), (8192, 768, 3072)]
     rows = []
     for (M, N, K) in shapes:
-        for mode in (['bf16'] if args.dtype == 'bf16' and args.shape else ['f32', 'f32-tf32x3', 'bf16-policy', 'bf16-buffers']):
-            if mode == 'f32' and M * N * K > 4096 ** 3 * 4:
+        for mode in (['bf16'] if args.dtype == 'bf16' and args.shape else ['f32-simt', 'f32', 'bf16-policy', 'bf16-buffers']):
+            if mode == 'f32-simt' and M * N * K > 4096 ** 3 * 4:
                 reps = 3
             else:
                 reps = max(args.steps, 3)
-            # 'f32-tf32x3': float32 operands on the tensor cores as three tf32 products (opt-in route)
-            os.environ['POLY_B200_FP32'] = 'tc' if mode == 'f32-tf32x3' else 'simt'
+            # 'f32': the default route (large problems: three tf32 products on the tensor cores, partial sums
+            # promoted to registers); 'f32-simt': the CUDA-core kernel
+            if mode == 'f32-simt':
+                os.environ['POLY_B200_FP32'] = 'simt'
             ms = time_gemm(lib, M, N, K, mode in ('bf16-policy', 'bf16'), reps=reps, bf16_buffers=(mode == 'bf16-buffers'))
             os.environ.pop('POLY_B200_FP32', None)
             tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
-            # fp32 CUDA-core kernel against the nominal FMA rate; the tensor-core routes against the measured
-            # bf16 peak (the tf32x3 route issues 3 tf32 products per multiply, at half the bf16 rate each)
-            peak = 75.0 if mode == 'f32' else peaks['bf16_tflops']
+            # CUDA-core kernel against the nominal FMA rate; the float32 tensor-core route against what three
+            # tf32 products per multiply allow (tf32 runs at half the bf16 rate: a sixth of the measured bf16 peak)
+            peak = 75.0 if mode == 'f32-simt' else peaks['bf16_tflops'] / 6.0 if mode == 'f32' else peaks['bf16_tflops']
             rows.append(dict(shape=f'{M}x{N}x{K}', mode=mode, us=ms * 1e3, tflops=tf, frac_of_peak=tf / peak))
     best = max((r for r in rows if not r['mode'].startswith('f32')), key=lambda r: r['tflops'])
     print(json.dumps(dict(metric='gemm_tflops', value=best['tflops'], unit='TFLOP/s', n_gpus=1, steps=args.steps,

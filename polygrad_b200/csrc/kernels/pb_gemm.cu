@@ -519,13 +519,18 @@ int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
     if (rc != PB_TC_UNSUPPORTED) return rc;
     if (dtype != PB_F32 || a_bf16 || c_bf16) { pb_set_error("gemm: 16-bit operands need the tensor-core kernel, which rejected this shape"); return -1; }
   }
-  /* float32 contractions on the tensor cores as three tf32 products.  POLY_B200_FP32=tcp: partial
-   * sums over two k-blocks are added up in registers (float32-accurate); =tc: the whole k axis is
-   * summed in tensor memory, whose accumulation truncates (error about 1e-8 * K of the result's rms).
-   * Default: the CUDA-core kernel. */
+  /* float32 contractions large enough to fill the machine run on the tensor cores as three tf32
+   * products, the partial sums of every eight k-blocks added up in registers (float32-accurate:
+   * the 1e-5 bound of this path holds at every K).  Small ones and scaled sums stay on the CUDA-core
+   * kernels.  POLY_B200_FP32=simt keeps everything there; =tcp sends every shape the tensor-core
+   * kernel accepts; =tc sums the whole k axis in tensor memory instead, whose accumulation
+   * truncates (error about 1e-8 * K of the result's rms; a few percent faster). */
   if (alpha == 1.0f) {
     const char *m = getenv("POLY_B200_FP32");
-    const int mode = !m ? 0 : strcmp(m, "tc") == 0 ? 1 : strcmp(m, "tcp") == 0 ? 2 : 0;
+    int mode = 0;
+    if (!m) mode = (double)M * (double)N * (double)K * (double)nbatch >= 268435456.0 ? 2 : 0;
+    else if (strcmp(m, "tc") == 0) mode = 1;
+    else if (strcmp(m, "tcp") == 0) mode = 2;
     if (mode) {
       int rc = pb_gemm_tc_run(*this, bufs, stream, mode);
       if (rc != PB_TC_UNSUPPORTED) return rc;

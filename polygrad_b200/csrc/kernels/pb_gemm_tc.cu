@@ -528,9 +528,11 @@ static const void *tc_operand(PbGemmProgram &p, PbTcOperand &cache, const void *
  * 2^-22.  The three products are one contraction over a k axis three times as
  * long: A' = [hi | hi | lo], B' = [hi | lo | hi], each segment Kp = K rounded up
  * to 4 elements (16-byte rows) and zero-filled past K.  Accumulation is fp32 in
- * TMEM, which truncates: measured against a float64 product the error is about
- * 1e-8 * K of the result's rms (a CPU float32 sum: 2e-7 to 4e-7), so this route
- * is opt-in (POLY_B200_FP32=tc) and not the float32 default. */
+ * TMEM, which truncates: summed over the whole k axis there, the error against
+ * a float64 product is about 1e-8 * K of the result's rms (a CPU float32 sum:
+ * 2e-7 to 4e-7).  The PROMOTE kernels therefore hand the partial sum of every
+ * few k-blocks to the epilogue warps, which add them up in registers; that
+ * keeps the error at the CPU's level for every K and is the float32 default. */
 __device__ __forceinline__ float tf32_rna(float a) {
   uint32_t u;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(a));
@@ -732,9 +734,12 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, int
   if (rc != 0) { pb_scratch_free(scr_a); pb_scratch_free(scr_b); return -1; }
   pb_tc_mark_used();
   if (promote) {
-    /* two 128-byte k-blocks (eight instructions) per partial sum; POLY_B200_TC_KCHUNK overrides (measurements) */
+    /* eight 128-byte k-blocks (32 instructions, 256 elements of the tripled k axis) per partial sum:
+     * measured on GPT-2 124M fp32, 2 blocks cost 58.9 ms per step, 4: 45.2, 8: 43.7, 16: 43.1 (no
+     * promotion: 42.5), and at 16 the error against a float64 product starts to show;
+     * POLY_B200_TC_KCHUNK overrides (measurements) */
     const char *kc = getenv("POLY_B200_TC_KCHUNK");
-    g.kchunk = kc && atoi(kc) > 0 ? atoi(kc) : 2;
+    g.kchunk = kc && atoi(kc) > 0 ? atoi(kc) : 8;
     rc = BN == 128 ? tc_launch<128, 1, true, true>(ma, mb, g, p.nbatch, stream) : tc_launch<64, 1, true, true>(ma, mb, g, p.nbatch, stream);
   } else if (fp32x3) {
     if (ctas == 2) rc = tc_launch<256, 2, false, true>(ma, mb, g, p.nbatch, stream);

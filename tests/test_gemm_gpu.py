@@ -190,8 +190,8 @@ def test_fp32_as_three_tf32_products(devices, policy, gpu, monkeypatch, shape):
     """POLY_B200_FP32=tc: float32 contractions on the tensor cores, a = hi + lo in tf32 and
     a.b = hi.hi + hi.lo + lo.hi with fp32 accumulation in TMEM.  That accumulation truncates: against a
     float64 product the error grows linearly with K (about 1e-8 * K of the result's rms; a CPU float32
-    sum stays at 2e-7 to 4e-7), which is why this route is opt-in and its bound against the CPU is 1e-4
-    here, between the float32 kernel's 1e-5 and the bf16 policy's 2e-2."""
+    sum stays at 2e-7 to 4e-7), which is why this variant is opt-in (the default promotes partial sums,
+    next test) and its bound against the CPU is 1e-4 here."""
     cpu, cuda = devices
     policy(False)
     monkeypatch.setenv('POLY_B200_FP32', 'tc')
@@ -210,8 +210,8 @@ def test_fp32_as_three_tf32_products(devices, policy, gpu, monkeypatch, shape):
 
 @pytest.mark.parametrize('shape', SHAPES + [(1024, 1024, 512), (1000, 900, 333), (512, 256, 3072), (256, 512, 8192)], ids=str)
 def test_fp32_tf32_products_with_promoted_partial_sums(devices, policy, gpu, monkeypatch, shape):
-    """POLY_B200_FP32=tcp: the three-product scheme with the partial sum of every two k-blocks (eight
-    instructions) moved from tensor memory to registers and added there with rounded float32 adds.
+    """POLY_B200_FP32=tcp (the default for large problems): the three-product scheme with the partial sum of
+    every eight k-blocks (32 instructions) moved from tensor memory to registers and added there with rounded float32 adds.
     The error against a float64 product no longer grows with K: the float32 bound of 1e-5 against the
     CPU holds at every K, and the error stays within a small multiple of the CPU's own rounding."""
     cpu, cuda = devices
@@ -231,18 +231,27 @@ def test_fp32_tf32_products_with_promoted_partial_sums(devices, policy, gpu, mon
         assert gpu.stats()['launches_precompiled'] >= 3
 
 
-def test_fp32_default_route_is_the_cuda_core_kernel(devices, policy, gpu, monkeypatch):
+def test_fp32_default_routes(devices, policy, gpu, monkeypatch):
+    """Large float32 contractions take the tensor-core route with promoted partial sums by default,
+    small ones the CUDA-core kernel; both within 1e-5 of the CPU."""
     cpu, cuda = devices
     policy(False)
     a, b = _ab((1024, 768, 512), 8)
     want = cpu.tensor(a).dot(cpu.tensor(b)).numpy()
     monkeypatch.delenv('POLY_B200_FP32', raising=False)
     got = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
-    monkeypatch.setenv('POLY_B200_FP32', 'tc')
-    tc = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
+    monkeypatch.setenv('POLY_B200_FP32', 'tcp')
+    tcp = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
+    monkeypatch.setenv('POLY_B200_FP32', 'simt')
+    simt = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
     assert_close(got, want, 1e-5, 'fp32 default route')
-    assert_close(tc, want, 1e-4, 'fp32 tensor-core route')
-    assert not np.array_equal(got, tc)         # two different kernels ran
+    assert_close(simt, want, 1e-5, 'fp32 CUDA-core route')
+    assert np.array_equal(got, tcp) and not np.array_equal(got, simt)
+    a, b = _ab((128, 256, 64), 8)                      # below the size threshold
+    monkeypatch.delenv('POLY_B200_FP32', raising=False)
+    small = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
+    monkeypatch.setenv('POLY_B200_FP32', 'simt')
+    assert np.array_equal(small, cuda.tensor(a).dot(cuda.tensor(b)).numpy())
 
 
 def test_fp32_tensor_core_route_keeps_infinities(devices, policy, monkeypatch):
