@@ -539,11 +539,11 @@ __device__ __forceinline__ float tf32_rna(float a) {
   return __uint_as_float(u);
 }
 
-__global__ void __launch_bounds__(256) pb200_split_tf32x3(const float *__restrict__ src, float *__restrict__ dst,
+__global__ void __launch_bounds__(256) pb200_split_tf32x3(const float *__restrict__ src, long long pitch, float *__restrict__ dst,
                                                           long long total, int K, int Kp, int is_b) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long row = i / Kp; const int k = (int)(i % Kp);
-    const float a = k < K ? src[row * Kp + k] : 0.0f;
+    const float a = k < K ? src[row * pitch + k] : 0.0f;
     float *o = dst + row * 3 * Kp;
     if (!(fabsf(a) <= 3.4028235e38f)) {
       /* an infinity or a NaN meets only the other operand's hi part, once: inf * b keeps b's sign
@@ -579,13 +579,25 @@ static const void *tc_operand_x3(PbGemmProgram &p, PbTcOperand &cache, const voi
     dst = cache.data;
     cache.src = src_buf; cache.version = ver; cache.misses++;
   }
-  void *dense = pb_scratch_alloc((size_t)(p.nbatch * rows * Kp) * 4);
-  bool ok = dense != nullptr && p.pack_into(dense, src_buf, off, is_a, PB_F32, PB_F32, Kp, stream) == 0;
+  /* an operand that already is a K-major matrix (an activation as the model stores it) is split
+   * where it lies; anything else is gathered into a dense [rows][Kp] copy first */
+  const bool direct = is_a ? p.a_direct : p.b_direct;
+  const long long sk = is_a ? p.a_sk : p.b_sk, srow = is_a ? p.a_sm : p.b_sn;
+  const bool in_place = direct && p.nbatch == 1 && (sk == 1 || p.K == 1) && (rows == 1 || srow >= p.K);
+  void *dense = nullptr;
+  bool ok = true;
+  const float *from = (const float *)src_buf + off;
+  long long pitch = rows > 1 ? srow : p.K;
+  if (!in_place) {
+    dense = pb_scratch_alloc((size_t)(p.nbatch * rows * Kp) * 4);
+    ok = dense != nullptr && p.pack_into(dense, src_buf, off, is_a, PB_F32, PB_F32, Kp, stream) == 0;
+    from = (const float *)dense; pitch = Kp;
+  }
   if (ok) {
     const long long total = p.nbatch * rows * Kp;
     long long blocks = (total + 255) / 256;
     if (blocks > 148LL * 32) blocks = 148LL * 32;
-    pb200_split_tf32x3<<<(unsigned)blocks, 256, 0, stream>>>((const float *)dense, (float *)dst, total, (int)p.K, (int)Kp, is_a ? 0 : 1);
+    pb200_split_tf32x3<<<(unsigned)blocks, 256, 0, stream>>>(from, pitch, (float *)dst, total, (int)p.K, (int)Kp, is_a ? 0 : 1);
     ok = cudaGetLastError() == cudaSuccess;
     p.launches++;
   }
