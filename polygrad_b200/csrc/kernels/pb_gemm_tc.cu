@@ -539,11 +539,18 @@ __device__ __forceinline__ float tf32_rna(float a) {
   return __uint_as_float(u);
 }
 
-__global__ void __launch_bounds__(256) pb200_split_tf32x3(const float *__restrict__ src, long long pitch, float *__restrict__ dst,
+struct SplitSrc {                      /* the source as [batch axes][rows][k], k contiguous */
+  const float *src; long long pitch; long long rows;
+  int nb; int bext[4]; long long bstr[4];
+};
+
+__global__ void __launch_bounds__(256) pb200_split_tf32x3(const SplitSrc in, float *__restrict__ dst,
                                                           long long total, int K, int Kp, int is_b) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long row = i / Kp; const int k = (int)(i % Kp);
-    const float a = k < K ? src[row * pitch + k] : 0.0f;
+    long long bz = row / in.rows, so = (row % in.rows) * in.pitch;
+    for (int d = 0; d < in.nb; d++) { so += (bz % in.bext[d]) * in.bstr[d]; bz /= in.bext[d]; }
+    const float a = k < K ? in.src[so + k] : 0.0f;
     float *o = dst + row * 3 * Kp;
     if (!(fabsf(a) <= 3.4028235e38f)) {
       /* an infinity or a NaN meets only the other operand's hi part, once: inf * b keeps b's sign
@@ -583,21 +590,26 @@ static const void *tc_operand_x3(PbGemmProgram &p, PbTcOperand &cache, const voi
    * where it lies; anything else is gathered into a dense [rows][Kp] copy first */
   const bool direct = is_a ? p.a_direct : p.b_direct;
   const long long sk = is_a ? p.a_sk : p.b_sk, srow = is_a ? p.a_sm : p.b_sn;
-  const bool in_place = direct && p.nbatch == 1 && (sk == 1 || p.K == 1) && (rows == 1 || srow >= p.K);
+  bool in_place = direct && (sk == 1 || p.K == 1) && srow >= 0 && p.b_ax.size() <= 4;
+  for (auto &b : p.b_ax) if ((is_a ? b.sa : b.sb) < 0) in_place = false;
   void *dense = nullptr;
   bool ok = true;
-  const float *from = (const float *)src_buf + off;
-  long long pitch = rows > 1 ? srow : p.K;
-  if (!in_place) {
+  SplitSrc in{};
+  in.rows = rows;
+  if (in_place) {
+    in.src = (const float *)src_buf + off; in.pitch = rows > 1 ? srow : 0;
+    in.nb = (int)p.b_ax.size();
+    for (int i = 0; i < in.nb; i++) { in.bext[i] = (int)p.b_ax[i].ext; in.bstr[i] = is_a ? p.b_ax[i].sa : p.b_ax[i].sb; }
+  } else {
     dense = pb_scratch_alloc((size_t)(p.nbatch * rows * Kp) * 4);
     ok = dense != nullptr && p.pack_into(dense, src_buf, off, is_a, PB_F32, PB_F32, Kp, stream) == 0;
-    from = (const float *)dense; pitch = Kp;
+    in.src = (const float *)dense; in.pitch = Kp; in.rows = p.nbatch * rows; in.nb = 0;
   }
   if (ok) {
     const long long total = p.nbatch * rows * Kp;
     long long blocks = (total + 255) / 256;
     if (blocks > 148LL * 32) blocks = 148LL * 32;
-    pb200_split_tf32x3<<<(unsigned)blocks, 256, 0, stream>>>(from, pitch, (float *)dst, total, (int)p.K, (int)Kp, is_a ? 0 : 1);
+    pb200_split_tf32x3<<<(unsigned)blocks, 256, 0, stream>>>(in, (float *)dst, total, (int)p.K, (int)Kp, is_a ? 0 : 1);
     ok = cudaGetLastError() == cudaSuccess;
     p.launches++;
   }
