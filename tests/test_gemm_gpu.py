@@ -231,6 +231,29 @@ def test_fp32_tf32_products_with_promoted_partial_sums(devices, policy, gpu, mon
         assert gpu.stats()['launches_precompiled'] >= 3
 
 
+@pytest.mark.parametrize('route', ['tcp', 'tc'])
+def test_fp32_tensor_core_route_batched_views(devices, policy, monkeypatch, route):
+    """The attention contractions with (batch, head) batch axes on the float32 tensor-core routes: q and k
+    are permuted views of [B, T, H, hd] storage (split where they lie, two batch strides each), the
+    scores feed the second contraction as a dense batched operand."""
+    cpu, cuda = devices
+    policy(False)
+    rng = np.random.default_rng(9)
+    B, T, H, hd = 2, 160, 3, 32
+    q = rng.standard_normal((B, T, H, hd)).astype(np.float32)
+    k = rng.standard_normal((B, T, H, hd)).astype(np.float32)
+
+    def chain(d):
+        qq = d.tensor(q).permute(0, 2, 1, 3)
+        kk = d.tensor(k).permute(0, 2, 1, 3).permute(0, 1, 3, 2)
+        return qq.dot(kk).dot(d.tensor(k).permute(0, 2, 1, 3))
+    monkeypatch.setenv('POLY_B200_FP32', 'simt')
+    want = chain(cpu).numpy()
+    monkeypatch.setenv('POLY_B200_FP32', route)
+    got = chain(cuda).numpy()
+    assert_close(got, want, 1e-5 if route == 'tcp' else 1e-4, f'batched attention contractions, {route}')
+
+
 def test_fp32_default_routes(devices, policy, gpu, monkeypatch):
     """Large float32 contractions take the tensor-core route with promoted partial sums by default,
     small ones the CUDA-core kernel; both within 1e-5 of the CPU."""
