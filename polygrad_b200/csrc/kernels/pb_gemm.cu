@@ -519,7 +519,7 @@ int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
     if (rc != PB_TC_UNSUPPORTED) return rc;
     if (dtype != PB_F32 || a_bf16 || c_bf16) { pb_set_error("gemm: 16-bit operands need the tensor-core kernel, which rejected this shape"); return -1; }
   }
-  /* float32 contractions of at least 2^26 multiply-adds run on the tensor cores as three tf32
+  /* float32 contractions of at least 2^28 multiply-adds run on the tensor cores as three tf32
    * products, the partial sums of every eight k-blocks added up in registers (float32-accurate:
    * the 1e-5 bound of this path holds at every K).  Small ones and scaled sums stay on the CUDA-core
    * kernels.  POLY_B200_FP32=simt keeps everything there; =tcp sends every shape the tensor-core
@@ -528,9 +528,11 @@ int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
   if (alpha == 1.0f) {
     const char *m = getenv("POLY_B200_FP32");
     int mode = 0;
-    /* measured crossover: 256 x 784 x 512 (2^26.6 multiply-adds) 26.6 us on the CUDA cores, 20.6 us here,
-     * 512 x 1024 x 256 26.8 / 13.8, 1024^3 149 / 36.5; below 2^26 the three launches are not worth it */
-    if (!m) mode = (double)M * (double)N * (double)K * (double)nbatch >= 67108864.0 ? 2 : 0;
+    /* back-to-back calls favour this route from far smaller sizes (256 x 784 x 512: 26.6 us on the CUDA
+     * cores, 20.6 us here), but inside a short dependent chain its extra launch and longer start-up
+     * cost more than they save: with the threshold at 2^26 the MLP forward went from 44.6 to 52.8 us
+     * and a small training step from 3.85 to 4.27 ms, so it stays at 2^28 multiply-adds */
+    if (!m) mode = (double)M * (double)N * (double)K * (double)nbatch >= 268435456.0 ? 2 : 0;
     else if (strcmp(m, "tc") == 0) mode = 1;
     else if (strcmp(m, "tcp") == 0) mode = 2;
     if (mode) {
