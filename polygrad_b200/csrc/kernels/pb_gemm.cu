@@ -519,7 +519,7 @@ int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
     if (rc != PB_TC_UNSUPPORTED) return rc;
     if (dtype != PB_F32 || a_bf16 || c_bf16) { pb_set_error("gemm: 16-bit operands need the tensor-core kernel, which rejected this shape"); return -1; }
   }
-  /* float32 contractions of at least 2^28 multiply-adds run on the tensor cores as three tf32
+  /* float32 contractions of at least 2^30 multiply-adds run on the tensor cores as three tf32
    * products, the partial sums of every eight k-blocks added up in registers (float32-accurate:
    * the 1e-5 bound of this path holds at every K).  Small ones and scaled sums stay on the CUDA-core
    * kernels.  POLY_B200_FP32=simt keeps everything there; =tcp sends every shape the tensor-core
@@ -531,8 +531,9 @@ int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
     /* back-to-back calls favour this route from far smaller sizes (256 x 784 x 512: 26.6 us on the CUDA
      * cores, 20.6 us here), but inside a short dependent chain its extra launch and longer start-up
      * cost more than they save: with the threshold at 2^26 the MLP forward went from 44.6 to 52.8 us
-     * and a small training step from 3.85 to 4.27 ms, so it stays at 2^28 multiply-adds */
-    if (!m) mode = (double)M * (double)N * (double)K * (double)nbatch >= 268435456.0 ? 2 : 0;
+     * and a small training step from 3.85 to 4.27 ms (and a single 2^28 contraction in that step cost
+     * 0.3 ms), so the threshold is 2^30 multiply-adds, 1024^3 */
+    if (!m) mode = (double)M * (double)N * (double)K * (double)nbatch >= 1073741824.0 ? 2 : 0;
     else if (strcmp(m, "tc") == 0) mode = 1;
     else if (strcmp(m, "tcp") == 0) mode = 2;
     if (mode) {

@@ -259,7 +259,7 @@ def test_fp32_default_routes(devices, policy, gpu, monkeypatch):
     small ones the CUDA-core kernel; both within 1e-5 of the CPU."""
     cpu, cuda = devices
     policy(False)
-    a, b = _ab((1024, 768, 512), 8)
+    a, b = _ab((1024, 1024, 1024), 8)
     want = cpu.tensor(a).dot(cpu.tensor(b)).numpy()
     monkeypatch.delenv('POLY_B200_FP32', raising=False)
     got = cuda.tensor(a).dot(cuda.tensor(b)).numpy()
