@@ -87,7 +87,12 @@ int  poly_b200_set_device(int device);
 int  poly_b200_device(void);
 
 /* Arithmetic of fp32 contractions (polygrad matmuls on float32 buffers):
- *   0  fp32 operands, fp32 FMA on the CUDA cores (default);
+ *   0  float32 arithmetic (default): contractions of at least 2^30 multiply-adds
+ *      run on the tensor cores as three tf32 products per multiply (a = hi + lo,
+ *      hi.hi + hi.lo + lo.hi) with the partial sums added up in float32
+ *      registers, within 1e-5 of the CPU at every K; smaller ones are fp32 FMAs
+ *      on the CUDA cores.  POLY_B200_FP32=simt|tcp|tc forces a route (tc: the
+ *      sums stay in tensor memory, error about 1e-8 * K of the result's rms);
  *   1  operands rounded to bfloat16 (nearest even), products and sums in fp32,
  *      on the tensor cores.  Also selected by POLY_B200_GEMM=bf16.
  * Contractions whose buffers are bfloat16 always take the tensor-core kernel. */
