@@ -168,6 +168,19 @@ unsigned long long poly_b200_last_dtoh_src(void);
 /* Release cached free blocks of the pool back to the driver. */
 void poly_b200_trim(void);
 
+/* Sizes of the pool's free blocks, i.e. what the next poly_cuda_alloc calls can be served
+ * from without a driver allocation: returns their count and writes the first `cap` sizes.
+ * Scratch that a captured CUDA graph addresses is never among them (it stays with the graph
+ * until the plan is freed or recaptured; polygrad keeps a plan's intermediates for the life
+ * of the plan in the same way, src/exec_plan.c:860-881, 1062). */
+int poly_b200_pool_free_sizes(unsigned long long *sizes, int cap);
+
+/* Tells the runtime about an access to a device buffer made outside poly_cuda_launch
+ * (mode 'r' read, 'w' partial write, 'W' whole-buffer overwrite, 'b' read and write): a zero
+ * fill recorded by poly_cuda_memset is carried out (or dropped before 'W') and a written
+ * buffer's converted operand copies are invalidated.  Host-side bookkeeping; 0 / -1. */
+int poly_b200_note_access(const void *ptr, char mode);
+
 /* CUDA events on the internal stream, for timing. */
 void *poly_b200_event_create(void);
 int   poly_b200_event_record(void *event);

@@ -44,6 +44,7 @@ void poly_b200_graph_destroy(void *exec);
 int poly_b200_memset_now(unsigned long long ptr, unsigned char val, size_t bytes);
 int poly_b200_timing_active(void);
 int poly_b200_ptr_on_host(const void *p);
+int poly_b200_note_access(const void *p, char mode);
 
 /* the original plan code, compiled under other names */
 PolyCompiledPlan *poly_ref_compile_schedule(PolyCtx *ctx, PolySchedule *schedule, PolyDeviceId device);
@@ -199,7 +200,7 @@ static void plan_destroy(PbPlan *p) {
   for (int s = 0; s < p->n_steps; s++) pb_step_release(&p->steps[s]);
   if (p->arena) poly_cuda_free(p->arena);
   free(p->steps); free(p->slot_bytes); free(p->slot_off); free(p->slot_alias); free(p->slot_inter); free(p->slot_ptr);
-  free(p->zero_step); free(p->zero_slot); free(p->graph_ext);
+  free(p->zero_step); free(p->zero_slot); free(p->graph_ext); free(p->graph_acc_ptr); free(p->graph_acc_mode);
   if (p->stage) for (int i = 0; i < p->n_sched_slots; i++) if (p->stage[i]) poly_cuda_free(p->stage[i]);
   free(p->stage); free(p->slot_acc); free(p->ext_seen); free(p->ext_host);
   free(p->base.slot_to_data);
@@ -334,6 +335,37 @@ static int run_eager(PbPlan *p) {
   return 0;
 }
 
+/* The accesses of the live steps to bound (external) buffers, in step order, as the
+ * eager run reports them launch by launch; a graph replay reports the same list. */
+static void record_graph_accesses(PbPlan *p) {
+  int cap = 0;
+  for (int s = 0; s < p->n_steps; s++) if (!p->steps[s].dead) cap += p->steps[s].n_params;
+  free(p->graph_acc_ptr); free(p->graph_acc_mode);
+  p->graph_acc_ptr = malloc(sizeof(void *) * (size_t)(cap + 1));
+  p->graph_acc_mode = malloc((size_t)(cap + 1));
+  p->n_graph_acc = 0;
+  for (int s = 0; s < p->n_steps; s++) {
+    const PbStep *st = &p->steps[s];
+    if (st->dead) continue;
+    for (int a = 0; a < st->n_params; a++) {
+      const char m = st->rw[a];
+      if (m == '-' || m == 0) continue;
+      const int sl = pb_plan_resolve(p, st->slot[a]);
+      if (sl < 0 || sl >= p->n_sched_slots || p->slot_inter[sl] || !p->slot_ptr[sl]) continue;
+      /* repeated reads of one buffer tell the runtime nothing new */
+      if (m == 'r') {
+        bool seen = false;
+        for (int i = p->n_graph_acc - 1; i >= 0 && !seen; i--)
+          if (p->graph_acc_ptr[i] == p->slot_ptr[sl]) seen = true;
+        if (seen) continue;
+      }
+      p->graph_acc_ptr[p->n_graph_acc] = p->slot_ptr[sl];
+      p->graph_acc_mode[p->n_graph_acc] = m;
+      p->n_graph_acc++;
+    }
+  }
+}
+
 static bool graph_valid(PbPlan *p) {
   if (!p->graph) return false;
   if (p->graph_epoch != poly_b200_pool_epoch()) return false;
@@ -403,6 +435,12 @@ static int run_steps(PbPlan *p) {
   const bool graphs = !env_is("POLY_B200_GRAPH", "0") && p->graph_failures < 4 && !getenv("POLY_B200_DRYRUN") &&
                       !poly_b200_timing_active();      /* per-launch timing needs individual launches */
   if (graphs && graph_valid(p)) {
+    /* what the launches of an eager run tell the runtime about bound buffers: pending zero fills
+     * are materialised or dropped, and written buffers get a new version, so that converted
+     * copies of them held by other plans (a forward plan's bf16 weights after a training step)
+     * are seen to be stale */
+    for (int i = 0; i < p->n_graph_acc; i++)
+      if (poly_b200_note_access(p->graph_acc_ptr[i], p->graph_acc_mode[i]) != 0) return -1;
     return poly_b200_graph_launch(p->graph, (unsigned long long)p->graph_kernels, (unsigned long long)p->graph_precompiled);
   }
   if (p->graph) { poly_b200_graph_destroy(p->graph); p->graph = NULL; p->runs = 1; }
@@ -421,7 +459,8 @@ static int run_steps(PbPlan *p) {
         free(p->graph_ext);
         p->graph_ext = malloc(sizeof(void *) * (size_t)(p->n_sched_slots + 1));
         for (int i = 0; i < p->n_sched_slots; i++) p->graph_ext[i] = p->slot_ptr[i];
-        /* the captured work has not run yet */
+        record_graph_accesses(p);
+        /* the captured work has not run yet; the capture run itself has noted its accesses */
         return poly_b200_graph_launch(p->graph, 0, 0);
       }
       p->graph_failures++;

@@ -47,6 +47,7 @@ typedef struct {
   int *zero_step, *zero_slot, n_zero;
   void *graph; unsigned long long graph_epoch; void **graph_ext;
   long long graph_kernels, graph_precompiled;
+  void **graph_acc_ptr; char *graph_acc_mode; int n_graph_acc;   /* accesses to bound buffers a replay reports */
   int runs, graph_failures;
 } PbPlan;
 

@@ -579,6 +579,8 @@ extern "C" int poly_b200_attention(const float *q, const float *k, const float *
   cudaStream_t stream = (cudaStream_t)poly_b200_stream();
   const long long BH = (long long)B * H, D = (long long)H * AT_HD;
   const size_t bytes = (size_t)BH * T * AT_HD * 2;
+  if (pb_note_read(q) != 0 || pb_note_read(k) != 0 || pb_note_read(v) != 0 || pb_note_read(mask) != 0 ||
+      pb_note_write(out, (size_t)BH * T * AT_HD * 4) != 0) return -1;
   void *qb = pb_scratch_alloc(bytes), *kb = pb_scratch_alloc(bytes), *vb = pb_scratch_alloc(bytes);
   int rc = -1;
   if (qb && kb && vb) {

@@ -706,6 +706,8 @@ extern "C" int poly_b200_gemm(long long M, long long N, long long K,
     g_direct[key] = p;
   }
   void *bufs[4] = {C, const_cast<void *>(A), const_cast<void *>(B), const_cast<float *>(bias)};
+  if (pb_note_read(A) != 0 || pb_note_read(B) != 0 || pb_note_read(bias) != 0 ||
+      pb_note_write(C, c_sm == N ? (size_t)(M * N) * 4 : 0) != 0) return -1;
   int rc = p->launch(bufs, (cudaStream_t)poly_b200_stream());
   if (rc == 0) pb_count_launch(true, p->n_launches());
   return rc;

@@ -85,6 +85,10 @@ int pb_gemm_tc_launch_raw(const void *a_bf16, long long a_pitch, const void *b_b
                           float *C, long long c_sm, long long M, long long N, long long K,
                           const float *bias, int relu, cudaStream_t stream);
 
+/* One-time set-up of everything pb_gemm_tc_launch_raw may need (shared-memory attribute of
+ * each tile-width variant, the tensor-map encoder, the SM count).  0 / -1. */
+int pb_gemm_tc_prepare_raw(void);
+
 /* POLY_B200_GEMM=bf16: run fp32 contractions with operands rounded to bf16
  * (round-to-nearest-even), products and sums in fp32, on the tensor cores. */
 bool pb_gemm_policy_bf16(void);

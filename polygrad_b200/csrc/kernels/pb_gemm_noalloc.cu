@@ -45,9 +45,15 @@ extern "C" int poly_b200_gemm_noalloc(long long M, long long N, long long K,
     cudaError_t e = cudaGetSymbolAddress(&p, pb200_noalloc_scratch);
     if (e != cudaSuccess || !p) { pb_set_error("poly_b200_gemm_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e)); return -1; }
     g_scratch_ptr[dev] = (unsigned char *)p;
+    /* the rest of the one-time set-up, so that no later call does any: the kernel variants'
+     * shared-memory attribute and the driver entry point that encodes tensor maps */
+    if (pb_gemm_tc_prepare_raw() != 0) { g_scratch_ptr[dev] = nullptr; return -1; }
   }
   unsigned char *sa = g_scratch_ptr[dev], *sb = sa + off_b;
   cudaStream_t stream = (cudaStream_t)poly_b200_stream();
+  /* bookkeeping for operands that are pool buffers (a host-side table lookup; allocates nothing) */
+  if (pb_note_read(A) != 0 || pb_note_read(B) != 0 || pb_note_read(bias) != 0 ||
+      pb_note_write(C, c_sm == N ? (size_t)(M * N) * 4 : 0) != 0) return -1;
   /* Both operands are rewritten in full on every call (the array keeps whatever
    * the previous call left; nothing in it has to start at zero: the kernel never
    * reads the pitch padding beyond K). */

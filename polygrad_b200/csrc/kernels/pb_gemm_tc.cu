@@ -449,23 +449,34 @@ static int make_map(CUtensorMap *map, const void *ptr, long long K, long long ro
   return 0;
 }
 
+/* One-time set-up of a kernel variant (the runtime drives one device per process). */
 template <int BN, int CTAS, bool PROMOTE = false, bool TF32 = false>
-static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, long long nbatch, cudaStream_t stream) {
+static int tc_configure() {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(pb200_gemm_tc<BN, CTAS, PROMOTE, TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<BN, CTAS>::BYTES);
     if (e != cudaSuccess) { pb_set_error("gemm: cannot reserve %d bytes of shared memory: %s", TcSmem<BN, CTAS>::BYTES, cudaGetErrorString(e)); return -1; }
     configured = true;
   }
+  return 0;
+}
+
+static int sm_count() {
+  static int sms = 0;
+  if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); if (sms <= 0) sms = 148; }
+  return sms;
+}
+
+template <int BN, int CTAS, bool PROMOTE = false, bool TF32 = false>
+static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, long long nbatch, cudaStream_t stream) {
+  if (tc_configure<BN, CTAS, PROMOTE, TF32>() != 0) return -1;
   g.tiles_m = (g.M + TC_BM * CTAS - 1) / (TC_BM * CTAS);
   g.tiles_n = (g.N + BN - 1) / BN;
   long long tiles = (long long)g.tiles_m * g.tiles_n * nbatch;
   if (tiles > 2147483647LL) { pb_set_error("gemm: too many tiles"); return -1; }
   g.n_tiles = (int)tiles;
   g.m_fast = g.N > g.M ? 1 : 0;
-  static int sms = 0;
-  if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); if (sms <= 0) sms = 148; }
-  const int units = sms / CTAS;
+  const int units = sm_count() / CTAS;
   const int grid = (int)(tiles < units ? tiles : units) * CTAS;
   cudaError_t e;
   if (CTAS == 1) {
@@ -783,6 +794,13 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, int
   return rc;
 }
 
+
+int pb_gemm_tc_prepare_raw(void) {
+  if (!encode_tiled()) { pb_set_error("gemm: cuTensorMapEncodeTiled not available"); return -1; }
+  sm_count();
+  if (tc_configure<256, 1>() != 0 || tc_configure<128, 1>() != 0 || tc_configure<64, 1>() != 0) return -1;
+  return 0;
+}
 
 /* Runs the tensor-core kernel on operands that are already bfloat16, K-major
  * ([rows][pitch], pitch a multiple of 8 elements, 16-byte aligned base).  Uses no

@@ -73,6 +73,9 @@ struct Runtime {
   int n_pending = 0;
   bool force_sync = false;
   bool capturing = false, capture_failed = false;
+  /* blocks given back while a stream capture is open: their addresses are baked into the
+   * captured work, so they stay out of the free list until the graph is destroyed */
+  std::vector<std::pair<size_t, void *>> capture_hold;
   uint64_t pool_epoch = 1;       /* bumps when cached blocks go back to the driver */
   PolyB200Stats st{};
 };
@@ -240,7 +243,14 @@ static void *pool_alloc(size_t bytes) {
   size_t rs = round_size(bytes);
   void *p = nullptr;
   auto it = R.free_blocks.find(rs);
-  if (it != R.free_blocks.end()) { p = it->second; R.free_blocks.erase(it); }
+  if (R.capturing) {
+    /* a block this capture already used and released: the captured work is one ordered chain,
+     * so a later node may use it again */
+    for (size_t i = 0; i < R.capture_hold.size() && !p; i++)
+      if (R.capture_hold[i].first == rs) { p = R.capture_hold[i].second; R.capture_hold.erase(R.capture_hold.begin() + (long)i); }
+  }
+  if (p) {}
+  else if (it != R.free_blocks.end()) { p = it->second; R.free_blocks.erase(it); }
   else if (R.dry) { p = calloc(1, rs); }
   else if (R.capturing) {
     /* no driver allocation inside a stream capture: the caller abandons the capture */
@@ -269,7 +279,8 @@ static void pool_free(void *p) {
   auto it = R.live.find((uintptr_t)p);
   if (it == R.live.end()) return;
   if (it->second.pending_zero) R.n_pending--;
-  R.free_blocks.insert({it->second.size, p});
+  if (R.capturing) R.capture_hold.push_back({it->second.size, p});
+  else R.free_blocks.insert({it->second.size, p});
   R.live.erase(it);
 }
 
@@ -282,6 +293,14 @@ extern "C" void poly_b200_trim(void) {
   }
   R.free_blocks.clear();
   R.st.bytes_allocated = R.held;
+}
+
+/* Sizes of the blocks the pool could hand out without asking the driver (diagnostics, tests).
+ * Returns how many there are; writes the first `cap` sizes. */
+extern "C" int poly_b200_pool_free_sizes(unsigned long long *sizes, int cap) {
+  int n = 0;
+  for (auto &kv : R.free_blocks) { if (sizes && n < cap) sizes[n] = kv.first; n++; }
+  return n;
 }
 
 extern "C" unsigned long long poly_cuda_alloc(size_t bytes) {
@@ -335,6 +354,22 @@ static int note_access(const void *p, char mode) {
   if (mode != 'r') it->second.version = R.version_counter++;
   return 0;
 }
+
+/* The same for code outside this file.  Reads are free while no zero fill is pending. */
+extern "C" int poly_b200_note_access(const void *p, char mode) {
+  if (!R.ok) return 0;
+  if (mode == 'r' && R.n_pending == 0) return 0;
+  return note_access(p, mode);
+}
+
+/* A write of `bytes` starting at p: a whole-buffer overwrite when it covers the allocation. */
+int pb_note_write(const void *p, size_t bytes) {
+  auto it = find_buf(p);
+  if (it == R.live.end()) return 0;
+  const bool whole = (uintptr_t)p == it->first && bytes >= it->second.requested;
+  return note_access(p, whole ? 'W' : 'w');
+}
+int pb_note_read(const void *p) { return p ? poly_b200_note_access(p, 'r') : 0; }
 
 extern "C" int poly_cuda_memset(unsigned long long ptr, unsigned char val, size_t bytes) {
   if (!ready()) return -1;
@@ -792,6 +827,19 @@ extern "C" int poly_b200_capture_begin(void) {
   return 0;
 }
 
+/* An executable graph together with the pool blocks its nodes address: scratch that the
+ * captured steps took and gave back.  The blocks return to the free list when the graph
+ * is destroyed, not before (every replay writes them). */
+struct GraphBox {
+  cudaGraphExec_t exec = nullptr;
+  std::vector<std::pair<size_t, void *>> held;
+};
+
+static void release_held(std::vector<std::pair<size_t, void *>> &held) {
+  for (auto &b : held) R.free_blocks.insert({b.first, b.second});
+  held.clear();
+}
+
 /* Ends the capture.  Returns an executable graph, or NULL when the capture was
  * abandoned (the enqueued work is then discarded and must be re-issued). */
 extern "C" void *poly_b200_capture_end(int discard) {
@@ -799,23 +847,42 @@ extern "C" void *poly_b200_capture_end(int discard) {
   R.capturing = false;
   cudaGraph_t graph = nullptr;
   cudaError_t e = cudaStreamEndCapture(R.stream, &graph);
-  if (e != cudaSuccess || !graph) { cudaGetLastError(); return nullptr; }
-  if (discard || R.capture_failed) { cudaGraphDestroy(graph); return nullptr; }
   cudaGraphExec_t exec = nullptr;
-  e = cudaGraphInstantiate(&exec, graph, 0);
-  cudaGraphDestroy(graph);
-  if (e != cudaSuccess) { cudaGetLastError(); return nullptr; }
-  return (void *)exec;
+  if (e != cudaSuccess || !graph) { cudaGetLastError(); graph = nullptr; }
+  else if (discard || R.capture_failed) { cudaGraphDestroy(graph); graph = nullptr; }
+  else {
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) { cudaGetLastError(); exec = nullptr; }
+  }
+  if (!exec) { release_held(R.capture_hold); return nullptr; }     /* the captured work never runs */
+  GraphBox *box = new GraphBox();
+  box->exec = exec;
+  box->held.swap(R.capture_hold);
+  return (void *)box;
 }
 
-extern "C" int poly_b200_graph_launch(void *exec, unsigned long long n_kernels, unsigned long long n_precompiled) {
-  if (!exec) return -1;
-  PB_CUDA(cudaGraphLaunch((cudaGraphExec_t)exec, R.stream));
+extern "C" int poly_b200_graph_launch(void *graph, unsigned long long n_kernels, unsigned long long n_precompiled) {
+  if (!graph) return -1;
+  PB_CUDA(cudaGraphLaunch(((GraphBox *)graph)->exec, R.stream));
   R.st.launches += n_kernels; R.st.launches_precompiled += n_precompiled; R.st.launches_generated += n_kernels - n_precompiled;
   return 0;
 }
 
-extern "C" void poly_b200_graph_destroy(void *exec) { if (exec) cudaGraphExecDestroy((cudaGraphExec_t)exec); }
+/* Bytes of pool scratch a graph keeps out of circulation (diagnostics, tests). */
+extern "C" unsigned long long poly_b200_graph_held_bytes(void *graph) {
+  unsigned long long n = 0;
+  if (graph) for (auto &b : ((GraphBox *)graph)->held) n += b.first;
+  return n;
+}
+
+extern "C" void poly_b200_graph_destroy(void *graph) {
+  if (!graph) return;
+  GraphBox *box = (GraphBox *)graph;
+  cudaGraphExecDestroy(box->exec);
+  release_held(box->held);       /* stream-ordered pool: later work on the stream may take them */
+  delete box;
+}
 
 /* Stream-ordered fill used by plans for buffers a kernel only partly writes. */
 extern "C" int poly_b200_memset_now(unsigned long long ptr, unsigned char val, size_t bytes) {

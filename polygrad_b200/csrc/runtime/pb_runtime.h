@@ -51,6 +51,13 @@ void  pb_count_launch(bool precompiled, int n = 1);
  * operands (bf16 weights) can be invalidated when the source is written. */
 uint64_t pb_buffer_version(const void *p);      /* changes whenever p's allocation is written */
 
+/* Entry points that launch on caller-supplied device pointers report their accesses like
+ * poly_cuda_launch does: a pending (lazy) zero fill of a pool buffer is materialised before a
+ * read or partial write and dropped before a whole-buffer overwrite, and a written buffer
+ * gets a new version.  Host-side bookkeeping only; allocates nothing. */
+int pb_note_read(const void *p);
+int pb_note_write(const void *p, size_t bytes);
+
 /* The tensor-core kernel bounds its barrier waits and records a code when one
  * runs out; the runtime reads it back at synchronisation points. */
 int  pb_gemm_tc_error(void);                    /* 0 = none, >0 = which wait gave up, <0 = cannot read */

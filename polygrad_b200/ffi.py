@@ -149,6 +149,8 @@ def _declare_cuda(lib):
     _sig(lib, 'poly_b200_synchronize', ctypes.c_int, [])
     _sig(lib, 'poly_b200_stream', _ptr, [])
     _sig(lib, 'poly_b200_trim', None, [])
+    _sig(lib, 'poly_b200_pool_free_sizes', ctypes.c_int, [ctypes.POINTER(U), ctypes.c_int])
+    _sig(lib, 'poly_b200_note_access', ctypes.c_int, [_ptr, ctypes.c_char])
     _sig(lib, 'poly_b200_timing_begin', None, [])
     _sig(lib, 'poly_b200_timing_end', ctypes.c_double, [ctypes.POINTER(ctypes.c_int)])
     _sig(lib, 'poly_b200_timing_active', ctypes.c_int, [])

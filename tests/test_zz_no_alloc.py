@@ -4,10 +4,13 @@ fully committed elsewhere, or where a driver allocation's implicit
 synchronisation is unacceptable).  Its scratch is a fixed array inside the
 library instead of pool memory.
 
-Checked against the allocating entry point poly_b200_gemm on the same inputs,
-on two calls in a row with different operands (the shared scratch keeps the
-previous call's contents), and for the size limit.  Runs last so that a failure
-here cannot hide the other tests' results."""
+Checked against numpy on the same bfloat16-rounded operands accumulated in
+float64 (1e-4) and against the allocating entry point poly_b200_gemm, on calls
+in a row with different operands (the shared scratch keeps the previous call's
+contents: the third problem is smaller and has a K that is not a multiple of 8,
+so its padded rows lie over what the larger call left); that the call leaves
+the runtime's pool untouched; and for the size limit.  Runs last so that a
+failure here cannot hide the other tests' results."""
 import ctypes
 
 import numpy as np
@@ -25,6 +28,17 @@ def _dev(lib, a):
     return d
 
 
+def _bf16_round(a):
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32)
+
+
+def _pool_state(lib):
+    n = lib.poly_b200_pool_free_sizes(None, 0)
+    return lib.stats()['bytes_allocated'], n
+
+
 def _run(lib, fn_name, a, b, bias, relu):
     m, k = a.shape
     n = b.shape[1]
@@ -33,7 +47,10 @@ def _run(lib, fn_name, a, b, bias, relu):
     if fn_name == 'poly_b200_gemm':
         rc = lib.poly_b200_gemm(m, n, k, da, k, 1, db, n, 1, dc, n, dx, relu, 0)
     else:
+        before = _pool_state(lib)
         rc = lib.poly_b200_gemm_noalloc(m, n, k, da, k, 1, db, n, 1, dc, n, dx, relu)
+        # the defining property: nothing taken from the driver, nothing taken from or given to the pool
+        assert _pool_state(lib) == before
     assert rc == 0, lib.last_error()
     out = np.empty((m, n), np.float32)
     assert lib.poly_cuda_copy_dtoh(out.ctypes.data, dc, out.nbytes) == 0
@@ -42,18 +59,23 @@ def _run(lib, fn_name, a, b, bias, relu):
     return out
 
 
-def test_noalloc_matches_allocating_entry_twice(gpu):
+def test_noalloc_matches_float64_and_the_allocating_entry(gpu):
     gpu.poly_b200_set_gemm_policy(1)
     try:
-        for call, (m, n, k) in enumerate([(300, 200, 136), (512, 768, 256)]):
+        for call, (m, n, k) in enumerate([(300, 200, 136), (512, 768, 256), (130, 70, 100)]):
             rng = np.random.default_rng(100 + call)
             a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
             b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
             bias = rng.uniform(-1, 1, n).astype(np.float32)
-            want = _run(gpu, 'poly_b200_gemm', a, b, bias, call)
-            got = _run(gpu, 'poly_b200_gemm_noalloc', a, b, bias, call)
+            relu = call & 1
+            want = _bf16_round(a).astype(np.float64) @ _bf16_round(b).astype(np.float64) + bias
+            if relu:
+                want = np.maximum(want, 0)
+            got = _run(gpu, 'poly_b200_gemm_noalloc', a, b, bias, relu)
+            sibling = _run(gpu, 'poly_b200_gemm', a, b, bias, relu)
             assert np.abs(want).max() > 0
-            assert_close(got, want, 1e-4, f'call {call}')
+            assert_close(got, want.astype(np.float32), 1e-4, f'call {call} vs float64')
+            assert_close(got, sibling, 1e-4, f'call {call} vs poly_b200_gemm')
     finally:
         gpu.poly_b200_set_gemm_policy(0)
 
