@@ -110,6 +110,19 @@ int poly_b200_gemm(long long M, long long N, long long K,
                    const void *B, long long b_sk, long long b_sn,
                    float *C, long long c_sm, const float *bias, int relu, int operands_bf16);
 
+/* The same with a choice of result format (no counterpart in polygrad; what the plan executor
+ * runs when a contraction's only reader takes bfloat16): POLY_B200_GEMM_C_BF16 stores C as
+ * bfloat16 (C then points to 2-byte elements, c_sm counts elements; N and c_sm multiples of 4),
+ * POLY_B200_GEMM_GELU applies GELU in its tanh form (polygrad's poly_gelu, src/frontend.c:603)
+ * after the bias and before that rounding, evaluated with the hardware tanh approximation
+ * (relative error about 2^-11, below bfloat16's 2^-9).  Tensor-core kernel only. */
+#define POLY_B200_GEMM_C_BF16 1
+#define POLY_B200_GEMM_GELU   2
+int poly_b200_gemm_ex(long long M, long long N, long long K,
+                      const void *A, long long a_sm, long long a_sk,
+                      const void *B, long long b_sk, long long b_sn,
+                      void *C, long long c_sm, const float *bias, int operands_bf16, int flags);
+
 /* Diagnostics: runs a one-thread kernel that waits, with a short limit, on a barrier nothing
  * arrives at -- the situation every barrier wait of the tensor-core kernels is bounded
  * against -- and checks that the wait gives up, records its code in the device error word
@@ -159,6 +172,61 @@ void *poly_b200_stream(void);
 /* Page-locked host memory for fast copies (cudaHostAlloc). */
 void *poly_b200_host_alloc(size_t bytes);
 void  poly_b200_host_free(void *p);
+
+/* Deferred readbacks.  polygrad reads an instance buffer back synchronously
+ * (poly_instance_readback_buf -> poly_cuda_copy_dtoh, src/instance.c:479-501).  After
+ * poly_b200_readback_defer(1) a copy_dtoh of at least 1 MiB into page-locked host memory
+ * (poly_b200_host_alloc) returns at once: the source is snapshotted on the device and crosses
+ * PCIe on a second stream while later launches run; the bytes are in place after
+ * poly_b200_readback_wait().  At most two such copies are in flight; the caller alternates
+ * between two host buffers.  0 / -1. */
+int poly_b200_readback_defer(int on);
+int poly_b200_readback_wait(void);
+
+/* ── data-parallel ranks (no counterpart in polygrad, whose CUDA runtime drives device 0 of
+ * one process only, src/runtime_cuda.c:192-243) ─────────────────────────────────────────
+ * One process per GPU; ranks hold replicas of the weights and disjoint batch rows and exchange
+ * nothing while a forward runs.  The one collective is the gather of results to a root rank,
+ * over NCCL point-to-point calls on a second stream (NCCL is loaded with dlopen on first use).
+ *
+ * poly_b200_comm_unique_id   rank 0 makes an id (returns its size, <= 128 bytes) and hands it to
+ *                            the other ranks by whatever means the launcher offers;
+ * poly_b200_comm_init        every rank joins; the runtime's device is the rank's device;
+ * poly_b200_gather_async     snapshots `bytes` at src on the main stream and sends them to the
+ *                            root behind whatever is launched next; on the root, rank r's bytes
+ *                            land at root_dst + poly_b200_gather_offset(r, bytes).  The root's
+ *                            buffer must stay untouched until the transfers have finished;
+ * poly_b200_comm_join        makes the main stream wait for the transfers enqueued so far;
+ * poly_b200_comm_wait        blocks the host until they are done;
+ * poly_b200_comm_max         replaces *value by its maximum over the ranks (step times).
+ * All return 0 / -1 unless stated. */
+int    poly_b200_comm_unique_id(void *id, size_t cap);
+int    poly_b200_comm_init(int rank, int world, const void *id, size_t id_bytes);
+int    poly_b200_comm_rank(void);
+int    poly_b200_comm_world(void);
+size_t poly_b200_gather_offset(int rank, size_t bytes);
+int    poly_b200_gather_async(const void *src, size_t bytes, void *root_dst, int root);
+int    poly_b200_comm_join(void);
+int    poly_b200_comm_wait(void);
+int    poly_b200_comm_max(double *value);
+void   poly_b200_comm_destroy(void);
+
+/* This rank's share of a global batch as n_micro forwards of one instance (exported by
+ * libpolygrad_b200.so; poly_instance_forward, polygrad src/instance.c:830, runs one batch of
+ * the instance's static shape).  inputs[i] is micro-batch i's host array for the input buffer
+ * `input_name`.  With gather != 0 each micro-batch's output buffer (index out_buf, out_bytes
+ * bytes) is gathered to `root` behind the next micro-batch's compute; micro-batch i of rank r
+ * is number poly_b200_shard_micro_index(r, world, i) = i * world + r of the global batch and
+ * lands at root_dst + that number * out_bytes.  0 / -1. */
+struct PolyInstance;
+int poly_b200_shard_micro_index(int rank, int world, int i);
+int poly_b200_forward_microbatches(struct PolyInstance *inst, const char *input_name, const float *const *inputs,
+                                   int n_micro, int out_buf, size_t out_bytes, void *root_dst, int root, int gather);
+
+/* `rows` rows of row_bytes, src_pitch bytes apart in one device buffer, into a dense device
+ * buffer (polygrad's allocator has no device-to-device copy: copy_between is unimplemented,
+ * src/exec_plan.c:290-294).  Stream-ordered; 0 / -1. */
+int poly_b200_copy_rows(unsigned long long dst, unsigned long long src, size_t row_bytes, size_t src_pitch, size_t rows);
 
 /* Device address that the most recent poly_cuda_copy_dtoh read from.  polygrad's
  * instance API hides device handles; a one-element readback followed by this

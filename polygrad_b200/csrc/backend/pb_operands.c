@@ -33,7 +33,7 @@
 enum { OP_C = 0, OP_A = 1, OP_B = 2, OP_X = 3 };
 typedef struct { char kind; long long ext, s[4]; } HAxis;          /* strides in C, A, B, X */
 typedef struct {
-  int nparams, params[4], relu, nax, abf16, cbf16;
+  int nparams, params[4], relu, nax, abf16, cbf16, gelu;
   long long alpha; int has_alpha;      /* bits of the float32 scale of the sum, when it is not 1 */
   long long off[4], numel[4];
   char dtype[8];
@@ -69,6 +69,7 @@ static bool hgemm_parse(const char *text, const char *pre, HGemm *g) {
   }
   g->abf16 = hget(text, pre, "abf16", buf, sizeof buf) ? atoi(buf) : 0;
   g->cbf16 = hget(text, pre, "cbf16", buf, sizeof buf) ? atoi(buf) : 0;
+  g->gelu = hget(text, pre, "gelu", buf, sizeof buf) ? atoi(buf) : 0;
   g->has_alpha = hget(text, pre, "alpha", buf, sizeof buf) ? 1 : 0;
   if (g->has_alpha) g->alpha = atoll(buf);
   return true;
@@ -85,6 +86,7 @@ static void hgemm_emit(PbStr *t, const char *pre, const HGemm *g) {
   pb_str_printf(t, "//%snaxes %d\n", pre, g->nax);
   if (g->abf16) pb_str_printf(t, "//%sabf16 1\n", pre);
   if (g->cbf16) pb_str_printf(t, "//%scbf16 1\n", pre);
+  if (g->gelu) pb_str_printf(t, "//%sgelu 1\n", pre);
   if (g->has_alpha) pb_str_printf(t, "//%salpha %lld\n", pre, g->alpha);
 }
 
@@ -392,6 +394,169 @@ static int retype_bf16(PbPlan *p) {
   return done;
 }
 
+/* ── GELU into the producing contraction's epilogue ──────────────────── */
+/* polygrad's GPT-2 MLP is fc contraction (+bias) -> GELU -> projection (reference
+ * src/modelzoo/models/gpt2.c:478-490); the GELU is a kernel of its own that reads the
+ * 8192 x 3072 float32 result and, under the bf16 policy, stores bfloat16 for the
+ * projection.  When that kernel is the only reader of the contraction's result it moves
+ * into the contraction's epilogue: bias, GELU, round to bfloat16, store.
+ *
+ * The elementwise kernel is recognised by what it computes, not by the shape of its op
+ * tree: its scalar function is evaluated on the host in double precision at sample
+ * points and compared with 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
+ * (poly_gelu, reference src/frontend.c:603-614).  The epilogue evaluates the same formula
+ * with the hardware tanh approximation (relative error about 2^-11, below the bfloat16
+ * rounding that follows), so the result is not bit-identical to the separate kernel's:
+ * the pass runs only under the bf16 policy, whose bound is 2e-2, and POLY_B200_EPILOGUE=0
+ * switches it off. */
+#include <math.h>
+
+static bool eval_scalar(const PbKern *k, PolyUOp *u, PolyUOp *x_load, double x, double *out, int depth) {
+  if (depth > 64) return false;
+  if (u == x_load) { *out = x; return true; }
+  double a = 0, b = 0, c = 0;
+  switch (u->op) {
+  case POLY_OP_CONST:
+    if (u->arg.kind == POLY_ARG_FLOAT) *out = (double)(float)u->arg.f;
+    else if (u->arg.kind == POLY_ARG_INT) *out = (double)u->arg.i;
+    else if (u->arg.kind == POLY_ARG_BOOL) *out = u->arg.b ? 1.0 : 0.0;
+    else return false;
+    return true;
+  case POLY_OP_CAST:
+    if (u->n_src != 1 || u->dtype.priority != 13) return false;
+    return eval_scalar(k, u->src[0], x_load, x, out, depth + 1);
+  case POLY_OP_NEG: case POLY_OP_EXP2: case POLY_OP_LOG2: case POLY_OP_SQRT: case POLY_OP_RECIPROCAL:
+    if (u->n_src != 1 || !eval_scalar(k, u->src[0], x_load, x, &a, depth + 1)) return false;
+    *out = u->op == POLY_OP_NEG ? -a : u->op == POLY_OP_EXP2 ? exp2(a) : u->op == POLY_OP_LOG2 ? log2(a) :
+           u->op == POLY_OP_SQRT ? sqrt(a) : 1.0 / a;
+    return true;
+  case POLY_OP_ADD: case POLY_OP_SUB: case POLY_OP_MUL: case POLY_OP_FDIV: case POLY_OP_MAX:
+  case POLY_OP_CMPLT: case POLY_OP_CMPNE: case POLY_OP_CMPEQ:
+    if (u->n_src != 2 || !eval_scalar(k, u->src[0], x_load, x, &a, depth + 1) ||
+        !eval_scalar(k, u->src[1], x_load, x, &b, depth + 1)) return false;
+    switch (u->op) {
+    case POLY_OP_ADD: *out = a + b; break;
+    case POLY_OP_SUB: *out = a - b; break;
+    case POLY_OP_MUL: *out = a * b; break;
+    case POLY_OP_FDIV: *out = a / b; break;
+    case POLY_OP_MAX: *out = a > b ? a : b; break;
+    case POLY_OP_CMPLT: *out = a < b; break;
+    case POLY_OP_CMPNE: *out = a != b; break;
+    default: *out = a == b; break;
+    }
+    return true;
+  case POLY_OP_WHERE:
+    if (u->n_src != 3 || !eval_scalar(k, u->src[0], x_load, x, &a, depth + 1) ||
+        !eval_scalar(k, u->src[1], x_load, x, &b, depth + 1) || !eval_scalar(k, u->src[2], x_load, x, &c, depth + 1)) return false;
+    *out = a != 0.0 ? b : c;
+    return true;
+  case POLY_OP_MULACC:
+    if (u->n_src != 3 || !eval_scalar(k, u->src[0], x_load, x, &a, depth + 1) ||
+        !eval_scalar(k, u->src[1], x_load, x, &b, depth + 1) || !eval_scalar(k, u->src[2], x_load, x, &c, depth + 1)) return false;
+    *out = a * b + c;
+    return true;
+  default:
+    return false;      /* loads of other buffers, ranges, integer arithmetic: not a function of x alone */
+  }
+}
+
+/* Is the step out[i] = gelu(in[i]) over two buffers of the same element layout? */
+static bool step_is_gelu(const PbStep *st, int *p_out, int *p_in) {
+  if (st->dead || st->precompiled || st->fused_rows || !st->sink || st->n_vars || st->n_params != 2) return false;
+  PbKern k;
+  if (pb_kern_build(&k, st->sink) != 0) { pb_kern_free(&k); return false; }
+  bool ok = false;
+  do {
+    if (k.n_stores != 1 || k.n_reduce_nodes != 0 || k.n_ranges > PB_MAX_RANGES) break;
+    PbStore *s = &k.stores[0];
+    if (s->index->n_src != 2) break;
+    const int po = s->param, pi = 1 - po;
+    if (po < 0 || po > 1 || st->rw[po] != 'W' || st->rw[pi] != 'r') break;
+    PolyDType a = k.params[po]->dtype, b = k.params[pi]->dtype;
+    if (a.priority != 13 || b.priority != 13 || a.bitsize != 32 || b.bitsize != 32 || a.ptr_size != b.ptr_size) break;
+    /* the one load: every LOAD node in the tree must be the same INDEX(PARAM pi, idx) as the store's index expression */
+    PolyUOp *x_load = NULL; bool one = true;
+    for (int n = 0; n < k.n_nodes && one; n++) {
+      PolyUOp *u = k.nodes[n].u;
+      if (u->op != POLY_OP_LOAD) continue;
+      if (u->src[0]->op != POLY_OP_INDEX || u->src[0]->n_src != 2 || u->src[0]->src[0]->op != POLY_OP_PARAM ||
+          (int)u->src[0]->src[0]->arg.i != pi || (x_load && x_load != u)) one = false;
+      else x_load = u;
+    }
+    if (!one || !x_load) break;
+    uint64_t all = 0;
+    for (int q = 0; q < k.n_ranges; q++) { if (k.extent[q] < 1) all = ~(uint64_t)0; all |= (uint64_t)1 << q; }
+    if (all == ~(uint64_t)0) break;
+    PbAffine so, si;
+    pb_fit_affine(&k, s->index->src[1], all, &so);
+    pb_fit_affine(&k, x_load->src[0]->src[1], all, &si);
+    if (!so.ok || !si.ok || so.offset != 0 || si.offset != 0) break;
+    bool same = true; long long covered = 1;
+    for (int q = 0; q < k.n_ranges; q++) { if (so.stride[q] != si.stride[q]) same = false; covered *= k.extent[q]; }
+    if (!same || covered != a.ptr_size) break;
+    /* the function itself */
+    static const double xs[] = {-9.0, -6.5, -4.0, -3.0, -2.25, -1.5, -1.0, -0.75, -0.5, -0.25, -0.1, -1e-3, 0.0, 1e-3, 0.1,
+                                0.25, 0.5, 0.75, 1.0, 1.5, 2.25, 3.0, 4.0, 6.5, 9.0, 0.3333, -0.6667, 1.2345, -2.718, 5.5};
+    bool match = true;
+    for (size_t i = 0; i < sizeof xs / sizeof xs[0] && match; i++) {
+      double y = 0;
+      if (!eval_scalar(&k, s->value, x_load, xs[i], &y, 0)) { match = false; break; }
+      const double x = xs[i], want = 0.5 * x * (1.0 + tanh(0.7978845608028654 * (x + 0.044715 * x * x * x)));
+      if (!(fabs(y - want) <= 2e-6 * (1.0 + fabs(want)))) match = false;
+    }
+    if (!match) break;
+    *p_out = po; *p_in = pi;
+    ok = true;
+  } while (0);
+  pb_kern_free(&k);
+  return ok;
+}
+
+static int fuse_gelu_epilogue(PbPlan *p) {
+  int done = 0;
+  PbSlotUse *u = malloc(sizeof(PbSlotUse) * (size_t)p->n_slots);
+  for (int e = 0; e < p->n_steps; e++) {
+    PbStep *E = &p->steps[e];
+    int po, pi;
+    if (!step_is_gelu(E, &po, &pi)) continue;
+    pb_slot_usage(p, u);
+    const int y = pb_plan_resolve(p, E->slot[po]), x = pb_plan_resolve(p, E->slot[pi]);
+    if (x == y || !p->slot_inter[x] || !p->slot_inter[y] || u[x].writers != 1 || u[x].readers != 1 || u[y].writers != 1) continue;
+    /* y is stored as bfloat16: every reader is a contraction that takes it as a bfloat16 A operand */
+    bool y16 = u[y].readers >= 1;
+    for (int s = 0; s < p->n_steps && y16; s++) {
+      PbStep *R = &p->steps[s];
+      if (R->dead || s == e || !pb_step_reads(p, R, y)) continue;
+      HGemm g;
+      if (s < e || step_kind(R) != K_GEMM || !hgemm_parse(R->text, "", &g) || !g.abf16 ||
+          pb_plan_resolve(p, R->slot[g.params[OP_A]]) != y) y16 = false;
+    }
+    if (!y16) continue;
+    /* the producer: a plain contraction writing all of x */
+    const int w = u[x].first_write;
+    PbStep *W = &p->steps[w];
+    HGemm g;
+    if (w >= e || step_kind(W) != K_GEMM || !hgemm_parse(W->text, "", &g) || strcmp(g.dtype, "f32") != 0 || g.cbf16 || g.gelu ||
+        g.relu || g.has_alpha || pb_plan_resolve(p, W->slot[g.params[OP_C]]) != x || g.params[OP_X] == g.params[OP_C] ||
+        W->rw[g.params[OP_C]] != 'W') continue;
+    /* nothing between the two steps may touch y (it becomes the contraction's output) */
+    bool clear = true;
+    for (int s = w; s < e && clear; s++)
+      if (!p->steps[s].dead && (pb_step_reads(p, &p->steps[s], y) || pb_step_writes(p, &p->steps[s], y))) clear = false;
+    if (!clear) continue;
+    g.cbf16 = 1; g.gelu = 1;
+    char *text = gemm_text(&g);
+    PolyCudaProgram *prog = compile_step_text(W, text, "gelu_epilogue");
+    if (!prog) { free(text); continue; }
+    step_set_program(W, prog, text);
+    W->slot[g.params[OP_C]] = y;
+    E->dead = true;
+    done++;
+  }
+  free(u);
+  return done;
+}
+
 /* ── attention output in the layout the next projection reads ────────── */
 /* out is [batch.., row, d] through strides; its only reader is a contraction
  * whose A operand walks it as rows x k with k split over (head, d), which is not
@@ -508,14 +673,17 @@ static int share_mask_tiles(PbPlan *p) {
 void pb_plan_operands(PbPlan *p) {
   const char *e = getenv("POLY_B200_OPERANDS");     /* "0": none, "fold": view folding only */
   if (e && strcmp(e, "0") == 0) return;
-  int folded = fold_views(p), kept = 0, outs = 0;
+  int folded = fold_views(p), kept = 0, outs = 0, gelus = 0;
   if (poly_b200_gemm_policy() && !(e && strcmp(e, "fold") == 0)) {
     kept = retype_bf16(p);
     outs = relayout_attention_out(p);
+    const char *ep = getenv("POLY_B200_EPILOGUE");
+    if (!(ep && strcmp(ep, "0") == 0)) gelus = fuse_gelu_epilogue(p);
   }
   int tiles = (e && strcmp(e, "notiles") == 0) ? 0 : share_mask_tiles(p);
   if (getenv("POLY_B200_DEBUG"))
     fprintf(stderr, "pb_operands: %d copies folded into operand strides, %d operands stored as bfloat16, "
                     "%d attention outputs written as bfloat16 matrices, "
-                    "%d attention steps reuse a mask classification\n", folded, kept, outs, tiles);
+                    "%d attention steps reuse a mask classification, %d GELU kernels moved into contraction epilogues\n",
+            folded, kept, outs, tiles, gelus);
 }

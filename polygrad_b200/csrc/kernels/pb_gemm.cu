@@ -664,6 +664,8 @@ PbGemmProgram *pb_parse_gemm(const PbHeader &h0, const char *prefix, std::string
   p->rw[(size_t)p->p_c] = x_is_c ? 'b' : (dense ? 'W' : 'w');
   p->a_bf16 = h.geti("abf16") != 0;
   p->c_bf16 = h.geti("cbf16") != 0;
+  p->gelu = h.geti("gelu") != 0;
+  if (p->gelu && (!p->c_bf16 || p->relu)) { err = "gemm: the GELU epilogue needs a bfloat16 result and no relu"; delete p; return nullptr; }
   if (p->alpha != 1.0f && p->dtype != PB_F32) { err = "gemm: a scaled sum needs fp32 operands"; delete p; return nullptr; }
   if ((p->a_bf16 || p->c_bf16) && (p->dtype != PB_F32 || x_is_c || p->alpha != 1.0f || !pb_gemm_tc_static_ok(*p))) {
     err = "gemm: bfloat16 operand/result storage is not possible for this shape"; delete p; return nullptr;
@@ -679,13 +681,32 @@ PbGemmProgram *pb_parse_gemm(const PbHeader &h0, const char *prefix, std::string
 static std::map<std::tuple<long long, long long, long long, long long, long long, long long, long long, long long, int, int, int>,
                 PbGemmProgram *> g_direct;
 
+static int gemm_direct(long long M, long long N, long long K, const void *A, long long a_sm, long long a_sk,
+                       const void *B, long long b_sk, long long b_sn, void *C, long long c_sm, const float *bias,
+                       int relu, int operands_bf16, int flags);
+
 extern "C" int poly_b200_gemm(long long M, long long N, long long K,
                               const void *A, long long a_sm, long long a_sk,
                               const void *B, long long b_sk, long long b_sn,
                               float *C, long long c_sm, const float *bias, int relu, int operands_bf16) {
+  return gemm_direct(M, N, K, A, a_sm, a_sk, B, b_sk, b_sn, C, c_sm, bias, relu, operands_bf16, 0);
+}
+
+/* flags: POLY_B200_GEMM_C_BF16 stores C as bfloat16, POLY_B200_GEMM_GELU applies tanh-GELU before that store. */
+extern "C" int poly_b200_gemm_ex(long long M, long long N, long long K,
+                                 const void *A, long long a_sm, long long a_sk,
+                                 const void *B, long long b_sk, long long b_sn,
+                                 void *C, long long c_sm, const float *bias, int operands_bf16, int flags) {
+  if ((flags & POLY_B200_GEMM_GELU) && !(flags & POLY_B200_GEMM_C_BF16)) { pb_set_error("poly_b200_gemm_ex: the GELU epilogue stores bfloat16"); return -1; }
+  return gemm_direct(M, N, K, A, a_sm, a_sk, B, b_sk, b_sn, C, c_sm, bias, 0, operands_bf16, flags);
+}
+
+static int gemm_direct(long long M, long long N, long long K, const void *A, long long a_sm, long long a_sk,
+                       const void *B, long long b_sk, long long b_sn, void *C, long long c_sm, const float *bias,
+                       int relu, int operands_bf16, int flags) {
   if (poly_cuda_init() != 0) return -1;
   if (M <= 0 || N <= 0 || K <= 0 || !A || !B || !C) { pb_set_error("poly_b200_gemm: bad arguments"); return -1; }
-  auto key = std::make_tuple(M, N, K, a_sm, a_sk, b_sk, b_sn, c_sm, relu, operands_bf16, bias ? 1 : 0);
+  auto key = std::make_tuple(M, N, K, a_sm, a_sk, b_sk, b_sn, c_sm, relu + 16 * flags, operands_bf16, bias ? 1 : 0);
   PbGemmProgram *p = nullptr;
   auto it = g_direct.find(key);
   if (it != g_direct.end()) p = it->second;
@@ -703,11 +724,14 @@ extern "C" int poly_b200_gemm(long long M, long long N, long long K,
     p->a_direct = (a_sk == 1 || a_sm == 1) && a_sk > 0 && a_sm >= 0;
     p->b_direct = (b_sk == 1 || b_sn == 1) && b_sk > 0 && b_sn >= 0;
     p->rw = "Wrrr";
+    p->c_bf16 = (flags & POLY_B200_GEMM_C_BF16) != 0;
+    p->gelu = (flags & POLY_B200_GEMM_GELU) != 0;
+    if (p->c_bf16 && !pb_gemm_tc_static_ok(*p)) { delete p; pb_set_error("poly_b200_gemm_ex: a bfloat16 result needs N, c_sm multiples of 4 and K >= 16"); return -1; }
     g_direct[key] = p;
   }
   void *bufs[4] = {C, const_cast<void *>(A), const_cast<void *>(B), const_cast<float *>(bias)};
   if (pb_note_read(A) != 0 || pb_note_read(B) != 0 || pb_note_read(bias) != 0 ||
-      pb_note_write(C, c_sm == N ? (size_t)(M * N) * 4 : 0) != 0) return -1;
+      pb_note_write(C, c_sm == N ? (size_t)(M * N) * (p->c_bf16 ? 2 : 4) : 0) != 0) return -1;
   int rc = p->launch(bufs, (cudaStream_t)poly_b200_stream());
   if (rc == 0) pb_count_launch(true, p->n_launches());
   return rc;

@@ -36,6 +36,7 @@ struct PbGemmProgram : PbAotProgram {
   float alpha = 1.0f;                 /* C = X + alpha * sum (relu); 1 except for fused optimizer updates */
   bool a_bf16 = false;                /* A's buffer holds bfloat16 (same element layout) although dtype is f32 */
   bool c_bf16 = false;                /* C is written as bfloat16 (round to nearest even) into the same element layout */
+  bool gelu = false;                  /* tanh-GELU applied after the addend, before the bfloat16 store (needs c_bf16) */
   std::vector<PbGemmAxis> m_ax, n_ax, k_ax, b_ax;   /* m, n by output stride (largest first); k by A stride */
   long long M = 1, N = 1, K = 1, nbatch = 1;
   bool a_direct = false, b_direct = false;          /* strides nest: usable without packing */

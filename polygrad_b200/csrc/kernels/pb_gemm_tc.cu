@@ -61,6 +61,7 @@ struct TcArgs {
   int ab_fmt;                      /* operand format: 0 float16, 1 bfloat16 (64 per 128-byte tile row), 2 tf32 (32 per row) */
   int vec_io;                      /* C rows (and addend rows) 16-byte aligned, N % 4 == 0 */
   int c_bf16;                      /* C holds bfloat16 (needs vec_io) */
+  int gelu;                        /* tanh-GELU after the addend (bfloat16 results only) */
   int tiles_m, tiles_n, n_tiles;   /* n_tiles = nbatch * tiles_m * tiles_n */
   int m_fast;                      /* consecutive tiles differ in the row tile (else in the column tile) */
   int kchunk;                      /* PROMOTE kernels: k-blocks summed in tensor memory before the partial sum moves to registers */
@@ -68,6 +69,16 @@ struct TcArgs {
 
 #define PB_TC_ERROR_FLAG pb200_tc_error_flag
 #include "pb_tc_ptx.cuh"
+
+/* 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) with the hardware tanh approximation (relative
+ * error about 2^-11); only used where the value is rounded to bfloat16 (2^-9) right afterwards. */
+__device__ __forceinline__ float gelu_tanh_approx(float x) {
+  const float u = x * fmaf(0.0356774081f, x * x, 0.7978845608f);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  const float h = 0.5f * x;
+  return fmaf(h, t, h);
+}
 
 /* Tile t of a batch entry -> (row tile, column tile).  Consecutive tiles run at the
  * same time on different SMs; they walk along the axis of the SMALLER operand, so
@@ -328,6 +339,7 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                   else { v.x += xb.x; v.y += xb.y; v.z += xb.z; v.w += xb.w; }
                   if (g.relu) { v.x = (0.f < v.x) ? v.x : 0.f; v.y = (0.f < v.y) ? v.y : 0.f; v.z = (0.f < v.z) ? v.z : 0.f; v.w = (0.f < v.w) ? v.w : 0.f; }
                   if (g.c_bf16) {
+                    if (g.gelu) { v.x = gelu_tanh_approx(v.x); v.y = gelu_tanh_approx(v.y); v.z = gelu_tanh_approx(v.z); v.w = gelu_tanh_approx(v.w); }
                     /* same element offset, 2-byte elements */
                     const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
                     uint2 w; w.x = *reinterpret_cast<const uint32_t *>(&lo); w.y = *reinterpret_cast<const uint32_t *>(&hi);
@@ -718,6 +730,7 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, int
     }
     g.vec_io = v ? 1 : 0;
     g.c_bf16 = p.c_bf16 ? 1 : 0;
+    g.gelu = p.gelu ? 1 : 0;
     if (p.c_bf16) {
       /* the kernel only forms element offsets from this base; elements are 2 bytes */
       g.C = reinterpret_cast<float *>(reinterpret_cast<__nv_bfloat16 *>(bufs[p.p_c]) + p.off_c);

@@ -77,6 +77,13 @@ struct Runtime {
    * captured work, so they stay out of the free list until the graph is destroyed */
   std::vector<std::pair<size_t, void *>> capture_hold;
   uint64_t pool_epoch = 1;       /* bumps when cached blocks go back to the driver */
+  /* deferred readbacks: device-to-host copies that run on a second stream behind later work */
+  bool defer = false;
+  cudaStream_t copy_stream = nullptr;
+  void *defer_stage[2] = {nullptr, nullptr}; size_t defer_bytes[2] = {0, 0};
+  cudaEvent_t defer_ready[2] = {nullptr, nullptr}, defer_done[2] = {nullptr, nullptr};
+  bool defer_used[2] = {false, false};
+  int defer_next = 0;
   PolyB200Stats st{};
 };
 static Runtime R;
@@ -436,15 +443,83 @@ extern "C" void poly_b200_host_free(void *p) {
   if (R.dry) free(p); else cudaFreeHost(p);
 }
 
+/* ── deferred readbacks ──────────────────────────────────────────────────
+ * polygrad reads results back synchronously (poly_instance_readback_buf ->
+ * poly_cuda_copy_dtoh, reference src/instance.c:479-501), so a caller that wants the
+ * full logits on the host pays compute + PCIe per step.  While deferral is on, a
+ * copy_dtoh whose destination is page-locked host memory returns at once: the source
+ * is snapshotted into one of two device staging buffers on the main stream (a
+ * device-to-device copy, about 0.5 ms for 1.65 GB) and copied to the host from there
+ * on a second stream, so the next steps run while the bytes cross PCIe.  The data is
+ * in place after poly_b200_readback_wait(). */
+static int defer_dtoh(void *dst, const void *src, size_t bytes) {
+  if (!R.copy_stream) {
+    PB_CUDA(cudaStreamCreateWithFlags(&R.copy_stream, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; i++) {
+      PB_CUDA(cudaEventCreateWithFlags(&R.defer_ready[i], cudaEventDisableTiming));
+      PB_CUDA(cudaEventCreateWithFlags(&R.defer_done[i], cudaEventDisableTiming));
+    }
+  }
+  const int k = R.defer_next;
+  R.defer_next ^= 1;
+  if (R.defer_bytes[k] < bytes) {
+    if (R.defer_stage[k]) {
+      if (R.defer_used[k]) PB_CUDA(cudaEventSynchronize(R.defer_done[k]));
+      pool_free(R.defer_stage[k]);
+    }
+    R.defer_stage[k] = pool_alloc(bytes);
+    R.defer_bytes[k] = R.defer_stage[k] ? bytes : 0;
+    if (!R.defer_stage[k]) return -1;
+  }
+  /* the staging buffer is free again when the copy that last read it has finished */
+  if (R.defer_used[k]) PB_CUDA(cudaStreamWaitEvent(R.stream, R.defer_done[k], 0));
+  PB_CUDA(cudaMemcpyAsync(R.defer_stage[k], src, bytes, cudaMemcpyDeviceToDevice, R.stream));
+  PB_CUDA(cudaEventRecord(R.defer_ready[k], R.stream));
+  PB_CUDA(cudaStreamWaitEvent(R.copy_stream, R.defer_ready[k], 0));
+  PB_CUDA(cudaMemcpyAsync(dst, R.defer_stage[k], bytes, cudaMemcpyDeviceToHost, R.copy_stream));
+  PB_CUDA(cudaEventRecord(R.defer_done[k], R.copy_stream));
+  R.defer_used[k] = true;
+  return 0;
+}
+
+extern "C" int poly_b200_readback_defer(int on) {
+  if (!ready()) return -1;
+  R.defer = on != 0 && !R.dry;
+  return 0;
+}
+
+extern "C" int poly_b200_readback_wait(void) {
+  if (!ready()) return -1;
+  if (R.dry || !R.copy_stream) return 0;
+  PB_CUDA(cudaStreamSynchronize(R.copy_stream));
+  return check_device_flags();
+}
+
 extern "C" int poly_cuda_copy_dtoh(void *dst, unsigned long long src, size_t bytes) {
   if (!ready()) return -1;
   void *p = (void *)(uintptr_t)src;
   g_last_dtoh_src = src;
   if (note_access(p, 'r') != 0) return -1;
   if (R.dry) { memcpy(dst, p, bytes); return 0; }
+  if (R.defer && !R.capturing && bytes >= ((size_t)1 << 20)) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, dst) == cudaSuccess && attr.type == cudaMemoryTypeHost) return defer_dtoh(dst, p, bytes);
+    cudaGetLastError();
+  }
   PB_CUDA(cudaMemcpyAsync(dst, p, bytes, cudaMemcpyDeviceToHost, R.stream));
   PB_CUDA(cudaStreamSynchronize(R.stream));
   return check_device_flags();
+}
+
+/* `rows` rows of row_bytes each, src_pitch apart in a device buffer, into a dense device buffer
+ * (the last position's logits of every sequence, for example).  Stream-ordered. */
+extern "C" int poly_b200_copy_rows(unsigned long long dst, unsigned long long src, size_t row_bytes, size_t src_pitch, size_t rows) {
+  if (!ready()) return -1;
+  void *d = (void *)(uintptr_t)dst; const void *s = (const void *)(uintptr_t)src;
+  if (note_access(s, 'r') != 0 || note_access(d, 'w') != 0) return -1;
+  if (R.dry) { for (size_t r = 0; r < rows; r++) memcpy((char *)d + r * row_bytes, (const char *)s + r * src_pitch, row_bytes); return 0; }
+  PB_CUDA(cudaMemcpy2DAsync(d, row_bytes, s, src_pitch, row_bytes, rows, cudaMemcpyDeviceToDevice, R.stream));
+  return 0;
 }
 
 /* ── events ──────────────────────────────────────────────────────────── */

@@ -157,6 +157,8 @@ def _declare_cuda(lib):
     LL = ctypes.c_longlong
     _sig(lib, 'poly_b200_gemm', ctypes.c_int, [LL, LL, LL, _ptr, LL, LL, _ptr, LL, LL, _ptr, LL, _ptr,
                                                ctypes.c_int, ctypes.c_int])
+    _sig(lib, 'poly_b200_gemm_ex', ctypes.c_int, [LL, LL, LL, _ptr, LL, LL, _ptr, LL, LL, _ptr, LL, _ptr,
+                                                  ctypes.c_int, ctypes.c_int])
     _sig(lib, 'poly_b200_gemm_noalloc', ctypes.c_int, [LL, LL, LL, _ptr, LL, LL, _ptr, LL, LL, _ptr, LL, _ptr, ctypes.c_int])
     _sig(lib, 'poly_b200_selftest_bounded_wait', ctypes.c_int, [])
     _sig(lib, 'poly_b200_instance_import_weights', ctypes.c_int,
@@ -167,6 +169,23 @@ def _declare_cuda(lib):
     _sig(lib, 'poly_b200_host_alloc', _ptr, [S])
     _sig(lib, 'poly_b200_host_free', None, [_ptr])
     _sig(lib, 'poly_b200_last_dtoh_src', U, [])
+    _sig(lib, 'poly_b200_copy_rows', ctypes.c_int, [U, U, S, S, S])
+    _sig(lib, 'poly_b200_readback_defer', ctypes.c_int, [ctypes.c_int])
+    _sig(lib, 'poly_b200_comm_unique_id', ctypes.c_int, [_ptr, S])
+    _sig(lib, 'poly_b200_comm_init', ctypes.c_int, [ctypes.c_int, ctypes.c_int, _ptr, S])
+    _sig(lib, 'poly_b200_comm_rank', ctypes.c_int, [])
+    _sig(lib, 'poly_b200_comm_world', ctypes.c_int, [])
+    _sig(lib, 'poly_b200_gather_offset', S, [ctypes.c_int, S])
+    _sig(lib, 'poly_b200_gather_async', ctypes.c_int, [_ptr, S, _ptr, ctypes.c_int])
+    _sig(lib, 'poly_b200_comm_join', ctypes.c_int, [])
+    _sig(lib, 'poly_b200_comm_wait', ctypes.c_int, [])
+    _sig(lib, 'poly_b200_comm_max', ctypes.c_int, [ctypes.POINTER(ctypes.c_double)])
+    _sig(lib, 'poly_b200_comm_destroy', None, [])
+    _sig(lib, 'poly_b200_shard_micro_index', ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int])
+    _sig(lib, 'poly_b200_forward_microbatches', ctypes.c_int,
+         [_ptr, ctypes.c_char_p, ctypes.POINTER(ctypes.POINTER(ctypes.c_float)), ctypes.c_int, ctypes.c_int, S, _ptr,
+          ctypes.c_int, ctypes.c_int])
+    _sig(lib, 'poly_b200_readback_wait', ctypes.c_int, [])
     _sig(lib, 'poly_b200_event_create', _ptr, [])
     _sig(lib, 'poly_b200_event_record', ctypes.c_int, [_ptr])
     _sig(lib, 'poly_b200_event_elapsed_ms', ctypes.c_float, [_ptr, _ptr])

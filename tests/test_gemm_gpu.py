@@ -291,3 +291,41 @@ def test_fp32_tensor_core_route_keeps_infinities(devices, policy, monkeypatch):
     assert np.array_equal(np.sign(got[np.isinf(want)]), np.sign(want[np.isinf(want)]))
     fin = np.isfinite(want)
     assert_close(got[fin], want[fin], 1e-4, 'finite rows')
+
+
+def _bf16_round(a):
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32)
+
+
+@pytest.mark.parametrize('m,n,k', [(256, 512, 128), (300, 3072, 768), (129, 68, 40)])
+@pytest.mark.parametrize('flags', [1, 3], ids=['bf16_result', 'gelu_bf16_result'])
+def test_gemm_ex_result_formats(gpu, m, n, k, flags):
+    """poly_b200_gemm_ex: the contraction's result (+ bias) stored as bfloat16, optionally through
+    tanh-GELU first, against numpy in float64 on the same bfloat16-rounded operands.  Bound: the
+    bfloat16 rounding of the result (2^-9 relative) plus the tanh approximation (2^-11): 4e-3."""
+    from polygrad_b200.tensor import f32_to_bf16_bits
+    rng = np.random.default_rng([m, n, k, flags])
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = (rng.uniform(-1, 1, (k, n)) * (2.0 / np.sqrt(k))).astype(np.float32)
+    bias = rng.uniform(-0.5, 0.5, n).astype(np.float32)
+    a16, b16 = f32_to_bf16_bits(a), f32_to_bf16_bits(b)
+    want = _bf16_round(a).astype(np.float64) @ _bf16_round(b).astype(np.float64) + bias
+    if flags & 2:
+        want = 0.5 * want * (1 + np.tanh(0.7978845608028654 * (want + 0.044715 * want ** 3)))
+    bufs = []
+    for arr in (a16, b16, bias):
+        d = gpu.poly_cuda_alloc(arr.nbytes)
+        assert d and gpu.poly_cuda_copy_htod(d, arr.ctypes.data, arr.nbytes) == 0
+        bufs.append(d)
+    dc = gpu.poly_cuda_alloc(m * n * 2)
+    rc = gpu.poly_b200_gemm_ex(m, n, k, bufs[0], k, 1, bufs[1], n, 1, dc, n, bufs[2], 1, flags)
+    assert rc == 0, gpu.last_error()
+    got16 = np.empty((m, n), np.uint16)
+    assert gpu.poly_cuda_copy_dtoh(got16.ctypes.data, dc, got16.nbytes) == 0
+    for d in bufs + [dc]:
+        gpu.poly_cuda_free(d)
+    got = (got16.astype(np.uint32) << 16).view(np.float32)
+    assert np.abs(got).max() > 0
+    assert_close(got, want.astype(np.float32), 4e-3, f'gemm_ex flags={flags} {m}x{n}x{k}')

@@ -127,10 +127,23 @@ def test_bf16_policy_plan_passes_in_dry_run():
     assert int(m.group(2)) == 4 * n_layer + 1             # LN1->qkv, qkv->attention, LN2->fc, GELU->proj; final LN->logits
     assert int(m.group(3)) == n_layer
     assert int(m.group(4)) == n_layer - 1                 # the mask is classified once
+    m = re.search(r'(\d+) GELU kernels moved into contraction epilogues', r.stderr)
+    assert m and int(m.group(1)) == n_layer               # recognised by evaluating the kernel's scalar function
     m = re.search(r'pb_plan: (\d+) steps', r.stderr)
-    # per layer: LN1 (with the residual add before it), qkv, attention, c_proj, LN2 (with its add), fc, GELU, proj;
+    # per layer: LN1 (with the residual add before it), qkv, attention, c_proj, LN2 (with its add), fc (with GELU), proj;
     # around them: two gathers, the mask generator, final LN (with the last add), logits
-    assert m and int(m.group(1)) == 5 + 8 * n_layer
+    assert m and int(m.group(1)) == 5 + 7 * n_layer
+
+
+def test_gelu_epilogue_can_be_switched_off():
+    env = dict(os.environ, POLY_B200_DRYRUN='1', POLY_B200_DEBUG='1', POLY_B200_CACHE='0', POLY_B200_GEMM='bf16',
+               POLY_B200_EPILOGUE='0')
+    r = subprocess.run([sys.executable, '-c', DRY_BF16 % dict(root=ROOT)], env=env, capture_output=True, text=True,
+                       timeout=900)
+    assert r.returncode == 0, r.stderr[-4000:]
+    assert re.search(r' 0 GELU kernels moved into contraction epilogues', r.stderr)
+    m = re.search(r'pb_plan: (\d+) steps', r.stderr)
+    assert m and int(m.group(1)) == 5 + 8 * 2
 
 
 DRY_TRAIN = '''

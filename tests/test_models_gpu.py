@@ -96,9 +96,11 @@ def test_plan_passes_change_no_bit_under_bf16_policy(gpu, monkeypatch):
     """The operand passes (slice copies folded into strides, operands produced as bfloat16 by the
     step before, attention output relaid, shared mask classification, key-block skipping) only move
     where a rounding happens or skip work that is exactly zero: the logits must be bit for bit those
-    of the same plan without them."""
+    of the same plan without them.  (The GELU epilogue is the one pass that changes arithmetic -- it
+    uses the hardware tanh approximation -- and is left out here; the next test bounds it.)"""
     cfg = dict(vocab_size=307, n_embd=128, n_head=2, n_layer=2, max_seq_len=256, max_batch=2)
     tokens = np.random.default_rng(21).integers(0, cfg['vocab_size'], (2, 256))
+    monkeypatch.setenv('POLY_B200_EPILOGUE', '0')
     gpu.poly_b200_set_gemm_policy(1)
     try:
         monkeypatch.delenv('POLY_B200_OPERANDS', raising=False)
@@ -111,6 +113,28 @@ def test_plan_passes_change_no_bit_under_bf16_policy(gpu, monkeypatch):
         gpu.poly_b200_set_gemm_policy(0)
     assert np.isfinite(with_passes).all()
     assert np.array_equal(with_passes.view(np.uint32), without.view(np.uint32))
+
+
+def test_gelu_epilogue_stays_within_the_bf16_rounding(gpu, monkeypatch):
+    """GELU moved into the fc contraction's epilogue (hardware tanh approximation, then the bfloat16
+    rounding the separate kernel also ends with) against the plan that keeps the separate kernel:
+    logits within 5e-3 relative, far inside the 2e-2 bound of the bf16 policy."""
+    cfg = dict(vocab_size=307, n_embd=128, n_head=2, n_layer=2, max_seq_len=256, max_batch=2)
+    tokens = np.random.default_rng(22).integers(0, cfg['vocab_size'], (2, 256))
+    gpu.poly_b200_set_gemm_policy(1)
+    try:
+        monkeypatch.delenv('POLY_B200_EPILOGUE', raising=False)
+        gpu.poly_b200_stats_reset()
+        fused = _run_gpt2(gpu, ffi.DEVICE_CUDA, cfg, tokens)
+        n_fused = gpu.stats()['launches']
+        monkeypatch.setenv('POLY_B200_EPILOGUE', '0')
+        gpu.poly_b200_stats_reset()
+        separate = _run_gpt2(gpu, ffi.DEVICE_CUDA, cfg, tokens)
+        n_separate = gpu.stats()['launches']
+    finally:
+        gpu.poly_b200_set_gemm_policy(0)
+    assert n_fused == n_separate - cfg['n_layer']          # one launch less per layer
+    assert_close(fused, separate, 5e-3, 'GELU in the epilogue vs the separate kernel')
 
 
 def test_gpt2_124m_full_width_properties(gpu):

@@ -52,3 +52,20 @@ def test_two_gloo_ranks_equal_one_global_forward(tmp_path):
     assert r['max_abs_diff'] == 0.0            # rows are independent: sharding changes nothing
     assert r['slowest'] == 11.0
     assert r['spans'] == [[0, 4], [4, 7]]
+
+
+def test_two_ranks_drive_the_micro_batch_loop(tmp_path):
+    """poly_b200_forward_microbatches on two ranks in dry-run mode: micro-batch i of rank r is number
+    i * world + r of the global batch and lands in that slot of the root's buffer; each micro-batch's
+    token ids are uploaded before its forward."""
+    out = tmp_path / 'micro.json'
+    cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node', '2',
+           '--master-addr', '127.0.0.1', '--master-port', str(free_port()),
+           os.path.join(HERE, 'gloo_micro_worker.py'), str(out)]
+    env = dict(os.environ, OMP_NUM_THREADS='1')
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    r = json.load(open(out))
+    assert r['world'] == 2 and r['uniform']
+    assert r['order'] == [0, 1, 0, 1, 0, 1]          # slot i * world + r holds rank r's micro-batch i
+    assert r['x_last'] == r['x_want']
