@@ -35,9 +35,9 @@
  *            S = Q Kᵀ (128x128x64) into tensor memory, then PV = P V
  *            (128x64x128) into another 64 columns;
  *   warps 0-7  two threads per query row (64 keys and 32 output columns each):
- *            read S from tensor memory in 32-column chunks (pass 1: x = s*scale
- *            + mask written back to tensor memory, row max exchanged through
- *            shared memory; pass 2: exponentials), write P as bf16 into shared
+ *            read S from tensor memory in 32-column chunks (pass 1: the row max of
+ *            x = s*scale + mask, exchanged through shared memory; pass 2: the
+ *            scores again, x and the exponentials), write P as bf16 into shared
  *            memory in the swizzled K-major tile layout the MMA reads, then add
  *            PV to the row's fp32 accumulators in registers.
  * Head size 64, T a multiple of 128.  All barrier waits are bounded.
@@ -222,42 +222,39 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const bool tile_is_const = (tile_c == tile_c);
       if (!__all_sync(0xffffffffu, mbar_wait(bar_s, ph, &abort_flag, 17))) { ok = false; break; }
       tc_fence_after_sync();
-      /* pass 1: x = s*scale + mask, written back over S in tensor memory; max over this thread's keys */
+      /* pass 1: the largest x = s*scale + mask over this thread's keys.  Nothing is written back: pass 2
+       * loads the scores again and forms the same x (one fused multiply-add per element, against a
+       * tensor-memory store and the wait for it).  Where the mask tile is one value c and the scale is
+       * not negative, x is a non-decreasing function of s, so the largest x is that of the largest s. */
       float m_part = __int_as_float(0xff800000);
+      const bool plain_max = tile_is_const && g.scale >= 0.0f;
 #pragma unroll 1
       for (int c = 0; c < 2; c++) {
         uint32_t r[32];
         tc_ld32(s_cols + c * 32, r);
         tc_wait_ld();
-        if (tile_is_const) {
-          /* the whole 128 x 128 mask tile holds one value: no loads */
+        if (plain_max) {
 #pragma unroll
-          for (int i = 0; i < 32; i++) {
-            const float x = __uint_as_float(r[i]) * g.scale + tile_c;
-            r[i] = __float_as_uint(x);
-            m_part = fmaxf(m_part, x);
-          }
+          for (int i = 0; i < 32; i++) m_part = fmaxf(m_part, __uint_as_float(r[i]));
+        } else if (tile_is_const) {
+#pragma unroll
+          for (int i = 0; i < 32; i++) m_part = fmaxf(m_part, fmaf(__uint_as_float(r[i]), g.scale, tile_c));
         } else if (g.mask_vec) {
 #pragma unroll
           for (int i = 0; i < 8; i++) {
             const float4 mv = reinterpret_cast<const float4 *>(mj + c * 32)[i];
-            const float x0 = __uint_as_float(r[4 * i]) * g.scale + mv.x, x1 = __uint_as_float(r[4 * i + 1]) * g.scale + mv.y;
-            const float x2 = __uint_as_float(r[4 * i + 2]) * g.scale + mv.z, x3 = __uint_as_float(r[4 * i + 3]) * g.scale + mv.w;
-            r[4 * i] = __float_as_uint(x0); r[4 * i + 1] = __float_as_uint(x1); r[4 * i + 2] = __float_as_uint(x2); r[4 * i + 3] = __float_as_uint(x3);
+            const float x0 = fmaf(__uint_as_float(r[4 * i]), g.scale, mv.x), x1 = fmaf(__uint_as_float(r[4 * i + 1]), g.scale, mv.y);
+            const float x2 = fmaf(__uint_as_float(r[4 * i + 2]), g.scale, mv.z), x3 = fmaf(__uint_as_float(r[4 * i + 3]), g.scale, mv.w);
             m_part = fmaxf(m_part, fmaxf(fmaxf(x0, x1), fmaxf(x2, x3)));
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; i++) {
-            const float x = __uint_as_float(r[i]) * g.scale + mj[(long long)(c * 32 + i) * g.mask_sk];
-            r[i] = __float_as_uint(x);
-            m_part = fmaxf(m_part, x);
-          }
+          for (int i = 0; i < 32; i++)
+            m_part = fmaxf(m_part, fmaf(__uint_as_float(r[i]), g.scale, mj[(long long)(c * 32 + i) * g.mask_sk]));
         }
-        tc_st32(s_cols + c * 32, r);
       }
+      if (plain_max) m_part = fmaf(m_part, g.scale, tile_c);
       xchg[half][row] = m_part;
-      tc_wait_st();
       /* exchange through an mbarrier rather than bar.sync: its wait is bounded like all others.
        * One arrival per warp (256 arrivals on one shared-memory word serialise). */
       __syncwarp();
@@ -275,13 +272,32 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         uint32_t r[32];
         tc_ld32(s_cols + c * 32, r);
         tc_wait_ld();
+        if (!tile_is_const) {
+          /* x in place of s (the mask values come from L1 this time) */
+          if (g.mask_vec) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+              const float4 mv = reinterpret_cast<const float4 *>(mj + c * 32)[i];
+              r[4 * i] = __float_as_uint(fmaf(__uint_as_float(r[4 * i]), g.scale, mv.x));
+              r[4 * i + 1] = __float_as_uint(fmaf(__uint_as_float(r[4 * i + 1]), g.scale, mv.y));
+              r[4 * i + 2] = __float_as_uint(fmaf(__uint_as_float(r[4 * i + 2]), g.scale, mv.z));
+              r[4 * i + 3] = __float_as_uint(fmaf(__uint_as_float(r[4 * i + 3]), g.scale, mv.w));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+              r[i] = __float_as_uint(fmaf(__uint_as_float(r[i]), g.scale, mj[(long long)(c * 32 + i) * g.mask_sk]));
+          }
+        }
 #pragma unroll
         for (int i8 = 0; i8 < 4; i8++) {
           uint32_t w[4];
 #pragma unroll
           for (int i2 = 0; i2 < 4; i2++) {
             const int i = i8 * 8 + i2 * 2;
-            const float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), LOG2E, -m_scaled)), p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), LOG2E, -m_scaled));
+            float x0 = __uint_as_float(r[i]), x1 = __uint_as_float(r[i + 1]);
+            if (tile_is_const) { x0 = fmaf(x0, g.scale, tile_c); x1 = fmaf(x1, g.scale, tile_c); }
+            const float p0 = fast_exp2(fmaf(x0, LOG2E, -m_scaled)), p1 = fast_exp2(fmaf(x1, LOG2E, -m_scaled));
             __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
             l_blk += p0 + p1;
             w[i2] = *reinterpret_cast<uint32_t *>(&pb);
@@ -292,8 +308,12 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
       l_run = l_run * alpha + l_blk;
       m_run = m_new;
+      /* the running maximum moves in the first blocks of a row and seldom afterwards: where no row of
+       * the warp moved, alpha is exactly 1 and the rescale is skipped (same bits either way) */
+      if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
-      for (int d = 0; d < 32; d++) acc[d] *= alpha;
+        for (int d = 0; d < 32; d++) acc[d] *= alpha;
+      }
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
@@ -563,6 +583,7 @@ int pb_attention_launch(const PbAttnOperand &q, const PbAttnOperand &k, const Pb
   if (!tiles_mode) pb_scratch_free(tiles);   /* stream-ordered pool: safe to hand back once the work is enqueued */
   pb_scratch_free(norms);
   pb_tc_mark_used();
+  pb_tc_configure_backoff();
   pb200_flash_attn<<<(unsigned)grid, AT_THREADS, AT_SMEM, stream>>>(mq, mk, mv, g);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { pb_set_error("attention launch: %s", cudaGetErrorString(e)); return -1; }

@@ -781,6 +781,7 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, int
   if (rc == 0) rc = make_map(&mb, vb.ptr, g.K, rowsB, p.nbatch, vb.pitch, vb.bpitch, BN / ctas, g.ab_fmt);
   if (rc != 0) { pb_scratch_free(scr_a); pb_scratch_free(scr_b); return -1; }
   pb_tc_mark_used();
+  pb_tc_configure_backoff();
   if (promote) {
     /* eight 128-byte k-blocks (32 instructions, 256 elements of the tripled k axis) per partial sum:
      * measured on GPT-2 124M fp32, 2 blocks cost 58.9 ms per step, 4: 45.2, 8: 43.7, 16: 43.1 (no
@@ -835,6 +836,7 @@ int pb_gemm_tc_launch_raw(const void *a_bf16, long long a_pitch, const void *b_b
   if (make_map(&ma, a_bf16, K, M, 1, a_pitch, M * a_pitch, TC_BM) != 0) return -1;
   if (make_map(&mb, b_bf16, K, N, 1, b_pitch, N * b_pitch, BN) != 0) return -1;
   pb_tc_mark_used();
+  pb_tc_configure_backoff();
   if (BN == 256) return tc_launch<256, 1>(ma, mb, g, 1, stream);
   if (BN == 128) return tc_launch<128, 1>(ma, mb, g, 1, stream);
   return tc_launch<64, 1>(ma, mb, g, 1, stream);

@@ -9,8 +9,16 @@
 #define PB_TC_PTX_CUH
 #include <cuda.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define TC_SPIN_LIMIT (1u << 25)
+
+/* Polls of a barrier before the waiting thread starts to sleep between polls.
+ * mbarrier.try_wait itself suspends the thread for a short, hardware-chosen time, so
+ * polling is cheap; __nanosleep frees issue slots but wakes late, which delays whatever
+ * the waiter does next (the next TMA load, the next MMA).  Set from the host
+ * (POLY_B200_TC_BACKOFF, polls; 0 = sleep from the ninth poll on). */
+__constant__ unsigned pb_tc_backoff_after = 1u << 14;
 
 /* ── PTX wrappers ────────────────────────────────────────────────────── */
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -39,7 +47,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                                           uint32_t limit = TC_SPIN_LIMIT) {
   for (uint32_t i = 0; i < limit; i++) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (i > 8) __nanosleep(32);          /* leave the issue slots to the working warps */
+    if (i > 8 && i >= pb_tc_backoff_after) __nanosleep(32);   /* a long wait: leave the issue slots to the working warps */
     if ((i & 255u) == 255u && *abort_flag) return false;
   }
   *abort_flag = 1;
@@ -161,6 +169,17 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   return d;
 }
 
+
+/* Host side: the including file's copy of the back-off threshold, set once from the environment. */
+static inline void pb_tc_configure_backoff(void) {
+  static bool done = false;
+  if (done) return;
+  done = true;
+  const char *e = getenv("POLY_B200_TC_BACKOFF");
+  if (!e || !e[0]) return;
+  const unsigned v = (unsigned)strtoul(e, nullptr, 10);
+  cudaMemcpyToSymbol(pb_tc_backoff_after, &v, sizeof v);
+}
 
 /* makes generic-proxy shared-memory writes visible to the async proxy (TMA, tcgen05.mma operands) */
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
