@@ -371,6 +371,299 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   }
 }
 
+/* ── second arrangement of the same computation ──────────────────────────
+ * The output accumulator stays in tensor memory: PV = P V is added there by the tensor
+ * cores block after block (accumulate flag), so the softmax threads neither read PV back
+ * nor carry 32 accumulators each; that leaves registers for a whole block of scores (64
+ * per thread), which are loaded ONCE, reduced to the row maximum, and turned into
+ * probabilities from registers.  As soon as every thread holds its scores the S region is
+ * free, so the next block's S = Q K' runs under this block's exponentials.  When a row's
+ * running maximum moves (the first blocks of a row; seldom afterwards) its part of the
+ * accumulator is rescaled in tensor memory (load, multiply, store) between two PV products.
+ * V is double-buffered so that the next block's V is requested one product ahead.
+ * Arithmetic per element is that of pb200_flash_attn (x = fma(s, scale, mask), p =
+ * exp2(fma(x, log2e, -m log2e)), bf16 P, fp32 sums); the block sums of P V are added by the
+ * tensor cores instead of with rounded fp32 adds. */
+#define AT2_SMEM (16384 /*Q*/ + 16384 /*K*/ + 32768 /*V: 2 x 16 KB*/ + 32768 /*P: 2 x 16 KB*/ + 256 + 1024)
+
+__global__ void __launch_bounds__(AT_THREADS, 2)
+pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_v, const AttnArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *sm = smem_raw + (base - raw);
+  const uint32_t s_q = base, s_k = base + 16384, s_v = base + 32768, s_p = base + 65536;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 98304);
+  const uint32_t bar_q = smem_u32(bars), bar_k = bar_q + 8, bar_v = bar_q + 16 /* two */, bar_s = bar_q + 32, bar_p = bar_q + 40,
+                 bar_o = bar_q + 48, bar_x = bar_q + 56, bar_f = bar_q + 64;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ float xchg[2][AT_BQ];
+  __shared__ unsigned long long s_live;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_bh = gridDim.x / g.n_qblocks;
+  const int qb = g.n_qblocks - 1 - (int)(blockIdx.x / n_bh), bh = blockIdx.x % n_bh;
+  const int nkb = g.T / AT_BK;
+
+  if (threadIdx.x == 0) {
+    unsigned long long live = 0;
+    float lrun = __int_as_float(0xff800000);
+    for (int j = 0; j < nkb; j++) {
+      const float c = g.tile_const[2 * (qb * nkb + j)], lmin = g.tile_const[2 * (qb * nkb + j) + 1];
+      float S = 0.0f;
+      bool skip = false;
+      if (g.qn) {
+        S = fabsf(g.scale) * g.qn[bh * g.n_qblocks + qb] * g.kn[bh * nkb + j];
+        skip = (c == c) && (c + S < lrun - 100.0f);
+      }
+      if (!skip) { live |= 1ull << j; lrun = fmaxf(lrun, lmin - S); }
+    }
+    s_live = live;
+    abort_flag = 0;
+    mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1); mbar_init(bar_v + 8, 1);
+    mbar_init(bar_s, 1); mbar_init(bar_p, 8); mbar_init(bar_o, 1); mbar_init(bar_x, 8); mbar_init(bar_f, 8);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 8) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tmem_s = tmem, tmem_pv = tmem + 128;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BK >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(AT_HD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      int c0 = 0, c1 = 0, c2 = 0;
+      {
+        int rem = bh;
+        if (g.nb > 0) { c0 = rem % g.bext[0]; rem /= g.bext[0]; }
+        if (g.nb > 1) { c1 = rem % g.bext[1]; rem /= g.bext[1]; }
+        if (g.nb > 2) { c2 = rem % g.bext[2]; }
+      }
+      mbar_expect_tx(bar_q, 16384);
+      tma_load_5d(s_q, &map_q, bar_q, 0, qb * AT_BQ, c0, c1, c2);
+      unsigned long long rem = s_live;
+      const int j0 = __ffsll((long long)rem) - 1;          /* the first block is always processed */
+      mbar_expect_tx(bar_k, 16384);
+      tma_load_5d(s_k, &map_k, bar_k, 0, j0 * AT_BK, c0, c1, c2);
+      mbar_expect_tx(bar_v, 16384);
+      tma_load_5d(s_v, &map_v, bar_v, 0, j0 * AT_BK, c0, c1, c2);
+      bool ok = mbar_wait(bar_q, 0, &abort_flag, 11) && mbar_wait(bar_k, 0, &abort_flag, 12);
+      const uint64_t dq = make_smem_desc(s_q), dk = make_smem_desc(s_k);
+      if (ok) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < AT_HD / 16; k++) tc_mma_bf16(tmem_s, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, k ? 1u : 0u);
+        tc_commit(bar_s);
+      }
+      for (uint32_t it = 0; rem && ok; it++) {
+        rem &= rem - 1;
+        const bool more = rem != 0;
+        const int jn = more ? __ffsll((long long)rem) - 1 : 0;
+        const uint32_t ph = it & 1u;
+        /* S(it) complete: K is free, request the next block of keys */
+        if (!mbar_wait(bar_s, ph, &abort_flag, 13)) break;
+        if (more) { mbar_expect_tx(bar_k, 16384); tma_load_5d(s_k, &map_k, bar_k, 0, jn * AT_BK, c0, c1, c2); }
+        /* V buffer (it+1)&1 was last read by PV(it-1): request the next block of values once that product is done */
+        if (more) {
+          if (it > 0 && !mbar_wait(bar_o, (it - 1) & 1u, &abort_flag, 16)) break;
+          const uint32_t vb = (it + 1) & 1u;
+          mbar_expect_tx(bar_v + 8 * vb, 16384);
+          tma_load_5d(s_v + vb * 16384, &map_v, bar_v + 8 * vb, 0, jn * AT_BK, c0, c1, c2);
+        }
+        /* every softmax thread holds its scores of block it: S may be overwritten */
+        if (!mbar_wait(bar_f, ph, &abort_flag, 21)) break;
+        if (more) {
+          if (!mbar_wait(bar_k, ph ^ 1u, &abort_flag, 12)) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int k = 0; k < AT_HD / 16; k++) tc_mma_bf16(tmem_s, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, k ? 1u : 0u);
+          tc_commit(bar_s);
+        }
+        /* P(it) written (and the accumulator rescaled where a maximum moved): add P V */
+        if (!mbar_wait(bar_p, ph, &abort_flag, 14)) break;
+        if (!mbar_wait(bar_v + 8 * ph, (it >> 1) & 1u, &abort_flag, 15)) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          const uint64_t da = make_smem_desc(s_p + h * 16384), db = make_smem_desc(s_v + ph * 16384 + h * 8192);
+#pragma unroll
+          for (int k = 0; k < 4; k++) tc_mma_bf16(tmem_pv, da + (uint64_t)(k * 2), db + (uint64_t)(k * 128), idesc_o, (it | (uint32_t)h | (uint32_t)k) ? 1u : 0u);
+        }
+        tc_commit(bar_o);
+      }
+    }
+  } else {
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = quarter * 32 + lane;
+    const long long q = (long long)qb * AT_BQ + row;
+    const float *mrow = g.mask + q * g.mask_sq;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t s_cols = tmem_s + lane_addr + half * 64, pv_cols = tmem_pv + lane_addr + half * 32;
+    const float LOG2E = 1.44269504088896340736f;
+    float m_run = __int_as_float(0xff800000), l_run = 0.0f;
+    uint8_t *p_row = sm + 65536 + half * 16384 + (row >> 3) * 1024 + (row & 7) * 128;
+    bool ok = true;
+    uint32_t xph = 0, it = 0;
+    for (unsigned long long rem = s_live; rem && ok; rem &= rem - 1, it++) {
+      const int j = __ffsll((long long)rem) - 1;
+      const uint32_t ph = it & 1u;
+      const float *mj = mrow + ((long long)j * AT_BK + half * 64) * g.mask_sk;
+      const float tile_c = g.tile_const[2 * (qb * nkb + j)];
+      const bool tile_is_const = (tile_c == tile_c);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_s, ph, &abort_flag, 17))) { ok = false; break; }
+      tc_fence_after_sync();
+      /* this thread's 64 scores, once */
+      uint32_t r0[32], r1[32];
+      tc_ld32(s_cols, r0);
+      tc_ld32(s_cols + 32, r1);
+      tc_wait_ld();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_f);
+      /* x = fma(s, scale, mask) in place; where the tile is one value c and the scale is not negative the
+       * largest x is that of the largest s, and x is formed together with the exponent below */
+      float m_part = __int_as_float(0xff800000);
+      const bool plain_max = tile_is_const && g.scale >= 0.0f;
+      if (plain_max) {
+#pragma unroll
+        for (int i = 0; i < 32; i++) m_part = fmaxf(m_part, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
+        m_part = fmaf(m_part, g.scale, tile_c);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          uint32_t (&r)[32] = c ? r1 : r0;
+          if (tile_is_const) {
+#pragma unroll
+            for (int i = 0; i < 32; i++) r[i] = __float_as_uint(fmaf(__uint_as_float(r[i]), g.scale, tile_c));
+          } else if (g.mask_vec) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+              const float4 mv = reinterpret_cast<const float4 *>(mj + c * 32)[i];
+              r[4 * i] = __float_as_uint(fmaf(__uint_as_float(r[4 * i]), g.scale, mv.x));
+              r[4 * i + 1] = __float_as_uint(fmaf(__uint_as_float(r[4 * i + 1]), g.scale, mv.y));
+              r[4 * i + 2] = __float_as_uint(fmaf(__uint_as_float(r[4 * i + 2]), g.scale, mv.z));
+              r[4 * i + 3] = __float_as_uint(fmaf(__uint_as_float(r[4 * i + 3]), g.scale, mv.w));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+              r[i] = __float_as_uint(fmaf(__uint_as_float(r[i]), g.scale, mj[(long long)(c * 32 + i) * g.mask_sk]));
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i++) m_part = fmaxf(m_part, __uint_as_float(r[i]));
+        }
+      }
+      xchg[half][row] = m_part;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_x);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_x, xph & 1u, &abort_flag, 19))) { ok = false; break; }
+      xph++;
+      const float m_other = xchg[half ^ 1][row];
+      const float m_new = fmaxf(m_run, fmaxf(m_part, m_other));
+      const float m_scaled = m_new * LOG2E;
+      const float alpha = fast_exp2((m_run - m_new) * LOG2E);
+      float l_blk = 0.0f;
+      /* probabilities, packed as bf16 pairs over the scores */
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        uint32_t (&r)[32] = c ? r1 : r0;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float x0 = __uint_as_float(r[i]), x1 = __uint_as_float(r[i + 1]);
+          if (plain_max) { x0 = fmaf(x0, g.scale, tile_c); x1 = fmaf(x1, g.scale, tile_c); }
+          const float p0 = fast_exp2(fmaf(x0, LOG2E, -m_scaled)), p1 = fast_exp2(fmaf(x1, LOG2E, -m_scaled));
+          __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+          l_blk += p0 + p1;
+          r[i >> 1] = *reinterpret_cast<uint32_t *>(&pb);
+        }
+      }
+      l_run = l_run * alpha + l_blk;
+      m_run = m_new;
+      /* the P tile and the accumulator are still in use by the previous block's product until it is done */
+      if (it > 0) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_o, (it - 1) & 1u, &abort_flag, 18))) { ok = false; break; }
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+          uint32_t o[32];
+          tc_ld32(pv_cols, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int d = 0; d < 32; d++) o[d] = __float_as_uint(__uint_as_float(o[d]) * alpha);
+          tc_st32(pv_cols, o);
+          tc_wait_st();
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        const uint32_t (&r)[32] = c ? r1 : r0;
+#pragma unroll
+        for (int i8 = 0; i8 < 4; i8++) {
+          const int chunk = c * 4 + i8;
+          *reinterpret_cast<uint4 *>(p_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(r[4 * i8], r[4 * i8 + 1], r[4 * i8 + 2], r[4 * i8 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p);
+    }
+    /* the last product, then the row sums of both halves */
+    if (ok && it > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar_o, (it - 1) & 1u, &abort_flag, 22));
+    if (ok) {
+      tc_fence_after_sync();
+      xchg[half][row] = l_run;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_x);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_x, xph & 1u, &abort_flag, 20));
+    }
+    if (ok) {
+      uint32_t o[32];
+      tc_ld32(pv_cols, o);
+      tc_wait_ld();
+      const float l_tot = l_run + xchg[half ^ 1][row];
+      int rem = bh; long long ob = 0;
+      for (int i = 0; i < g.nb; i++) { const int x = rem % g.bext[i]; rem /= g.bext[i]; ob += x * g.o_sb[i]; }
+      const long long oe = ob + q * g.o_sm + half * 32;
+      const float inv = 1.0f / l_tot;
+      if (g.out_bf16) {
+        __nv_bfloat16 *op = reinterpret_cast<__nv_bfloat16 *>(g.O) + oe;
+#pragma unroll
+        for (int d = 0; d < 32; d += 8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(o[d + 2 * i]) * inv, __uint_as_float(o[d + 2 * i + 1]) * inv);
+            w[i] = *reinterpret_cast<const uint32_t *>(&v2);
+          }
+          *reinterpret_cast<uint4 *>(op + d) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else {
+        float *op = g.O + oe;
+#pragma unroll
+        for (int d = 0; d < 32; d += 4)
+          *reinterpret_cast<float4 *>(op + d) = make_float4(__uint_as_float(o[d]) * inv, __uint_as_float(o[d + 1]) * inv,
+                                                            __uint_as_float(o[d + 2]) * inv, __uint_as_float(o[d + 3]) * inv);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (abort_flag) { for (int i = 0; i < 2000; i++) __nanosleep(1000); }
+  if (warp == 8) {
+    tc_fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+  }
+}
+
 /* Classifies the mask by 128 x 128 tile.  out[2*tile]: the tile's value if all its
  * entries are equal (the zeros below and the -1e9 above the diagonal of a causal
  * mask, for instance), so that the attention kernel adds it without reading the
@@ -544,9 +837,13 @@ int pb_attention_launch(const PbAttnOperand &q, const PbAttnOperand &k, const Pb
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(pb200_flash_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(pb200_flash_attn2, cudaFuncAttributeMaxDynamicSharedMemorySize, AT2_SMEM);
     if (e != cudaSuccess) { pb_set_error("attention: cannot reserve shared memory: %s", cudaGetErrorString(e)); return -1; }
     configured = true;
   }
+  /* POLY_B200_ATTN=1: the first arrangement (accumulators in registers) */
+  const char *variant = getenv("POLY_B200_ATTN");
+  const bool v1 = variant && variant[0] == '1';
   CUtensorMap mq, mk, mv;
   if (attn_map(&mq, q, T, nb, bext, AT_BQ) != 0) return -1;
   if (attn_map(&mk, k, T, nb, bext, AT_BK) != 0) return -1;
@@ -584,7 +881,8 @@ int pb_attention_launch(const PbAttnOperand &q, const PbAttnOperand &k, const Pb
   pb_scratch_free(norms);
   pb_tc_mark_used();
   pb_tc_configure_backoff();
-  pb200_flash_attn<<<(unsigned)grid, AT_THREADS, AT_SMEM, stream>>>(mq, mk, mv, g);
+  if (v1) pb200_flash_attn<<<(unsigned)grid, AT_THREADS, AT_SMEM, stream>>>(mq, mk, mv, g);
+  else pb200_flash_attn2<<<(unsigned)grid, AT_THREADS, AT2_SMEM, stream>>>(mq, mk, mv, g);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { pb_set_error("attention launch: %s", cudaGetErrorString(e)); return -1; }
   return 0;
