@@ -62,6 +62,8 @@ struct TcArgs {
   int vec_io;                      /* C rows (and addend rows) 16-byte aligned, N % 4 == 0 */
   int c_bf16;                      /* C holds bfloat16 (needs vec_io) */
   int gelu;                        /* tanh-GELU after the addend (bfloat16 results only) */
+  int pack16;                      /* bfloat16 result, N and the row pitch multiples of 8, addend absent or one value per column:
+                                      bias, activation and rounding happen in registers and the staged tile holds bfloat16 */
   int tiles_m, tiles_n, n_tiles;   /* n_tiles = nbatch * tiles_m * tiles_n */
   int m_fast;                      /* consecutive tiles differ in the row tile (else in the column tile) */
   int kchunk;                      /* PROMOTE kernels: k-blocks summed in tensor memory before the partial sum moves to registers */
@@ -82,6 +84,21 @@ __device__ __forceinline__ float gelu_tanh_approx(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
   const float h = 0.5f * x;
   return fmaf(h, t, h);
+}
+
+/* Shared-memory and global accesses of the epilogue by explicit state space (a pointer derived from the
+ * dynamic shared-memory base is otherwise treated as generic, which costs address checks and keeps the
+ * compiler from reordering loads of the staged tile around the global stores). */
+__device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void stg_v4(void *p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 /* Tile t of a batch entry -> (row tile, column tile).  Consecutive tiles run at the
@@ -257,6 +274,15 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
      * hardware ties a warp to that quarter) and one half of the tile's columns ── */
     const int q = warp & 3, half = (warp - 2) >> 2;
     float *stg = epi + (warp - 2) * 32 * 32;
+    /* addresses into this warp's 4 KB staging tile, fixed for the whole kernel.  float32 tile: 32 rows x 128 B,
+     * thread `lane` writes row `lane` (16-byte chunk c at c ^ (lane & 7)) and reads, in pass i8, row i8*4 + lane/8,
+     * chunk lane%8.  bfloat16 tile: 32 rows x 64 B, chunk c of row r at c ^ ((r >> 1) & 3); pass i4 reads row
+     * i4*8 + lane/4, chunk lane%4.  Bytes 2048.. of the tile hold the bias of the warp's 128 columns then. */
+    const uint32_t stg_s = smem_u32(stg);
+    const uint32_t wr32 = stg_s + lane * 128, wr16 = stg_s + lane * 64;
+    const uint32_t rd32_a = stg_s + (lane >> 3) * 128 + (((lane & 7) ^ (lane >> 3)) << 4);          /* passes with even i8 */
+    const uint32_t rd32_b = stg_s + (4 + (lane >> 3)) * 128 + (((lane & 7) ^ (4 + (lane >> 3))) << 4); /* odd i8 */
+    const uint32_t rd16 = stg_s + (lane >> 2) * 64 + (((lane & 3) ^ ((lane >> 3) & 3)) << 4);       /* (row >> 1) & 3 does not depend on the pass */
     uint32_t it = 0;
     bool ok = true;
     for (int t = unit; t < g.n_tiles && ok; t += n_units) {
@@ -267,6 +293,29 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       for (int i = 0; i < g.nb; i++) { const int x = bz % g.bext[i]; bz /= g.bext[i]; oc += x * g.c_sb[i]; ox += x * g.x_sb[i]; }
       constexpr int NCH = (BN / 2) / 32;
       const int colh = nt * BN + half * (BN / 2);
+      const int row0 = (mt * CTAS + (int)rank) * TC_BM + q * 32;
+      const int rows = min(32, g.M - row0);
+      float *__restrict__ C = g.C + oc;
+      const float *__restrict__ X = g.has_x ? g.X + ox : nullptr;
+      const bool x_bcast = X && g.x_sm == 0;       /* bias: one value per column */
+      /* float32 result with a bias: this lane's four bias values of every 32-column chunk, fetched before the
+       * accumulator is waited for */
+      [[maybe_unused]] float4 xb4[NCH];
+      if (x_bcast && g.vec_io && !g.c_bf16) {
+#pragma unroll
+        for (int ci = 0; ci < NCH; ci++) {
+          const int n = colh + ci * 32 + (lane & 7) * 4;
+          xb4[ci] = n < g.N ? __ldg(reinterpret_cast<const float4 *>(X + n)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+      if (g.pack16 && X) {
+        /* the bias of this warp's columns, once per tile, beside the staged tile (all lanes read the same
+         * 16 bytes at a time later: a broadcast) */
+        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (lane * 4 < BN / 2 && colh + lane * 4 < g.N) b = __ldg(reinterpret_cast<const float4 *>(X + colh + lane * 4));
+        sts_v4(stg_s + 2048 + lane * 16, __float_as_uint(b.x), __float_as_uint(b.y), __float_as_uint(b.z), __float_as_uint(b.w));
+        __syncwarp();
+      }
       uint32_t buf = 0;
       [[maybe_unused]] float acc[PROMOTE ? NCH : 1][32];
       if constexpr (PROMOTE) {
@@ -311,14 +360,9 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         }
 #endif
       }
-      const int row0 = (mt * CTAS + (int)rank) * TC_BM + q * 32;
-      const int rows = min(32, g.M - row0);
-      float *__restrict__ C = g.C + oc;
-      const float *__restrict__ X = g.has_x ? g.X + ox : nullptr;
       /* chunks of 32 columns; the tensor-memory load of the next chunk is in
        * flight while this one is transposed and stored */
       const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * (BN / 2);
-      const bool x_bcast = X && g.x_sm == 0;       /* bias: one value per column */
       [[maybe_unused]] uint32_t r[PROMOTE ? 1 : 2][32];
       /* the value of column j of chunk ci: from registers (PROMOTE) or from the load in flight */
       auto val = [&](int ci, int j) -> float {
@@ -333,7 +377,63 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             tc_wait_ld();
             if (ci + 1 < NCH && col0 + 32 < g.N) tc_ld32(tbase + (ci + 1) * 32, r[(ci + 1) & 1]);
           }
-          if (g.vec_io) {
+          if (g.pack16) {
+            /* bfloat16 result: the thread's 32 values of its row get bias, activation and rounding here, in
+             * registers, and the staged tile is 32 rows x 64 bytes -- half the shared-memory traffic of staging
+             * float32 and converting on the way out. */
+            uint32_t w[16];
+#pragma unroll
+            for (int j4 = 0; j4 < 8; j4++) {
+              float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (X) { const uint4 u = lds_v4(stg_s + 2048 + (ci * 8 + j4) * 16); b4 = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w)); }
+              float v0 = val(ci, j4 * 4) + b4.x, v1 = val(ci, j4 * 4 + 1) + b4.y, v2 = val(ci, j4 * 4 + 2) + b4.z, v3 = val(ci, j4 * 4 + 3) + b4.w;
+              if (g.relu) { v0 = (0.f < v0) ? v0 : 0.f; v1 = (0.f < v1) ? v1 : 0.f; v2 = (0.f < v2) ? v2 : 0.f; v3 = (0.f < v3) ? v3 : 0.f; }
+              if (g.gelu) { v0 = gelu_tanh_approx(v0); v1 = gelu_tanh_approx(v1); v2 = gelu_tanh_approx(v2); v3 = gelu_tanh_approx(v3); }
+              const __nv_bfloat162 lo = __floats2bfloat162_rn(v0, v1), hi = __floats2bfloat162_rn(v2, v3);
+              w[j4 * 2] = *reinterpret_cast<const uint32_t *>(&lo); w[j4 * 2 + 1] = *reinterpret_cast<const uint32_t *>(&hi);
+            }
+            const uint32_t sw = (lane >> 1) & 3;
+#pragma unroll
+            for (int c = 0; c < 4; c++) sts_v4(wr16 + ((c ^ sw) << 4), w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+            __syncwarp();
+            const int n = col0 + (lane & 3) * 8;
+            if (n < g.N) {
+              uint4 v[4];
+#pragma unroll
+              for (int i4 = 0; i4 < 4; i4++) v[i4] = lds_v4(rd16 + i4 * 512);
+              __nv_bfloat16 *cb = reinterpret_cast<__nv_bfloat16 *>(g.C) + (C - g.C) + (long long)(row0 + (lane >> 2)) * g.c_sm + n;
+              const long long cstep = 8 * g.c_sm;
+#pragma unroll
+              for (int i4 = 0; i4 < 4; i4++) {
+                if (i4 * 8 + (lane >> 2) < rows) stg_v4(cb, v[i4].x, v[i4].y, v[i4].z, v[i4].w);
+                cb += cstep;
+              }
+            }
+          } else if (g.vec_io && !g.c_bf16 && (!X || x_bcast)) {
+            /* float32 result, no addend or one value per column: the staged 32 x 32 tile is read back with all
+             * eight loads in flight, then bias / relu and eight 128-bit stores of 4 rows x 128 B each */
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+              sts_v4(wr32 + ((c ^ (lane & 7)) << 4), __float_as_uint(val(ci, c * 4)), __float_as_uint(val(ci, c * 4 + 1)),
+                     __float_as_uint(val(ci, c * 4 + 2)), __float_as_uint(val(ci, c * 4 + 3)));
+            __syncwarp();
+            const int n = col0 + (lane & 7) * 4;
+            if (n < g.N) {
+              uint4 v[8];
+#pragma unroll
+              for (int i8 = 0; i8 < 8; i8++) v[i8] = lds_v4(((i8 & 1) ? rd32_b : rd32_a) + (i8 >> 1) * 1024);
+              const float4 xb = X ? xb4[ci] : make_float4(0.f, 0.f, 0.f, 0.f);
+              float *cp = C + (long long)(row0 + (lane >> 3)) * g.c_sm + n;
+              const long long cstep = 4 * g.c_sm;
+#pragma unroll
+              for (int i8 = 0; i8 < 8; i8++) {
+                float a0 = __uint_as_float(v[i8].x) + xb.x, a1 = __uint_as_float(v[i8].y) + xb.y, a2 = __uint_as_float(v[i8].z) + xb.z, a3 = __uint_as_float(v[i8].w) + xb.w;
+                if (g.relu) { a0 = (0.f < a0) ? a0 : 0.f; a1 = (0.f < a1) ? a1 : 0.f; a2 = (0.f < a2) ? a2 : 0.f; a3 = (0.f < a3) ? a3 : 0.f; }
+                if (i8 * 4 + (lane >> 3) < rows) stg_v4(cp, __float_as_uint(a0), __float_as_uint(a1), __float_as_uint(a2), __float_as_uint(a3));
+                cp += cstep;
+              }
+            }
+          } else if (g.vec_io) {
             /* rows of C (and of the addend) are 16-byte aligned: 128-bit shared and
              * global accesses, 16-byte chunks XOR-swizzled by row so that both the
              * row-per-thread writes and the 4-rows-per-warp reads are conflict-free */
@@ -763,6 +863,13 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, int
     g.vec_io = v ? 1 : 0;
     g.c_bf16 = p.c_bf16 ? 1 : 0;
     g.gelu = p.gelu ? 1 : 0;
+    {
+      bool pk = p.c_bf16 && v && g.N % 8 == 0 && g.c_sm % 8 == 0 && (!g.has_x || g.x_sm == 0) &&
+                (reinterpret_cast<uintptr_t>(bufs[p.p_c]) & 15) == 0 && p.off_c % 8 == 0;
+      for (int i = 0; i < g.nb; i++) if (g.c_sb[i] % 8 || (g.has_x && g.x_sb[i] != 0)) pk = false;
+      const char *e = getenv("POLY_B200_TC_PACK16");        /* "0": stage float32 and convert on the way out (measurements) */
+      g.pack16 = pk && !(e && e[0] == '0') ? 1 : 0;
+    }
     if (p.c_bf16) {
       /* the kernel only forms element offsets from this base; elements are 2 bytes */
       g.C = reinterpret_cast<float *>(reinterpret_cast<__nv_bfloat16 *>(bufs[p.p_c]) + p.off_c);

@@ -13,12 +13,13 @@
 
 #define TC_SPIN_LIMIT (1u << 25)
 
-/* Polls of a barrier before the waiting thread starts to sleep between polls.
- * mbarrier.try_wait itself suspends the thread for a short, hardware-chosen time, so
- * polling is cheap; __nanosleep frees issue slots but wakes late, which delays whatever
- * the waiter does next (the next TMA load, the next MMA).  Set from the host
- * (POLY_B200_TC_BACKOFF, polls; 0 = sleep from the ninth poll on). */
-__constant__ unsigned pb_tc_backoff_after = 1u << 14;
+/* Polls of a barrier before the waiting thread starts to sleep between polls.  Sleeping
+ * frees issue slots for the warps that work (the epilogue warps share their schedulers
+ * with the waiting ones) but wakes a little late; measured on the contraction and the
+ * attention kernel, polling 16384 times first changed no time and added a quarter to the
+ * instructions executed, so the default is to sleep from the ninth poll on.  Set from the
+ * host (POLY_B200_TC_BACKOFF, polls) for measurements. */
+__constant__ unsigned pb_tc_backoff_after = 0;
 
 /* ── PTX wrappers ────────────────────────────────────────────────────── */
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
