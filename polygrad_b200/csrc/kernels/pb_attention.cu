@@ -468,9 +468,10 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const bool more = rem != 0;
         const int jn = more ? __ffsll((long long)rem) - 1 : 0;
         const uint32_t ph = it & 1u;
-        /* S(it) complete: K is free, request the next block of keys */
+        /* S(it) complete (it was issued one iteration ago).  The key block after this one is normally on its
+         * way already (requested below, one iteration ahead); only the very first request happens here */
         if (!mbar_wait(bar_s, ph, &abort_flag, 13)) break;
-        if (more) { mbar_expect_tx(bar_k, 16384); tma_load_5d(s_k, &map_k, bar_k, 0, jn * AT_BK, c0, c1, c2); }
+        if (more && it == 0) { mbar_expect_tx(bar_k, 16384); tma_load_5d(s_k, &map_k, bar_k, 0, jn * AT_BK, c0, c1, c2); }
         /* V buffer (it+1)&1 was last read by PV(it-1): request the next block of values once that product is done */
         if (more) {
           if (it > 0 && !mbar_wait(bar_o, (it - 1) & 1u, &abort_flag, 16)) break;
@@ -486,6 +487,14 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
           for (int k = 0; k < AT_HD / 16; k++) tc_mma_bf16(tmem_s, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, k ? 1u : 0u);
           tc_commit(bar_s);
+          /* that product is short; once it has read K, the keys of the block after next are requested -- a whole
+           * iteration before they are needed, instead of at the moment they are */
+          const unsigned long long rem2 = rem & (rem - 1);
+          if (rem2) {
+            if (!mbar_wait(bar_s, ph ^ 1u, &abort_flag, 23)) break;
+            mbar_expect_tx(bar_k, 16384);
+            tma_load_5d(s_k, &map_k, bar_k, 0, (__ffsll((long long)rem2) - 1) * AT_BK, c0, c1, c2);
+          }
         }
         /* P(it) written (and the accumulator rescaled where a maximum moved): add P V */
         if (!mbar_wait(bar_p, ph, &abort_flag, 14)) break;

@@ -117,8 +117,10 @@ def test_plan_passes_change_no_bit_under_bf16_policy(gpu, monkeypatch):
 
 def test_gelu_epilogue_stays_within_the_bf16_rounding(gpu, monkeypatch):
     """GELU moved into the fc contraction's epilogue (hardware tanh approximation, then the bfloat16
-    rounding the separate kernel also ends with) against the plan that keeps the separate kernel:
-    logits within 5e-3 relative, far inside the 2e-2 bound of the bf16 policy."""
+    rounding the separate kernel also ends with) against the plan that keeps the separate kernel.  The
+    approximation moves an activation by at most 2^-11 of its size, which now and then tips the bfloat16
+    rounding that follows to the neighbouring value (2^-8); the logits stay within 1e-2 relative (measured:
+    largest difference 1 % of the rms, 80 of 157184 logits beyond 5e-3), inside the 2e-2 bound of the policy."""
     cfg = dict(vocab_size=307, n_embd=128, n_head=2, n_layer=2, max_seq_len=256, max_batch=2)
     tokens = np.random.default_rng(22).integers(0, cfg['vocab_size'], (2, 256))
     gpu.poly_b200_set_gemm_policy(1)
@@ -134,7 +136,7 @@ def test_gelu_epilogue_stays_within_the_bf16_rounding(gpu, monkeypatch):
     finally:
         gpu.poly_b200_set_gemm_policy(0)
     assert n_fused == n_separate - cfg['n_layer']          # one launch less per layer
-    assert_close(fused, separate, 5e-3, 'GELU in the epilogue vs the separate kernel')
+    assert_close(fused, separate, 1e-2, 'GELU in the epilogue vs the separate kernel')
 
 
 def test_gpt2_124m_full_width_properties(gpu):
