@@ -97,6 +97,14 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
   return v;
 }
+__device__ __forceinline__ uint32_t lds_b32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void stg_b32(void *p, uint32_t a) {
+  asm volatile("st.global.b32 [%0], %1;" ::"l"(p), "r"(a) : "memory");
+}
 __device__ __forceinline__ void stg_v4(void *p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -478,6 +486,34 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 }
                 cp += cstep;
                 if (xp) xp += xstep;
+              }
+            }
+          } else if (!g.c_bf16 && (!X || x_bcast)) {
+            /* float32 result whose rows are not 16-byte aligned (a 50257-wide vocabulary): staged like the aligned
+             * tile, read back a row per pass with lane = column, eight rows' loads in flight at a time; a warp's
+             * store is 128 contiguous bytes of one row */
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+              sts_v4(wr32 + ((c ^ (lane & 7)) << 4), __float_as_uint(val(ci, c * 4)), __float_as_uint(val(ci, c * 4 + 1)),
+                     __float_as_uint(val(ci, c * 4 + 2)), __float_as_uint(val(ci, c * 4 + 3)));
+            __syncwarp();
+            const int n = col0 + lane;
+            if (n < g.N) {
+              const float xb = X ? X[(long long)n * g.x_sn] : 0.0f;
+              float *cp = C + (long long)row0 * g.c_sm + n;
+              const uint32_t rd = stg_s + (lane & 3) * 4, hi = (uint32_t)lane >> 2;
+#pragma unroll
+              for (int r8 = 0; r8 < 4; r8++) {
+                uint32_t v[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[i] = lds_b32(rd + (r8 * 8 + i) * 128 + ((hi ^ (uint32_t)i) << 4));   /* word `lane` of row r8*8+i */
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                  float a = __uint_as_float(v[i]) + xb;
+                  if (g.relu) a = (0.f < a) ? a : 0.f;
+                  if (r8 * 8 + i < rows) stg_b32(cp, __float_as_uint(a));
+                  cp += g.c_sm;
+                }
               }
             }
           } else {
