@@ -67,10 +67,6 @@ struct TcArgs {
   int tiles_m, tiles_n, n_tiles;   /* n_tiles = nbatch * tiles_m * tiles_n */
   int m_fast;                      /* consecutive tiles differ in the row tile (else in the column tile) */
   int kchunk;                      /* PROMOTE kernels: k-blocks summed in tensor memory before the partial sum moves to registers */
-#ifdef PB_TC_DIAG
-  int diag;                        /* measurement builds only: 1 no global stores, 2 no staged read-back either, 3 tensor-memory
-                                      loads only, 4 no epilogue work at all, 5 no mainloop (stores only) */
-#endif
 };
 
 #define PB_TC_ERROR_FLAG pb200_tc_error_flag
@@ -186,9 +182,6 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-#ifdef PB_TC_DIAG
-      if (g.diag == 5) ok = false;
-#endif
       for (int t = unit; t < g.n_tiles && ok; t += n_units) {
         int nt, mt; const int bz = t / (g.tiles_n * g.tiles_m);
         tile_coords(g, t, &mt, &nt);
@@ -220,9 +213,6 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((TC_BM * CTAS) >> 4) << 24);
       uint32_t stage = 0, phase = 0, it = 0;
       bool ok = true;
-#ifdef PB_TC_DIAG
-      if (g.diag == 5) ok = false;
-#endif
       /* the four instructions of one k-block; `first` clears the accumulator */
       auto issue_block = [&](uint32_t tmem_d, bool first) {
         const uint32_t sa = base + stage * S::STAGE, sb = sa + S::STAGE_A;
@@ -355,18 +345,8 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         buf = it & 1u;
         const uint32_t use = it >> 1;
         it++;
-#ifdef PB_TC_DIAG
-        if (g.diag != 5)
-#endif
         if (!mbar_wait(bar_tfull + 8 * buf, use & 1u, &abort_flag, 4)) { ok = false; break; }
         tc_fence_after_sync();
-#ifdef PB_TC_DIAG
-        if (g.diag == 4) {
-          tc_fence_before_sync();
-          if (lane == 0) { if constexpr (CTAS == 2) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * buf, 0)); else mbar_arrive(bar_tempty + 8 * buf); }
-          continue;
-        }
-#endif
       }
       /* chunks of 32 columns; the tensor-memory load of the next chunk is in
        * flight while this one is transposed and stored */
@@ -446,16 +426,10 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
              * global accesses, 16-byte chunks XOR-swizzled by row so that both the
              * row-per-thread writes and the 4-rows-per-warp reads are conflict-free */
             float4 *stg4 = reinterpret_cast<float4 *>(stg);
-#ifdef PB_TC_DIAG
-            if (g.diag == 3) { float a = 0.f; for (int j = 0; j < 32; j++) a += val(ci, j); if (a == 123.456f) C[0] = a; __syncwarp(); continue; }
-#endif
 #pragma unroll
             for (int c4 = 0; c4 < 8; c4++)
               stg4[lane * 8 + (c4 ^ (lane & 7))] = make_float4(val(ci, c4 * 4), val(ci, c4 * 4 + 1), val(ci, c4 * 4 + 2), val(ci, c4 * 4 + 3));
             __syncwarp();
-#ifdef PB_TC_DIAG
-            if (g.diag == 2) { __syncwarp(); continue; }
-#endif
             const int c4 = lane & 7, rsub = lane >> 3;
             const int n = col0 + c4 * 4;
             if (n < g.N) {
@@ -479,9 +453,6 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     uint2 w; w.x = *reinterpret_cast<const uint32_t *>(&lo); w.y = *reinterpret_cast<const uint32_t *>(&hi);
                     *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(g.C) + (cp - g.C)) = w;
                   } else
-#ifdef PB_TC_DIAG
-                  if (g.diag == 1) { if (v.x + v.y + v.z + v.w == 123.456f) *reinterpret_cast<float4 *>(cp) = v; } else
-#endif
                   *reinterpret_cast<float4 *>(cp) = v;
                 }
                 cp += cstep;
@@ -647,9 +618,6 @@ static int sm_count() {
 template <int BN, int CTAS, bool PROMOTE = false, bool TF32 = false>
 static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, long long nbatch, cudaStream_t stream) {
   if (tc_configure<BN, CTAS, PROMOTE, TF32>() != 0) return -1;
-#ifdef PB_TC_DIAG
-  { const char *d = getenv("POLY_B200_TC_DIAG"); g.diag = d ? atoi(d) : 0; }
-#endif
   g.tiles_m = (g.M + TC_BM * CTAS - 1) / (TC_BM * CTAS);
   g.tiles_n = (g.N + BN - 1) / BN;
   long long tiles = (long long)g.tiles_m * g.tiles_n * nbatch;
