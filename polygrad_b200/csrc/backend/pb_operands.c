@@ -650,8 +650,8 @@ static int share_mask_tiles(PbPlan *p) {
       if (pb_plan_resolve(p, S->slot[3]) == mslot && Ts == T && memcmp(a.mask, fa.mask, sizeof a.mask) == 0) members[nm++] = s;
     }
     if (nm == 0) continue;
-    /* two floats per 128 x 128 tile of the mask */
-    const int tslot = pb_plan_add_slot(p, 2 * (T / 128) * (T / 128) * (int64_t)sizeof(float));
+    /* one record of eight floats per 128 x 128 tile of the mask */
+    const int tslot = pb_plan_add_slot(p, 8 * (T / 128) * (T / 128) * (int64_t)sizeof(float));
     int ok_members = 0;
     for (int i = -1; i < nm; i++) {
       PbStep *S = i < 0 ? F : &p->steps[members[i]];

@@ -53,6 +53,7 @@ __device__ int pb200_attn_error_flag = 0;
 #define AT_BQ 128      /* query rows per CTA */
 #define AT_BK 128      /* keys per block */
 #define AT_HD 64
+#define AT_REC 8       /* floats per mask-tile record, see pb200_mask_tiles */
 #define AT_THREADS 288
 #define AT_SMEM (16384 /*Q*/ + 16384 /*K*/ + 16384 /*V: 128 keys x 128 B*/ + 32768 /*P: 2 x 16 KB*/ + 256 + 1024)
 
@@ -69,8 +70,7 @@ struct AttnArgs {
   long long mask_sq, mask_sk;     /* mask[q*mask_sq + k*mask_sk] */
   float scale;
   int mask_vec;                   /* mask rows contiguous and 16-byte aligned */
-  const float *tile_const;        /* per (query block, key block) two floats: the tile's one value (NaN if it varies),
-                                     and min over rows of the row's largest mask value in the tile */
+  const float *tile_const;        /* per (query block, key block) one record of AT_REC floats, see pb200_mask_tiles */
   const float *qn, *kn;           /* per (batch*head, block of 128 rows): upper bound of the largest row 2-norm; null: no skipping */
   int T, n_qblocks;
   int nb; int bext[3]; long long o_sb[3]; long long o_sm;   /* O[batch..][row*o_sm + d] */
@@ -104,7 +104,7 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     unsigned long long live = 0;
     float lrun = __int_as_float(0xff800000);
     for (int j = 0; j < nkb; j++) {
-      const float c = g.tile_const[2 * (qb * nkb + j)], lmin = g.tile_const[2 * (qb * nkb + j) + 1];
+      const float c = g.tile_const[AT_REC * (qb * nkb + j)], lmin = g.tile_const[AT_REC * (qb * nkb + j) + 1];
       float S = 0.0f;
       bool skip = false;
       if (g.qn) {
@@ -218,7 +218,7 @@ pb200_flash_attn(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const int j = __ffsll((long long)rem) - 1;
       const uint32_t ph = it & 1u;
       const float *mj = mrow + ((long long)j * AT_BK + half * 64) * g.mask_sk;
-      const float tile_c = g.tile_const[2 * (qb * nkb + j)];
+      const float tile_c = g.tile_const[AT_REC * (qb * nkb + j)];
       const bool tile_is_const = (tile_c == tile_c);
       if (!__all_sync(0xffffffffu, mbar_wait(bar_s, ph, &abort_flag, 17))) { ok = false; break; }
       tc_fence_after_sync();
@@ -396,39 +396,57 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const uint32_t s_q = base, s_k = base + 16384, s_v = base + 32768, s_p = base + 65536;
   uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 98304);
   const uint32_t bar_q = smem_u32(bars), bar_k = bar_q + 8, bar_v = bar_q + 16 /* two */, bar_s = bar_q + 32, bar_p = bar_q + 40,
-                 bar_o = bar_q + 48, bar_x = bar_q + 56, bar_f = bar_q + 64;
+                 bar_o = bar_q + 48, bar_f = bar_q + 56, bar_x = bar_q + 64 /* four: one per pair of warps sharing rows */;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ float xchg[2][AT_BQ];
   __shared__ unsigned long long s_live;
+  /* per key block, from the mask-tile records and the row-norm bounds: fetched by 64 threads at once, because the
+   * choice of blocks below is a serial scan that would otherwise wait for global memory once per block */
+  __shared__ float s_tc[64], s_lm[64], s_kn[64], s_kind[64], s_d[64], s_lo[64], s_hi[64];
+  __shared__ float s_qn;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_bh = gridDim.x / g.n_qblocks;
   const int qb = g.n_qblocks - 1 - (int)(blockIdx.x / n_bh), bh = blockIdx.x % n_bh;
   const int nkb = g.T / AT_BK;
 
-  if (threadIdx.x == 0) {
-    unsigned long long live = 0;
-    float lrun = __int_as_float(0xff800000);
-    for (int j = 0; j < nkb; j++) {
-      const float c = g.tile_const[2 * (qb * nkb + j)], lmin = g.tile_const[2 * (qb * nkb + j) + 1];
-      float S = 0.0f;
-      bool skip = false;
-      if (g.qn) {
-        S = fabsf(g.scale) * g.qn[bh * g.n_qblocks + qb] * g.kn[bh * nkb + j];
-        skip = (c == c) && (c + S < lrun - 100.0f);
-      }
-      if (!skip) { live |= 1ull << j; lrun = fmaxf(lrun, lmin - S); }
-    }
-    s_live = live;
+  if ((int)threadIdx.x < nkb) {
+    const int j = threadIdx.x;
+    const float *rec = g.tile_const + (long long)AT_REC * (qb * nkb + j);
+    const float4 r0 = *reinterpret_cast<const float4 *>(rec), r1 = *reinterpret_cast<const float4 *>(rec + 4);
+    s_tc[j] = r0.x; s_lm[j] = r0.y; s_kind[j] = r0.z; s_d[j] = r0.w; s_lo[j] = r1.x; s_hi[j] = r1.y;
+    s_kn[j] = g.qn ? g.kn[bh * nkb + j] : 0.0f;
+  }
+  if (threadIdx.x == 64) s_qn = g.qn ? g.qn[bh * g.n_qblocks + qb] : 0.0f;
+  if (threadIdx.x == 96) {
     abort_flag = 0;
     mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1); mbar_init(bar_v + 8, 1);
-    mbar_init(bar_s, 1); mbar_init(bar_p, 8); mbar_init(bar_o, 1); mbar_init(bar_x, 8); mbar_init(bar_f, 8);
+    mbar_init(bar_s, 1); mbar_init(bar_p, 8); mbar_init(bar_o, 1); mbar_init(bar_f, 8);
+    for (int i = 0; i < 4; i++) mbar_init(bar_x + 8 * i, 2);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 8) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(256u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    /* which key blocks to process (see the head of this file) */
+    unsigned long long live = 0;
+    float lrun = __int_as_float(0xff800000);
+    const float qn = s_qn;
+    for (int j = 0; j < nkb; j++) {
+      const float c = s_tc[j], lmin = s_lm[j];
+      float S = 0.0f;
+      bool skip = false;
+      if (g.qn) {
+        S = fabsf(g.scale) * qn * s_kn[j];
+        skip = (c == c) && (c + S < lrun - 100.0f);
+      }
+      if (!skip) { live |= 1ull << j; lrun = fmaxf(lrun, lmin - S); }
+    }
+    s_live = live;
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -516,17 +534,24 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const float *mrow = g.mask + q * g.mask_sq;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t s_cols = tmem_s + lane_addr + half * 64, pv_cols = tmem_pv + lane_addr + half * 32;
+    const uint32_t bar_xq = bar_x + 8 * quarter;
     const float LOG2E = 1.44269504088896340736f;
     float m_run = __int_as_float(0xff800000), l_run = 0.0f;
     uint8_t *p_row = sm + 65536 + half * 16384 + (row >> 3) * 1024 + (row & 7) * 128;
+    /* where this thread's 32 output values go (the divisions are kept off the end of the kernel) */
+    long long oe;
+    {
+      int rem = bh; long long ob = 0;
+      for (int i = 0; i < g.nb; i++) { const int x = rem % g.bext[i]; rem /= g.bext[i]; ob += x * g.o_sb[i]; }
+      oe = ob + q * g.o_sm + half * 32;
+    }
     bool ok = true;
     uint32_t xph = 0, it = 0;
     for (unsigned long long rem = s_live; rem && ok; rem &= rem - 1, it++) {
       const int j = __ffsll((long long)rem) - 1;
       const uint32_t ph = it & 1u;
-      const float *mj = mrow + ((long long)j * AT_BK + half * 64) * g.mask_sk;
-      const float tile_c = g.tile_const[2 * (qb * nkb + j)];
-      const bool tile_is_const = (tile_c == tile_c);
+      const float tile_c = s_tc[j];
+      const bool tile_is_const = (tile_c == tile_c), tile_is_step = s_kind[j] == 2.0f;
       if (!__all_sync(0xffffffffu, mbar_wait(bar_s, ph, &abort_flag, 17))) { ok = false; break; }
       tc_fence_after_sync();
       /* this thread's 64 scores, once */
@@ -537,21 +562,29 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_f);
-      /* x = fma(s, scale, mask) in place; where the tile is one value c and the scale is not negative the
-       * largest x is that of the largest s, and x is formed together with the exponent below */
+      /* The largest x = fma(s, scale, mask) of this thread's keys.  Where the tile is one value c and the scale is
+       * not negative, x is a non-decreasing function of s: the largest x is that of the largest s, and the scores
+       * stay as they are (the exponent below is formed from them directly).  Otherwise x replaces s in place. */
       float m_part = __int_as_float(0xff800000);
-      const bool plain_max = tile_is_const && g.scale >= 0.0f;
-      if (plain_max) {
+      const bool plain = tile_is_const && g.scale >= 0.0f;
+      if (plain) {
 #pragma unroll
         for (int i = 0; i < 32; i++) m_part = fmaxf(m_part, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
         m_part = fmaf(m_part, g.scale, tile_c);
       } else {
+        const float lo = s_lo[j], hi = s_hi[j];
+        const int thr = (int)s_d[j] + row - half * 64;        /* key index k within the thread's 64 has the upper value where k > thr */
+        const float *mj = mrow + ((long long)j * AT_BK + half * 64) * g.mask_sk;
 #pragma unroll
         for (int c = 0; c < 2; c++) {
           uint32_t (&r)[32] = c ? r1 : r0;
           if (tile_is_const) {
 #pragma unroll
             for (int i = 0; i < 32; i++) r[i] = __float_as_uint(fmaf(__uint_as_float(r[i]), g.scale, tile_c));
+          } else if (tile_is_step) {
+            /* the entries of a step tile from the indices: no loads */
+#pragma unroll
+            for (int i = 0; i < 32; i++) r[i] = __float_as_uint(fmaf(__uint_as_float(r[i]), g.scale, (c * 32 + i > thr) ? lo : hi));
           } else if (g.mask_vec) {
 #pragma unroll
             for (int i = 0; i < 8; i++) {
@@ -570,31 +603,35 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           for (int i = 0; i < 32; i++) m_part = fmaxf(m_part, __uint_as_float(r[i]));
         }
       }
+      /* the row's other half is with the thread of the same lane four warps away: one barrier per such pair */
       xchg[half][row] = m_part;
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_x);
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_x, xph & 1u, &abort_flag, 19))) { ok = false; break; }
+      if (lane == 0) mbar_arrive(bar_xq);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_xq, xph & 1u, &abort_flag, 19))) { ok = false; break; }
       xph++;
       const float m_other = xchg[half ^ 1][row];
       const float m_new = fmaxf(m_run, fmaxf(m_part, m_other));
       const float m_scaled = m_new * LOG2E;
       const float alpha = fast_exp2((m_run - m_new) * LOG2E);
-      float l_blk = 0.0f;
-      /* probabilities, packed as bf16 pairs over the scores */
+      /* probabilities p = exp2((x - m) log2e), two at a time (packed fp32 multiply-adds), packed as bf16 pairs over
+       * the scores.  plain: x log2e - m log2e = s (scale log2e) + (c log2e - m log2e), one multiply-add per pair. */
+      const float2 mul2 = plain ? make_float2(g.scale * LOG2E, g.scale * LOG2E) : make_float2(LOG2E, LOG2E);
+      const float add1 = plain ? fmaf(tile_c, LOG2E, -m_scaled) : -m_scaled;
+      const float2 add2 = make_float2(add1, add1);
+      float2 l2 = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int c = 0; c < 2; c++) {
         uint32_t (&r)[32] = c ? r1 : r0;
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float x0 = __uint_as_float(r[i]), x1 = __uint_as_float(r[i + 1]);
-          if (plain_max) { x0 = fmaf(x0, g.scale, tile_c); x1 = fmaf(x1, g.scale, tile_c); }
-          const float p0 = fast_exp2(fmaf(x0, LOG2E, -m_scaled)), p1 = fast_exp2(fmaf(x1, LOG2E, -m_scaled));
-          __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-          l_blk += p0 + p1;
+          const float2 e = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), mul2, add2);
+          const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+          __nv_bfloat162 pb = __floats2bfloat162_rn(pp.x, pp.y);
+          l2 = __fadd2_rn(l2, pp);
           r[i >> 1] = *reinterpret_cast<uint32_t *>(&pb);
         }
       }
-      l_run = l_run * alpha + l_blk;
+      l_run = l_run * alpha + (l2.x + l2.y);
       m_run = m_new;
       /* the P tile and the accumulator are still in use by the previous block's product until it is done */
       if (it > 0) {
@@ -630,17 +667,14 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       tc_fence_after_sync();
       xchg[half][row] = l_run;
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_x);
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_x, xph & 1u, &abort_flag, 20));
+      if (lane == 0) mbar_arrive(bar_xq);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_xq, xph & 1u, &abort_flag, 20));
     }
     if (ok) {
       uint32_t o[32];
       tc_ld32(pv_cols, o);
       tc_wait_ld();
       const float l_tot = l_run + xchg[half ^ 1][row];
-      int rem = bh; long long ob = 0;
-      for (int i = 0; i < g.nb; i++) { const int x = rem % g.bext[i]; rem /= g.bext[i]; ob += x * g.o_sb[i]; }
-      const long long oe = ob + q * g.o_sm + half * 32;
       const float inv = 1.0f / l_tot;
       if (g.out_bf16) {
         __nv_bfloat16 *op = reinterpret_cast<__nv_bfloat16 *>(g.O) + oe;
@@ -673,33 +707,54 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   }
 }
 
-/* Classifies the mask by 128 x 128 tile.  out[2*tile]: the tile's value if all its
- * entries are equal (the zeros below and the -1e9 above the diagonal of a causal
- * mask, for instance), so that the attention kernel adds it without reading the
- * tile; NaN for any other tile, which is then read.  out[2*tile + 1]: the smallest,
- * over the tile's rows, of the row's largest entry (-inf if a row holds a NaN) --
- * after the tile is processed every row's running maximum is at least that much
- * minus the bound on |score|.  Exact for every mask. */
+/* Classifies the mask by 128 x 128 tile into one record of AT_REC floats per tile:
+ *   [0] the tile's value if all its entries are equal (the zeros below and the -1e9 above
+ *       the diagonal of a causal mask, for instance), so that the attention kernel adds it
+ *       without reading the tile; NaN otherwise;
+ *   [1] the smallest, over the tile's rows, of the row's largest entry (-inf if a row holds a
+ *       NaN) -- after the tile is processed every row's running maximum is at least that much
+ *       minus the bound on |score|;
+ *   [2] 2.0 for a "step" tile, whose entry (r, c) is [4] where c - r > [3] and [5] elsewhere
+ *       (the diagonal tiles of a causal mask: -1e9 above the diagonal, 0 on and below it), so
+ *       that the kernel forms the entries from the indices instead of loading 64 KB; else 0.
+ * Every claim is checked bit for bit against all 16384 entries: exact for every mask. */
 __global__ void __launch_bounds__(256) pb200_mask_tiles(const float *mask, long long sq, long long sk, int nk, float *out) {
   const int qi = blockIdx.y, ki = blockIdx.x;
   const float *t = mask + (long long)qi * AT_BQ * sq + (long long)ki * AT_BK * sk;
   const float first = t[0];
+  /* step hypothesis from the corners and from row 0: lo = top right, hi = bottom left, and row 0 holds hi in
+   * columns 0 .. d and lo beyond (d = -1: lo from column 0 on) */
+  const unsigned lo_b = __float_as_uint(t[(long long)(AT_BK - 1) * sk]), hi_b = __float_as_uint(t[(long long)(AT_BQ - 1) * sq]);
+  __shared__ int s_d;
+  if (threadIdx.x == 0) s_d = -1;
+  __syncthreads();
+  if (threadIdx.x < AT_BK && __float_as_uint(t[(long long)threadIdx.x * sk]) == hi_b) atomicMax(&s_d, (int)threadIdx.x);
+  __syncthreads();
+  const int d = s_d;
   /* differences are OR-ed, not tested one by one, so that the loads are independent */
-  unsigned diff = 0;
+  unsigned diff = 0, sdiff = 0;
   if (sk == 1 && (sq & 3) == 0 && (reinterpret_cast<uintptr_t>(t) & 15) == 0) {
 #pragma unroll 8
     for (int e = threadIdx.x; e < AT_BQ * AT_BK / 4; e += 256) {
-      const uint4 v = *reinterpret_cast<const uint4 *>(t + (long long)(e / (AT_BK / 4)) * sq + (e % (AT_BK / 4)) * 4);
+      const int r = e / (AT_BK / 4), c = (e % (AT_BK / 4)) * 4;
+      const uint4 v = *reinterpret_cast<const uint4 *>(t + (long long)r * sq + c);
       const unsigned f = __float_as_uint(first);
       diff |= (v.x ^ f) | (v.y ^ f) | (v.z ^ f) | (v.w ^ f);
+      sdiff |= (v.x ^ (c - r > d ? lo_b : hi_b)) | (v.y ^ (c + 1 - r > d ? lo_b : hi_b)) |
+               (v.z ^ (c + 2 - r > d ? lo_b : hi_b)) | (v.w ^ (c + 3 - r > d ? lo_b : hi_b));
     }
   } else {
 #pragma unroll 8
-    for (int e = threadIdx.x; e < AT_BQ * AT_BK; e += 256)
-      diff |= __float_as_uint(t[(long long)(e / AT_BK) * sq + (long long)(e % AT_BK) * sk]) ^ __float_as_uint(first);
+    for (int e = threadIdx.x; e < AT_BQ * AT_BK; e += 256) {
+      const int r = e / AT_BK, c = e % AT_BK;
+      const unsigned v = __float_as_uint(t[(long long)r * sq + (long long)c * sk]);
+      diff |= v ^ __float_as_uint(first);
+      sdiff |= v ^ (c - r > d ? lo_b : hi_b);
+    }
   }
   const bool same = diff == 0;
   const int all = __syncthreads_and(same ? 1 : 0);
+  const int step = __syncthreads_and(sdiff == 0 ? 1 : 0);
   /* row maxima: a warp per row, 16 rows per warp */
   const int wid = threadIdx.x >> 5, ln = threadIdx.x & 31;
   float mx = __int_as_float(0x7f800000);               /* running min over this warp's rows */
@@ -720,8 +775,14 @@ __global__ void __launch_bounds__(256) pb200_mask_tiles(const float *mask, long 
   if (threadIdx.x == 0) {
     float m = s_min[0];
     for (int i = 1; i < 8; i++) m = fminf(m, s_min[i]);
-    out[2 * (qi * nk + ki)] = (all && first == first) ? first : __int_as_float(0x7fc00000);
-    out[2 * (qi * nk + ki) + 1] = m;
+    float *rec = out + (long long)AT_REC * (qi * nk + ki);
+    const float lo = __uint_as_float(lo_b), hi = __uint_as_float(hi_b);
+    const bool is_const = all && first == first;
+    rec[0] = is_const ? first : __int_as_float(0x7fc00000);
+    rec[1] = m;
+    /* a step tile has two different finite-or-infinite values (NaNs are left to the general path) */
+    rec[2] = (!is_const && step && lo == lo && hi == hi && lo_b != hi_b) ? 2.0f : 0.0f;
+    rec[3] = (float)d; rec[4] = lo; rec[5] = hi; rec[6] = 0.0f; rec[7] = 0.0f;
   }
 }
 
@@ -866,7 +927,7 @@ int pb_attention_launch(const PbAttnOperand &q, const PbAttnOperand &k, const Pb
   long long grid = BH * g.n_qblocks;
   if (grid > 2147483647LL) { pb_set_error("attention: grid too large"); return -1; }
   const int nq = g.n_qblocks, nk = (int)(T / AT_BK);
-  float *tiles = tiles_mode ? tiles_buf : (float *)pb_scratch_alloc((size_t)2 * nq * nk * sizeof(float));
+  float *tiles = tiles_mode ? tiles_buf : (float *)pb_scratch_alloc((size_t)AT_REC * nq * nk * sizeof(float));
   if (!tiles) { pb_set_error("attention: out of scratch memory"); return -1; }
   /* bounds on |q.k| per block, for leaving out key blocks that cannot contribute (POLY_B200_ATTN_SKIP=0: never) */
   float *norms = nullptr;

@@ -67,7 +67,7 @@ int pb_attention_launch(const PbAttnOperand &q, const PbAttnOperand &k, const Pb
                         const float *mask, long long mask_sq, long long mask_sk,
                         float scale, void *out, bool out_bf16, int nb, const int *bext, const long long *o_sb, long long o_sm,
                         long long BH, long long T, cudaStream_t stream, float *tiles = nullptr, int tiles_mode = 0);
-/* tiles_mode 1: the mask classification (two floats per 128 x 128 tile of the mask) is computed into `tiles`,
+/* tiles_mode 1: the mask classification (a record of eight floats per 128 x 128 tile of the mask) is computed into `tiles`,
  * 2: it is read from there; 0: the launch uses scratch of its own. */
 
 /* Can the tensor-core kernel run this problem whatever the buffer addresses are
