@@ -419,14 +419,29 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     s_kn[j] = g.qn ? g.kn[bh * nkb + j] : 0.0f;
   }
   if (threadIdx.x == 64) s_qn = g.qn ? g.qn[bh * g.n_qblocks + qb] : 0.0f;
-  if (threadIdx.x == 96) {
-    abort_flag = 0;
-    mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1); mbar_init(bar_v + 8, 1);
-    mbar_init(bar_s, 1); mbar_init(bar_p, 8); mbar_init(bar_o, 1); mbar_init(bar_f, 8);
-    for (int i = 0; i < 4; i++) mbar_init(bar_x + 8 * i, 2);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
+  /* batch coordinates of this (batch, head) for the tensor maps */
+  int c0 = 0, c1 = 0, c2 = 0;
   if (warp == 8) {
+    int rem = bh;
+    if (g.nb > 0) { c0 = rem % g.bext[0]; rem /= g.bext[0]; }
+    if (g.nb > 1) { c1 = rem % g.bext[1]; rem /= g.bext[1]; }
+    if (g.nb > 2) { c2 = rem % g.bext[2]; }
+    if (lane == 0) {
+      abort_flag = 0;
+      mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1); mbar_init(bar_v + 8, 1);
+      mbar_init(bar_s, 1); mbar_init(bar_p, 8); mbar_init(bar_o, 1); mbar_init(bar_f, 8);
+      for (int i = 0; i < 4; i++) mbar_init(bar_x + 8 * i, 2);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      /* Q and the first block of keys and values are requested at once: block 0 is always processed (nothing can be
+       * left out before a running maximum exists), so these loads run under the rest of the set-up */
+      mbar_expect_tx(bar_q, 16384);
+      tma_load_5d(s_q, &map_q, bar_q, 0, qb * AT_BQ, c0, c1, c2);
+      mbar_expect_tx(bar_k, 16384);
+      tma_load_5d(s_k, &map_k, bar_k, 0, 0, c0, c1, c2);
+      mbar_expect_tx(bar_v, 16384);
+      tma_load_5d(s_v, &map_v, bar_v, 0, 0, c0, c1, c2);
+    }
+    __syncwarp();
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(256u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -444,7 +459,7 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         S = fabsf(g.scale) * qn * s_kn[j];
         skip = (c == c) && (c + S < lrun - 100.0f);
       }
-      if (!skip) { live |= 1ull << j; lrun = fmaxf(lrun, lmin - S); }
+      if (!skip || j == 0) { live |= 1ull << j; lrun = fmaxf(lrun, lmin - S); }
     }
     s_live = live;
   }
@@ -458,21 +473,7 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (lane == 0) {
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BK >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(AT_HD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-      int c0 = 0, c1 = 0, c2 = 0;
-      {
-        int rem = bh;
-        if (g.nb > 0) { c0 = rem % g.bext[0]; rem /= g.bext[0]; }
-        if (g.nb > 1) { c1 = rem % g.bext[1]; rem /= g.bext[1]; }
-        if (g.nb > 2) { c2 = rem % g.bext[2]; }
-      }
-      mbar_expect_tx(bar_q, 16384);
-      tma_load_5d(s_q, &map_q, bar_q, 0, qb * AT_BQ, c0, c1, c2);
-      unsigned long long rem = s_live;
-      const int j0 = __ffsll((long long)rem) - 1;          /* the first block is always processed */
-      mbar_expect_tx(bar_k, 16384);
-      tma_load_5d(s_k, &map_k, bar_k, 0, j0 * AT_BK, c0, c1, c2);
-      mbar_expect_tx(bar_v, 16384);
-      tma_load_5d(s_v, &map_v, bar_v, 0, j0 * AT_BK, c0, c1, c2);
+      unsigned long long rem = s_live;                     /* bit 0 is always set; its loads are under way */
       bool ok = mbar_wait(bar_q, 0, &abort_flag, 11) && mbar_wait(bar_k, 0, &abort_flag, 12);
       const uint64_t dq = make_smem_desc(s_q), dk = make_smem_desc(s_k);
       if (ok) {
@@ -566,14 +567,25 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
        * not negative, x is a non-decreasing function of s: the largest x is that of the largest s, and the scores
        * stay as they are (the exponent below is formed from them directly).  Otherwise x replaces s in place. */
       float m_part = __int_as_float(0xff800000);
-      const bool plain = tile_is_const && g.scale >= 0.0f;
+      const bool plain = tile_is_const && g.scale >= 0.0f, step = tile_is_step && g.scale >= 0.0f;
+      const float lo = s_lo[j], hi = s_hi[j];
+      const int thr = (int)s_d[j] + row - half * 64;        /* key k of the thread's 64 has the value lo where k > thr, else hi */
       if (plain) {
 #pragma unroll
         for (int i = 0; i < 32; i++) m_part = fmaxf(m_part, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
         m_part = fmaf(m_part, g.scale, tile_c);
+      } else if (step) {
+        /* two values: the largest score of either side of the step, then x of each (the scores stay as they are) */
+        float m_lo = __int_as_float(0xff800000), m_hi = m_lo;
+        const float ninf = m_lo;
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          const float a = __uint_as_float(r0[i]), b = __uint_as_float(r1[i]);
+          m_lo = fmaxf(m_lo, fmaxf(i > thr ? a : ninf, 32 + i > thr ? b : ninf));
+          m_hi = fmaxf(m_hi, fmaxf(i > thr ? ninf : a, 32 + i > thr ? ninf : b));
+        }
+        m_part = fmaxf(m_lo == ninf ? ninf : fmaf(m_lo, g.scale, lo), m_hi == ninf ? ninf : fmaf(m_hi, g.scale, hi));
       } else {
-        const float lo = s_lo[j], hi = s_hi[j];
-        const int thr = (int)s_d[j] + row - half * 64;        /* key index k within the thread's 64 has the upper value where k > thr */
         const float *mj = mrow + ((long long)j * AT_BK + half * 64) * g.mask_sk;
 #pragma unroll
         for (int c = 0; c < 2; c++) {
@@ -582,7 +594,7 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
             for (int i = 0; i < 32; i++) r[i] = __float_as_uint(fmaf(__uint_as_float(r[i]), g.scale, tile_c));
           } else if (tile_is_step) {
-            /* the entries of a step tile from the indices: no loads */
+            /* (negative scale) the entries of a step tile from the indices: no loads */
 #pragma unroll
             for (int i = 0; i < 32; i++) r[i] = __float_as_uint(fmaf(__uint_as_float(r[i]), g.scale, (c * 32 + i > thr) ? lo : hi));
           } else if (g.mask_vec) {
@@ -615,20 +627,38 @@ pb200_flash_attn2(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       const float alpha = fast_exp2((m_run - m_new) * LOG2E);
       /* probabilities p = exp2((x - m) log2e), two at a time (packed fp32 multiply-adds), packed as bf16 pairs over
        * the scores.  plain: x log2e - m log2e = s (scale log2e) + (c log2e - m log2e), one multiply-add per pair. */
-      const float2 mul2 = plain ? make_float2(g.scale * LOG2E, g.scale * LOG2E) : make_float2(LOG2E, LOG2E);
-      const float add1 = plain ? fmaf(tile_c, LOG2E, -m_scaled) : -m_scaled;
-      const float2 add2 = make_float2(add1, add1);
+      const bool raw = plain || step;                  /* r0, r1 still hold the scores */
+      const float2 mul2 = raw ? make_float2(g.scale * LOG2E, g.scale * LOG2E) : make_float2(LOG2E, LOG2E);
+      const float add_hi = plain ? fmaf(tile_c, LOG2E, -m_scaled) : step ? fmaf(hi, LOG2E, -m_scaled) : -m_scaled;
+      const float add_lo = step ? fmaf(lo, LOG2E, -m_scaled) : add_hi;
       float2 l2 = make_float2(0.0f, 0.0f);
+      if (step) {
 #pragma unroll
-      for (int c = 0; c < 2; c++) {
-        uint32_t (&r)[32] = c ? r1 : r0;
+        for (int c = 0; c < 2; c++) {
+          uint32_t (&r)[32] = c ? r1 : r0;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float2 e = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), mul2, add2);
-          const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
-          __nv_bfloat162 pb = __floats2bfloat162_rn(pp.x, pp.y);
-          l2 = __fadd2_rn(l2, pp);
-          r[i >> 1] = *reinterpret_cast<uint32_t *>(&pb);
+          for (int i = 0; i < 32; i += 2) {
+            const float2 add2 = make_float2(c * 32 + i > thr ? add_lo : add_hi, c * 32 + i + 1 > thr ? add_lo : add_hi);
+            const float2 e = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), mul2, add2);
+            const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+            __nv_bfloat162 pb = __floats2bfloat162_rn(pp.x, pp.y);
+            l2 = __fadd2_rn(l2, pp);
+            r[i >> 1] = *reinterpret_cast<uint32_t *>(&pb);
+          }
+        }
+      } else {
+        const float2 add2 = make_float2(add_hi, add_hi);
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          uint32_t (&r)[32] = c ? r1 : r0;
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float2 e = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), mul2, add2);
+            const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+            __nv_bfloat162 pb = __floats2bfloat162_rn(pp.x, pp.y);
+            l2 = __fadd2_rn(l2, pp);
+            r[i >> 1] = *reinterpret_cast<uint32_t *>(&pb);
+          }
         }
       }
       l_run = l_run * alpha + (l2.x + l2.y);
