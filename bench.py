@@ -516,7 +516,10 @@ def run_b200(args, cfg, rank, world, local_rank):
                         kind=args.gather, bytes_into_root_per_step=int(g_bytes * (world - 1)),
                         overlapped='snapshot on the main stream, NCCL send/recv on a second stream behind the next forward',
                         root_ingress_gbs=g_bytes * (world - 1) / (ms_step * 1e-3) / 1e9,
-                        nvlink_peer_copy_gbs=770.0)),
+                        nvlink_peer_copy_gbs=770.0,
+                        frac_of_nvlink=g_bytes * (world - 1) / (ms_step * 1e-3) / 1e9 / 770.0,
+                        note='rank 0 takes in the other ranks\' logits; 770 GB/s is the peer-copy rate measured on this pool '
+                             '(900 nominal per direction); from three ranks on the gather, not the forward, bounds `value`')),
                     e2e=dict(value=e2e_value, unit='tokens/s', h2d_bytes_per_step=int(tokens.nbytes),
                              d2h_bytes_per_step=int(out_bytes), ms_per_step=ms_e2e,
                              overlap='the device-to-host copy of step i runs on a second stream while step i+1 computes',
