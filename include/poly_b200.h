@@ -272,6 +272,8 @@ typedef struct {
   uint64_t bytes_allocated;     /* bytes currently held from the driver (live + cached) */
   uint64_t programs_compiled;   /* NVRTC compilations (cache misses) */
   uint64_t programs_cached;     /* programs served from the in-process or disk cache */
+  uint64_t bytes_htod;          /* bytes copied host -> device by poly_cuda_copy_htod */
+  uint64_t bytes_dtoh;          /* bytes copied device -> host by poly_cuda_copy_dtoh */
 } PolyB200Stats;
 void poly_b200_stats(PolyB200Stats *out);
 void poly_b200_stats_reset(void);
@@ -290,6 +292,17 @@ void poly_b200_stats_reset(void);
 struct PolyInstance;
 int poly_b200_instance_import_weights(struct PolyInstance *inst, const unsigned char *data, long long len,
                                       long long *bytes_to_device);
+
+/* The eager entry points (exported by libpolygrad_b200.so; declared in polygrad's src/frontend.h:424-430,
+ * defined by the reference at src/frontend.c:2444, 2450, 2670, 2676 and here in backend/pb_eager.c):
+ *   int  poly_realize_cuda(PolyCtx *, PolyUOp *sink, PolyBufferBinding *, int n)   host pointers in the bindings
+ *   int  poly_cuda_copyback(PolyBufferBinding *, int n)    results left on the device -> host
+ *   void poly_cuda_flush_buffers(void)                     drop what is left on the device, uncopied
+ *   void poly_cuda_prog_cache_flush(void)                  drop the kept plans
+ * poly_b200_eager_stats reports how many calls found a kept plan for their graph (compared by structure,
+ * buffers by position) and how many compiled one, the plans kept now and the results now on the device.
+ * Any pointer may be NULL. */
+void poly_b200_eager_stats(unsigned long long *hits, unsigned long long *misses, int *plans_kept, int *buffers_resident);
 
 /* Text of the last error reported by this library ("" if none). */
 const char *poly_b200_last_error(void);

@@ -51,7 +51,6 @@ PolyCompiledPlan *poly_ref_compile_schedule(PolyCtx *ctx, PolySchedule *schedule
 int poly_ref_compiled_plan_run(PolyCompiledPlan *plan, void **slot_data, int n_slots,
                                struct PolyVarBinding *var_bindings, int n_var_bindings);
 void poly_ref_compiled_plan_free(PolyCompiledPlan *plan);
-int poly_ref_realize_cuda(PolyCtx *ctx, PolyUOp *tensor_sink, PolyBufferBinding *bindings, int n_bindings);
 
 #define PB_MAX_PLANS 1024
 static PbPlan *g_plans[PB_MAX_PLANS];
@@ -476,59 +475,4 @@ void poly_compiled_plan_free(PolyCompiledPlan *plan) {
   plan_destroy(p);
 }
 
-/* ── the eager entry point ───────────────────────────────────────────── */
-/* poly_realize_cuda (reference: src/frontend.c:2450-2650; polygrad's Python
- * Tensor(device='cuda') calls it, py/polygrad/tensor.py:322-361) takes HOST
- * pointers in its bindings.  The reference schedules the graph, uploads every
- * binding into a device buffer it keeps per host pointer, runs the kernels one
- * by one (an allocation and a synchronisation each) and leaves the results on
- * the device for poly_cuda_copyback.  Here the schedule is compiled into a plan
- * like any other -- intermediates in one arena, copies elided, row chains and
- * attention fused -- and the plan runs with the host pointers bound directly:
- * buffers the steps read are uploaded, buffers they write are back in host
- * memory when the call returns.  poly_cuda_copyback then finds no device buffer
- * registered for these pointers and has nothing to do.
- *
- * The plan is built and freed per call, as the reference schedules per call:
- * its callers make a new output buffer, hence a new SINK, for every realize,
- * and polygrad's plan cache is keyed by the SINK's address (src/frontend.c:2135)
- * -- it would fill with entries that are never hit again.  Kernel programs are
- * still reused through the runtime's cache, which is keyed by program text.
- * Graphs with DEFINE_VAR parameters keep the reference route, as does
- * everything under POLY_B200_LEGACY=ref. */
-int poly_realize_cuda(PolyCtx *ctx, PolyUOp *tensor_sink, PolyBufferBinding *bindings, int n_bindings) {
-  if (env_is("POLY_B200_LEGACY", "ref") || env_is("POLY_B200_PLAN", "ref"))
-    return poly_ref_realize_cuda(ctx, tensor_sink, bindings, n_bindings);
-  if (!tensor_sink || tensor_sink->op != POLY_OP_SINK) {
-    fprintf(stderr, "polygrad: realize_cuda: expected SINK\n");
-    return -1;
-  }
-  if (!poly_cuda_available()) {
-    fprintf(stderr, "polygrad: realize_cuda: CUDA not available\n");
-    return -1;
-  }
-  PolySchedule *sched = poly_schedule_for(ctx, tensor_sink, POLY_MODE_CALL);
-  if (!sched) return -1;
-  PolyCompiledPlan *plan = poly_compile_schedule(ctx, sched, POLY_DEVICE_CUDA);
-  if (!plan || !as_pb_plan(plan)) {
-    if (plan) poly_compiled_plan_free(plan);
-    poly_schedule_free(sched);
-    return poly_ref_realize_cuda(ctx, tensor_sink, bindings, n_bindings);
-  }
-  int rc = -1;
-  void **slot_data = calloc((size_t)(sched->n_buf_slots > 0 ? sched->n_buf_slots : 1), sizeof(void *));
-  if (slot_data) {
-    for (int s = 0; s < sched->n_buf_slots; s++) {
-      if (sched->buf_slots[s].is_intermediate) continue;
-      for (int b = 0; b < n_bindings; b++)
-        if (bindings[b].buffer == sched->buf_slots[s].buf_uop) { slot_data[s] = bindings[b].handle.ptr; break; }
-    }
-    rc = poly_compiled_plan_run(plan, slot_data, sched->n_buf_slots, NULL, 0);
-    /* results must not depend on anything the plan owns once it is gone */
-    if (rc == 0 && poly_b200_synchronize() != 0) rc = -1;
-    free(slot_data);
-  }
-  poly_compiled_plan_free(plan);
-  poly_schedule_free(sched);
-  return rc;
-}
+PbPlan *pb_plan_of(PolyCompiledPlan *plan) { return plan ? as_pb_plan(plan) : NULL; }

@@ -53,6 +53,9 @@ typedef struct {
 
 enum { PB_ACC_READ = 1, PB_ACC_WRITE = 2 };
 
+/* The plan behind a handle, NULL when the handle is one of polygrad's own plans (pb_exec_plan.c). */
+PbPlan *pb_plan_of(PolyCompiledPlan *plan);
+
 int  pb_plan_resolve(const PbPlan *p, int slot);
 int  pb_plan_add_slot(PbPlan *p, int64_t bytes);
 void pb_step_release(PbStep *st);

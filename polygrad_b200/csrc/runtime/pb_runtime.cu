@@ -402,6 +402,7 @@ extern "C" int poly_cuda_copy_htod(unsigned long long dst, const void *src, size
   auto it = find_buf(p);
   char mode = (it != R.live.end() && (uintptr_t)p == it->first && bytes >= it->second.requested) ? 'W' : 'w';
   if (note_access(p, mode) != 0) return -1;
+  R.st.bytes_htod += bytes;
   if (R.dry) { memcpy(p, src, bytes); return 0; }
   /* pageable sources are staged before the call returns, pinned ones are not:
    * wait so that the caller may reuse src in both cases */
@@ -500,6 +501,7 @@ extern "C" int poly_cuda_copy_dtoh(void *dst, unsigned long long src, size_t byt
   void *p = (void *)(uintptr_t)src;
   g_last_dtoh_src = src;
   if (note_access(p, 'r') != 0) return -1;
+  R.st.bytes_dtoh += bytes;
   if (R.dry) { memcpy(dst, p, bytes); return 0; }
   if (R.defer && !R.capturing && bytes >= ((size_t)1 << 20)) {
     cudaPointerAttributes attr;

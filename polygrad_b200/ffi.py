@@ -53,7 +53,7 @@ class GPT2Config(ctypes.Structure):
 class PolyB200Stats(ctypes.Structure):
     _fields_ = [(n, ctypes.c_uint64) for n in (
         'launches', 'launches_precompiled', 'launches_generated', 'memsets_elided',
-        'memsets_executed', 'bytes_allocated', 'programs_compiled', 'programs_cached')]
+        'memsets_executed', 'bytes_allocated', 'programs_compiled', 'programs_cached', 'bytes_htod', 'bytes_dtoh')]
 
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
@@ -186,6 +186,12 @@ def _declare_cuda(lib):
          [_ptr, ctypes.c_char_p, ctypes.POINTER(ctypes.POINTER(ctypes.c_float)), ctypes.c_int, ctypes.c_int, S, _ptr,
           ctypes.c_int, ctypes.c_int])
     _sig(lib, 'poly_b200_readback_wait', ctypes.c_int, [])
+    _sig(lib, 'poly_realize_cuda', ctypes.c_int, [_ptr, _ptr, ctypes.POINTER(PolyBufferBinding), ctypes.c_int])
+    _sig(lib, 'poly_cuda_copyback', ctypes.c_int, [ctypes.POINTER(PolyBufferBinding), ctypes.c_int])
+    _sig(lib, 'poly_cuda_flush_buffers', None, [])
+    _sig(lib, 'poly_cuda_prog_cache_flush', None, [])
+    _sig(lib, 'poly_b200_eager_stats', None, [ctypes.POINTER(ctypes.c_ulonglong), ctypes.POINTER(ctypes.c_ulonglong),
+                                              ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)])
     _sig(lib, 'poly_b200_event_create', _ptr, [])
     _sig(lib, 'poly_b200_event_record', ctypes.c_int, [_ptr])
     _sig(lib, 'poly_b200_event_elapsed_ms', ctypes.c_float, [_ptr, _ptr])
@@ -221,6 +227,14 @@ class Library:
         st = PolyB200Stats()
         self.c.poly_b200_stats(ctypes.byref(st))
         return {n: getattr(st, n) for n, _ in PolyB200Stats._fields_}
+
+    def eager_stats(self):
+        """Counters of the eager entry point: calls that found a kept plan, calls that compiled one,
+        plans kept now, results now left on the device."""
+        hits, misses = ctypes.c_ulonglong(), ctypes.c_ulonglong()
+        kept, resident = ctypes.c_int(), ctypes.c_int()
+        self.c.poly_b200_eager_stats(ctypes.byref(hits), ctypes.byref(misses), ctypes.byref(kept), ctypes.byref(resident))
+        return dict(hits=hits.value, misses=misses.value, plans_kept=kept.value, buffers_resident=resident.value)
 
     def last_error(self):
         return self.c.poly_b200_last_error().decode(errors='replace')

@@ -126,3 +126,35 @@ def test_fully_masked_rows_and_nan_mask_tiles(gpu, monkeypatch):
     mask[200, 7] = np.nan
     a, b = both_ways(gpu, monkeypatch, q, k, v, mask, np.float32(0.125))
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32), )
+
+
+@pytest.mark.parametrize('case', ['offset5', 'shifted200', 'one_entry_off', 'negative_scale', 'inf_above'])
+def test_step_tiles_are_formed_from_indices_exactly(gpu, monkeypatch, case):
+    """Mask tiles of the form (c - r > d ? lo : hi) -- the diagonal tiles of a causal mask -- are recognised by
+    the classification kernel (checked against all 16384 entries) and their entries come from the indices
+    instead of being loaded.  Other offsets and values, a step that crosses off-diagonal tiles, a mask that
+    misses the form by one entry (general path), a negative scale (entries synthesised, x formed in place) and
+    -inf above the step: each against the chain on bf16-rounded q, k, v (1e-2), with and without block skipping
+    bit for bit."""
+    T = 512 if case == 'shifted200' else 256
+    rng = np.random.default_rng(sum(map(ord, case)))
+    q, k, v = (rng.standard_normal((2, T, 2, 64)).astype(np.float32) for _ in range(3))
+    r, c = np.arange(T)[:, None], np.arange(T)[None, :]
+    scale = np.float32(0.125)
+    if case == 'offset5':
+        mask = np.where(c - r > 5, np.float32(-1e4), np.float32(0.5))
+    elif case == 'shifted200':
+        mask = np.where(c - r > 200, np.float32(-1e9), np.float32(-0.25))
+    elif case == 'one_entry_off':
+        mask = np.where(c > r, np.float32(-1e9), np.float32(0))
+        mask[77, 30] = np.float32(-3.0)          # below the diagonal: the tile is no step tile any more
+        mask[140, 150] = np.float32(-2.0)        # above it, in the second diagonal tile
+    elif case == 'negative_scale':
+        mask = np.where(c > r, np.float32(-1e9), np.float32(0))
+        scale = np.float32(-0.125)
+    else:
+        mask = np.where(c > r, np.float32(-np.inf), np.float32(0))
+    mask = np.ascontiguousarray(mask, dtype=np.float32)
+    a, b = both_ways(gpu, monkeypatch, q, k, v, mask, scale)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    assert_close(a, reference(bf16(q), bf16(k), bf16(v), mask, scale), 1e-2, case)

@@ -178,3 +178,59 @@ def test_training_plan_in_dry_run():
     # every bound buffer that is written (parameters, logits are not part of this plan, loss) has one writer
     written = [a for _, args in steps for a in args.split() if a[0] in 'Wwb' and a.endswith('x')]
     assert len(written) == len(set(written)) and len(written) >= 17
+
+
+DRY_EAGER = '''
+import json, sys
+sys.path.insert(0, %(root)r)
+import numpy as np
+from polygrad_b200 import ffi
+from polygrad_b200.tensor import Device
+lib = ffi.product()
+assert lib.poly_cuda_init() == 0
+
+def bindings(pairs):
+    b = (ffi.PolyBufferBinding * len(pairs))()
+    for i, (buf, host) in enumerate(pairs):
+        b[i].buffer = buf; b[i].handle.ptr = host.ctypes.data
+        b[i].handle.nbytes = host.nbytes; b[i].handle.domain = ffi.DEVICE_CPU
+    return b
+
+dev = Device(lib, ffi.DEVICE_CUDA)
+x = np.arange(64 * 32, dtype=np.float32).reshape(64, 32)
+log = []
+for i in range(4):
+    t = dev.tensor(x + i).softmax(-1)
+    out_buf = lib.poly_buffer_by_id(dev.ctx, t.numel(), ffi.DTYPE_IDS['float32'])
+    out = np.full(t.numel(), 7.0, np.float32)
+    sink = lib.poly_sink1(dev.ctx, lib.poly_store_val(dev.ctx, out_buf, t.uop))
+    pairs = list(t.leaves) + [(out_buf, out)]
+    assert lib.poly_realize_cuda(dev.ctx, sink, bindings(pairs), len(pairs)) == 0
+    after_run = dict(lib.eager_stats(), untouched=bool((out == 7).all()), **lib.stats())
+    assert lib.poly_cuda_copyback(bindings(pairs), len(pairs)) == 0
+    log.append([after_run, dict(lib.eager_stats(), **lib.stats())])
+dev.close()
+log.append(lib.eager_stats())
+print(json.dumps(log))
+'''
+
+
+def test_eager_entry_keeps_plans_and_results_in_dry_run():
+    """The eager entry point's bookkeeping, with no device: the second and later calls (new leaves,
+    new output buffer, new SINK) find the first call's plan; only the buffer the graph reads is
+    uploaded; the result is left where the plan wrote it until poly_cuda_copyback, which copies that
+    buffer alone; destroying the context releases the plan."""
+    import json
+    env = dict(os.environ, POLY_B200_DRYRUN='1', POLY_B200_DRYRUN_NOCOMPILE='1')
+    env.pop('POLY_B200_LEGACY', None)
+    r = subprocess.run([sys.executable, '-c', DRY_EAGER % dict(root=ROOT)], env=env, capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stderr[-4000:]
+    log = json.loads(r.stdout.strip().splitlines()[-1])
+    nbytes = 64 * 32 * 4
+    for i, (ran, copied) in enumerate(log[:4]):
+        assert ran['misses'] == 1 and ran['hits'] == i and ran['plans_kept'] == 1
+        assert ran['buffers_resident'] == 1 and ran['untouched']
+        assert ran['bytes_htod'] == (i + 1) * nbytes and ran['bytes_dtoh'] == i * nbytes
+        assert copied['buffers_resident'] == 0 and copied['bytes_dtoh'] == (i + 1) * nbytes
+    assert log[4]['plans_kept'] == 0 and log[4]['buffers_resident'] == 0

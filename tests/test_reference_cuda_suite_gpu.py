@@ -33,7 +33,7 @@ def test_polygrad_cuda_suite_passes_on_this_backend(gpu):
         pytest.skip('oracle/_ref/polygrad_cuda_test not built (make -C oracle cuda_tests, needs the polygrad checkout)')
     env = dict(os.environ, PATH=os.path.join(ROOT, 'oracle', 'shim') + os.pathsep + os.environ.get('PATH', ''))
     r = subprocess.run([BINARY, 'cuda'], env=env, capture_output=True, text=True, timeout=600)
-    results = dict((name, verdict) for verdict, name in re.findall(r'\[(PASS|FAIL)\] (\w+)', r.stdout))
+    results = dict((name, outcome) for outcome, name in re.findall(r'\[(PASS|FAIL)\] (\w+)', r.stdout))
     assert GPU_TESTS <= set(results), (sorted(results), r.stdout[-2000:], r.stderr[-2000:])
     failed = sorted(n for n in GPU_TESTS if results[n] != 'PASS')
     assert not failed, (failed, r.stdout[-3000:], r.stderr[-3000:])
