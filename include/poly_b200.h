@@ -211,6 +211,23 @@ int    poly_b200_comm_wait(void);
 int    poly_b200_comm_max(double *value);
 void   poly_b200_comm_destroy(void);
 
+/* Data-parallel training steps.  polygrad builds one plan per training step in which every gradient is
+ * fused into the update of its parameter (src/instance.c:1150-1215), so there is no gradient buffer to
+ * reduce; for plain SGD, p - lr * g is linear in g and averaging the UPDATED parameters over the ranks
+ * equals one step on the mean gradient.  While update averaging is on (also POLY_B200_AVERAGE_UPDATES=1),
+ * every plan that updates bound buffers in place (poly_instance_train_step's) all-reduces each bound float32
+ * buffer it writes -- parameters and the loss -- with ncclAvg right after the step that writes it last; the
+ * all-reduces run on the communicator's stream behind the rest of the backward pass, and the plan returns
+ * with the main stream ordered after them.  Such plans run launch by launch (no CUDA graph).  With Adam the
+ * moments are averaged as well, which is local-step averaging, not a step on the mean gradient.
+ * Every rank must run the same plan: poly_b200_average_trace returns the number of all-reduces issued so far
+ * and a running hash of their element counts, equal on all ranks when they did. */
+void poly_b200_set_update_averaging(int on);
+int  poly_b200_update_averaging(void);
+int  poly_b200_average_enqueue(void *ptr, size_t count);   /* float32, in place, behind the main stream's work so far */
+int  poly_b200_average_join(void);                          /* main stream waits for the all-reduces enqueued so far */
+void poly_b200_average_trace(unsigned long long *calls, unsigned long long *hash);
+
 /* This rank's share of a global batch as n_micro forwards of one instance (exported by
  * libpolygrad_b200.so; poly_instance_forward, polygrad src/instance.c:830, runs one batch of
  * the instance's static shape).  inputs[i] is micro-batch i's host array for the input buffer

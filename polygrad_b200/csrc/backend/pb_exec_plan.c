@@ -45,6 +45,8 @@ int poly_b200_memset_now(unsigned long long ptr, unsigned char val, size_t bytes
 int poly_b200_timing_active(void);
 int poly_b200_ptr_on_host(const void *p);
 int poly_b200_note_access(const void *p, char mode);
+int poly_b200_average_enqueue(void *ptr, size_t count);
+int poly_b200_average_join(void);
 
 /* the original plan code, compiled under other names */
 PolyCompiledPlan *poly_ref_compile_schedule(PolyCtx *ctx, PolySchedule *schedule, PolyDeviceId device);
@@ -202,6 +204,7 @@ static void plan_destroy(PbPlan *p) {
   free(p->zero_step); free(p->zero_slot); free(p->graph_ext); free(p->graph_acc_ptr); free(p->graph_acc_mode);
   if (p->stage) for (int i = 0; i < p->n_sched_slots; i++) if (p->stage[i]) poly_cuda_free(p->stage[i]);
   free(p->stage); free(p->slot_acc); free(p->ext_seen); free(p->ext_host);
+  free(p->avg_at); free(p->avg_slot);
   free(p->base.slot_to_data);
   free(p);
 }
@@ -278,6 +281,31 @@ PolyCompiledPlan *poly_compile_schedule(PolyCtx *ctx, PolySchedule *sched, PolyD
     }
   }
 
+  /* where a data-parallel training step averages what it wrote: after the last write of each bound
+   * float32 buffer of a plan that updates in place (parameters, the loss) */
+  if (pb_plan_updates_in_place(p)) {
+    const int n = sched->n_buf_slots;
+    int *last = malloc(sizeof(int) * (size_t)(n > 0 ? n : 1));
+    p->avg_at = malloc(sizeof(int) * (size_t)(n > 0 ? n : 1));
+    p->avg_slot = malloc(sizeof(int) * (size_t)(n > 0 ? n : 1));
+    for (int i = 0; i < n; i++) last[i] = -1;
+    for (int s = 0; s < p->n_steps; s++) {
+      const PbStep *st = &p->steps[s];
+      if (st->dead) continue;
+      for (int a = 0; a < st->n_params; a++) {
+        int sl = pb_plan_resolve(p, st->slot[a]);
+        char m = st->rw[a];
+        if (sl >= 0 && sl < n && !p->slot_inter[sl] && (m == 'w' || m == 'W' || m == 'b')) last[sl] = s;
+      }
+    }
+    for (int s = 0; s < p->n_steps; s++)
+      for (int i = 0; i < n; i++)
+        if (last[i] == s && poly_dtype_eq(poly_dtype_scalar(sched->buf_slots[i].dtype), POLY_FLOAT32)) {
+          p->avg_at[p->n_avg] = s; p->avg_slot[p->n_avg] = i; p->n_avg++;
+        }
+    free(last);
+  }
+
   /* fields other polygrad code may look at */
   p->base.n_slot_to_data = sched->n_buf_slots;
   p->base.slot_to_data = calloc((size_t)(sched->n_buf_slots > 0 ? sched->n_buf_slots : 1), sizeof(void *));
@@ -310,8 +338,21 @@ PolyCompiledPlan *poly_compile_schedule(PolyCtx *ctx, PolySchedule *sched, PolyD
 }
 
 /* ── run ─────────────────────────────────────────────────────────────── */
+static int g_average_updates = -1;
+static bool average_updates(void) {
+  if (g_average_updates < 0) { const char *e = getenv("POLY_B200_AVERAGE_UPDATES"); g_average_updates = (e && e[0] == '1') ? 1 : 0; }
+  return g_average_updates == 1;
+}
+/* Data-parallel training (there is nothing like it in the reference: one device, src/runtime_cuda.c:192):
+ * while on, every plan that updates bound buffers in place averages each of them over the ranks of the
+ * communicator (poly_b200_comm_init) right after the step that writes it last, behind the rest of
+ * the plan.  Exact for plain SGD, whose update is linear in the gradient. */
+void poly_b200_set_update_averaging(int on) { g_average_updates = on ? 1 : 0; }
+int  poly_b200_update_averaging(void) { return average_updates() ? 1 : 0; }
+
 static int run_eager(PbPlan *p) {
-  int zi = 0;
+  int zi = 0, ai = 0;
+  const bool avg = p->n_avg > 0 && average_updates();
   for (int s = 0; s < p->n_steps; s++) {
     for (zi = 0; zi < p->n_zero; zi++)
       if (p->zero_step[zi] == s) {
@@ -330,7 +371,13 @@ static int run_eager(PbPlan *p) {
       }
     }
     if (poly_cuda_launch(st->prog, st->argv, st->n_params, 1, 1, 1, 256, 1, 1) != 0) return -1;
+    for (; avg && ai < p->n_avg && p->avg_at[ai] <= s; ai++) {
+      const int sl = p->avg_slot[ai];
+      if (p->avg_at[ai] == s && p->slot_ptr[sl] &&
+          poly_b200_average_enqueue(p->slot_ptr[sl], (size_t)p->slot_bytes[sl] / sizeof(float)) != 0) return -1;
+    }
   }
+  if (avg && poly_b200_average_join() != 0) return -1;
   return 0;
 }
 
@@ -432,7 +479,8 @@ int poly_compiled_plan_run(PolyCompiledPlan *plan, void **slot_data, int n_slots
 static int run_steps(PbPlan *p) {
   p->runs++;
   const bool graphs = !env_is("POLY_B200_GRAPH", "0") && p->graph_failures < 4 && !getenv("POLY_B200_DRYRUN") &&
-                      !poly_b200_timing_active();      /* per-launch timing needs individual launches */
+                      !poly_b200_timing_active() &&    /* per-launch timing needs individual launches */
+                      !(p->n_avg > 0 && average_updates());   /* collectives are issued between the launches */
   if (graphs && graph_valid(p)) {
     /* what the launches of an eager run tell the runtime about bound buffers: pending zero fills
      * are materialised or dropped, and written buffers get a new version, so that converted

@@ -452,7 +452,7 @@ static int fuse_attention(PbPlan *p) {
  * work later in the list (a producer into the chain that consumes it, a copy
  * into the strides of its readers) on the assumption that a buffer written once
  * keeps its value; such a plan therefore runs its steps as scheduled. */
-static bool updates_in_place(const PbPlan *p) {
+bool pb_plan_updates_in_place(const PbPlan *p) {
   PbSlotUse *u = malloc(sizeof(PbSlotUse) * (size_t)p->n_slots);
   pb_slot_usage(p, u);
   bool found = false;
@@ -463,7 +463,7 @@ static bool updates_in_place(const PbPlan *p) {
 }
 
 void pb_plan_fuse(PbPlan *p) {
-  if (updates_in_place(p)) {
+  if (pb_plan_updates_in_place(p)) {
     if (getenv("POLY_B200_DEBUG")) fprintf(stderr, "pb_fuse: plan updates bound buffers in place; steps run as scheduled\n");
     return;
   }

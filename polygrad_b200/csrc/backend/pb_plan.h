@@ -49,6 +49,9 @@ typedef struct {
   long long graph_kernels, graph_precompiled;
   void **graph_acc_ptr; char *graph_acc_mode; int n_graph_acc;   /* accesses to bound buffers a replay reports */
   int runs, graph_failures;
+  /* a plan that updates bound buffers in place (a training step): after step avg_at[i] nothing in the
+   * plan writes bound float32 slot avg_slot[i] any more; sorted by step */
+  int *avg_at, *avg_slot, n_avg;
 } PbPlan;
 
 enum { PB_ACC_READ = 1, PB_ACC_WRITE = 2 };
@@ -62,6 +65,8 @@ void pb_step_release(PbStep *st);
 
 /* Rewrites the step list in place (pb_fuse.c). */
 void pb_plan_fuse(PbPlan *p);
+/* Does some step read a bound buffer that another step writes (an optimizer step does)? */
+bool pb_plan_updates_in_place(const PbPlan *p);
 
 /* Helpers shared by the passes. */
 typedef struct { int writers, readers, first_write, last_write, last_read; } PbSlotUse;

@@ -1,6 +1,7 @@
 /*
- * pb_comm.cu -- the one collective of the data-parallel forward path: gathering
- * every rank's logits to a root rank over NVLink with NCCL.
+ * pb_comm.cu -- the collectives of the data-parallel paths: gathering every
+ * rank's logits to a root rank (forward), and averaging what a training step
+ * wrote over the ranks (see the end of the file), over NVLink with NCCL.
  *
  * polygrad has no multi-device execution at all (its CUDA runtime is a singleton
  * on device 0, reference src/runtime_cuda.c:192-243).  Here one process drives one
@@ -47,6 +48,10 @@ static struct {
   cudaEvent_t ready[2] = {nullptr, nullptr}, done[2] = {nullptr, nullptr};
   bool used[2] = {false, false};
   int next = 0;
+  /* averaging of updated buffers */
+  cudaEvent_t avg_ready = nullptr, avg_done = nullptr;
+  bool avg_pending = false;
+  unsigned long long avg_calls = 0, avg_trace = 1469598103934665603ull;
 } CM;
 
 static bool load_nccl() {
@@ -194,5 +199,54 @@ extern "C" void poly_b200_comm_destroy(void) {
   }
   if (CM.comm && NC.CommDestroy) NC.CommDestroy(CM.comm);
   if (CM.stream) cudaStreamDestroy(CM.stream);
+  if (CM.avg_ready) cudaEventDestroy(CM.avg_ready);
+  if (CM.avg_done) cudaEventDestroy(CM.avg_done);
+  CM.avg_ready = CM.avg_done = nullptr; CM.avg_pending = false;
   CM.comm = nullptr; CM.stream = nullptr; CM.rank = -1; CM.world = 0; CM.next = 0;
+}
+
+/* ── averaging what a training step wrote ────────────────────────────── */
+/* polygrad fuses every gradient into the update of its parameter inside one
+ * plan (reference src/instance.c:1150-1215: ASSIGN(p, p - lr * grad) per
+ * parameter, all in one SINK), so a data-parallel step has no gradient buffer
+ * to reduce.  For plain SGD the update is linear in the gradient:
+ *     mean_r(p - lr * g_r) = p - lr * mean_r(g_r),
+ * so averaging each parameter over the ranks right after its update gives
+ * exactly the parameters of one step on the mean gradient.  The plan executor
+ * calls poly_b200_average_enqueue after the last step that writes a bound
+ * buffer: the all-reduce runs on the second stream behind the rest of the
+ * backward pass, and poly_b200_average_join makes the main stream wait for
+ * all of them before the plan returns.  Every rank issues the same calls in
+ * the same order (same plan), which is what NCCL requires;
+ * poly_b200_average_trace exposes a running hash of the sizes to check that. */
+extern "C" int poly_b200_average_enqueue(void *ptr, size_t count) {
+  if (!ptr || count == 0) { pb_set_error("poly_b200_average_enqueue: bad arguments"); return -1; }
+  CM.avg_calls++;
+  CM.avg_trace = (CM.avg_trace ^ (unsigned long long)count) * 1099511628211ull;
+  if (pb_dry_run() || CM.world <= 1) return 0;
+  cudaStream_t main_stream = (cudaStream_t)poly_b200_stream();
+  if (poly_b200_note_access(ptr, 'b') != 0) return -1;
+  if (!CM.avg_ready) {
+    PB_CU(cudaEventCreateWithFlags(&CM.avg_ready, cudaEventDisableTiming));
+    PB_CU(cudaEventCreateWithFlags(&CM.avg_done, cudaEventDisableTiming));
+  }
+  PB_CU(cudaEventRecord(CM.avg_ready, main_stream));
+  PB_CU(cudaStreamWaitEvent(CM.stream, CM.avg_ready, 0));
+  PB_NCCL(NC.AllReduce(ptr, ptr, count, ncclFloat32, ncclAvg, CM.comm, CM.stream));
+  CM.avg_pending = true;
+  return 0;
+}
+
+extern "C" int poly_b200_average_join(void) {
+  if (!CM.avg_pending) return 0;
+  cudaStream_t main_stream = (cudaStream_t)poly_b200_stream();
+  PB_CU(cudaEventRecord(CM.avg_done, CM.stream));
+  PB_CU(cudaStreamWaitEvent(main_stream, CM.avg_done, 0));
+  CM.avg_pending = false;
+  return 0;
+}
+
+extern "C" void poly_b200_average_trace(unsigned long long *calls, unsigned long long *hash) {
+  if (calls) *calls = CM.avg_calls;
+  if (hash) *hash = CM.avg_trace;
 }

@@ -181,6 +181,11 @@ def _declare_cuda(lib):
     _sig(lib, 'poly_b200_comm_wait', ctypes.c_int, [])
     _sig(lib, 'poly_b200_comm_max', ctypes.c_int, [ctypes.POINTER(ctypes.c_double)])
     _sig(lib, 'poly_b200_comm_destroy', None, [])
+    _sig(lib, 'poly_b200_set_update_averaging', None, [ctypes.c_int])
+    _sig(lib, 'poly_b200_update_averaging', ctypes.c_int, [])
+    _sig(lib, 'poly_b200_average_enqueue', ctypes.c_int, [_ptr, S])
+    _sig(lib, 'poly_b200_average_join', ctypes.c_int, [])
+    _sig(lib, 'poly_b200_average_trace', None, [ctypes.POINTER(ctypes.c_ulonglong), ctypes.POINTER(ctypes.c_ulonglong)])
     _sig(lib, 'poly_b200_shard_micro_index', ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int])
     _sig(lib, 'poly_b200_forward_microbatches', ctypes.c_int,
          [_ptr, ctypes.c_char_p, ctypes.POINTER(ctypes.POINTER(ctypes.c_float)), ctypes.c_int, ctypes.c_int, S, _ptr,

@@ -59,6 +59,30 @@ def main():
                        x_last=np.asarray(inst.read('x')).reshape(-1)[:4].tolist(),
                        x_want=micro[-1].reshape(-1)[:4].tolist()), open(out_path, 'w'))
     inst.free()
+
+    # a data-parallel training step: every rank must issue the same all-reduces in the same order
+    trainer = Instance.gpt2(lib, **CFG)
+    trainer.init_params(gpt2_init(2))
+    trainer.set_device(ffi.DEVICE_CUDA)
+    trainer.set_optimizer(ffi.OPTIM_SGD, 1e-2)
+    lib.poly_b200_set_update_averaging(1)
+    calls, trace = ctypes.c_ulonglong(), ctypes.c_ulonglong()
+    per_step = []
+    for step in range(3):
+        trainer.train_step(**trainer.gpt2_inputs(micro[step]))
+        lib.poly_b200_average_trace(ctypes.byref(calls), ctypes.byref(trace))
+        per_step.append([calls.value, trace.value])
+    lib.poly_b200_set_update_averaging(0)
+    trainer.train_step(**trainer.gpt2_inputs(micro[0]))
+    lib.poly_b200_average_trace(ctypes.byref(calls), ctypes.byref(trace))
+    mine = dict(per_step=per_step, after_off=calls.value, n_params=lib.poly_instance_param_count(trainer.h))
+    traces = [None] * world if rank == 0 else None
+    dist.gather_object(mine, traces, dst=0)
+    if rank == 0:
+        result = json.load(open(out_path))
+        result['averaging'] = traces
+        json.dump(result, open(out_path, 'w'))
+    trainer.free()
     lib.poly_b200_comm_destroy()
     dist.barrier()
     dist.destroy_process_group()

@@ -69,3 +69,12 @@ def test_two_ranks_drive_the_micro_batch_loop(tmp_path):
     assert r['world'] == 2 and r['uniform']
     assert r['order'] == [0, 1, 0, 1, 0, 1]          # slot i * world + r holds rank r's micro-batch i
     assert r['x_last'] == r['x_want']
+    # data-parallel training steps: with update averaging on, each step of each rank issues one
+    # all-reduce per parameter plus one for the loss, the same sizes in the same order on both ranks
+    # (NCCL matches collectives by order); with it off, none
+    a0, a1 = r['averaging']
+    n = a0['n_params']
+    assert n > 0 and a0['per_step'] == a1['per_step']
+    assert [c for c, _ in a0['per_step']] == [n + 1, 2 * (n + 1), 3 * (n + 1)]
+    assert len({h for _, h in a0['per_step']}) == 3
+    assert a0['after_off'] == 3 * (n + 1) and a1['after_off'] == 3 * (n + 1)
