@@ -783,56 +783,106 @@ def run_mlp(args):
 
 
 TRAIN_CFG = dict(vocab_size=2048, n_embd=256, n_head=4, n_layer=4, max_seq_len=128, max_batch=4)
+# 67 M parameters (268 MB to average per step): enough for the averaging to run between the launches
+TRAIN_CFG_MEDIUM = dict(vocab_size=50257, n_embd=768, n_head=12, n_layer=4, max_seq_len=256, max_batch=8)
 
 
 def run_train(args):
     """One optimizer step (forward, backward, SGD update in one plan) of a small GPT-2 through
-    poly_instance_train_step on the device, with the CPU reference timed on the same configuration."""
+    poly_instance_train_step on the device, with the CPU reference timed on the same configuration.
+    On N ranks every rank steps on its own tokens and the backend averages each updated parameter over
+    the ranks behind the rest of the backward pass (data-parallel SGD); the step time is the max over
+    ranks and is given with and without the averaging."""
     from polygrad_b200 import ffi
     from polygrad_b200.instance import Instance, gpt2_init
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
     lib = ffi.product()
     lib.poly_b200_set_device(int(os.environ.get('LOCAL_RANK', '0')))
     if lib.poly_cuda_init() != 0:
         raise SystemExit('bench: no usable B200: ' + lib.last_error())
-    cfg = TRAIN_CFG
-    tokens = np.random.default_rng(SEED).integers(0, cfg['vocab_size'], (cfg['max_batch'], cfg['max_seq_len']))
+    dist = comm_setup(lib, rank, world) if world > 1 else None
+    cfg = TRAIN_CFG_MEDIUM if args.train_config == 'medium' else TRAIN_CFG
+    tokens = np.random.default_rng(SEED + rank).integers(0, cfg['vocab_size'], (cfg['max_batch'], cfg['max_seq_len']))
     n_tok = cfg['max_batch'] * cfg['max_seq_len']
 
-    def steps_of(library, device, warmup, steps):
+    def steps_of(library, device, warmup, steps, averaging=False):
         inst = Instance.gpt2(library, **cfg)
         inst.init_params(gpt2_init(SEED))
         if device != ffi.DEVICE_CPU:
             inst.set_device(device)
+            library.poly_b200_set_update_averaging(1 if averaging else 0)
         inst.set_optimizer(ffi.OPTIM_SGD, 1e-6)
         io = inst.gpt2_inputs(tokens)
         losses = [inst.train_step(**io) for _ in range(warmup)]
         if device != ffi.DEVICE_CPU:
             library.poly_b200_synchronize()
             library.poly_b200_stats_reset()
+            if dist is not None:
+                dist.barrier()
         t0 = time.perf_counter()
         losses += [inst.train_step(**io) for _ in range(steps)]
         ms = (time.perf_counter() - t0) / steps * 1e3
+        if device != ffi.DEVICE_CPU:
+            library.poly_b200_set_update_averaging(0)
+            if dist is not None:
+                t = ctypes.c_double(ms)
+                library.poly_b200_comm_max(ctypes.byref(t))
+                ms = t.value
         inst.free()
         return ms, losses
 
     warm = max(args.warmup, 3)
-    ms, losses = steps_of(lib, ffi.DEVICE_CUDA, warm, args.steps)
+    ms_alone, losses = steps_of(lib, ffi.DEVICE_CUDA, warm, args.steps)
     st = lib.stats()
+    ms = ms_alone
+    averaging = None
+    if world > 1:
+        n_par = sum(int(np.prod(shape)) for _, shape, role in _train_param_shapes(lib, cfg))
+        ms, _ = steps_of(lib, ffi.DEVICE_CUDA, warm, args.steps, averaging=True)
+        calls = ctypes.c_ulonglong()
+        lib.poly_b200_average_trace(ctypes.byref(calls), None)
+        forced = {}
+        for name, flag in (('between_the_launches', '1'), ('after_the_plan', '0')):
+            os.environ['POLY_B200_AVERAGE_INLINE'] = flag
+            forced[name] = steps_of(lib, ffi.DEVICE_CUDA, warm, args.steps, averaging=True)[0]
+        del os.environ['POLY_B200_AVERAGE_INLINE']
+        averaging = dict(ms_per_step=ms, ms_per_step_without=ms_alone, ms_per_step_forced=forced,
+                         allreduces_per_step=calls.value // (warm + args.steps),
+                         float32_averaged_per_step=n_par + 1, mbytes_averaged_per_step=(n_par + 1) * 4 / 1e6,
+                         placement='between the launches' if (n_par + 1) * 4 >= 64 << 20 else 'after the plan',
+                         note='ncclAvg per parameter on a second stream; plans with 64 MB or more to average issue each '
+                              'all-reduce after the parameter\'s update step, smaller ones keep their CUDA graph and '
+                              'average after it')
     cpu = None
     ref_path = os.path.join(ROOT, 'oracle', '_ref', 'libpolygrad_ref.so')
-    if os.path.isfile(ref_path) and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and os.path.isfile(ref_path) and not args.no_cpu_baseline:
         cms, closses = steps_of(ffi.load_reference(ref_path), ffi.DEVICE_CPU, 1, 2)
         cpu = dict(value=n_tok / (cms * 1e-3), unit='tokens/s', cores=1, kind='reference', ms_per_step=cms,
                    sample='same configuration, 2 steps after 1 warm-up',
                    loss_rel_diff_step0=abs(losses[0] - closses[0]) / abs(closses[0]))
-    print(json.dumps(dict(metric='train_tokens_per_s', value=n_tok / (ms * 1e-3), unit='tokens/s', n_gpus=1,
-                          steps=args.steps, warmup=warm, ms_per_step=ms, higher_is_better=True, dtype='f32',
-                          data='synthetic',
-                          config=dict(workload='GPT-2 train step (SGD), V=2048 D=256 H=4 L=4, batch 4x128', **cfg),
-                          timing='host wall around poly_instance_train_step (each step ends with the loss read back)',
-                          launches_per_step=st['launches'] // max(args.steps, 1),
-                          precompiled_per_step=st['launches_precompiled'] // max(args.steps, 1),
-                          cpu_baseline=cpu)), flush=True)
+    if rank == 0:
+        print(json.dumps(dict(metric='train_tokens_per_s', value=world * n_tok / (ms * 1e-3), unit='tokens/s', n_gpus=world,
+                              steps=args.steps, warmup=warm, ms_per_step=ms, higher_is_better=True, dtype='f32',
+                              data='synthetic', scaling='weak',
+                              config=dict(workload='GPT-2 train step (SGD), V={vocab_size} D={n_embd} H={n_head} L={n_layer}, batch {max_batch}x{max_seq_len} per rank'.format(**cfg), **cfg),
+                              timing='host wall around poly_instance_train_step (each step ends with the loss read back), max over ranks',
+                              launches_per_step=st['launches'] // max(args.steps, 1),
+                              precompiled_per_step=st['launches_precompiled'] // max(args.steps, 1),
+                              averaging=averaging, cpu_baseline=cpu)), flush=True)
+    if dist is not None:
+        lib.poly_b200_synchronize()
+        dist.barrier()
+        lib.poly_b200_comm_destroy()
+        dist.destroy_process_group()
+
+
+def _train_param_shapes(lib, cfg):
+    from polygrad_b200.instance import Instance
+    inst = Instance.gpt2(lib, **cfg)
+    out = [(n, inst.bufs[n][1], inst.bufs[n][2]) for n in inst.params]
+    inst.free()
+    return out
 
 
 def run_attention(args):
@@ -887,6 +937,7 @@ def main():
     ap.add_argument('--gather', default='full', choices=['full', 'last', 'none'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-sustained', action='store_true', help='skip the 3 s sustained loop')
+    ap.add_argument('--train-config', default='small', choices=['small', 'medium'], help='size of the --workload train model')
     ap.add_argument('--no-configs4', action='store_true', help='skip the GPT-2 1.5B global-batch-64 record')
     ap.add_argument('--profile', action='store_true', help='stop after the timed steps (for ncu launch lists)')
     args = ap.parse_args()

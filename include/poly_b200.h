@@ -226,6 +226,7 @@ void poly_b200_set_update_averaging(int on);
 int  poly_b200_update_averaging(void);
 int  poly_b200_average_enqueue(void *ptr, size_t count);   /* float32, in place, behind the main stream's work so far */
 int  poly_b200_average_join(void);                          /* main stream waits for the all-reduces enqueued so far */
+void poly_b200_average_group_bytes(size_t bytes);           /* enqueued buffers go out in NCCL groups of this size (0: 1 MB) or 64 buffers */
 void poly_b200_average_trace(unsigned long long *calls, unsigned long long *hash);
 
 /* This rank's share of a global batch as n_micro forwards of one instance (exported by

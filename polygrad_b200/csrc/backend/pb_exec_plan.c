@@ -47,6 +47,7 @@ int poly_b200_ptr_on_host(const void *p);
 int poly_b200_note_access(const void *p, char mode);
 int poly_b200_average_enqueue(void *ptr, size_t count);
 int poly_b200_average_join(void);
+void poly_b200_average_group_bytes(size_t bytes);
 
 /* the original plan code, compiled under other names */
 PolyCompiledPlan *poly_ref_compile_schedule(PolyCtx *ctx, PolySchedule *schedule, PolyDeviceId device);
@@ -350,9 +351,35 @@ static bool average_updates(void) {
 void poly_b200_set_update_averaging(int on) { g_average_updates = on ? 1 : 0; }
 int  poly_b200_update_averaging(void) { return average_updates() ? 1 : 0; }
 
+/* Where the averaging happens.  A plan with much to average (64 MB or more) runs launch by launch and
+ * issues each all-reduce right after the step that writes the buffer last, so the transfers hide
+ * behind the rest of the backward pass; its kernels are long enough for the launches to run ahead.
+ * A small plan is bound by the host's launches instead: it keeps its CUDA graph and averages
+ * everything it wrote after the replay (a few all-reduce groups over NVLink).
+ * POLY_B200_AVERAGE_INLINE=0/1 forces one or the other. */
+static bool average_inline(const PbPlan *p) {
+  if (p->n_avg == 0 || !average_updates()) return false;
+  const char *e = getenv("POLY_B200_AVERAGE_INLINE");
+  if (e && (e[0] == '0' || e[0] == '1') && !e[1]) return e[0] == '1';
+  int64_t bytes = 0;
+  for (int i = 0; i < p->n_avg; i++) bytes += p->slot_bytes[p->avg_slot[i]];
+  return bytes >= ((int64_t)64 << 20);
+}
+
+static int average_after(PbPlan *p) {
+  int rc = 0;
+  poly_b200_average_group_bytes((size_t)1 << 30);      /* nothing left to hide behind: as few groups as possible */
+  for (int i = 0; i < p->n_avg && rc == 0; i++) {
+    const int sl = p->avg_slot[i];
+    if (p->slot_ptr[sl]) rc = poly_b200_average_enqueue(p->slot_ptr[sl], (size_t)p->slot_bytes[sl] / sizeof(float));
+  }
+  poly_b200_average_group_bytes(0);
+  return rc != 0 ? rc : poly_b200_average_join();
+}
+
 static int run_eager(PbPlan *p) {
   int zi = 0, ai = 0;
-  const bool avg = p->n_avg > 0 && average_updates();
+  const bool avg = average_inline(p);
   for (int s = 0; s < p->n_steps; s++) {
     for (zi = 0; zi < p->n_zero; zi++)
       if (p->zero_step[zi] == s) {
@@ -472,6 +499,7 @@ int poly_compiled_plan_run(PolyCompiledPlan *plan, void **slot_data, int n_slots
   int n_staged = 0;
   if (bind_slots(p, slot_data, n_slots, &n_staged) != 0) return -1;
   int rc = run_steps(p);
+  if (rc == 0 && p->n_avg > 0 && average_updates() && !average_inline(p)) rc = average_after(p);
   if (rc == 0 && n_staged > 0) rc = return_slots(p);
   return rc;
 }
@@ -480,7 +508,7 @@ static int run_steps(PbPlan *p) {
   p->runs++;
   const bool graphs = !env_is("POLY_B200_GRAPH", "0") && p->graph_failures < 4 && !getenv("POLY_B200_DRYRUN") &&
                       !poly_b200_timing_active() &&    /* per-launch timing needs individual launches */
-                      !(p->n_avg > 0 && average_updates());   /* collectives are issued between the launches */
+                      !average_inline(p);              /* collectives are issued between the launches */
   if (graphs && graph_valid(p)) {
     /* what the launches of an eager run tell the runtime about bound buffers: pending zero fills
      * are materialised or dropped, and written buffers get a new version, so that converted

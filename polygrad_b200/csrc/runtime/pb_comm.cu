@@ -51,8 +51,12 @@ static struct {
   /* averaging of updated buffers */
   cudaEvent_t avg_ready = nullptr, avg_done = nullptr;
   bool avg_pending = false;
-  unsigned long long avg_calls = 0, avg_trace = 1469598103934665603ull;
+  unsigned long long avg_calls = 0, avg_groups = 0, avg_trace = 1469598103934665603ull;
 } CM;
+
+static struct { void *ptr; size_t count; } g_avg_wait[64];
+static int g_n_avg_wait = 0;
+static size_t g_avg_wait_bytes = 0, g_avg_group_bytes = (size_t)1 << 20;
 
 static bool load_nccl() {
   if (NC.lib) return true;
@@ -202,6 +206,7 @@ extern "C" void poly_b200_comm_destroy(void) {
   if (CM.avg_ready) cudaEventDestroy(CM.avg_ready);
   if (CM.avg_done) cudaEventDestroy(CM.avg_done);
   CM.avg_ready = CM.avg_done = nullptr; CM.avg_pending = false;
+  g_n_avg_wait = 0; g_avg_wait_bytes = 0;
   CM.comm = nullptr; CM.stream = nullptr; CM.rank = -1; CM.world = 0; CM.next = 0;
 }
 
@@ -214,30 +219,51 @@ extern "C" void poly_b200_comm_destroy(void) {
  * so averaging each parameter over the ranks right after its update gives
  * exactly the parameters of one step on the mean gradient.  The plan executor
  * calls poly_b200_average_enqueue after the last step that writes a bound
- * buffer: the all-reduce runs on the second stream behind the rest of the
+ * buffer: the all-reduces run on the second stream behind the rest of the
  * backward pass, and poly_b200_average_join makes the main stream wait for
  * all of them before the plan returns.  Every rank issues the same calls in
  * the same order (same plan), which is what NCCL requires;
  * poly_b200_average_trace exposes a running hash of the sizes to check that. */
-extern "C" int poly_b200_average_enqueue(void *ptr, size_t count) {
-  if (!ptr || count == 0) { pb_set_error("poly_b200_average_enqueue: bad arguments"); return -1; }
-  CM.avg_calls++;
-  CM.avg_trace = (CM.avg_trace ^ (unsigned long long)count) * 1099511628211ull;
-  if (pb_dry_run() || CM.world <= 1) return 0;
+/* Small buffers (biases, LayerNorm gains) wait for company: the all-reduces of up to 64 buffers or
+ * 1 MB (poly_b200_average_group_bytes: when nothing is left to overlap with, larger groups mean
+ * fewer launches) go out as one NCCL group behind one event.  The rule depends only on the sizes,
+ * so every rank forms the same groups. */
+extern "C" void poly_b200_average_group_bytes(size_t bytes) { g_avg_group_bytes = bytes ? bytes : ((size_t)1 << 20); }
+
+static int average_flush(void) {
+  if (g_n_avg_wait == 0) return 0;
   cudaStream_t main_stream = (cudaStream_t)poly_b200_stream();
-  if (poly_b200_note_access(ptr, 'b') != 0) return -1;
   if (!CM.avg_ready) {
     PB_CU(cudaEventCreateWithFlags(&CM.avg_ready, cudaEventDisableTiming));
     PB_CU(cudaEventCreateWithFlags(&CM.avg_done, cudaEventDisableTiming));
   }
   PB_CU(cudaEventRecord(CM.avg_ready, main_stream));
   PB_CU(cudaStreamWaitEvent(CM.stream, CM.avg_ready, 0));
-  PB_NCCL(NC.AllReduce(ptr, ptr, count, ncclFloat32, ncclAvg, CM.comm, CM.stream));
+  const int n = g_n_avg_wait;
+  g_n_avg_wait = 0; g_avg_wait_bytes = 0;
+  PB_NCCL(NC.GroupStart());
+  for (int i = 0; i < n; i++)
+    PB_NCCL(NC.AllReduce(g_avg_wait[i].ptr, g_avg_wait[i].ptr, g_avg_wait[i].count, ncclFloat32, ncclAvg, CM.comm, CM.stream));
+  PB_NCCL(NC.GroupEnd());
   CM.avg_pending = true;
+  CM.avg_groups++;
+  return 0;
+}
+
+extern "C" int poly_b200_average_enqueue(void *ptr, size_t count) {
+  if (!ptr || count == 0) { pb_set_error("poly_b200_average_enqueue: bad arguments"); return -1; }
+  CM.avg_calls++;
+  CM.avg_trace = (CM.avg_trace ^ (unsigned long long)count) * 1099511628211ull;
+  if (pb_dry_run() || CM.world <= 1) return 0;
+  if (poly_b200_note_access(ptr, 'b') != 0) return -1;
+  g_avg_wait[g_n_avg_wait].ptr = ptr; g_avg_wait[g_n_avg_wait].count = count;
+  g_n_avg_wait++; g_avg_wait_bytes += count * sizeof(float);
+  if (g_n_avg_wait == 64 || g_avg_wait_bytes >= g_avg_group_bytes) return average_flush();
   return 0;
 }
 
 extern "C" int poly_b200_average_join(void) {
+  if (average_flush() != 0) return -1;
   if (!CM.avg_pending) return 0;
   cudaStream_t main_stream = (cudaStream_t)poly_b200_stream();
   PB_CU(cudaEventRecord(CM.avg_done, CM.stream));

@@ -729,34 +729,44 @@ static bool parse_work(const std::string &s, std::vector<WorkTerm> &out) {
 /* ── per-launch device timing (measurement aid) ──────────────────────── */
 static bool g_timing = false;
 static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_timing_events;
+static std::vector<std::string> g_timing_names;
 
 extern "C" int poly_b200_timing_active(void) { return g_timing ? 1 : 0; }
 extern "C" void poly_b200_timing_begin(void) {
   for (auto &e : g_timing_events) { cudaEventDestroy(e.first); cudaEventDestroy(e.second); }
   g_timing_events.clear();
+  g_timing_names.clear();
   g_timing = true;
 }
 /* Stops timing and returns the summed device time of the launches since
- * poly_b200_timing_begin, in milliseconds; *n_launches receives their count. */
+ * poly_b200_timing_begin, in milliseconds; *n_launches receives their count.
+ * POLY_B200_TIMING_DUMP=1 also lists every launch (index, program, ms) on stderr. */
 extern "C" double poly_b200_timing_end(int *n_launches) {
   g_timing = false;
   double total = 0.0;
   if (R.ok && !R.dry) cudaStreamSynchronize(R.stream);
+  const char *dump = getenv("POLY_B200_TIMING_DUMP");
+  size_t i = 0;
   for (auto &e : g_timing_events) {
     float ms = 0.0f;
     if (cudaEventElapsedTime(&ms, e.first, e.second) == cudaSuccess) total += ms;
+    if (dump && dump[0] == '1')
+      fprintf(stderr, "pb_timing: %4zu %-28s %9.4f ms\n", i, i < g_timing_names.size() ? g_timing_names[i].c_str() : "?", ms);
     cudaEventDestroy(e.first); cudaEventDestroy(e.second);
+    i++;
   }
   if (n_launches) *n_launches = (int)g_timing_events.size();
   g_timing_events.clear();
+  g_timing_names.clear();
   return total;
 }
-static void timing_mark(bool before) {
+static void timing_mark(bool before, const char *name = nullptr) {
   if (!g_timing || R.dry) return;
   if (before) {
     cudaEvent_t a, b;
     if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
     g_timing_events.push_back({a, b});
+    g_timing_names.push_back(name ? name : "");
     cudaEventRecord(a, R.stream);
   } else if (!g_timing_events.empty()) cudaEventRecord(g_timing_events.back().second, R.stream);
 }
@@ -836,7 +846,7 @@ extern "C" int poly_cuda_launch(PolyCudaProgram *prog, void **args, int n_args,
   }
   if (prog->kind == PolyCudaProgram::AOT) {
     if (R.dry) return 0;
-    timing_mark(true);
+    timing_mark(true, prog->name.c_str());
     int rc = prog->aot->launch(bufs, R.stream);
     timing_mark(false);
     if (rc == 0) pb_count_launch(true, prog->aot->n_launches());
@@ -864,7 +874,7 @@ extern "C" int poly_cuda_launch(PolyCudaProgram *prog, void **args, int n_args,
   for (int i = 0; i < prog->n_params; i++) kargs[n++] = &bufs[i];
   for (int v = 0; v < prog->n_vars; v++) kargs[n++] = &vars[v];
   kargs[n++] = &work;
-  timing_mark(true);
+  timing_mark(true, prog->name.c_str());
   CUresult_ rc = DRV.LaunchKernel(prog->module->fn, (unsigned)grid, 1, 1, (unsigned)prog->block, 1, 1, 0,
                                   (CUstream_)R.stream, kargs, nullptr);
   timing_mark(false);

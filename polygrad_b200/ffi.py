@@ -185,6 +185,7 @@ def _declare_cuda(lib):
     _sig(lib, 'poly_b200_update_averaging', ctypes.c_int, [])
     _sig(lib, 'poly_b200_average_enqueue', ctypes.c_int, [_ptr, S])
     _sig(lib, 'poly_b200_average_join', ctypes.c_int, [])
+    _sig(lib, 'poly_b200_average_group_bytes', None, [S])
     _sig(lib, 'poly_b200_average_trace', None, [ctypes.POINTER(ctypes.c_ulonglong), ctypes.POINTER(ctypes.c_ulonglong)])
     _sig(lib, 'poly_b200_shard_micro_index', ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int])
     _sig(lib, 'poly_b200_forward_microbatches', ctypes.c_int,

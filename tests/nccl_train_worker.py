@@ -14,7 +14,7 @@ from polygrad_b200 import ffi, shard                             # noqa: E402
 from polygrad_b200.instance import Instance, gpt2_init           # noqa: E402
 
 CFG = dict(vocab_size=64, n_embd=48, n_head=4, n_layer=2, max_seq_len=16, max_batch=2)
-STEPS, SEED, INIT_SEED, LR = 3, 23, 7, 1e-5
+STEPS, SEED, INIT_SEED, LR = 4, 23, 7, 1e-5
 
 
 def tokens_of(rank, world, step):

@@ -37,12 +37,15 @@ def test_two_ranks_gather_micro_batches_bit_exact(tmp_path):
     assert r['max'] == 2.0
 
 
-def test_two_ranks_train_on_the_mean_gradient(tmp_path, ref_lib):
+@pytest.mark.parametrize('inline', ['0', '1'], ids=['after_the_replay', 'between_the_launches'])
+def test_two_ranks_train_on_the_mean_gradient(tmp_path, ref_lib, inline):
     """Data-parallel SGD: two ranks, the same parameters, different tokens, three steps with the
     backend averaging every updated parameter over the ranks.  Stock polygrad on the CPU takes, for
     each step, one step per rank's tokens from the common parameters and averages the results --
     for SGD the same as one step on the mean gradient.  Both replicas must end bit-identical to each
-    other, and within the single-GPU training tolerance (1e-4) of the CPU."""
+    other, and within the single-GPU training tolerance (1e-4) of the CPU.  Both places the averaging
+    can happen are run: after the plan's graph replay (what a plan this small gets) and between the
+    launches, behind the rest of the backward pass (what a plan with 64 MB or more to average gets)."""
     if _gpu_count() < 2:
         pytest.skip('needs two GPUs')
     import numpy as np
@@ -54,7 +57,7 @@ def test_two_ranks_train_on_the_mean_gradient(tmp_path, ref_lib):
     s = socket.socket(); s.bind(('127.0.0.1', 0)); port = s.getsockname()[1]; s.close()
     cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node', '2',
            '--master-addr', '127.0.0.1', '--master-port', str(port), os.path.join(HERE, 'nccl_train_worker.py'), str(tmp_path)]
-    env = dict(os.environ, NCCL_NVLS_ENABLE='0', OMP_NUM_THREADS='1')
+    env = dict(os.environ, NCCL_NVLS_ENABLE='0', OMP_NUM_THREADS='1', POLY_B200_AVERAGE_INLINE=inline)
     p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, (p.stdout[-2000:], p.stderr[-4000:])
     got = [np.load(tmp_path / f'rank{r}.npz') for r in range(2)]
