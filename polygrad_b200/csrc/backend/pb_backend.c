@@ -47,6 +47,17 @@ char *poly_render_cuda(PolyUOp **uops, int n, const char *fn_name, int launch_bo
     pb_kern_free(&k);
     return NULL;
   }
+  if (getenv("POLY_B200_DUMP_UOPS")) {      /* the analysed tree, sources first: index, node, indices of its sources */
+    fprintf(stderr, "=== UOPS %s ===\n", fn_name ? fn_name : "?");
+    for (int i = 0; i < k.n_nodes; i++) {
+      char *t = poly_uop_str(k.nodes[i].u);
+      fprintf(stderr, "%4d %s <-", i, t ? t : "?");
+      for (int j = 0; j < k.nodes[i].u->n_src; j++) fprintf(stderr, " %d", pb_kern_node(&k, k.nodes[i].u->src[j]));
+      fprintf(stderr, "\n");
+      free(t);
+    }
+    fprintf(stderr, "=== END UOPS ===\n");
+  }
   char *src = NULL;
   const char *no_aot = getenv("POLY_B200_NO_AOT");
   if (!no_aot || no_aot[0] == '0') src = pb_classify_aot(&k, fn_name);

@@ -556,31 +556,43 @@ static bool reduce_dtype_ok(PolyDType dt) {
 }
 
 static char *render_group_reduce(PbKern *k, const int *usage) {
-  if (k->n_stores != 1 || k->n_reduce_nodes != 1) return NULL;
+  if (k->n_stores != 1 || k->n_reduce_nodes < 1 || k->n_reduce_nodes > 2) return NULL;
   PbStore *st = &k->stores[0];
   int rid = -1;
-  for (int i = 0; i < k->n_nodes; i++) if (k->nodes[i].u->op == POLY_OP_REDUCE) rid = i;
+  for (int i = 0; i < k->n_nodes; i++) if (k->nodes[i].u->op == POLY_OP_REDUCE) rid = i;   /* sources come first: the outer one */
   PolyUOp *red = k->nodes[rid].u;
   if (!reduce_dtype_ok(red->dtype)) return NULL;
   PolyOps op = reduce_op(red);
   if (op != POLY_OP_ADD && op != POLY_OP_MAX && op != POLY_OP_MUL) return NULL;
   /* the REDUCE must feed the store value, not the store index or gate */
   if (k->nodes[pb_kern_node(k, st->index)].has_reduce) return NULL;
+  /* a reduction of a reduction with the same operation (x.sum(-1).sum(-1)) is one reduction over
+   * the axes of both */
+  PolyUOp *inner = NULL;
+  if (k->n_reduce_nodes == 2) {
+    inner = red->src[0];
+    if (inner->op != POLY_OP_REDUCE || reduce_op(inner) != op || !poly_dtype_eq(inner->dtype, red->dtype) ||
+        k->nodes[pb_kern_node(k, inner)].n_uses != 1) return NULL;
+  }
+  PolyUOp *val = inner ? inner->src[0] : red->src[0];
 
   int raxes[PB_MAX_AXES]; int nr = 0; int64_t ktot = 1;
   uint64_t rmask = 0;
-  for (int i = 1; i < red->n_src; i++) {
-    int r = pb_kern_range_id(k, red->src[i]);
-    if (r < 0 || nr >= PB_MAX_AXES) return NULL;
-    if (k->extent[r] < 0) return NULL;
-    raxes[nr++] = r; ktot *= k->extent[r]; rmask |= (uint64_t)1 << r;
+  for (int pass = 0; pass < (inner ? 2 : 1); pass++) {
+    PolyUOp *from = pass == 0 ? red : inner;
+    for (int i = 1; i < from->n_src; i++) {
+      int r = pb_kern_range_id(k, from->src[i]);
+      if (r < 0 || nr >= PB_MAX_AXES) return NULL;
+      if (k->extent[r] < 0) return NULL;
+      raxes[nr++] = r; ktot *= k->extent[r]; rmask |= (uint64_t)1 << r;
+    }
   }
   if (ktot < 64) return NULL;
 
   /* loads under the reduction: is there one that is contiguous along a reduce axis? */
   bool *seen = calloc((size_t)k->n_nodes, 1);
   LoadInfo loads[32];
-  int nl = collect_loads(k, pb_kern_node(k, red->src[0]), loads, 32, 0, seen);
+  int nl = collect_loads(k, pb_kern_node(k, val), loads, 32, 0, seen);
   free(seen);
   uint64_t all = 0;
   for (int r = 0; r < k->n_ranges; r++) all |= (uint64_t)1 << r;
@@ -639,6 +651,22 @@ static char *render_group_reduce(PbKern *k, const int *usage) {
   if (ktot >= 2048 || n_out_max < 2048) { group = ktot >= 8192 ? 512 : 256; if (ktot < 512) group = 128; block = group; }
   else { group = 32; block = 256; }
 
+  /* A few outputs, each a very long reduction (a loss: one scalar over every logit), would occupy
+   * a few SMs.  The reduction is then cut into `split` interleaved parts, one block each; a block
+   * leaves its partial result in module-scope memory and takes a ticket, and the block that draws
+   * the last ticket combines the partials in index order (so the result does not depend on which
+   * block finishes when), applies the rest of the kernel and resets the ticket counter. */
+  int split = 1;
+  {
+    const char *e = getenv("POLY_B200_SPLIT_REDUCE");
+    if (!(e && e[0] == '0') && group == block && k->n_vars == 0 && n_out_max <= 256 && ktot >= ((int64_t)1 << 17)) {
+      int64_t want = (148 * 4 + n_out_max - 1) / n_out_max, by_len = ktot / ((int64_t)group * 16);
+      if (want > by_len) want = by_len;
+      if (want > 1024) want = 1024;
+      if (want >= 2) split = (int)want;
+    }
+  }
+
   Gen g; memset(&g, 0, sizeof g);
   g.k = k;
   g.emitted = malloc(sizeof(int) * (size_t)k->n_nodes);
@@ -655,21 +683,31 @@ static char *render_group_reduce(PbKern *k, const int *usage) {
 
   const char *rt = ctype_of(&g, red->dtype);
   pb_str_puts(g.o, PRELUDE);
+  if (split > 1) {
+    pb_str_printf(g.o, "__device__ %s part_[%lld];\n__device__ unsigned int ticket_[%lld];\n", rt,
+                  (long long)(n_out_max * split), (long long)n_out_max);
+  }
   emit_signature(&g, written, block);
   pb_str_puts(g.o, " {\n");
   g.indent = 1;
   int per_block = block / group;
   ind(&g); pb_str_printf(g.o, "const int lane_ = threadIdx.x %% %d;\n", group);
-  ind(&g); pb_str_printf(g.o, "const long long out_ = (long long)blockIdx.x * %d + threadIdx.x / %d;\n", per_block, group);
+  if (split > 1) {
+    ind(&g); pb_str_printf(g.o, "const int split_ = blockIdx.x %% %d;\n", split);
+    ind(&g); pb_str_printf(g.o, "const long long out_ = blockIdx.x / %d;\n", split);
+  } else {
+    ind(&g); pb_str_printf(g.o, "const long long out_ = (long long)blockIdx.x * %d + threadIdx.x / %d;\n", per_block, group);
+  }
   if (group == block) { ind(&g); pb_str_printf(g.o, "__shared__ %s red_[32];\n", rt); }
   /* whole groups leave together, so the shuffles below always see full warps */
-  ind(&g); pb_str_puts(g.o, "if (out_ >= n_work) return;\n");
+  if (split > 1) { ind(&g); pb_str_puts(g.o, "if (blockIdx.x >= n_work) return;\n"); }
+  else { ind(&g); pb_str_puts(g.o, "if (out_ >= n_work) return;\n"); }
   int order[PB_MAX_AXES];
   order_loop_axes(k, st, order, NULL);
   if (st->n_loop > 0) emit_decompose(&g, wide ? "out_" : "(int)out_", order, st->n_loop);
 
   /* loop-invariant part of the reduced value */
-  int vid = pb_kern_node(k, red->src[0]);
+  int vid = pb_kern_node(k, val);
   hoist(&g, vid);
 
   char idn[96];
@@ -679,7 +717,13 @@ static char *render_group_reduce(PbKern *k, const int *usage) {
   int rorder[PB_MAX_AXES]; int n = 0;
   rorder[n++] = fastest;
   for (int j = nr - 1; j >= 0; j--) if (raxes[j] != fastest) rorder[n++] = raxes[j];
-  ind(&g); pb_str_printf(g.o, "for (%s k_ = lane_; k_ < %lld; k_ += %d) {\n", g.idx_t, (long long)ktot, group);
+  if (split > 1) {
+    ind(&g); pb_str_printf(g.o, "for (long long kk_ = (long long)split_ * %d + lane_; kk_ < %lldLL; kk_ += %lldLL) {\n",
+                           group, (long long)ktot, (long long)group * split);
+    ind(&g); pb_str_printf(g.o, "  const %s k_ = (%s)kk_;\n", g.idx_t, g.idx_t);
+  } else {
+    ind(&g); pb_str_printf(g.o, "for (%s k_ = lane_; k_ < %lld; k_ += %d) {\n", g.idx_t, (long long)ktot, group);
+  }
   g.indent++;
   uint64_t saved = g.bound;
   open_scope(&g);
@@ -689,9 +733,9 @@ static char *render_group_reduce(PbKern *k, const int *usage) {
   } else {
     emit_decompose(&g, "k_", rorder, nr);
   }
-  emit_src(&g, red->src[0]);
+  emit_src(&g, val);
   char v[64], cmb[256];
-  ref(&g, red->src[0], v, sizeof v);
+  ref(&g, val, v, sizeof v);
   combine_expr(op, "acc_", v, cmb, sizeof cmb);
   ind(&g); pb_str_printf(g.o, "acc_ = %s;\n", cmb);
   close_scope(&g);
@@ -714,6 +758,16 @@ static char *render_group_reduce(PbKern *k, const int *usage) {
     ind(&g); pb_str_puts(g.o, "if (threadIdx.x != 0) return;\n");
     ind(&g); pb_str_puts(g.o, "acc_ = red_[0];\n");
     ind(&g); pb_str_printf(g.o, "for (int w_ = 1; w_ < %d; ++w_) { const %s x_ = red_[w_]; acc_ = %s; }\n", nw, rt, sh);
+    if (split > 1) {
+      ind(&g); pb_str_printf(g.o, "part_[out_ * %d + split_] = acc_;\n", split);
+      ind(&g); pb_str_puts(g.o, "__threadfence();\n");
+      ind(&g); pb_str_printf(g.o, "if (atomicAdd(&ticket_[out_], 1u) != %du) return;\n", split - 1);
+      ind(&g); pb_str_puts(g.o, "__threadfence();\n");
+      ind(&g); pb_str_printf(g.o, "const volatile %s* vp_ = part_ + out_ * %d;\n", rt, split);
+      ind(&g); pb_str_puts(g.o, "acc_ = vp_[0];\n");
+      ind(&g); pb_str_printf(g.o, "for (int w_ = 1; w_ < %d; ++w_) { const %s x_ = vp_[w_]; acc_ = %s; }\n", split, rt, sh);
+      ind(&g); pb_str_puts(g.o, "ticket_[out_] = 0u;\n");
+    }
   } else {
     ind(&g); pb_str_puts(g.o, "if (lane_ != 0) return;\n");
   }
@@ -729,7 +783,8 @@ static char *render_group_reduce(PbKern *k, const int *usage) {
     PbStr sz; pb_str_init(&sz);
     size_expr(k, st->loop, st->n_loop, &sz);
     char line[512];
-    snprintf(line, sizeof line, "//launch group block=%d group=%d work=%s", block, group, sz.s);
+    if (split > 1) snprintf(line, sizeof line, "//launch group block=%d group=%d work=c%lld", block, group, (long long)(n_out_max * split));
+    else snprintf(line, sizeof line, "//launch group block=%d group=%d work=%s", block, group, sz.s);
     pb_str_free(&sz);
     emit_header(k, &h, line, usage);
     if (k->uses_half) pb_str_puts(&h, "#include <cuda_fp16.h>\n");
