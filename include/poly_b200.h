@@ -311,6 +311,13 @@ struct PolyInstance;
 int poly_b200_instance_import_weights(struct PolyInstance *inst, const unsigned char *data, long long len,
                                       long long *bytes_to_device);
 
+/* Scheduled kernels that were cut into contraction and elementwise steps by the plans compiled so far
+ * (exported by libpolygrad_b200.so).  A backward kernel in which the scheduler fused a computed operand
+ * or several reductions into one kernel is run as: operand temporaries, one contraction per reduction,
+ * an elementwise remainder.  POLY_B200_OUTLINE=0 switches the cut off; POLY_B200_OUTLINE_MIN_WORK sets
+ * the multiply-adds a kernel's contractions must hold for it (default 4194304). */
+long long poly_b200_kernels_cut(void);
+
 /* The eager entry points (exported by libpolygrad_b200.so; declared in polygrad's src/frontend.h:424-430,
  * defined by the reference at src/frontend.c:2444, 2450, 2670, 2676 and here in backend/pb_eager.c):
  *   int  poly_realize_cuda(PolyCtx *, PolyUOp *sink, PolyBufferBinding *, int n)   host pointers in the bindings

@@ -28,20 +28,7 @@
 /* POLY_B200_DEBUG=1 prints why a kernel was not given to a precompiled kernel */
 #define REJECT(why) do { if (getenv("POLY_B200_DEBUG")) fprintf(stderr, "pb_classify: %s:%d: %s\n", __func__, __LINE__, why); return NULL; } while (0)
 
-/* ── virtual axes: a kernel range, or one factor of a split range ────── */
-typedef struct {
-  int range;        /* kernel range id */
-  int64_t extent;   /* extent of this factor */
-  int64_t mult;     /* contribution to the range value: value += x * mult */
-  bool reduce;
-} VAxis;
-
-typedef struct {
-  bool ok;
-  int64_t offset;
-  int64_t stride[2 * PB_MAX_AXES];
-} VFit;
-
+/* virtual axes (VAxis, VFit): pb_kern.h */
 static uint64_t rng_next(uint64_t *s) {
   uint64_t x = *s; x ^= x << 13; x ^= x >> 7; x ^= x << 17; *s = x; return x;
 }
@@ -114,8 +101,8 @@ static void collect_divisors(PolyUOp *e, int64_t *out, int *n, int cap, int dept
 /* Build virtual axes for the ranges in `mask` such that every expression in
  * exprs[] is affine; tries no split, one split, two splits of different
  * ranges, then one range split in three. */
-static bool find_axes(const PbKern *k, uint64_t mask, PolyUOp **exprs, int n_exprs,
-                      VAxis *va, int *nva, VFit *fits) {
+bool pb_find_axes(const PbKern *k, uint64_t mask, PolyUOp **exprs, int n_exprs,
+                  VAxis *va, int *nva, VFit *fits) {
   int ids[PB_MAX_RANGES]; int n = 0;
   for (int r = 0; r < k->n_ranges; r++) if (mask >> r & 1) ids[n++] = r;
   if (n > PB_MAX_AXES) return false;
@@ -279,7 +266,7 @@ static char *classify_gather(PbKern *k) {
   for (int i = 0; i < st->n_loop; i++) mask |= (uint64_t)1 << st->loop[i];
   PolyUOp *exprs[4] = { st->index->src[1], load_index(idx), load_index(ar), load_index(tab) };
   VAxis va[2 * PB_MAX_AXES]; int nva; VFit fit[4];
-  if (!find_axes(k, mask, exprs, 4, va, &nva, fit)) REJECT("pattern");
+  if (!pb_find_axes(k, mask, exprs, 4, va, &nva, fit)) REJECT("pattern");
   int params[4] = { st->param, load_param(idx), load_param(ar), load_param(tab) };
   for (int i = 0; i < 4; i++) if (!in_bounds(&fit[i], va, nva, param_numel(k, params[i]))) REJECT("pattern");
   /* arange must be read as arange[v] */
@@ -384,7 +371,7 @@ static char *classify_gemm(PbKern *k) {
   PolyUOp *exprs[4] = { st->index->src[1], load_index(la), load_index(lb), addend ? load_index(addend) : NULL };
   int ne = addend ? 4 : 3;
   VAxis va[2 * PB_MAX_AXES]; int nva; VFit fit[4];
-  if (!find_axes(k, mask, exprs, ne, va, &nva, fit)) REJECT("pattern");
+  if (!pb_find_axes(k, mask, exprs, ne, va, &nva, fit)) REJECT("pattern");
   int params[4] = { st->param, load_param(la), load_param(lb), addend ? load_param(addend) : -1 };
   for (int i = 0; i < ne; i++) if (!in_bounds(&fit[i], va, nva, param_numel(k, params[i]))) REJECT("pattern");
   if (params[1] == params[0] || params[2] == params[0]) REJECT("pattern");
@@ -483,7 +470,7 @@ static char *classify_transpose(PbKern *k) {
   for (int i = 0; i < st->n_loop; i++) mask |= (uint64_t)1 << st->loop[i];
   PolyUOp *exprs[2] = { st->index->src[1], load_index(ld) };
   VAxis va[2 * PB_MAX_AXES]; int nva; VFit fit[2];
-  if (!find_axes(k, mask, exprs, 2, va, &nva, fit)) REJECT("not affine");
+  if (!pb_find_axes(k, mask, exprs, 2, va, &nva, fit)) REJECT("not affine");
   if (!in_bounds(&fit[0], va, nva, param_numel(k, po)) || !in_bounds(&fit[1], va, nva, param_numel(k, pi))) REJECT("bounds");
   int x = -1, y = -1;
   for (int i = 0; i < nva; i++) {

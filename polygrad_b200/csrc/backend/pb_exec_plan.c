@@ -29,6 +29,7 @@
  * POLY_B200_PLAN=ref forces that path for everything (debugging).
  */
 #include "pb_plan.h"
+#include "pb_outline.h"
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -95,6 +96,71 @@ static int lower_step(PolyCtx *ctx, PolySchedule *sched, int item_idx, const cha
   st->n_params = np;
   for (int i = 0; i < np; i++) st->slot[i] = item->buf_slot_indices[i];
   return 0;
+}
+
+static long long g_kernels_cut = 0;
+/* Scheduled kernels that plans compiled so far run as several steps (pb_outline.c). */
+long long poly_b200_kernels_cut(void) { return g_kernels_cut; }
+
+/* A kernel the renderer had to take as generated code although it holds contractions: cut it
+ * (pb_outline.c), lower the pieces, and keep them if every contraction among them is now run by
+ * the contraction kernels.  Temporaries become plan slots and are placed in the arena like any
+ * other intermediate.  Returns the number of steps written to out (0: the kernel stays whole). */
+static int lower_cut(PbPlan *p, PolyCtx *ctx, PolySchedule *sched, int item_idx, const char *fn_name, const PbStep *whole, PbStep *out) {
+  PbPiece pieces[PB_MAX_PIECES];
+  int64_t temp_numel[PB_MAX_TEMPS];
+  int n_temps = 0;
+  const int n = pb_outline(ctx, whole->sink, pieces, PB_MAX_PIECES, temp_numel, &n_temps);
+  if (n < 2) return 0;
+  PolyExecItem *item = &sched->items[item_idx];
+  int temp_slot[PB_MAX_TEMPS];
+  for (int t = 0; t < n_temps; t++) temp_slot[t] = -1;
+  int done = 0;
+  bool ok = true;
+  for (int i = 0; i < n && ok; i++) {
+    PbStep *st = &out[i];
+    memset(st, 0, sizeof *st);
+    st->item = item_idx;
+    char name[96];
+    snprintf(name, sizeof name, "%s_p%d", fn_name, i);
+    int n_lin = 0;
+    PolyUOp **lin = poly_linearize_cuda(ctx, pieces[i].sink, &n_lin);
+    if (!lin) { ok = false; break; }
+    st->sink = lin[0];
+    char *src = poly_render_cuda(lin, n_lin, name, 256);
+    free(lin);
+    if (!src) { ok = false; break; }
+    if (pieces[i].must_be_contraction && !strstr(src, "//kind gemm")) {
+      if (getenv("POLY_B200_DEBUG")) fprintf(stderr, "pb_plan: %s: piece %d is not recognised as a contraction; the kernel stays whole\n", fn_name, i);
+      free(src); ok = false; break;
+    }
+    if (getenv("POLY_DUMP_KERNELS")) fprintf(stderr, "=== CUDA KERNEL %s ===\n%s\n=== END ===\n", name, src);
+    st->prog = poly_compile_cuda(src, name);
+    st->text = src;
+    done = i + 1;
+    if (!st->prog) { ok = false; break; }
+    int np = 0, nv = 0, pre = 0;
+    poly_b200_program_info(st->prog, st->rw, (int)sizeof st->rw, &np, &nv, &pre);
+    st->precompiled = pre; st->n_vars = nv; st->n_params = np;
+    if (np != pieces[i].n_params || nv != 0) { ok = false; break; }
+    for (int a = 0; a < np && ok; a++) {
+      const int src_of = pieces[i].param_src[a];
+      if (src_of >= 0) {
+        if (src_of >= item->n_buf_slots) ok = false;
+        else st->slot[a] = item->buf_slot_indices[src_of];
+      } else {
+        const int t = -src_of - 1;
+        if (t >= n_temps) { ok = false; break; }
+        if (temp_slot[t] < 0) temp_slot[t] = pb_plan_add_slot(p, temp_numel[t] * (int64_t)sizeof(float));
+        st->slot[a] = temp_slot[t];
+      }
+    }
+  }
+  if (!ok) {
+    for (int i = 0; i < done; i++) pb_step_release(&out[i]);
+    return 0;
+  }
+  return n;
 }
 
 void pb_step_release(PbStep *st) {
@@ -222,8 +288,9 @@ PolyCompiledPlan *poly_compile_schedule(PolyCtx *ctx, PolySchedule *sched, PolyD
   p->base.device = device;
   p->base.allocator = &POLY_CUDA_ALLOCATOR;
   p->ctx = ctx;
-  p->n_steps = sched->n_items;
-  p->steps = calloc((size_t)(sched->n_items > 0 ? sched->n_items : 1), sizeof(PbStep));
+  int steps_cap = sched->n_items + PB_MAX_PIECES;
+  p->n_steps = 0;
+  p->steps = calloc((size_t)steps_cap, sizeof(PbStep));
 
   static int plan_counter = 0;
   bool has_vars = false;
@@ -231,27 +298,50 @@ PolyCompiledPlan *poly_compile_schedule(PolyCtx *ctx, PolySchedule *sched, PolyD
     if (sched->items[sched->exec_order[s]].n_var_uops > 0) has_vars = true;
   if (has_vars) { plan_destroy(p); return poly_ref_compile_schedule(ctx, sched, device); }
 
-  for (int s = 0; s < sched->n_items; s++) {
-    int k = sched->exec_order[s];
-    if (sched->items[k].kind != POLY_EXEC_COMPUTE) {
-      fprintf(stderr, "polygrad: compile_schedule: non-COMPUTE item %d not supported\n", k);
-      plan_destroy(p); return NULL;
-    }
-    char fn_name[64];
-    snprintf(fn_name, sizeof fn_name, "plan%d_k%d", plan_counter, k);
-    if (lower_step(ctx, sched, k, fn_name, &p->steps[s]) != 0) {
-      fprintf(stderr, "polygrad: compile_schedule: backend 'cuda' failed for kernel %d\n", k);
-      plan_destroy(p); return NULL;
-    }
-  }
-  plan_counter++;
-
   p->n_slots = 0;
   for (int i = 0; i < sched->n_buf_slots; i++) {
     int idx = pb_plan_add_slot(p, sched->buf_slots[i].nbytes > 0 ? sched->buf_slots[i].nbytes : (int64_t)sizeof(float));
     p->slot_inter[idx] = sched->buf_slots[i].is_intermediate ? 1 : 0;
   }
   p->n_sched_slots = sched->n_buf_slots;
+
+  int n_cut = 0;
+  for (int s = 0; s < sched->n_items; s++) {
+    int k = sched->exec_order[s];
+    if (sched->items[k].kind != POLY_EXEC_COMPUTE) {
+      fprintf(stderr, "polygrad: compile_schedule: non-COMPUTE item %d not supported\n", k);
+      plan_destroy(p); return NULL;
+    }
+    if (p->n_steps + PB_MAX_PIECES > steps_cap) {
+      steps_cap = steps_cap * 2 + PB_MAX_PIECES;
+      PbStep *ns = realloc(p->steps, sizeof(PbStep) * (size_t)steps_cap);
+      if (!ns) { plan_destroy(p); return NULL; }
+      memset(ns + p->n_steps, 0, sizeof(PbStep) * (size_t)(steps_cap - p->n_steps));
+      p->steps = ns;
+    }
+    char fn_name[64];
+    snprintf(fn_name, sizeof fn_name, "plan%d_k%d", plan_counter, k);
+    PbStep *st = &p->steps[p->n_steps];
+    if (lower_step(ctx, sched, k, fn_name, st) != 0) {
+      fprintf(stderr, "polygrad: compile_schedule: backend 'cuda' failed for kernel %d\n", k);
+      p->n_steps++;                       /* so that what the step already holds is released */
+      plan_destroy(p); return NULL;
+    }
+    int n_here = 1;
+    if (!st->precompiled && !env_is("POLY_B200_OUTLINE", "0")) {
+      PbStep cut[PB_MAX_PIECES];
+      int n = lower_cut(p, ctx, sched, k, fn_name, st, cut);
+      if (n > 0) {
+        pb_step_release(st);
+        memcpy(st, cut, sizeof(PbStep) * (size_t)n);
+        n_here = n; n_cut++;
+      }
+    }
+    p->n_steps += n_here;
+  }
+  plan_counter++;
+  g_kernels_cut += n_cut;
+  if (n_cut > 0 && getenv("POLY_B200_DEBUG")) fprintf(stderr, "pb_plan: %d kernels cut into contractions and elementwise pieces\n", n_cut);
 
   if (!env_is("POLY_B200_FUSE", "0")) pb_plan_fuse(p);
 

@@ -8,7 +8,8 @@
  * poly_symbolic_simple() rewrite the index expressions are canonical and every
  * reduction is still a single REDUCE node, which is the form analysed here.
  *
- * Nothing in this directory creates UOps: the kernel is read, never rewritten.
+ * Only pb_outline.c creates UOps (kernels cut out of a scheduled kernel); everything
+ * else reads the kernel and never rewrites it.
  */
 #ifndef PB_KERN_H
 #define PB_KERN_H
@@ -92,6 +93,25 @@ typedef struct {
  * lines and random interior points.  Ranges with var extents use the var's
  * max value. */
 void pb_fit_affine(const PbKern *k, PolyUOp *e, uint64_t mask, PbAffine *out);
+
+/* ── virtual axes: a kernel range, or one factor of a split range ────── */
+typedef struct {
+  int range;        /* kernel range id */
+  int64_t extent;   /* extent of this factor */
+  int64_t mult;     /* contribution to the range value: value += x * mult */
+  bool reduce;
+} VAxis;
+
+typedef struct {
+  bool ok;
+  int64_t offset;
+  int64_t stride[2 * PB_MAX_AXES];
+} VFit;
+
+/* Build virtual axes for the ranges in `mask` such that every expression in
+ * exprs[] is affine in them (pb_classify.c); va needs 2 * PB_MAX_AXES entries. */
+bool pb_find_axes(const PbKern *k, uint64_t mask, PolyUOp **exprs, int n_exprs,
+                  VAxis *va, int *nva, VFit *fits);
 
 /* C type used in generated code for a scalar dtype (NULL if unsupported). */
 const char *pb_ctype(PolyDType dt);

@@ -513,7 +513,7 @@ void *PbGemmProgram::pack_operand(const void *src, long long off, bool is_a, int
 
 int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
   launches = 0;
-  /* a scaled sum (an optimizer update fused behind a weight gradient) runs on the fp32 kernel */
+  /* a scaled sum (an optimizer update fused behind a weight gradient) is a float32 contraction */
   if (dtype != PB_F32 || a_bf16 || c_bf16 || (pb_gemm_policy_bf16() && alpha == 1.0f)) {
     int rc = pb_gemm_tc_run(*this, bufs, stream);
     if (rc != PB_TC_UNSUPPORTED) return rc;
@@ -521,11 +521,11 @@ int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
   }
   /* float32 contractions of at least 2^30 multiply-adds run on the tensor cores as three tf32
    * products, the partial sums of every eight k-blocks added up in registers (float32-accurate:
-   * the 1e-5 bound of this path holds at every K).  Small ones and scaled sums stay on the CUDA-core
-   * kernels.  POLY_B200_FP32=simt keeps everything there; =tcp sends every shape the tensor-core
+   * the 1e-5 bound of this path holds at every K; a scale factor is applied to the sum before the
+   * addend).  Small ones stay on the CUDA-core kernels.  POLY_B200_FP32=simt keeps everything there; =tcp sends every shape the tensor-core
    * kernel accepts; =tc sums the whole k axis in tensor memory instead, whose accumulation
    * truncates (error about 1e-8 * K of the result's rms; a few percent faster). */
-  if (alpha == 1.0f) {
+  {
     const char *m = getenv("POLY_B200_FP32");
     int mode = 0;
     /* back-to-back calls favour this route from far smaller sizes (256 x 784 x 512: 26.6 us on the CUDA
@@ -536,6 +536,7 @@ int PbGemmProgram::launch(void *const *bufs, cudaStream_t stream) {
     if (!m) mode = (double)M * (double)N * (double)K * (double)nbatch >= 1073741824.0 ? 2 : 0;
     else if (strcmp(m, "tc") == 0) mode = 1;
     else if (strcmp(m, "tcp") == 0) mode = 2;
+    if (alpha != 1.0f && mode == 1) mode = 0;          /* a scaled sum: the promoted kernels or the CUDA cores */
     if (mode) {
       int rc = pb_gemm_tc_run(*this, bufs, stream, mode);
       if (rc != PB_TC_UNSUPPORTED) return rc;

@@ -67,6 +67,7 @@ struct TcArgs {
   int tiles_m, tiles_n, n_tiles;   /* n_tiles = nbatch * tiles_m * tiles_n */
   int m_fast;                      /* consecutive tiles differ in the row tile (else in the column tile) */
   int kchunk;                      /* PROMOTE kernels: k-blocks summed in tensor memory before the partial sum moves to registers */
+  float alpha;                     /* PROMOTE kernels: the sum is scaled by this before the addend (a parameter update behind a gradient) */
 };
 
 #define PB_TC_ERROR_FLAG pb200_tc_error_flag
@@ -354,7 +355,7 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
       [[maybe_unused]] uint32_t r[PROMOTE ? 1 : 2][32];
       /* the value of column j of chunk ci: from registers (PROMOTE) or from the load in flight */
       auto val = [&](int ci, int j) -> float {
-        if constexpr (PROMOTE) return acc[ci][j]; else return __uint_as_float(r[ci & 1][j]);
+        if constexpr (PROMOTE) return acc[ci][j] * g.alpha; else return __uint_as_float(r[ci & 1][j]);
       };
       if constexpr (!PROMOTE) { if (colh < g.N) tc_ld32(tbase, r[0]); }
 #pragma unroll
@@ -824,6 +825,7 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, int
   bool swap = false;
   if (p.c_sn != 1 || p.N == 1) { if (p.c_sm == 1 && p.M > 1) swap = true; else if (p.c_sn != 1) return PB_TC_UNSUPPORTED; }
   if (p.K < 16) return PB_TC_UNSUPPORTED;
+  if (p.alpha != 1.0f && !promote) return PB_TC_UNSUPPORTED;      /* only the promoted kernels scale the sum */
   const long long Kp = fp32x3 ? ((p.K + 3) & ~3LL) : ((p.K + 7) & ~7LL);
   void *scr_a = nullptr, *scr_b = nullptr;
   TcView va, vb;
@@ -851,6 +853,7 @@ int pb_gemm_tc_run(PbGemmProgram &p, void *const *bufs, cudaStream_t stream, int
   g.C = (float *)bufs[p.p_c] + p.off_c;
   g.c_sm = swap ? p.c_sn : p.c_sm;
   g.has_x = p.has_x ? 1 : 0; g.relu = p.relu ? 1 : 0;
+  g.alpha = p.alpha;
   g.ab_fmt = fp32x3 ? 2 : (p.dtype == PB_F16 ? 0 : 1);
   if (p.has_x) { g.X = (const float *)bufs[p.p_x] + p.off_x; g.x_sm = swap ? p.x_sn : p.x_sm; g.x_sn = swap ? p.x_sm : p.x_sn; }
   g.nb = (int)p.b_ax.size();
@@ -969,6 +972,7 @@ int pb_gemm_tc_launch_raw(const void *a_bf16, long long a_pitch, const void *b_b
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
   g.C = C; g.c_sm = c_sm;
   g.has_x = bias ? 1 : 0; g.relu = relu ? 1 : 0;
+  g.alpha = 1.0f;
   g.ab_fmt = 1;
   g.X = bias; g.x_sm = 0; g.x_sn = 1;
   g.nb = 0;

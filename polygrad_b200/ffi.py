@@ -192,6 +192,7 @@ def _declare_cuda(lib):
          [_ptr, ctypes.c_char_p, ctypes.POINTER(ctypes.POINTER(ctypes.c_float)), ctypes.c_int, ctypes.c_int, S, _ptr,
           ctypes.c_int, ctypes.c_int])
     _sig(lib, 'poly_b200_readback_wait', ctypes.c_int, [])
+    _sig(lib, 'poly_b200_kernels_cut', ctypes.c_longlong, [])
     _sig(lib, 'poly_realize_cuda', ctypes.c_int, [_ptr, _ptr, ctypes.POINTER(PolyBufferBinding), ctypes.c_int])
     _sig(lib, 'poly_cuda_copyback', ctypes.c_int, [ctypes.POINTER(PolyBufferBinding), ctypes.c_int])
     _sig(lib, 'poly_cuda_flush_buffers', None, [])

@@ -118,6 +118,33 @@ def test_square_contraction_fp32(devices, gpu, monkeypatch, n, rows, _, route):
     assert_close(got[sel], want, 1e-5, f'fp32 {route} n={n}')
 
 
+@pytest.mark.parametrize('route', ['default', 'simt'])
+def test_scaled_contraction_behind_an_addend_fp32(devices, gpu, monkeypatch, route):
+    """x - 0.01 * (a . b) in one kernel, the form of a parameter update behind a weight gradient
+    (reference src/instance.c:1158-1162), at 2048^3: by default on the tensor cores (three tf32 products,
+    the sum scaled before the addend), and on the CUDA cores."""
+    cpu, cuda = devices
+    if route == 'simt':
+        monkeypatch.setenv('POLY_B200_FP32', 'simt')
+    else:
+        monkeypatch.delenv('POLY_B200_FP32', raising=False)
+    gpu.poly_b200_set_gemm_policy(0)
+    n, rows = 2048, 64
+    rng = np.random.default_rng([n, 5])
+    a = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    b = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    x = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    sel = _slice_rows(n, rows, n + 2)
+    gpu.poly_b200_stats_reset()
+    got = (cuda.tensor(x) - cuda.tensor(a).dot(cuda.tensor(b)) * 0.01).numpy()
+    st = gpu.stats()
+    assert st['launches_generated'] == 0 and st['launches_precompiled'] >= 1
+    want = (cpu.tensor(x[sel]) - cpu.tensor(a[sel]).dot(cpu.tensor(b)) * 0.01).numpy()
+    assert_close(got[sel], want, 1e-5, f'scaled fp32 {route}')
+    # the part the contraction contributes, on its own
+    assert_close(got[sel].astype(np.float64) - x[sel], want.astype(np.float64) - x[sel], 1e-4, f'scaled sum {route}')
+
+
 @pytest.mark.parametrize('n,_,rows', SQUARES, ids=lambda v: str(v))
 def test_square_contraction_bf16_buffers(devices, n, _, rows):
     cpu, cuda = devices
