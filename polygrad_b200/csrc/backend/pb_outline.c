@@ -25,13 +25,20 @@
  *   2. if the kernel then still is not a single contraction with a known
  *      epilogue, each contraction is cut out into a kernel that writes a
  *      temporary laid out like the kernel's output, and the remainder reads
- *      those temporaries elementwise.
+ *      those temporaries elementwise.  A contraction that only counts inside a
+ *      window of an output axis -- the gradients of q, k and v written side by
+ *      side into one buffer: where(0 <= c - 96 < 48, sum(...), 0) + ... -- is
+ *      computed over that window alone (the axis is replaced by a shorter one,
+ *      shifted), and the remainder reads the temporary at the shifted position
+ *      under the same condition.
  *
  * The pieces are ordinary kernel trees (SINK over END over STORE), so the
  * classifier and the renderers treat them like scheduled kernels.  The caller
  * keeps the cut only if every contraction in it is then recognised.
  */
 #include "pb_outline.h"
+#include "pat.h"
+#include "codegen.h"
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -363,6 +370,128 @@ static PolyUOp *some_f32_load(PbKern *k) {
   return NULL;
 }
 
+/* ── a reduction that counts only inside a window of the output axes ─── */
+typedef struct { int range; int64_t shift, extent; bool lo, hi; } Window;   /* 0 <= range + shift < extent */
+
+static bool range_plus_const(PbKern *k, PolyUOp *e, int *range, int64_t *shift) {
+  if (e->op == POLY_OP_RANGE) { *range = pb_kern_range_id(k, e); *shift = 0; return *range >= 0; }
+  if (e->op == POLY_OP_ADD && e->src[0]->op == POLY_OP_RANGE && e->src[1]->op == POLY_OP_CONST && e->src[1]->arg.kind == POLY_ARG_INT) {
+    *range = pb_kern_range_id(k, e->src[0]); *shift = e->src[1]->arg.i; return *range >= 0;
+  }
+  if (e->op == POLY_OP_ADD && e->src[1]->op == POLY_OP_RANGE && e->src[0]->op == POLY_OP_CONST && e->src[0]->arg.kind == POLY_ARG_INT) {
+    *range = pb_kern_range_id(k, e->src[1]); *shift = e->src[0]->arg.i; return *range >= 0;
+  }
+  return false;
+}
+
+static bool int_const(PolyUOp *u, int64_t *v) {
+  if (u->op != POLY_OP_CONST || u->arg.kind != POLY_ARG_INT) return false;
+  *v = u->arg.i; return true;
+}
+
+/* mask as a conjunction of  !(e < 0)  and  e < E  with e = range (+ const) */
+static bool parse_windows(PbKern *k, PolyUOp *mask, Window *w, int *n, int cap) {
+  if (mask->op == POLY_OP_AND) return parse_windows(k, mask->src[0], w, n, cap) && parse_windows(k, mask->src[1], w, n, cap);
+  int r; int64_t shift, bound;
+  bool is_lo;
+  if (mask->op == POLY_OP_NEG && mask->src[0]->op == POLY_OP_CMPLT && int_const(mask->src[0]->src[1], &bound) && bound == 0 &&
+      range_plus_const(k, mask->src[0]->src[0], &r, &shift)) is_lo = true;
+  else if (mask->op == POLY_OP_CMPLT && int_const(mask->src[1], &bound) && range_plus_const(k, mask->src[0], &r, &shift)) is_lo = false;
+  else return false;
+  int at = -1;
+  for (int i = 0; i < *n; i++) if (w[i].range == r && w[i].shift == shift) at = i;
+  if (at < 0) {
+    /* a second, different shift of the same range would be another window: not handled */
+    for (int i = 0; i < *n; i++) if (w[i].range == r) {
+      const bool triv_old = w[i].shift == 0, triv_new = shift == 0;
+      if (!triv_old && !triv_new) return false;
+    }
+    if (*n >= cap) return false;
+    at = (*n)++;
+    w[at] = (Window){ r, shift, -1, false, false };
+  }
+  if (is_lo) w[at].lo = true; else { w[at].hi = true; w[at].extent = bound; }
+  return true;
+}
+
+/* The piece that computes `red` over its window: the windowed output axes replaced by shorter ones.
+ * On success *sink_out is the kernel (simplified), *numel its temporary's size and *read_index where the
+ * parent finds an element, over the parent's own ranges. */
+static bool windowed_piece(Cut *c, PolyUOp *red, PolyUOp *mask, PolyUOp **sink_out, int64_t *numel, PolyUOp **read_index,
+                           int *old_of_new, int *n_params) {
+  PbKern *k = c->k;
+  PbStore *st = &k->stores[0];
+  Window w[PB_MAX_AXES]; int nw = 0;
+  if (!parse_windows(k, mask, w, &nw, PB_MAX_AXES)) { DBG("window: condition is not a conjunction of range tests"); return false; }
+  /* per loop range: the window, or the whole range */
+  int64_t shift[PB_MAX_RANGES], ext[PB_MAX_RANGES];
+  for (int r = 0; r < k->n_ranges; r++) { shift[r] = 0; ext[r] = k->extent[r]; }
+  bool any = false;
+  for (int i = 0; i < nw; i++) {
+    const Window *x = &w[i];
+    if (k->is_reduce[x->range]) return false;
+    if (x->shift == 0 && (!x->hi || x->extent >= k->extent[x->range])) continue;         /* always true */
+    if (!x->lo || !x->hi) return false;
+    if (-x->shift < 0 || x->extent - x->shift > k->extent[x->range] || x->extent < 1) return false;
+    if (shift[x->range] != 0 || ext[x->range] != k->extent[x->range]) return false;       /* two windows on one range */
+    shift[x->range] = x->shift; ext[x->range] = x->extent; any = true;
+  }
+  if (!any) return false;
+  Sub m = {0};
+  PolyUOp *ranges[PB_MAX_AXES];
+  PolyUOp *idx_t = NULL, *ridx = NULL;
+  int64_t rm = 1, total = 1;
+  for (int i = 0; i < st->n_loop; i++) total *= ext[st->loop[i]];
+  if (total >= ((int64_t)1 << 30)) { sub_free(&m); return false; }
+  /* laid out like the output: the axis with the largest output stride outermost */
+  int order[PB_MAX_AXES];
+  {
+    uint64_t lm = 0;
+    for (int i = 0; i < st->n_loop; i++) { lm |= (uint64_t)1 << st->loop[i]; order[i] = i; }
+    PbAffine oa;
+    pb_fit_affine(k, st->index->src[1], lm, &oa);
+    if (oa.ok)
+      for (int i = 1; i < st->n_loop; i++)
+        for (int j = i; j > 0 && llabs(oa.stride[st->loop[order[j - 1]]]) < llabs(oa.stride[st->loop[order[j]]]); j--) {
+          int t = order[j]; order[j] = order[j - 1]; order[j - 1] = t;
+        }
+  }
+  rm = total;
+  for (int o = 0; o < st->n_loop; o++) {
+    const int i = order[o], r = st->loop[i];
+    rm /= ext[r];
+    PolyUOp *nr = k->ranges[r];
+    if (shift[r] != 0 || ext[r] != k->extent[r]) {
+      nr = poly_uop1(c->ctx, POLY_OP_RANGE, c->t_int, ci(c, ext[r]), poly_arg_range(64 + r, POLY_AXIS_LOOP));
+      sub_put(&m, k->ranges[r], shift[r] ? ibin(c, POLY_OP_ADD, nr, ci(c, -shift[r])) : nr);
+    }
+    ranges[i] = nr;
+    idx_t = iadd(c, idx_t, iscale(c, nr, rm));
+    PolyUOp *pos = shift[r] ? ibin(c, POLY_OP_ADD, k->ranges[r], ci(c, shift[r])) : k->ranges[r];
+    ridx = iadd(c, ridx, iscale(c, pos, rm));
+  }
+  PolyUOp *value = rebuild(c->ctx, &m, red);
+  sub_free(&m);
+  if (!value || !idx_t) return false;
+  value = renumber_params(c, value, 1, old_of_new, n_params);
+  if (!value) return false;
+  PolyUOp *sink = wrap_store(c, param_like(c, k->params[st->param], 0, total), idx_t, value, ranges, st->n_loop);
+  if (!sink) return false;
+  sink = poly_graph_rewrite(c->ctx, sink, poly_symbolic_simple());
+  if (!sink) return false;
+  /* is it a contraction now? */
+  PbKern kp;
+  bool good = false;
+  if (pb_kern_build(&kp, sink) == 0 && kp.n_reduce_nodes == 1 && kp.n_stores == 1) {
+    for (int i = 0; i < kp.n_nodes && !good; i++)
+      if (kp.nodes[i].u->op == POLY_OP_REDUCE) good = contraction_like(&kp, kp.nodes[i].u);
+  }
+  pb_kern_free(&kp);
+  if (!good) { DBG("window: the reduction over its window is not a contraction"); return false; }
+  *sink_out = sink; *numel = total; *read_index = ridx;
+  return true;
+}
+
 int pb_outline(PolyCtx *ctx, PolyUOp *sink, PbPiece *pieces, int cap, int64_t *temp_numel, int *n_temps) {
   *n_temps = 0;
   int n_pieces = 0, result = 0;
@@ -382,15 +511,17 @@ int pb_outline(PolyCtx *ctx, PolyUOp *sink, PbPiece *pieces, int cap, int64_t *t
   { const char *e = getenv("POLY_B200_OUTLINE_MIN_WORK"); if (e && e[0]) min_work = atoll(e); }
   PolyUOp *reds[PB_MAX_TEMPS]; int n_red = 0; int64_t work = 0;
   for (int i = 0; i < k.n_nodes; i++) {
-    PolyUOp *u = k.nodes[i].u;
+    PolyUOp *u = k.nodes[i].u, *fa, *fb; bool selects;
     if (u->op != POLY_OP_REDUCE) continue;
     if (k.nodes[pb_kern_node(&k, u->src[0])].has_reduce) goto done;       /* nested */
+    if (!reduce_factors(u, &fa, &fb, &selects)) continue;
+    work += reduce_work(&k, u);
     if (contraction_like(&k, u)) {
       if (n_red >= PB_MAX_TEMPS) goto done;
-      reds[n_red++] = u; work += reduce_work(&k, u);
+      reds[n_red++] = u;
     }
   }
-  if (n_red == 0 || work < min_work) goto done;
+  if (work < min_work) goto done;
   PolyUOp *load_like = some_f32_load(&k);
   if (!load_like) goto done;
 
@@ -471,24 +602,36 @@ int pb_outline(PolyCtx *ctx, PolyUOp *sink, PbPiece *pieces, int cap, int64_t *t
     Sub subst2 = {0};
     for (int i = 0; i < k2.n_nodes && ok; i++) {
       PolyUOp *u = k2.nodes[i].u;
-      if (u->op != POLY_OP_REDUCE || !contraction_like(&k2, u)) continue;
+      if (u->op != POLY_OP_REDUCE) continue;
       if (n_pieces >= cap - 1 || *n_temps >= PB_MAX_TEMPS || next_param >= PB_MAX_PARAMS) { ok = false; break; }
       PbPiece *pc = &pieces[n_pieces];
       memset(pc, 0, sizeof *pc);
       int old_of_new[PB_MAX_PARAMS], np = 0;
-      PolyUOp *value = renumber_params(&c2, u, 1, old_of_new, &np);
-      if (!value) { ok = false; break; }
+      int64_t numel = out_numel;
+      PolyUOp *read_index = st->index->src[1];
+      if (contraction_like(&k2, u)) {
+        PolyUOp *value = renumber_params(&c2, u, 1, old_of_new, &np);
+        if (!value) { ok = false; break; }
+        pc->sink = wrap_store(&c2, param_like(&c2, k2.params[st->param], 0, out_numel), st->index->src[1], value, ranges, st->n_loop);
+        if (!pc->sink) { ok = false; break; }
+      } else {
+        /* where(window, sum, 0): the sum over its window alone */
+        const PbNode *nd = &k2.nodes[i];
+        PolyUOp *par = nd->n_uses == 1 && nd->only_parent >= 0 ? k2.nodes[nd->only_parent].u : NULL;
+        PolyUOp *fa, *fb; bool selects;
+        if (!par || par->op != POLY_OP_WHERE || par->src[1] != u || par->src[2]->op != POLY_OP_CONST ||
+            !reduce_factors(u, &fa, &fb, &selects) || selects) continue;
+        if (!windowed_piece(&c2, u, par->src[0], &pc->sink, &numel, &read_index, old_of_new, &np)) continue;
+      }
       const int t = (*n_temps)++;
-      temp_numel[t] = out_numel;
+      temp_numel[t] = numel;
       pc->n_params = np;
       pc->param_src[0] = -(t + 1);
       for (int q = 1; q < np; q++) pc->param_src[q] = source_of[old_of_new[q]];
       pc->must_be_contraction = true;
-      pc->sink = wrap_store(&c2, param_like(&c2, k2.params[st->param], 0, out_numel), st->index->src[1], value, ranges, st->n_loop);
-      if (!pc->sink) { ok = false; break; }
       n_pieces++;
-      PolyUOp *npar = param_like(&c2, k2.params[st->param], next_param, out_numel);
-      PolyUOp *nindex = poly_uop2(ctx, POLY_OP_INDEX, st->index->dtype, npar, st->index->src[1], st->index->arg);
+      PolyUOp *npar = param_like(&c2, k2.params[st->param], next_param, numel);
+      PolyUOp *nindex = poly_uop2(ctx, POLY_OP_INDEX, st->index->dtype, npar, read_index, st->index->arg);
       sub_put(&subst2, u, poly_uop1(ctx, POLY_OP_LOAD, load_like->dtype, nindex, load_like->arg));
       source_of[next_param++] = -(t + 1);
     }
