@@ -783,7 +783,7 @@ def run_mlp(args):
 
 
 TRAIN_CFG = dict(vocab_size=2048, n_embd=256, n_head=4, n_layer=4, max_seq_len=128, max_batch=4)
-# 67 M parameters (268 MB to average per step): enough for the averaging to run between the launches
+# 67 M parameters (268 MB to average per step)
 TRAIN_CFG_MEDIUM = dict(vocab_size=50257, n_embd=768, n_head=12, n_layer=4, max_seq_len=256, max_batch=8)
 
 
@@ -850,8 +850,8 @@ def run_train(args):
         averaging = dict(ms_per_step=ms, ms_per_step_without=ms_alone, ms_per_step_forced=forced,
                          allreduces_per_step=calls.value // (warm + args.steps),
                          float32_averaged_per_step=n_par + 1, mbytes_averaged_per_step=(n_par + 1) * 4 / 1e6,
-                         placement='between the launches' if (n_par + 1) * 4 >= 64 << 20 else 'after the plan',
-                         note='ncclAvg per parameter on a second stream; plans with 64 MB or more to average issue each '
+                         placement='between the launches' if (n_par + 1) * 4 >= 1 << 30 else 'after the plan',
+                         note='ncclAvg per parameter on a second stream; plans with 1 GB or more to average issue each '
                               'all-reduce after the parameter\'s update step, smaller ones keep their CUDA graph and '
                               'average after it')
     cpu = None

@@ -216,9 +216,10 @@ void   poly_b200_comm_destroy(void);
  * reduce; for plain SGD, p - lr * g is linear in g and averaging the UPDATED parameters over the ranks
  * equals one step on the mean gradient.  While update averaging is on (also POLY_B200_AVERAGE_UPDATES=1),
  * every plan that updates bound buffers in place (poly_instance_train_step's) all-reduces each bound float32
- * buffer it writes -- parameters and the loss -- with ncclAvg right after the step that writes it last; the
- * all-reduces run on the communicator's stream behind the rest of the backward pass, and the plan returns
- * with the main stream ordered after them.  Such plans run launch by launch (no CUDA graph).  With Adam the
+ * buffer it writes -- parameters and the loss -- with ncclAvg.  A plan with less than 1 GB to average keeps its
+ * CUDA graph and averages after the replay in a few NCCL groups; a larger one runs launch by launch and issues
+ * each all-reduce right after the step that writes the buffer last, on the communicator's stream behind the rest
+ * of the backward pass.  Either way the plan returns with the main stream ordered after the all-reduces.  With Adam the
  * moments are averaged as well, which is local-step averaging, not a step on the mean gradient.
  * Every rank must run the same plan: poly_b200_average_trace returns the number of all-reduces issued so far
  * and a running hash of their element counts, equal on all ranks when they did. */

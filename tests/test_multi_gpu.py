@@ -45,7 +45,7 @@ def test_two_ranks_train_on_the_mean_gradient(tmp_path, ref_lib, inline):
     for SGD the same as one step on the mean gradient.  Both replicas must end bit-identical to each
     other, and within the single-GPU training tolerance (1e-4) of the CPU.  Both places the averaging
     can happen are run: after the plan's graph replay (what a plan this small gets) and between the
-    launches, behind the rest of the backward pass (what a plan with 64 MB or more to average gets)."""
+    launches, behind the rest of the backward pass (what a plan with 1 GB or more to average gets)."""
     if _gpu_count() < 2:
         pytest.skip('needs two GPUs')
     import numpy as np
