@@ -138,26 +138,34 @@ def test_gpt2_train_steps_match_cpu(ref_lib, gpu, optim, lr):
         assert_close(got, want, ptol, f'{name} after 3 steps')
 
 
-def test_gpt2_train_steps_with_backward_kernels_cut(ref_lib, gpu, monkeypatch):
-    """The same three SGD steps with every backward kernel that holds a contraction cut into operand
+@pytest.mark.parametrize('optim,lr', [(ffi.OPTIM_SGD, 1e-5), (ffi.OPTIM_ADAMW, 1e-4)], ids=['sgd', 'adamw'])
+def test_gpt2_train_steps_with_backward_kernels_cut(ref_lib, gpu, monkeypatch, optim, lr):
+    """The same three steps with every backward kernel that holds a contraction cut into operand
     temporaries, contraction steps and an elementwise remainder (at this width the cut would not pay
     and is forced): weight gradients whose operand is a sum of gradient contributions, the tied
-    embedding's gradient (head contraction + lookup selection + update in one scheduled kernel).
-    Same tolerances as the uncut run."""
+    embedding's gradient (head contraction + lookup selection + update in one scheduled kernel), the
+    q/k/v gradients written side by side, and under AdamW the moment updates that each hold the
+    gradient's contraction.  Same tolerances as the uncut run."""
     monkeypatch.setenv('POLY_B200_OUTLINE_MIN_WORK', '0')
     cfg = dict(vocab_size=64, n_embd=48, n_head=4, n_layer=2, max_seq_len=16, max_batch=2)
     tokens = np.random.default_rng(17).integers(0, cfg['vocab_size'], (cfg['max_batch'], cfg['max_seq_len']))
-    want_l, want_p = _train_gpt2(ref_lib, ffi.DEVICE_CPU, cfg, tokens, ffi.OPTIM_SGD, 1e-5, 3)
+    want_l, want_p = _train_gpt2(ref_lib, ffi.DEVICE_CPU, cfg, tokens, optim, lr, 3)
     cut_before = gpu.poly_b200_kernels_cut()
-    gpu.poly_b200_stats_reset()
-    got_l, got_p = _train_gpt2(gpu, ffi.DEVICE_CUDA, cfg, tokens, ffi.OPTIM_SGD, 1e-5, 3)
+    got_l, got_p = _train_gpt2(gpu, ffi.DEVICE_CUDA, cfg, tokens, optim, lr, 3)
     assert gpu.poly_b200_kernels_cut() - cut_before >= 2 * cfg['n_layer'] + 1
     np.testing.assert_allclose(got_l, want_l, rtol=1e-4)
+    ptol = 1e-4 if optim == ffi.OPTIM_SGD else 1e-3
+    d = cfg['n_embd']
     for name in want_p:
-        assert_close(got_p[name], want_p[name], 1e-4, f'{name} after 3 steps, kernels cut')
-        moved = want_p[name].astype(np.float64) - _initial(cfg, name)
-        if np.sqrt(np.mean(moved ** 2)) > 1e-6:
-            assert_close(got_p[name].astype(np.float64) - _initial(cfg, name), moved, 2e-2, f'update of {name}')
+        got, want, first = got_p[name], want_p[name], _initial(cfg, name)
+        if optim != ffi.OPTIM_SGD and name.endswith('attn.c_attn.bias'):
+            # gradients that are rounding noise around zero (see test_gpt2_train_steps_match_cpu)
+            assert np.abs(got[d:2 * d] - want[d:2 * d]).max() <= 2 * 3 * lr * 1.01
+            got, want, first = (np.delete(a, np.s_[d:2 * d]) for a in (got, want, first))
+        assert_close(got, want, ptol, f'{name} after 3 steps, kernels cut')
+        moved = want.astype(np.float64) - first
+        if optim == ffi.OPTIM_SGD and np.sqrt(np.mean(moved ** 2)) > 1e-6:
+            assert_close(got.astype(np.float64) - first, moved, 2e-2, f'update of {name}')
 
 
 _INITIAL = {}
