@@ -704,6 +704,20 @@ struct SplitSrc {                      /* the source as [batch axes][rows][k], k
   int nb; int bext[4]; long long bstr[4];
 };
 
+/* one value into its three segments: x0 goes to [0, Kp), x1 to [Kp, 2Kp), x2 to [2Kp, 3Kp) */
+__device__ __forceinline__ void split_one(float a, int is_b, float &x0, float &x1, float &x2) {
+  if (!(fabsf(a) <= 3.4028235e38f)) {
+    /* an infinity or a NaN meets only the other operand's hi part, once: inf * b keeps b's sign
+     * (and inf * 0 is NaN) as in the plain product, instead of meeting lo parts of either sign */
+    x0 = a; x1 = 0.0f; x2 = 0.0f;
+    return;
+  }
+  float hi = tf32_rna(a);
+  if (!(fabsf(hi) <= 3.4028235e38f)) hi = __uint_as_float(__float_as_uint(a) & 0xffffe000u);   /* rounding overflowed: truncate */
+  const float lo = tf32_rna(a - hi);
+  x0 = hi; x1 = is_b ? lo : hi; x2 = is_b ? hi : lo;
+}
+
 __global__ void __launch_bounds__(256) pb200_split_tf32x3(const SplitSrc in, float *__restrict__ dst,
                                                           long long total, int K, int Kp, int is_b) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -712,16 +726,62 @@ __global__ void __launch_bounds__(256) pb200_split_tf32x3(const SplitSrc in, flo
     for (int d = 0; d < in.nb; d++) { so += (bz % in.bext[d]) * in.bstr[d]; bz /= in.bext[d]; }
     const float a = k < K ? in.src[so + k] : 0.0f;
     float *o = dst + row * 3 * Kp;
-    if (!(fabsf(a) <= 3.4028235e38f)) {
-      /* an infinity or a NaN meets only the other operand's hi part, once: inf * b keeps b's sign
-       * (and inf * 0 is NaN) as in the plain product, instead of meeting lo parts of either sign */
-      o[k] = a; o[Kp + k] = 0.0f; o[2 * Kp + k] = 0.0f;
-      continue;
+    split_one(a, is_b, o[k], o[Kp + k], o[2 * Kp + k]);
+  }
+}
+
+/* The same with four consecutive k per thread: one 128-bit load, three 128-bit stores.  Needs rows of the
+ * source that start on 16-byte boundaries (Kp is a multiple of 4, so the destination's always do). */
+__global__ void __launch_bounds__(256) pb200_split_tf32x3_v4(const SplitSrc in, float *__restrict__ dst,
+                                                             long long total4, int K, int Kp, int is_b) {
+  const int kq = Kp >> 2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / kq; const int k = (int)(i % kq) << 2;
+    long long bz = row / in.rows, so = (row % in.rows) * in.pitch;
+    for (int d = 0; d < in.nb; d++) { so += (bz % in.bext[d]) * in.bstr[d]; bz /= in.bext[d]; }
+    float4 a;
+    if (k + 3 < K) a = *reinterpret_cast<const float4 *>(in.src + so + k);
+    else {
+      a.x = k < K ? in.src[so + k] : 0.0f; a.y = k + 1 < K ? in.src[so + k + 1] : 0.0f;
+      a.z = k + 2 < K ? in.src[so + k + 2] : 0.0f; a.w = 0.0f;
     }
-    float hi = tf32_rna(a);
-    if (!(fabsf(hi) <= 3.4028235e38f)) hi = __uint_as_float(__float_as_uint(a) & 0xffffe000u);   /* rounding overflowed: truncate */
-    const float lo = tf32_rna(a - hi);
-    o[k] = hi; o[Kp + k] = is_b ? lo : hi; o[2 * Kp + k] = is_b ? hi : lo;
+    float4 x0, x1, x2;
+    split_one(a.x, is_b, x0.x, x1.x, x2.x); split_one(a.y, is_b, x0.y, x1.y, x2.y);
+    split_one(a.z, is_b, x0.z, x1.z, x2.z); split_one(a.w, is_b, x0.w, x1.w, x2.w);
+    float *o = dst + row * 3 * Kp + k;
+    *reinterpret_cast<float4 *>(o) = x0;
+    *reinterpret_cast<float4 *>(o + Kp) = x1;
+    *reinterpret_cast<float4 *>(o + 2 * Kp) = x2;
+  }
+}
+
+/* An operand stored with its row axis contiguous and k strided (a weight gradient reads the
+ * activations transposed): 32 x 32 tiles through shared memory, read along the rows, written along k
+ * in the split form.  dst row of (batch z, r) is z * R + r; k in [K, Kp) is zero-filled. */
+struct SplitTrArgs {
+  const float *src; float *dst;
+  int R, K, Kp; long long s_k;
+  int naxes; int ext[6]; long long sstride[6];     /* the other axes of the source, fastest first */
+  int is_b;
+};
+
+__global__ void __launch_bounds__(256) pb200_split_tf32x3_tr(const SplitTrArgs a) {
+  __shared__ float tile[32][33];
+  long long rem = blockIdx.z, o = 0;
+  for (int d = 0; d < a.naxes; d++) { const long long x = rem % a.ext[d]; rem /= a.ext[d]; o += x * a.sstride[d]; }
+  const int r0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int j = ty; j < 32; j += 8) {
+    const int k = k0 + j, r = r0 + tx;
+    tile[j][tx] = (k < a.K && r < a.R) ? a.src[o + (long long)k * a.s_k + r] : 0.0f;
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    const int r = r0 + j, k = k0 + tx;
+    if (r < a.R && k < a.Kp) {
+      float *d = a.dst + ((long long)blockIdx.z * a.R + r) * 3 * a.Kp;
+      split_one(tile[tx][j], a.is_b, d[k], d[a.Kp + k], d[2 * a.Kp + k]);
+    }
   }
 }
 
@@ -761,15 +821,45 @@ static const void *tc_operand_x3(PbGemmProgram &p, PbTcOperand &cache, const voi
     in.nb = (int)p.b_ax.size();
     for (int i = 0; i < in.nb; i++) { in.bext[i] = (int)p.b_ax[i].ext; in.bstr[i] = is_a ? p.b_ax[i].sa : p.b_ax[i].sb; }
   } else {
+    /* rows contiguous, one strided k axis: transposed and split in one pass */
+    const std::vector<PbGemmAxis> &rax = is_a ? p.m_ax : p.n_ax;
+    auto sel = [&](const PbGemmAxis &x) { return is_a ? x.sa : x.sb; };
+    const char *e = getenv("POLY_B200_SPLIT_TR");
+    if (!(e && e[0] == '0') && p.k_ax.size() == 1 && !rax.empty() && sel(rax.back()) == 1 && sel(p.k_ax[0]) != 1 &&
+        rax.size() - 1 + p.b_ax.size() <= 6 && rax.back().ext <= 2147483647LL) {
+      SplitTrArgs t{};
+      t.src = (const float *)src_buf + off; t.dst = (float *)dst;
+      t.R = (int)rax.back().ext; t.K = (int)p.K; t.Kp = (int)Kp; t.s_k = sel(p.k_ax[0]); t.is_b = is_a ? 0 : 1;
+      long long nz = 1;
+      bool fits = true;
+      for (int i = (int)rax.size() - 2; i >= 0; i--) { t.ext[t.naxes] = (int)rax[i].ext; t.sstride[t.naxes++] = sel(rax[i]); nz *= rax[i].ext; }
+      for (size_t i = 0; i < p.b_ax.size(); i++) { t.ext[t.naxes] = (int)p.b_ax[i].ext; t.sstride[t.naxes++] = sel(p.b_ax[i]); nz *= p.b_ax[i].ext; }
+      if (nz > 65535 || (Kp + 31) / 32 > 65535) fits = false;
+      if (fits) {
+        dim3 grid((unsigned)((t.R + 31) / 32), (unsigned)((Kp + 31) / 32), (unsigned)nz);
+        pb200_split_tf32x3_tr<<<grid, 256, 0, stream>>>(t);
+        ok = cudaGetLastError() == cudaSuccess;
+        p.launches++;
+        if (!ok) {
+          if (*scratch) { pb_scratch_free(*scratch); *scratch = nullptr; }
+          else cache.version = 0;
+          return nullptr;
+        }
+        return dst;
+      }
+    }
     dense = pb_scratch_alloc((size_t)(p.nbatch * rows * Kp) * 4);
     ok = dense != nullptr && p.pack_into(dense, src_buf, off, is_a, PB_F32, PB_F32, Kp, stream) == 0;
     in.src = (const float *)dense; in.pitch = Kp; in.rows = p.nbatch * rows; in.nb = 0;
   }
   if (ok) {
     const long long total = p.nbatch * rows * Kp;
-    long long blocks = (total + 255) / 256;
+    bool v4 = (reinterpret_cast<uintptr_t>(in.src) & 15) == 0 && in.pitch % 4 == 0;
+    for (int i = 0; i < in.nb; i++) if (in.bstr[i] % 4) v4 = false;
+    long long blocks = ((v4 ? total / 4 : total) + 255) / 256;
     if (blocks > 148LL * 32) blocks = 148LL * 32;
-    pb200_split_tf32x3<<<(unsigned)blocks, 256, 0, stream>>>(in, (float *)dst, total, (int)p.K, (int)Kp, is_a ? 0 : 1);
+    if (v4) pb200_split_tf32x3_v4<<<(unsigned)blocks, 256, 0, stream>>>(in, (float *)dst, total / 4, (int)p.K, (int)Kp, is_a ? 0 : 1);
+    else pb200_split_tf32x3<<<(unsigned)blocks, 256, 0, stream>>>(in, (float *)dst, total, (int)p.K, (int)Kp, is_a ? 0 : 1);
     ok = cudaGetLastError() == cudaSuccess;
     p.launches++;
   }

@@ -254,6 +254,29 @@ def test_fp32_tensor_core_route_batched_views(devices, policy, monkeypatch, rout
     assert_close(got, want, 1e-5 if route == 'tcp' else 1e-4, f'batched attention contractions, {route}')
 
 
+@pytest.mark.parametrize('tokens,d_in,d_out', [(512, 192, 320), (1000, 77, 130)], ids=str)
+def test_fp32_tensor_core_route_transposed_operands(devices, policy, gpu, monkeypatch, tokens, d_in, d_out):
+    """The weight-gradient form x^T . dy on the promoted tensor-core route: both operands are stored with
+    their row axis contiguous and the contraction axis (the tokens) strided, so both are transposed and
+    split into their tf32 parts in one pass (POLY_B200_SPLIT_TR=0: gathered into a dense copy first, then
+    split; same bits)."""
+    cpu, cuda = devices
+    policy(False)
+    rng = np.random.default_rng([tokens, d_in])
+    x = rng.standard_normal((tokens, d_in)).astype(np.float32)
+    dy = rng.standard_normal((tokens, d_out)).astype(np.float32)
+    monkeypatch.setenv('POLY_B200_FP32', 'simt')
+    want = cpu.tensor(x).permute(1, 0).dot(cpu.tensor(dy)).numpy()
+    monkeypatch.setenv('POLY_B200_FP32', 'tcp')
+    gpu.poly_b200_stats_reset()
+    got = cuda.tensor(x).permute(1, 0).dot(cuda.tensor(dy)).numpy()
+    assert gpu.stats()['launches_precompiled'] == 3             # two transposing splits and the contraction
+    assert_close(got, want, 1e-5, 'x^T . dy, promoted tf32x3')
+    monkeypatch.setenv('POLY_B200_SPLIT_TR', '0')
+    two_pass = cuda.tensor(x).permute(1, 0).dot(cuda.tensor(dy)).numpy()
+    assert np.array_equal(got.view(np.uint32), two_pass.view(np.uint32))
+
+
 def test_fp32_default_routes(devices, policy, gpu, monkeypatch):
     """Large float32 contractions take the tensor-core route with promoted partial sums by default,
     small ones the CUDA-core kernel; both within 1e-5 of the CPU."""
