@@ -821,19 +821,21 @@ static const void *tc_operand_x3(PbGemmProgram &p, PbTcOperand &cache, const voi
     in.nb = (int)p.b_ax.size();
     for (int i = 0; i < in.nb; i++) { in.bext[i] = (int)p.b_ax[i].ext; in.bstr[i] = is_a ? p.b_ax[i].sa : p.b_ax[i].sb; }
   } else {
-    /* rows contiguous, one strided k axis: transposed and split in one pass */
-    const std::vector<PbGemmAxis> &rax = is_a ? p.m_ax : p.n_ax;
+    /* a strided matrix per batch entry with its rows contiguous and k strided (a weight gradient reads the
+     * activations transposed; the token axes (batch, position) nest into one k axis): transposed and split
+     * in one pass */
     auto sel = [&](const PbGemmAxis &x) { return is_a ? x.sa : x.sb; };
     const char *e = getenv("POLY_B200_SPLIT_TR");
-    if (!(e && e[0] == '0') && p.k_ax.size() == 1 && !rax.empty() && sel(rax.back()) == 1 && sel(p.k_ax[0]) != 1 &&
-        rax.size() - 1 + p.b_ax.size() <= 6 && rax.back().ext <= 2147483647LL) {
+    if (!(e && e[0] == '0') && direct && srow == 1 && sk > 1 && rows > 1 && p.b_ax.size() <= 6 && rows <= 2147483647LL) {
       SplitTrArgs t{};
       t.src = (const float *)src_buf + off; t.dst = (float *)dst;
-      t.R = (int)rax.back().ext; t.K = (int)p.K; t.Kp = (int)Kp; t.s_k = sel(p.k_ax[0]); t.is_b = is_a ? 0 : 1;
+      t.R = (int)rows; t.K = (int)p.K; t.Kp = (int)Kp; t.s_k = sk; t.is_b = is_a ? 0 : 1;
       long long nz = 1;
       bool fits = true;
-      for (int i = (int)rax.size() - 2; i >= 0; i--) { t.ext[t.naxes] = (int)rax[i].ext; t.sstride[t.naxes++] = sel(rax[i]); nz *= rax[i].ext; }
-      for (size_t i = 0; i < p.b_ax.size(); i++) { t.ext[t.naxes] = (int)p.b_ax[i].ext; t.sstride[t.naxes++] = sel(p.b_ax[i]); nz *= p.b_ax[i].ext; }
+      for (size_t i = 0; i < p.b_ax.size(); i++) {
+        if (sel(p.b_ax[i]) < 0) fits = false;
+        t.ext[t.naxes] = (int)p.b_ax[i].ext; t.sstride[t.naxes++] = sel(p.b_ax[i]); nz *= p.b_ax[i].ext;
+      }
       if (nz > 65535 || (Kp + 31) / 32 > 65535) fits = false;
       if (fits) {
         dim3 grid((unsigned)((t.R + 31) / 32), (unsigned)((Kp + 31) / 32), (unsigned)nz);

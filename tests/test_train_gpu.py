@@ -138,15 +138,23 @@ def test_gpt2_train_steps_match_cpu(ref_lib, gpu, optim, lr):
         assert_close(got, want, ptol, f'{name} after 3 steps')
 
 
-@pytest.mark.parametrize('optim,lr', [(ffi.OPTIM_SGD, 1e-5), (ffi.OPTIM_ADAMW, 1e-4)], ids=['sgd', 'adamw'])
-def test_gpt2_train_steps_with_backward_kernels_cut(ref_lib, gpu, monkeypatch, optim, lr):
+@pytest.mark.parametrize('optim,lr,route', [(ffi.OPTIM_SGD, 1e-5, None), (ffi.OPTIM_SGD, 1e-5, 'tcp'), (ffi.OPTIM_ADAMW, 1e-4, None)],
+                         ids=['sgd', 'sgd_tensor_cores', 'adamw'])
+def test_gpt2_train_steps_with_backward_kernels_cut(ref_lib, gpu, monkeypatch, optim, lr, route):
     """The same three steps with every backward kernel that holds a contraction cut into operand
     temporaries, contraction steps and an elementwise remainder (at this width the cut would not pay
     and is forced): weight gradients whose operand is a sum of gradient contributions, the tied
     embedding's gradient (head contraction + lookup selection + update in one scheduled kernel), the
     q/k/v gradients written side by side, and under AdamW the moment updates that each hold the
-    gradient's contraction.  Same tolerances as the uncut run."""
+    gradient's contraction.  Same tolerances as the uncut run.  `sgd_tensor_cores` also sends every
+    float32 contraction the tensor-core kernel accepts through it (three tf32 products, operands split --
+    and, where their rows are the contiguous axis, transposed -- on the way; scaled sums included), as
+    happens by default from 2^30 multiply-adds."""
     monkeypatch.setenv('POLY_B200_OUTLINE_MIN_WORK', '0')
+    if route:
+        monkeypatch.setenv('POLY_B200_FP32', route)
+    else:
+        monkeypatch.delenv('POLY_B200_FP32', raising=False)
     cfg = dict(vocab_size=64, n_embd=48, n_head=4, n_layer=2, max_seq_len=16, max_batch=2)
     tokens = np.random.default_rng(17).integers(0, cfg['vocab_size'], (cfg['max_batch'], cfg['max_seq_len']))
     want_l, want_p = _train_gpt2(ref_lib, ffi.DEVICE_CPU, cfg, tokens, optim, lr, 3)
