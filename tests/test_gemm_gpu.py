@@ -277,6 +277,41 @@ def test_fp32_tensor_core_route_transposed_operands(devices, policy, gpu, monkey
     assert np.array_equal(got.view(np.uint32), two_pass.view(np.uint32))
 
 
+FUSED_FORMS = {
+    # an operand that is computed on the fly: the scheduler folds the sum into the reduction
+    'sum_of_two_as_operand': lambda t: (t['a'] + t['a2']).dot(t['b']),
+    # an activation in front of the contraction
+    'relu_operand_and_bias': lambda t: t['a'].relu().dot(t['b']) + t['bias'],
+    # two contractions added in one kernel
+    'sum_of_two_contractions': lambda t: t['a'].dot(t['b']) + t['a2'].dot(t['b2']),
+    # a scaled contraction behind an elementwise expression of two buffers
+    'update_by_two_products': lambda t: t['x'] - (t['a'].dot(t['b']) + t['a2'].dot(t['b2'])) * 0.05,
+}
+
+
+@pytest.mark.parametrize('form', sorted(FUSED_FORMS))
+def test_kernels_with_fused_operands_or_several_contractions(devices, policy, gpu, form):
+    """Graphs whose contraction the scheduler fuses with a computed operand, or several contractions it
+    puts into one kernel: by default (the contractions hold 2^24 multiply-adds here) such a kernel is cut
+    into operand temporaries, one contraction each and an elementwise remainder, all on precompiled or
+    vectorised kernels; with POLY_B200_OUTLINE=0 it runs whole as generated code.  Both within 1e-5 of
+    the CPU."""
+    cpu, cuda = devices
+    policy(False)
+    m, n, k = 256, 384, 192
+    rng = np.random.default_rng([m, n, k, 11])
+    arrays = dict(a=rng.uniform(-1, 1, (m, k)), a2=rng.uniform(-1, 1, (m, k)), b=rng.uniform(-1, 1, (k, n)),
+                  b2=rng.uniform(-1, 1, (k, n)), bias=rng.uniform(-1, 1, (n,)), x=rng.uniform(-1, 1, (m, n)))
+    arrays = {name: v.astype(np.float32) for name, v in arrays.items()}
+    build = FUSED_FORMS[form]
+    want = build({name: cpu.tensor(v) for name, v in arrays.items()}).numpy()
+    gpu.poly_b200_stats_reset()
+    got = build({name: cuda.tensor(v) for name, v in arrays.items()}).numpy()
+    st = gpu.stats()
+    assert_close(got, want, 1e-5, form)
+    assert st['launches_precompiled'] >= 1, 'no contraction kernel ran'
+
+
 def test_fp32_default_routes(devices, policy, gpu, monkeypatch):
     """Large float32 contractions take the tensor-core route with promoted partial sums by default,
     small ones the CUDA-core kernel; both within 1e-5 of the CPU."""
