@@ -14,6 +14,9 @@
  *           are affine in the kernel's ranges (after splitting a range where
  *           a view introduced div/mod, e.g. the head-merge read in
  *           src/modelzoo/models/gpt2.c:436-452).
+ *   scatter the gradient of that lookup: for every table row, the sum of the
+ *           gradient rows whose token is that row; executed as a scan of the
+ *           tokens per group of table rows followed by ordered row sums.
  *   copy    a pure data movement whose source and destination differ in their
  *           contiguous axis (permute): executed as a tiled transpose.
  *
@@ -228,8 +231,8 @@ static bool in_bounds(const VFit *f, const VAxis *va, int nva, int64_t numel) {
 
 /* ── gather ──────────────────────────────────────────────────────────── */
 /* equality test of two loads, in any of the forms the frontend produces */
-static bool match_equal(PolyUOp *c, PolyUOp **a, PolyUOp **b) {
-  if (c->op == POLY_OP_CAST) return match_equal(c->src[0], a, b);
+bool pb_match_equal(PolyUOp *c, PolyUOp **a, PolyUOp **b) {
+  if (c->op == POLY_OP_CAST) return pb_match_equal(c->src[0], a, b);
   if (c->op == POLY_OP_CMPEQ) { *a = c->src[0]; *b = c->src[1]; return true; }
   if (c->op == POLY_OP_NEG && c->src[0]->op == POLY_OP_CMPNE) { *a = c->src[0]->src[0]; *b = c->src[0]->src[1]; return true; }
   if (c->op == POLY_OP_WHERE && c->src[0]->op == POLY_OP_CMPNE && const_is(c->src[1], 0.0) &&
@@ -251,7 +254,7 @@ static char *classify_gather(PbKern *k) {
   PolyUOp *w = red->src[0];
   if (w->op != POLY_OP_WHERE || !const_is(w->src[2], 0.0)) REJECT("pattern");
   PolyUOp *ea, *eb;
-  if (!match_equal(w->src[0], &ea, &eb)) REJECT("pattern");
+  if (!pb_match_equal(w->src[0], &ea, &eb)) REJECT("pattern");
   PolyUOp *tab = w->src[1];
   if (!is_plain_load(ea) || !is_plain_load(eb) || !is_plain_load(tab)) REJECT("pattern");
   uint64_t rbit = (uint64_t)1 << rv;
@@ -297,6 +300,93 @@ static char *classify_gather(PbKern *k) {
     } else { pb_str_free(&tok); pb_str_free(&feat); pb_str_free(&h); REJECT("pattern"); }
   }
   if (ntok > 4 || nfeat > 3) { pb_str_free(&tok); pb_str_free(&feat); pb_str_free(&h); REJECT("pattern"); }
+  pb_str_printf(&h, "//tok%s\n//feat%s\n", tok.s ? tok.s : "", feat.s ? feat.s : "");
+  pb_str_free(&tok); pb_str_free(&feat);
+  return pb_str_take(&h);
+}
+
+/* ── scatter: the lookup's gradient ──────────────────────────────────── */
+/* The backward of the one-hot lookup sums, for every table row v, the rows of the incoming gradient
+ * whose token is v:  out[v, d] = sum_t where(ids[t] == arange[v], g[t, d], 0)  (reference: the gradient of
+ * the WHERE/REDUCE pair of src/modelzoo/models/gpt2.c:93-153 under src/autograd.c).  Same tree as the
+ * lookup with the roles of the axes exchanged: the reduction runs over the token axes, `arange` is
+ * indexed by an output axis. */
+static char *classify_scatter(PbKern *k) {
+  if (k->n_stores != 1 || k->n_reduce_nodes < 1 || k->n_reduce_nodes > 2 || !all_const_extents(k)) REJECT("pattern");
+  PbStore *st = &k->stores[0];
+  if (st->index->n_src != 2 || st->value->op != POLY_OP_REDUCE) REJECT("pattern");
+  PolyUOp *red = st->value;
+  PolyOps rop = red->arg.kind == POLY_ARG_OPS ? red->arg.ops : (PolyOps)red->arg.i;
+  if (rop != POLY_OP_ADD || red->n_src < 2) REJECT("pattern");
+  /* a sum of a sum (x.sum(0).sum(0) over batch and position) is one sum over both */
+  PolyUOp *inner = NULL;
+  if (k->n_reduce_nodes == 2) {
+    inner = red->src[0];
+    if (inner->op != POLY_OP_REDUCE || inner->n_src < 2 || k->nodes[pb_kern_node(k, inner)].n_uses != 1) REJECT("pattern");
+    PolyOps iop = inner->arg.kind == POLY_ARG_OPS ? inner->arg.ops : (PolyOps)inner->arg.i;
+    if (iop != POLY_OP_ADD || !is_f32(inner->dtype)) REJECT("pattern");
+  }
+  uint64_t rmask = 0;
+  for (int i = 1; i < red->n_src; i++) { int r = pb_kern_range_id(k, red->src[i]); if (r < 0) REJECT("pattern"); rmask |= (uint64_t)1 << r; }
+  for (int i = 1; inner && i < inner->n_src; i++) { int r = pb_kern_range_id(k, inner->src[i]); if (r < 0) REJECT("pattern"); rmask |= (uint64_t)1 << r; }
+  PolyUOp *w = inner ? inner->src[0] : red->src[0];
+  if (w->op != POLY_OP_WHERE || !const_is(w->src[2], 0.0)) REJECT("pattern");
+  PolyUOp *ea, *eb;
+  if (!pb_match_equal(w->src[0], &ea, &eb)) REJECT("pattern");
+  PolyUOp *src = w->src[1];
+  if (!is_plain_load(ea) || !is_plain_load(eb) || !is_plain_load(src)) REJECT("pattern");
+  if (!is_f32(ea->dtype) || !is_f32(eb->dtype) || !is_f32(src->dtype) || !is_f32(red->dtype)) REJECT("dtype");
+  if (k->params[st->param]->dtype.priority != 13) REJECT("dtype");
+
+  uint64_t mask = rmask;
+  for (int i = 0; i < st->n_loop; i++) mask |= (uint64_t)1 << st->loop[i];
+  /* which side of the equality is the token's id and which the table row's number is read off the
+   * strides (the index expressions may mention ranges they do not depend on) */
+  PolyUOp *exprs[4] = { st->index->src[1], load_index(ea), load_index(eb), load_index(src) };
+  VAxis va[2 * PB_MAX_AXES]; int nva; VFit fit[4];
+  if (!pb_find_axes(k, mask, exprs, 4, va, &nva, fit)) REJECT("pattern");
+  bool a_red = false, a_out = false, b_red = false, b_out = false;
+  for (int i = 0; i < nva; i++) {
+    if (va[i].extent <= 1) continue;
+    if (fit[1].stride[i]) { if (va[i].reduce) a_red = true; else a_out = true; }
+    if (fit[2].stride[i]) { if (va[i].reduce) b_red = true; else b_out = true; }
+  }
+  PolyUOp *idx, *ar;
+  if (a_red && !a_out && b_out && !b_red) { idx = ea; ar = eb; }
+  else if (b_red && !b_out && a_out && !a_red) { idx = eb; ar = ea; VFit t = fit[1]; fit[1] = fit[2]; fit[2] = t; }
+  else REJECT("pattern");
+  int params[4] = { st->param, load_param(idx), load_param(ar), load_param(src) };
+  for (int i = 0; i < 4; i++) if (!in_bounds(&fit[i], va, nva, param_numel(k, params[i]))) REJECT("pattern");
+  for (int i = 1; i < 4; i++) if (params[i] == params[0]) REJECT("pattern");
+  /* one output axis is the table row: arange is read as arange[v] there and nowhere else */
+  int vax = -1;
+  for (int i = 0; i < nva; i++) if (va[i].extent > 1 && fit[2].stride[i] != 0) { if (vax >= 0) REJECT("pattern"); vax = i; }
+  if (vax < 0 || va[vax].reduce || fit[2].offset != 0 || fit[2].stride[vax] != 1) REJECT("pattern");
+  if (fit[0].stride[vax] == 0 || fit[1].stride[vax] != 0 || fit[3].stride[vax] != 0) REJECT("pattern");
+
+  PbStr h; pb_str_init(&h);
+  pb_str_puts(&h, "//PB200 1\n//kind scatter\n");
+  pb_str_printf(&h, "//nparams %d\n", k->n_params);
+  pb_str_printf(&h, "//params %d %d %d %d\n", params[0], params[1], params[2], params[3]);
+  pb_str_printf(&h, "//vocab %lld %lld\n", (long long)va[vax].extent, (long long)fit[0].stride[vax]);
+  pb_str_printf(&h, "//offsets %lld %lld %lld\n", (long long)fit[0].offset, (long long)fit[1].offset, (long long)fit[3].offset);
+  int ntok = 0, nfeat = 0;
+  PbStr tok, feat; pb_str_init(&tok); pb_str_init(&feat);
+  /* token axes (reduced): innermost first, i.e. the later virtual axis of a later range first */
+  for (int i = nva - 1; i >= 0; i--) {
+    if (i == vax || va[i].extent == 1) continue;
+    if (va[i].reduce) {
+      if (fit[0].stride[i] != 0) { pb_str_free(&tok); pb_str_free(&feat); pb_str_free(&h); REJECT("pattern"); }
+      pb_str_printf(&tok, " %lld %lld %lld", (long long)va[i].extent, (long long)fit[1].stride[i], (long long)fit[3].stride[i]);
+      ntok++;
+    } else {
+      /* a feature axis: walks the output and the source, not the ids */
+      if (fit[1].stride[i] != 0 || fit[0].stride[i] == 0) { pb_str_free(&tok); pb_str_free(&feat); pb_str_free(&h); REJECT("pattern"); }
+      pb_str_printf(&feat, " %lld %lld %lld", (long long)va[i].extent, (long long)fit[0].stride[i], (long long)fit[3].stride[i]);
+      nfeat++;
+    }
+  }
+  if (ntok < 1 || ntok > 4 || nfeat > 3) { pb_str_free(&tok); pb_str_free(&feat); pb_str_free(&h); REJECT("pattern"); }
   pb_str_printf(&h, "//tok%s\n//feat%s\n", tok.s ? tok.s : "", feat.s ? feat.s : "");
   pb_str_free(&tok); pb_str_free(&feat);
   return pb_str_take(&h);
@@ -515,6 +605,8 @@ static char *classify_transpose(PbKern *k) {
 char *pb_classify_aot(PbKern *k, const char *fn_name) {
   (void)fn_name;
   char *r = classify_gather(k);
+  if (r) return r;
+  r = classify_scatter(k);
   if (r) return r;
   r = classify_gemm(k);
   if (r) return r;

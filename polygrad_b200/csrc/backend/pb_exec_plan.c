@@ -130,7 +130,7 @@ static int lower_cut(PbPlan *p, PolyCtx *ctx, PolySchedule *sched, int item_idx,
     char *src = poly_render_cuda(lin, n_lin, name, 256);
     free(lin);
     if (!src) { ok = false; break; }
-    if (pieces[i].must_be_contraction && !strstr(src, "//kind gemm")) {
+    if (pieces[i].must_be_contraction && !strstr(src, "//kind gemm") && !strstr(src, "//kind scatter")) {
       if (getenv("POLY_B200_DEBUG")) fprintf(stderr, "pb_plan: %s: piece %d is not recognised as a contraction; the kernel stays whole\n", fn_name, i);
       free(src); ok = false; break;
     }

@@ -113,6 +113,9 @@ typedef struct {
 bool pb_find_axes(const PbKern *k, uint64_t mask, PolyUOp **exprs, int n_exprs,
                   VAxis *va, int *nva, VFit *fits);
 
+/* c as an equality test of two values, in any of the forms the frontend produces (pb_classify.c). */
+bool pb_match_equal(PolyUOp *c, PolyUOp **a, PolyUOp **b);
+
 /* C type used in generated code for a scalar dtype (NULL if unsupported). */
 const char *pb_ctype(PolyDType dt);
 

@@ -346,6 +346,29 @@ static bool contraction_like(PbKern *k, PolyUOp *red) {
   return M >= 8 && N >= 8 && K >= 8;
 }
 
+/* where(ids[t] == arange[v], y, 0) summed over the tokens: the lookup's gradient, which has a kernel of
+ * its own (classify_scatter) -- one side of the equality walks only the reduction, the other only output
+ * axes, both plain loads. */
+static bool lookup_selection(PbKern *k, PolyUOp *red, PolyUOp *cond) {
+  PolyUOp *a, *b;
+  if (!pb_match_equal(cond, &a, &b) || !is_plain_load(a) || !is_plain_load(b)) return false;
+  PbStore *st = &k->stores[0];
+  uint64_t mask = 0;
+  for (int i = 0; i < st->n_loop; i++) mask |= (uint64_t)1 << st->loop[i];
+  for (int i = 1; i < red->n_src; i++) { int r = pb_kern_range_id(k, red->src[i]); if (r >= 0) mask |= (uint64_t)1 << r; }
+  /* by what the indices really walk (they may mention ranges they do not depend on) */
+  PolyUOp *exprs[2] = { a->src[0]->src[1], b->src[0]->src[1] };
+  VAxis va[2 * PB_MAX_AXES]; int nva = 0; VFit fit[2];
+  if (!pb_find_axes(k, mask, exprs, 2, va, &nva, fit)) return false;
+  bool a_red = false, a_out = false, b_red = false, b_out = false;
+  for (int i = 0; i < nva; i++) {
+    if (va[i].extent <= 1) continue;
+    if (fit[0].stride[i]) { if (va[i].reduce) a_red = true; else a_out = true; }
+    if (fit[1].stride[i]) { if (va[i].reduce) b_red = true; else b_out = true; }
+  }
+  return (a_red && !a_out && b_out && !b_red) || (b_red && !b_out && a_out && !a_red);
+}
+
 static int64_t reduce_work(PbKern *k, PolyUOp *red) {
   int64_t w = 1;
   for (int r = 0; r < k->n_ranges; r++) {
@@ -536,6 +559,7 @@ int pb_outline(PolyCtx *ctx, PolyUOp *sink, PbPiece *pieces, int cap, int64_t *t
       for (int s = 1; s >= 0 && ok; s--) {
         /* what is stored: the factor without constant scale, or the 0/1 value of a condition */
         PolyUOp *e = operand_core(f[s]), *deps_of = e, *stored = e;
+        if (selects && s == 0 && lookup_selection(&k, reds[i], f[0])) continue;   /* stays: the scatter kernel takes it */
         if (selects && s == 0) {
           e = f[0]; deps_of = f[0];
           stored = poly_uop3(ctx, POLY_OP_WHERE, reds[i]->dtype, f[0],
@@ -564,7 +588,7 @@ int pb_outline(PolyCtx *ctx, PolyUOp *sink, PbPiece *pieces, int cap, int64_t *t
         }
         put_back[s] = have;
       }
-      if (ok && selects) {
+      if (ok && selects && put_back[0]) {
         /* where(c, y, 0) becomes onehot * y, y with whatever was substituted in it */
         PolyUOp *y = rebuild(ctx, &subst, f[1]);
         PolyUOp *prod = y && put_back[0] ? poly_uop2(ctx, POLY_OP_MUL, reds[i]->dtype, put_back[0], y, poly_arg_none()) : NULL;
@@ -583,7 +607,7 @@ int pb_outline(PolyCtx *ctx, PolyUOp *sink, PbPiece *pieces, int cap, int64_t *t
     PbKern k2;
     if (pb_kern_build(&k2, current) == 0 && k2.n_reduce_nodes == 1) {
       char *hdr = pb_classify_aot(&k2, "outline");
-      if (hdr) { single = strstr(hdr, "//kind gemm") != NULL; free(hdr); }
+      if (hdr) { single = strstr(hdr, "//kind gemm") != NULL || strstr(hdr, "//kind scatter") != NULL; free(hdr); }
     }
     pb_kern_free(&k2);
   }

@@ -160,3 +160,134 @@ PbAotProgram *pb_make_gather(const PbHeader &h, std::string &err) {
     }
   return p;
 }
+
+/* ── the lookup's gradient ───────────────────────────────────────────── */
+/* out[v, d] = sum_t (ids[t] == arange[v]) ? src[t, d] : 0 for every table row v (reference: the backward
+ * of the one-hot lookup, which polygrad runs as a contraction over all tokens for every row).  A block
+ * owns SCATTER_ROWS consecutive rows: its threads scan the tokens once, noting which token matches
+ * which of the block's rows (any `arange` contents: NaNs match nothing, duplicates match several rows),
+ * the few matches are put in token order, and every (row, d) element is the sum of its matching source
+ * rows in that order, starting from +0 -- the order and the value of the reference's accumulation, in
+ * which the non-matching tokens add +0.  Rows nobody refers to are written as +0.
+ * HBM traffic: the output written once, the ids read once per block (from L2), the matching source rows. */
+struct ScatterArgs {
+  float *out; const float *ids; const float *arange; const float *src;
+  long long vocab, out_vstride;
+  long long out_off, ids_off, src_off;
+  int ntok; long long tok_ext[4], tok_ids[4], tok_src[4];
+  int nfeat; long long feat_ext[3], feat_out[3], feat_src[3];
+  long long n_tokens, n_feat;
+};
+
+#define SCATTER_THREADS 256
+#define SCATTER_ROWS 16
+#define SCATTER_MAX_MATCH 1024
+
+__global__ void __launch_bounds__(SCATTER_THREADS) pb200_scatter_rows(const ScatterArgs a) {
+  __shared__ float s_ar[SCATTER_ROWS];
+  __shared__ int s_count;
+  __shared__ unsigned long long s_match[SCATTER_MAX_MATCH];      /* (row << 40) | token, sorted ascending */
+  __shared__ int s_first[SCATTER_ROWS + 1];
+  const long long v0 = (long long)blockIdx.x * SCATTER_ROWS;
+  const int rows = (int)min((long long)SCATTER_ROWS, a.vocab - v0);
+  if (threadIdx.x < SCATTER_ROWS) s_ar[threadIdx.x] = threadIdx.x < rows ? a.arange[v0 + threadIdx.x] : __int_as_float(0x7fc00000);
+  if (threadIdx.x == 0) s_count = 0;
+  __syncthreads();
+  for (long long t = threadIdx.x; t < a.n_tokens; t += SCATTER_THREADS) {
+    long long rem = t, o = a.ids_off;
+    for (int i = 0; i < a.ntok; i++) { const long long x = rem % a.tok_ext[i]; rem /= a.tok_ext[i]; o += x * a.tok_ids[i]; }
+    const float id = a.ids[o];
+#pragma unroll
+    for (int r = 0; r < SCATTER_ROWS; r++) {
+      if (id == s_ar[r]) {
+        const int slot = atomicAdd(&s_count, 1);
+        if (slot < SCATTER_MAX_MATCH) s_match[slot] = ((unsigned long long)r << 40) | (unsigned long long)t;
+      }
+    }
+  }
+  __syncthreads();
+  const int count = s_count;
+  const bool listed = count <= SCATTER_MAX_MATCH;
+  if (listed && threadIdx.x == 0) {
+    /* by row, then by token: the order the reference adds in */
+    for (int i = 1; i < count; i++) {
+      const unsigned long long x = s_match[i]; int j = i - 1;
+      while (j >= 0 && s_match[j] > x) { s_match[j + 1] = s_match[j]; j--; }
+      s_match[j + 1] = x;
+    }
+    int at = 0;
+    for (int r = 0; r <= SCATTER_ROWS; r++) {
+      while (at < count && (int)(s_match[at] >> 40) < r) at++;
+      s_first[r] = at;
+    }
+  }
+  __syncthreads();
+  const long long elems = (long long)rows * a.n_feat;
+  for (long long e = threadIdx.x; e < elems; e += SCATTER_THREADS) {
+    const int r = (int)(e / a.n_feat);
+    long long fr = e % a.n_feat, o = a.out_off + (v0 + r) * a.out_vstride, s = a.src_off;
+    for (int i = 0; i < a.nfeat; i++) { const long long x = fr % a.feat_ext[i]; fr /= a.feat_ext[i]; o += x * a.feat_out[i]; s += x * a.feat_src[i]; }
+    float acc = 0.0f;
+    if (listed) {
+      for (int m = s_first[r]; m < s_first[r + 1]; m++) {
+        long long rem = (long long)(s_match[m] & 0xffffffffffull), so = s;
+        for (int i = 0; i < a.ntok; i++) { const long long x = rem % a.tok_ext[i]; rem /= a.tok_ext[i]; so += x * a.tok_src[i]; }
+        acc = acc + a.src[so];
+      }
+    } else {
+      /* more matches than the list holds (a batch of one repeated token): plain ordered scan */
+      const float want = s_ar[r];
+      for (long long t = 0; t < a.n_tokens; t++) {
+        long long rem = t, oi = a.ids_off, so = s;
+        for (int i = 0; i < a.ntok; i++) { const long long x = rem % a.tok_ext[i]; rem /= a.tok_ext[i]; oi += x * a.tok_ids[i]; so += x * a.tok_src[i]; }
+        if (a.ids[oi] == want) acc = acc + a.src[so];
+      }
+    }
+    a.out[o] = acc;
+  }
+}
+
+struct ScatterProgram : PbAotProgram {
+  ScatterArgs a{};
+  int n_launches() const override { return 1; }
+  int p_out, p_ids, p_arange, p_src;
+  int launch(void *const *bufs, cudaStream_t stream) override {
+    ScatterArgs g = a;
+    g.out = (float *)bufs[p_out]; g.ids = (const float *)bufs[p_ids];
+    g.arange = (const float *)bufs[p_arange]; g.src = (const float *)bufs[p_src];
+    if (g.vocab <= 0 || g.n_feat <= 0) return 0;
+    const long long grid = (g.vocab + SCATTER_ROWS - 1) / SCATTER_ROWS;
+    if (grid > 2147483647LL) { pb_set_error("scatter: too many table rows"); return -1; }
+    pb200_scatter_rows<<<(unsigned)grid, SCATTER_THREADS, 0, stream>>>(g);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { pb_set_error("scatter launch: %s", cudaGetErrorString(e)); return -1; }
+    return 0;
+  }
+};
+
+PbAotProgram *pb_make_scatter(const PbHeader &h, std::string &err) {
+  auto params = h.getv("params"), vocab = h.getv("vocab"), off = h.getv("offsets");
+  auto tok = h.getv("tok"), feat = h.getv("feat");
+  if (params.size() != 4 || vocab.size() != 2 || off.size() != 3 || tok.size() % 3 || feat.size() % 3 ||
+      tok.empty() || tok.size() > 12 || feat.size() > 9) { err = "malformed scatter header"; return nullptr; }
+  ScatterProgram *p = new ScatterProgram();
+  p->n_params = (int)h.geti("nparams");
+  p->p_out = (int)params[0]; p->p_ids = (int)params[1]; p->p_arange = (int)params[2]; p->p_src = (int)params[3];
+  p->rw.assign((size_t)p->n_params, '-');
+  for (int i = 1; i < 4; i++) p->rw[(size_t)params[i]] = 'r';
+  p->rw[(size_t)params[0]] = 'w';
+  ScatterArgs &a = p->a;
+  a.vocab = vocab[0]; a.out_vstride = vocab[1];
+  a.out_off = off[0]; a.ids_off = off[1]; a.src_off = off[2];
+  a.ntok = (int)tok.size() / 3; a.nfeat = (int)feat.size() / 3;
+  a.n_tokens = 1; a.n_feat = 1;
+  for (int i = 0; i < a.ntok; i++) { a.tok_ext[i] = tok[3 * i]; a.tok_ids[i] = tok[3 * i + 1]; a.tok_src[i] = tok[3 * i + 2]; a.n_tokens *= a.tok_ext[i]; }
+  for (int i = 0; i < a.nfeat; i++) { a.feat_ext[i] = feat[3 * i]; a.feat_out[i] = feat[3 * i + 1]; a.feat_src[i] = feat[3 * i + 2]; a.n_feat *= a.feat_ext[i]; }
+  if (a.n_tokens >= (1LL << 40)) { err = "scatter: too many tokens"; delete p; return nullptr; }
+  /* feature axes: smallest output stride first so that consecutive threads write consecutive floats */
+  for (int i = 1; i < a.nfeat; i++)
+    for (int j = i; j > 0 && llabs(a.feat_out[j]) < llabs(a.feat_out[j - 1]); j--) {
+      std::swap(a.feat_ext[j], a.feat_ext[j - 1]); std::swap(a.feat_out[j], a.feat_out[j - 1]); std::swap(a.feat_src[j], a.feat_src[j - 1]);
+    }
+  return p;
+}

@@ -813,6 +813,7 @@ extern "C" PolyCudaProgram *poly_compile_cuda(const char *source, const char *fn
     p->kind = PolyCudaProgram::AOT;
     std::string err;
     if (kind == "gather") p->aot = pb_make_gather(h, err);
+    else if (kind == "scatter") p->aot = pb_make_scatter(h, err);
     else if (kind == "gemm") p->aot = pb_make_gemm(h, err);
     else if (kind == "copy") p->aot = pb_make_copy(h, err);
     else if (kind == "attn") p->aot = pb_make_attn(h, err);

@@ -36,6 +36,7 @@ struct PbAotProgram {
 
 /* Factories, one per kernel family; return nullptr and set err on bad headers. */
 PbAotProgram *pb_make_gather(const PbHeader &h, std::string &err);
+PbAotProgram *pb_make_scatter(const PbHeader &h, std::string &err);
 PbAotProgram *pb_make_gemm(const PbHeader &h, std::string &err);
 PbAotProgram *pb_make_copy(const PbHeader &h, std::string &err);
 PbAotProgram *pb_make_attn(const PbHeader &h, std::string &err);
