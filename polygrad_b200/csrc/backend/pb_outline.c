@@ -454,7 +454,7 @@ static bool windowed_piece(Cut *c, PolyUOp *red, PolyUOp *mask, PolyUOp **sink_o
     const Window *x = &w[i];
     if (k->is_reduce[x->range]) return false;
     if (x->shift == 0 && (!x->hi || x->extent >= k->extent[x->range])) continue;         /* always true */
-    if (!x->lo || !x->hi) return false;
+    if (!x->hi || (!x->lo && x->shift != 0)) return false;       /* a range is never negative: 0 <= r needs no test */
     if (-x->shift < 0 || x->extent - x->shift > k->extent[x->range] || x->extent < 1) return false;
     if (shift[x->range] != 0 || ext[x->range] != k->extent[x->range]) return false;       /* two windows on one range */
     shift[x->range] = x->shift; ext[x->range] = x->extent; any = true;
