@@ -68,6 +68,7 @@ struct TcArgs {
   int m_fast;                      /* consecutive tiles differ in the row tile (else in the column tile) */
   int kchunk;                      /* PROMOTE kernels: k-blocks summed in tensor memory before the partial sum moves to registers */
   float alpha;                     /* PROMOTE kernels: the sum is scaled by this before the addend (a parameter update behind a gradient) */
+  int stream_out;                  /* the result is far larger than L2: its stores are marked evict-first (unaligned float32 rows) */
 };
 
 #define PB_TC_ERROR_FLAG pb200_tc_error_flag
@@ -101,6 +102,10 @@ __device__ __forceinline__ uint32_t lds_b32(uint32_t addr) {
 }
 __device__ __forceinline__ void stg_b32(void *p, uint32_t a) {
   asm volatile("st.global.b32 [%0], %1;" ::"l"(p), "r"(a) : "memory");
+}
+/* streaming store: the line is the first to leave L2 (a result far larger than L2 must not push the operands out) */
+__device__ __forceinline__ void stg_b32_cs(void *p, uint32_t a) {
+  asm volatile("st.global.cs.b32 [%0], %1;" ::"l"(p), "r"(a) : "memory");
 }
 __device__ __forceinline__ void stg_v4(void *p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
@@ -483,7 +488,7 @@ pb200_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 for (int i = 0; i < 8; i++) {
                   float a = __uint_as_float(v[i]) + xb;
                   if (g.relu) a = (0.f < a) ? a : 0.f;
-                  if (r8 * 8 + i < rows) stg_b32(cp, __float_as_uint(a));
+                  if (r8 * 8 + i < rows) { if (g.stream_out) stg_b32_cs(cp, __float_as_uint(a)); else stg_b32(cp, __float_as_uint(a)); }
                   cp += g.c_sm;
                 }
               }
@@ -625,6 +630,10 @@ static int tc_launch(const CUtensorMap &ma, const CUtensorMap &mb, TcArgs &g, lo
   if (tiles > 2147483647LL) { pb_set_error("gemm: too many tiles"); return -1; }
   g.n_tiles = (int)tiles;
   g.m_fast = g.N > g.M ? 1 : 0;
+  {
+    const char *e = getenv("POLY_B200_TC_STREAM");           /* "0": ordinary stores (measurements) */
+    g.stream_out = !(e && e[0] == '0') && (double)g.M * (double)g.N * (double)nbatch * 4.0 >= 512.0 * 1024 * 1024;
+  }
   const int units = sm_count() / CTAS;
   const int grid = (int)(tiles < units ? tiles : units) * CTAS;
   cudaError_t e;
