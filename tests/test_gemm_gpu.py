@@ -110,6 +110,30 @@ def test_every_tile_width(devices, policy, monkeypatch, width, shape):
     assert_close(got, want16, 1e-4, f'width {width} {shape}')
 
 
+@pytest.mark.parametrize('epilogue', ['plain', 'bias', 'bias_relu'])
+@pytest.mark.parametrize('shape', [(300, 333, 64), (130, 1001, 96), (257, 50257 // 64 + 2, 48), (64, 67, 32)], ids=str)
+def test_float32_rows_that_are_not_16_byte_aligned(devices, policy, monkeypatch, shape, epilogue):
+    """A float32 result whose row pitch is not a multiple of four floats (the 50257-wide logits): the staged
+    tile goes out an element per lane, rows of any alignment, with and without a bias and ReLU, ragged last
+    chunk included.  Within the bf16 tolerance of the CPU, and the same bits on a second run."""
+    cpu, cuda = devices
+    a, b = _ab(shape, 8)
+    bias = np.random.default_rng(shape[1]).uniform(-1, 1, (shape[1],)).astype(np.float32)
+
+    def build(d, bf16):
+        ta, tb = (d.tensor(a, 'bfloat16').cast('float32'), d.tensor(b, 'bfloat16').cast('float32')) if bf16 else (d.tensor(a), d.tensor(b))
+        out = ta.dot(tb)
+        if epilogue != 'plain':
+            out = out + d.tensor(bias)
+        return out.relu() if epilogue == 'bias_relu' else out
+    want16 = build(cpu, True).numpy()
+    policy(True)
+    got = build(cuda, False).numpy()
+    again = build(cuda, False).numpy()
+    assert_close(got, want16, 1e-4, f'unaligned rows {shape} {epilogue}')
+    assert np.array_equal(got.view(np.uint32), again.view(np.uint32))
+
+
 @pytest.mark.parametrize('shape', [(300, 500, 100), (257, 1000, 72), (512, 768, 256), (129, 65, 17), (1024, 256, 2048)], ids=str)
 def test_cta_pairs(devices, policy, monkeypatch, shape):
     """The cta_group::2 form of the kernel (two CTAs per 256 x 256 tile), forced for shapes that would
