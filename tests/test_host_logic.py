@@ -234,3 +234,29 @@ def test_eager_entry_keeps_plans_and_results_in_dry_run():
         assert ran['bytes_htod'] == (i + 1) * nbytes and ran['bytes_dtoh'] == i * nbytes
         assert copied['buffers_resident'] == 0 and copied['bytes_dtoh'] == (i + 1) * nbytes
     assert log[4]['plans_kept'] == 0 and log[4]['buffers_resident'] == 0
+
+
+def test_backward_kernels_are_cut_in_dry_run():
+    """With the cut forced at a width where it would not pay, the training plan's kernels that hold
+    contractions next to other work are lowered as several steps: operand temporaries and remainders as
+    generated code, every contraction as a contraction program, the lookup's gradient as a scatter program
+    (kept in place, not turned into a one-hot temporary), the q/k/v gradients over their windows."""
+    env = dict(os.environ, POLY_B200_DRYRUN='1', POLY_B200_DEBUG='1', POLY_B200_CACHE='0', POLY_DUMP_KERNELS='1',
+               POLY_B200_OUTLINE_MIN_WORK='0')
+    r = subprocess.run([sys.executable, '-c', DRY_TRAIN % dict(root=ROOT)], env=env, capture_output=True, text=True,
+                       timeout=900)
+    assert r.returncode == 0, r.stderr[-4000:]
+    m = re.search(r'pb_plan: (\d+) kernels cut into contractions and elementwise pieces', r.stderr)
+    assert m and int(m.group(1)) >= 4
+    pieces = re.findall(r'^=== CUDA KERNEL (plan\d+_k\d+)_p(\d+) ===\n//PB200 1\n//kind (\w+)', r.stderr, flags=re.M)
+    by_kernel = {}
+    for name, _, kind in pieces:
+        by_kernel.setdefault(name, []).append(kind)
+    assert len(by_kernel) >= 4
+    for name, kinds in by_kernel.items():
+        assert kinds[-1] in ('jit', 'gemm'), (name, kinds)                 # the remainder, or a single contraction
+        assert any(k in ('gemm', 'scatter') for k in kinds), (name, kinds)
+    all_kinds = [k for kinds in by_kernel.values() for k in kinds]
+    assert all_kinds.count('scatter') >= 1                                 # the lookups' gradients (token and position tables)
+    assert any(kinds.count('gemm') == 3 for kinds in by_kernel.values())   # q, k and v gradients of the one layer
+    assert 'stays whole' not in r.stderr
